@@ -1,0 +1,429 @@
+#!/usr/bin/env python
+"""Benchmark of the paged decode hot path: one step = infiniopPagedCaching (the newest token's
+K/V rows) followed by infiniopPagedAttention over the paged KV cache.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5] [--impl reference]
+
+One JSON line on stdout (rank 0).  `value` is KV-read bandwidth of the whole job in GB/s:
+algorithmic KV bytes of one step (every K and V element of every live token once, independent of
+the GQA group size and of how the work is split) summed over all ranks, divided by the device-timed
+step (max over ranks).  Multi-GPU runs shard by sequence: every rank owns its sequences, its block
+tables and its own cache pool; there is no data-path collective (scaling "weak": each rank runs a
+full copy of the workload with its own seed; workload c5 instead splits one 2048-sequence batch
+round-robin, "strong").
+
+`--impl reference` times the CPU restatement of the reference's checker (oracle/, all host
+threads) on the same workload; only rank 0 works.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "paged_attn_decode_kv_read_bandwidth"
+UNIT = "GB/s"
+FALLBACK_HBM_GBS = 6650.0
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one pagedDecodeStreamKernel launch, from the ncu
+# capture summarised under profiles/ (None until a capture exists for that workload).
+NCU_TRAFFIC_BYTES = {"c2": None}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--cpu-seqs", type=int, default=0, help="sequences in the CPU sample (0 = the whole batch)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def workload_config(name, case, n_gpus):
+    return {
+        "workload": {
+            "c2": "configs[1]: Llama-3-8B-shape decode, bf16, batch 64 per GPU, 32/8 heads, head 128, block 16, every seq_len 4096, "
+                  "permuted tables over a 16384-block pool, 64 new K/V rows cached before attention",
+            "c3": "configs[2]: ragged 72B-shape decode, bf16, batch 256, 64/8 heads, head 128, block 16, seq_lens log-uniform [16,32768]",
+            "c4": "configs[3]: long-context decode, fp16, batch 2, 32/8 heads, head 128, block 16, seq_lens 131072",
+            "c5": "configs[4]: 2048-sequence batch, bf16, 64/8 heads, head 128, seq_lens U[1024,8192], round-robin over the GPUs",
+        }[name],
+        "num_seqs_per_gpu": case.num_seqs,
+        "tokens_per_gpu": case.total_tokens,
+        "kv_bytes_per_gpu": case.kv_bytes,
+        "parallelism": f"sequence-sharded x{n_gpus}, no collective",
+        "l2": "inputs larger than L2 (KV working set per step >> 126 MB)" if case.kv_bytes > (256 << 20) else "L2 flushed between steps",
+    }
+
+
+def make_case(name, rank, world, device):
+    from infinicore_b200 import workloads
+
+    if name == "c2":
+        return workloads.config2_llama8b(seed=2 + rank, device=device)
+    if name == "c3":
+        return workloads.config3_ragged72b(seed=3 + rank, device=device)
+    if name == "c4":
+        return workloads.config4_longctx(seed=4 + rank, device=device)
+    return workloads.config5_shard(rank, world, device=device)
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the oracle (a port of the reference's torch checker) on all host threads
+# ---------------------------------------------------------------------------------------------
+def cpu_sample(case_name, num_seqs_cap):
+    """A bounded CPU-resident sample of the workload: the first `num_seqs_cap` sequences of it (same
+    shapes, lengths and value distribution; pool sized to the sample)."""
+    import torch
+
+    from infinicore_b200 import workloads
+
+    if case_name == "c2":
+        n = num_seqs_cap or 64
+        return workloads.config2_llama8b(seed=2, device="cpu", num_seqs=n), f"{n} of 64 sequences x 4096 tokens"
+    if case_name == "c3":
+        n = num_seqs_cap or 32
+        return workloads.config3_ragged72b(seed=3, device="cpu", num_seqs=n), f"{n} of 256 sequences"
+    if case_name == "c4":
+        return workloads.config4_longctx(seed=4, device="cpu", num_seqs=1, seq_len=32768), "1 sequence x 32768 of 131072 tokens"
+    lens = workloads.config5_lengths()[: (num_seqs_cap or 32)]
+    c = workloads.build_case("c5_cpu_sample", dtype=torch.bfloat16, seq_lens=lens, num_heads=64, num_kv_heads=8,
+                             head_size=128, block_size=16, seed=5, device="cpu")
+    return c, f"{len(lens)} of 2048 sequences"
+
+
+def run_cpu(case, steps, warmup):
+    """Times `steps` passes of caching + attention on the CPU oracle; returns (GB/s, ms/step, threads)."""
+    import numpy as np
+    import torch
+
+    import oracle
+
+    def bits(t):
+        return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+    code = 12 if case.dtype == torch.float16 else 19
+    q, kc, vc = bits(case.q), bits(case.k_cache), bits(case.v_cache)
+    nk, nv = bits(case.new_k), bits(case.new_v)
+    bt, sl, sm = case.block_tables.numpy(), case.seq_lens.numpy(), case.slot_mapping.numpy()
+    out = np.zeros((case.num_seqs, case.num_heads, vc.shape[3]), dtype=np.float64)
+
+    def step():
+        oracle.paged_caching(kc, vc, nk, nv, sm)
+        oracle.paged_attention(q, kc, vc, bt, sl, case.scale, code, mode="reference", out=out)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return case.kv_bytes / dt / 1e9, dt * 1e3, oracle.num_threads()
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    case, sample = cpu_sample(args.workload, args.cpu_seqs)
+    steps = max(1, min(args.steps, 20))
+    warmup = max(1, min(args.warmup, 3))
+    gbs, ms, threads = run_cpu(case, steps, warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if args.workload != "c4" else "f16", "data": "synthetic",
+        "config": {"workload": workload_config(args.workload, case, 1)["workload"], "sample": sample},
+        "seqs_per_s": case.num_seqs / (ms / 1e3),
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample + " per step"},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "the reference has no CPU kernel for this path; this is the C/OpenMP port of its torch checker",
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.file, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        for row in self.file.read().splitlines():
+            parts = [p.strip() for p in row.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        try:
+            os.unlink(self.file.name)
+        except OSError:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+class AbiStep:
+    """Descriptors + workspace for one rank's decode step, called through the C ABI on torch's current stream."""
+
+    def __init__(self, case):
+        import torch
+
+        from infinicore_b200.libinfiniop import (LIBINFINIOP, InfiniDeviceEnum, TestTensor, check_error, create_handle,
+                                                 infiniopOperatorDescriptor_t, to_infini_dtype)
+
+        self.lib = LIBINFINIOP
+        self.check = check_error
+        self.case = case
+        dev = case.q.device.index
+        check_error(LIBINFINIOP.infinirtSetDevice(InfiniDeviceEnum.NVIDIA, dev))
+        self.handle = create_handle()
+        self.out = torch.zeros((case.num_seqs, case.num_heads, case.v_cache.shape[3]), dtype=case.dtype, device=case.q.device)
+
+        def tt(t):
+            return TestTensor.from_torch(t, to_infini_dtype(t.dtype), InfiniDeviceEnum.NVIDIA)
+
+        a = [tt(self.out), tt(case.q), tt(case.k_cache), tt(case.v_cache), tt(case.block_tables), tt(case.seq_lens)]
+        self.attn = infiniopOperatorDescriptor_t()
+        check_error(LIBINFINIOP.infiniopCreatePagedAttentionDescriptor(self.handle, ctypes.byref(self.attn), *[t.descriptor for t in a], None, case.scale))
+        size = ctypes.c_size_t(0)
+        check_error(LIBINFINIOP.infiniopGetPagedAttentionWorkspaceSize(self.attn, ctypes.byref(size)))
+        self.ws_size = size.value
+        self.ws = torch.empty(max(size.value, 1), dtype=torch.uint8, device=case.q.device)
+        c = [tt(case.k_cache), tt(case.v_cache), tt(case.new_k), tt(case.new_v), tt(case.slot_mapping)]
+        self.cache = infiniopOperatorDescriptor_t()
+        check_error(LIBINFINIOP.infiniopCreatePagedCachingDescriptor(self.handle, ctypes.byref(self.cache), *[t.descriptor for t in c]))
+        for t in a + c:
+            t.destroy_desc()
+        self.launches_per_step = 1 + (3 if self.ws_size > 0 else 1)
+
+    def caching(self, stream):
+        c = self.case
+        self.check(self.lib.infiniopPagedCaching(self.cache, None, 0, c.k_cache.data_ptr(), c.v_cache.data_ptr(),
+                                                 c.new_k.data_ptr(), c.new_v.data_ptr(), c.slot_mapping.data_ptr(), stream))
+
+    def attention(self, stream):
+        c = self.case
+        self.check(self.lib.infiniopPagedAttention(self.attn, self.ws.data_ptr(), self.ws_size, self.out.data_ptr(), c.q.data_ptr(),
+                                                   c.k_cache.data_ptr(), c.v_cache.data_ptr(), c.block_tables.data_ptr(),
+                                                   c.seq_lens.data_ptr(), None, stream))
+
+
+def gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    import infinicore_b200 as ib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this library has no CPU path (use --impl reference for the CPU port)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    case = make_case(args.workload, rank, world, device)
+    step = AbiStep(case)
+    stream = torch.cuda.current_stream(device)
+    sptr = stream.cuda_stream
+    small_ws = case.kv_bytes <= (256 << 20)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device) if small_ws else None
+
+    def one_step():
+        step.caching(sptr)
+        step.attention(sptr)
+
+    # ---- device-resident timing -------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        one_step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    K = args.steps
+    attn_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    cache_events = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    flush_ms = 0.0
+    barrier()
+    start.record(stream)
+    for i in range(K):
+        if flush is not None:
+            flush.fill_(i & 0xff)
+        cache_events[i].record(stream)
+        step.caching(sptr)
+        attn_events[i][0].record(stream)
+        step.attention(sptr)
+        attn_events[i][1].record(stream)
+    end.record(stream)
+    barrier()
+    total_ms = start.elapsed_time(end)
+    if flush is not None:
+        # the scrub is not part of the step: subtract its measured share
+        flush_ms = sum(start.elapsed_time(cache_events[0]) if i == 0 else attn_events[i - 1][1].elapsed_time(cache_events[i]) for i in range(K))
+    ms_per_step = max_over_ranks((total_ms - flush_ms) / K)
+    attn_ms = statistics.mean(a.elapsed_time(b) for a, b in attn_events)
+    attn_ms_min = min(a.elapsed_time(b) for a, b in attn_events)
+    cache_ms = statistics.mean(c.elapsed_time(a) for c, (a, _) in zip(cache_events, attn_events))
+    clocks = sampler.stop() if rank == 0 else None
+
+    kv_bytes_all = sum_over_ranks(float(case.kv_bytes))
+    seqs_all = sum_over_ranks(float(case.num_seqs))
+    value = kv_bytes_all / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the public Python API, host buffers in and out ---------------------
+    host_in = {k: getattr(case, k).cpu().pin_memory() for k in ("q", "new_k", "new_v", "slot_mapping", "block_tables", "seq_lens")}
+    dev_in = {k: torch.empty_like(getattr(case, k)) for k in host_in}
+    host_out = torch.empty(step.out.shape, dtype=step.out.dtype).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host_in.values())
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step():
+        for k, h in host_in.items():
+            dev_in[k].copy_(h, non_blocking=True)
+        ib.paged_caching(case.k_cache, case.v_cache, dev_in["new_k"], dev_in["new_v"], dev_in["slot_mapping"])
+        out = ib.paged_attention(dev_in["q"], case.k_cache, case.v_cache, dev_in["block_tables"], dev_in["seq_lens"], None, case.scale)
+        host_out.copy_(out, non_blocking=True)
+        stream.synchronize()  # the host reads the step's result before it issues the next step
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(K):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1) / K)
+    e2e_value = kv_bytes_all / (e2e_ms * 1e-3) / 1e9
+
+    # ---- CPU baseline (rank 0, N = 1 only) -------------------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sample_case, sample = cpu_sample(args.workload, args.cpu_seqs)
+        gbs, ms, threads = run_cpu(sample_case, steps=3, warmup=1)
+        cpu = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample + " per step, 3 timed steps",
+               "ms_per_step": ms}
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        achieved = case.kv_bytes / (attn_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if args.workload == "c5" else "weak",
+            "vs_baseline": None, "dtype": "f16" if case.dtype == torch.float16 else "bf16", "data": "synthetic",
+            "config": workload_config(args.workload, case, world),
+            "seqs_per_s": seqs_all / (ms_per_step * 1e-3),
+            "frac_of_hbm_peak": value / (peak * world),
+            "roofline": {
+                "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_kind": f"of {peak_kind}",
+                "kernel": "pagedDecodeStreamKernel (timed with its plan and combine launches: events bracket infiniopPagedAttention)",
+                "algorithmic_bytes_per_launch": case.kv_bytes, "attn_ms_mean": attn_ms, "attn_ms_min": attn_ms_min,
+                "caching_ms_mean": cache_ms,
+            },
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "note": "q, new K/V rows, slots, block tables and lengths copied in from pinned host memory and the output copied "
+                            "back every step; the KV cache itself is device state"},
+            "gpu_launches": step.launches_per_step * K,
+            "clocks": clocks,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

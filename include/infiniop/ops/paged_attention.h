@@ -1,0 +1,66 @@
+/*
+ * Paged-attention decode: one query token per sequence, GQA/MHA, over a
+ * block-table-indexed paged KV cache.  Replaces reference
+ * include/infiniop/ops/paged_attention.h:33-91 with identical signatures.
+ *
+ * Tensors (element strides honoured wherever the reference honours them):
+ *   out           [num_seqs, num_heads, value_size]           F16 | BF16
+ *   q             [num_seqs, num_heads, head_size]            same dtype
+ *   k_cache       [num_blocks, num_kv_heads, block_size, head_size]
+ *   v_cache       [num_blocks, num_kv_heads, block_size, value_size]
+ *   block_tables  [num_seqs, max_num_blocks_per_seq]          I64 | I32 | U32
+ *   seq_lens      [num_seqs]                                  same index dtype
+ *   alibi_slopes  [num_heads] F32, optional (descriptor and pointer may be NULL)
+ *
+ * Token j of sequence i lives at cache[block_tables[i][j / block_size], :, j % block_size, :];
+ * q-head h reads kv-head h / (num_heads / num_kv_heads).  A sequence with
+ * seq_len <= 0 leaves its output rows untouched.
+ *
+ * The workspace is caller-owned scratch of at least GetWorkspaceSize bytes,
+ * 256-byte aligned, contents undefined on entry.  Execute is asynchronous on
+ * `stream` (NULL = the default stream), performs no allocation and no
+ * host<->device synchronisation.
+ */
+#ifndef __INFINIOP_PAGED_ATTENTION_API_H__
+#define __INFINIOP_PAGED_ATTENTION_API_H__
+
+#include "../operator_descriptor.h"
+
+typedef struct InfiniopDescriptor *infiniopPagedAttentionDescriptor_t;
+
+/* reference include/infiniop/ops/paged_attention.h:33-43 */
+__INFINI_C __export infiniStatus_t infiniopCreatePagedAttentionDescriptor(
+    infiniopHandle_t handle,
+    infiniopPagedAttentionDescriptor_t *desc_ptr,
+    infiniopTensorDescriptor_t out_desc,
+    infiniopTensorDescriptor_t q_desc,
+    infiniopTensorDescriptor_t k_cache_desc,
+    infiniopTensorDescriptor_t v_cache_desc,
+    infiniopTensorDescriptor_t block_tables_desc,
+    infiniopTensorDescriptor_t seq_lens_desc,
+    infiniopTensorDescriptor_t alibi_slopes_desc,
+    float scale);
+
+/* reference include/infiniop/ops/paged_attention.h:52-53 */
+__INFINI_C __export infiniStatus_t infiniopGetPagedAttentionWorkspaceSize(
+    infiniopPagedAttentionDescriptor_t desc, size_t *size);
+
+/* reference include/infiniop/ops/paged_attention.h:71-82 */
+__INFINI_C __export infiniStatus_t infiniopPagedAttention(
+    infiniopPagedAttentionDescriptor_t desc,
+    void *workspace,
+    size_t workspace_size,
+    void *out,
+    const void *q,
+    const void *k_cache,
+    const void *v_cache,
+    const void *block_tables,
+    const void *seq_lens,
+    const void *alibi_slopes,
+    void *stream);
+
+/* reference include/infiniop/ops/paged_attention.h:90-91 */
+__INFINI_C __export infiniStatus_t infiniopDestroyPagedAttentionDescriptor(
+    infiniopPagedAttentionDescriptor_t desc);
+
+#endif

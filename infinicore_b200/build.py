@@ -1,0 +1,132 @@
+"""Builds libinfinirt.so and libinfiniop.so for sm_100a with nvcc, in-tree.
+
+The reference builds the same two libraries with xmake (xmake.lua, xmake/nvidia.lua);
+xmake is not a dependency here - this script is the build.  Output goes to
+infinicore_b200/lib/, which doubles as $INFINI_ROOT/lib for loaders that follow the
+reference's layout (test/infiniop/libinfiniop/liboperators.py:11-56).
+
+    python -m infinicore_b200.build [--force] [--verbose]
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+ROOT = PKG.parent
+CSRC = PKG / "csrc"
+INCLUDE = ROOT / "include"
+LIB = PKG / "lib"
+OBJ = PKG / "build"
+
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON = [
+    "-std=c++17",
+    "-O3",
+    "-lineinfo",
+    "-Xcompiler",
+    "-fPIC,-fvisibility=hidden,-Wall",
+    "--expt-relaxed-constexpr",
+    f"-I{INCLUDE}",
+    f"-I{CSRC}",
+]
+
+RT_SOURCES = ["runtime/infinirt.cu"]
+OP_SOURCES = [
+    "handle.cu",
+    "paged_caching/paged_caching.cu",
+    "paged_attention/operator.cu",
+    "paged_attention/decode_generic.cu",
+    "paged_attention/decode_stream.cu",
+]
+
+
+def nvcc() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found; this library has no non-CUDA build")
+    return exe
+
+
+def _digest(paths) -> str:
+    h = hashlib.sha256()
+    for p in sorted(paths):
+        h.update(str(p).encode())
+        h.update(p.read_bytes())
+    h.update(" ".join(COMMON + ARCH_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _headers():
+    return list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh")) + list(INCLUDE.rglob("*.h"))
+
+
+def _compile(src: str, verbose: bool, extra=()) -> Path:
+    src_path = CSRC / src
+    obj = OBJ / (src.replace("/", "_") + ".o")
+    stamp = obj.with_suffix(".sha")
+    want = _digest([src_path] + _headers())
+    if obj.exists() and stamp.exists() and stamp.read_text() == want:
+        return obj
+    cmd = [nvcc(), *COMMON, *ARCH_FLAGS, *extra, "-c", str(src_path), "-o", str(obj)]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+        print(" ".join(cmd), flush=True)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed on {src}")
+    stamp.write_text(want)
+    return obj
+
+
+def _link(objs, out: Path, extra, verbose: bool) -> None:
+    cmd = [nvcc(), "-shared", *ARCH_FLAGS, "-o", str(out), *map(str, objs), "-cudart", "shared", *extra]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError(f"link failed for {out.name}")
+
+
+def build(force: bool = False, verbose: bool = False) -> dict:
+    """Compiles what is stale and returns {"infinirt": path, "infiniop": path}."""
+    LIB.mkdir(exist_ok=True)
+    OBJ.mkdir(exist_ok=True)
+    if force:
+        for f in OBJ.glob("*.sha"):
+            f.unlink()
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        rt_objs = list(pool.map(lambda s: _compile(s, verbose), RT_SOURCES))
+        op_objs = list(pool.map(lambda s: _compile(s, verbose), OP_SOURCES))
+    librt = LIB / "libinfinirt.so"
+    libop = LIB / "libinfiniop.so"
+    newest_obj = max(o.stat().st_mtime for o in rt_objs + op_objs)
+    if force or not librt.exists() or librt.stat().st_mtime < newest_obj:
+        _link(rt_objs, librt, [], verbose)
+    if force or not libop.exists() or libop.stat().st_mtime < newest_obj:
+        _link(op_objs, libop, [f"-L{LIB}", "-linfinirt", "-Xlinker", "-rpath=$ORIGIN"], verbose)
+    return {"infinirt": librt, "infiniop": libop}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--verbose", action="store_true", help="echo commands and ptxas resource usage")
+    args = ap.parse_args()
+    out = build(force=args.force, verbose=args.verbose)
+    for k, v in out.items():
+        print(f"{k}: {v}")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,888 @@
+// Streaming paged-attention decode for sm_100a.
+//
+// What it computes is what the reference's split-KV decode computes
+// (src/infiniop/ops/paged_attention/cuda/kernel_v2.cuh:620-1074 partial pass, :556-616
+// combine): out[s,h,:] = softmax_t(scale * q[s,h,:] . K[s,t,kv(h),:]) . V[s,t,kv(h),:], fp32
+// online softmax in the log2 domain.  How it gets there is different, and built around the
+// one thing that bounds this op on a B200 - reading every K/V byte exactly once at HBM speed:
+//
+//  * Work decomposition.  A "tile" is 16 consecutive tokens of one KV page for one kv-head.
+//    A "unit" is (sequence, kv-head, group of <= 8 q-heads that share that kv-head); its length
+//    is ceil(seq_len / 16) tiles.  All units are laid end to end in one linear tile space and
+//    that space is cut into equal contiguous ranges, one per persistent warp ("worker").  Every
+//    worker therefore streams the same number of bytes (+-1 tile) whatever the mix of
+//    sequence lengths, with no host knowledge of seq_lens: a one-CTA plan kernel builds the
+//    per-sequence tile prefix and each range's starting (sequence, kv-head, tile) on the device.
+//  * Data movement.  Each worker owns a private ring of `stages` shared-memory slots.  Lanes
+//    0..2*HD/64-1 each issue one non-multicast `cp.async.bulk.tensor` (TMA) box of
+//    16 rows x 128 bytes with the 128-byte swizzle; completion is tracked by one mbarrier per
+//    slot.  Block-table entries are fetched one tile ahead of the TMA issue that needs them, so
+//    the table -> page indirection is off the critical path and the ring never drains at page,
+//    kv-head or sequence boundaries.
+//  * Arithmetic.  All q-heads of the GQA group consume the same staged tile:
+//    S^T[8 heads x 16 tokens] = Q.K^T and O[8 heads x HD] += P.V run as warp-level
+//    mma.sync.m16n8k16 (bf16/fp16 in, fp32 accumulate) with ldmatrix / ldmatrix.trans operand
+//    loads that are bank-conflict-free under the swizzle.  P is rounded to the cache dtype
+//    before the PV product, as the reference's torch check does
+//    (test/infiniop/paged_attention.py:43).  Rows 8..15 of the M dimension are padding.
+//  * Reduction.  A worker that covers a whole unit writes the normalised output directly.
+//    Otherwise it writes (acc, m, l) to workspace slot (unit + range): along the linear space the
+//    pair (unit, range) only ever moves forward in one or both coordinates, so that sum is
+//    unique.  A combine kernel merges the slots of every split unit.  No kernel waits on another
+//    CTA; the only waits are mbarrier waits on a worker's own TMA copies, and those are bounded.
+//
+// HBM traffic per launch: K and V tiles once each (the algorithmic bytes), plus q/out, block
+// tables, and 8*(HD+2)*4 bytes written and read back per (unit, range) boundary - at most
+// units + workers records.
+#include "kernels.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+namespace b200::paged_attention {
+
+namespace {
+
+constexpr int kTileTokens = 16;
+constexpr int kHeadsPerTile = 8;
+constexpr int kMaxStages = 8;
+constexpr int kMaxWarps = 8;
+constexpr int kPlanThreads = 1024;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull; // an mbarrier wait gives up after 2 s
+
+struct PlanHeader {
+    int error;      // set non-zero by a worker whose bounded wait ran out
+    int num_ranges; // ranges actually used (<= number of workers)
+    long long total_tiles;
+    long long range_len;
+};
+
+struct StreamArgs {
+    DecodeParams p;
+    PlanHeader *header;
+    long long *prefix;  // [num_seqs + 1] tiles before each sequence (one kv-head, one head tile)
+    int4 *range_start;  // [workers] (sequence, unit-within-sequence, tile) where a range begins
+    float *partials;    // [(units + workers)] records of 8 * (HD + 2) floats
+    int units_per_seq;  // num_kv_heads * head_tiles
+    int head_tiles;
+    int tiles_per_page; // block_size / 16
+    int stages;
+    int num_workers;
+};
+
+// ---------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smemAddr(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbarInit(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbarExpectTx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbarTryWait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+__device__ __forceinline__ unsigned long long globalTimerNs() {
+    unsigned long long v;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(v));
+    return v;
+}
+
+// Bounded wait: false means the time limit ran out (the copy it waits for never landed).
+__device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity) {
+    if (mbarTryWait(bar, parity)) {
+        return true;
+    }
+    const unsigned long long t0 = globalTimerNs();
+    while (!mbarTryWait(bar, parity)) {
+        if (globalTimerNs() - t0 > kWaitLimitNs) {
+            return false;
+        }
+    }
+    return true;
+}
+
+// One TMA box {64 elements, 16 rows, 1 kv-head, 1 block} of a 4-D map
+// {head_size, block_size, num_kv_heads, num_blocks} into swizzled shared memory.
+__device__ __forceinline__ void tmaLoadBox(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                           int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+__device__ __forceinline__ void ldmatrixX4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr)
+                 : "memory");
+}
+
+__device__ __forceinline__ void ldmatrixX4Trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr)
+                 : "memory");
+}
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1);
+
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                        uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float fastExp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t packPair(float lo, float hi, __nv_bfloat16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+__device__ __forceinline__ uint32_t packPair(float lo, float hi, __half) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// ---------------------------------------------------------------------------------------
+// Plan kernel: tile prefix per sequence, range length, and where each range starts.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kPlanThreads)
+    pagedDecodePlanKernel(const StreamArgs a) {
+    __shared__ long long warp_sums[kPlanThreads / 32];
+    __shared__ long long running_s;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int wid = tid >> 5;
+    const int num_seqs = a.p.num_seqs;
+    const long long capacity = static_cast<long long>(a.p.max_blocks_per_seq) * a.p.block_size;
+
+    if (tid == 0) {
+        running_s = 0;
+        a.prefix[0] = 0;
+    }
+    __syncthreads();
+
+    for (int base = 0; base < num_seqs; base += kPlanThreads) {
+        const int s = base + tid;
+        long long tiles = 0;
+        if (s < num_seqs) {
+            long long len = loadIndex(a.p.seq_lens, s, a.p.index_is_64);
+            len = len < 0 ? 0 : (len > capacity ? capacity : len);
+            tiles = (len + kTileTokens - 1) / kTileTokens;
+        }
+        long long incl = tiles;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const long long n = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) {
+                incl += n;
+            }
+        }
+        if (lane == 31) {
+            warp_sums[wid] = incl;
+        }
+        __syncthreads();
+        if (wid == 0) {
+            long long v = warp_sums[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const long long n = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) {
+                    v += n;
+                }
+            }
+            warp_sums[lane] = v; // inclusive over warps
+        }
+        __syncthreads();
+        const long long before = running_s + (wid > 0 ? warp_sums[wid - 1] : 0);
+        if (s < num_seqs) {
+            a.prefix[s + 1] = before + incl;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            running_s += warp_sums[kPlanThreads / 32 - 1];
+        }
+        __syncthreads();
+    }
+
+    const long long seq_tiles = running_s;
+    const long long total = seq_tiles * a.units_per_seq;
+    long long range_len = (total + a.num_workers - 1) / a.num_workers;
+    if (range_len < 1) {
+        range_len = 1;
+    }
+    const int num_ranges = static_cast<int>((total + range_len - 1) / range_len);
+    if (tid == 0) {
+        a.header->error = 0;
+        a.header->num_ranges = num_ranges;
+        a.header->total_tiles = total;
+        a.header->range_len = range_len;
+    }
+
+    // Where does range r start?  Position x belongs to the last sequence s with
+    // prefix[s] * units_per_seq <= x, i.e. prefix[s] <= x / units_per_seq.
+    for (int r = tid; r < num_ranges; r += kPlanThreads) {
+        const long long x = r * range_len;
+        const long long y = x / a.units_per_seq;
+        int lo = 0, hi = num_seqs; // invariant: prefix[lo] <= y < prefix[hi] (prefix[num_seqs] = seq_tiles > y)
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (a.prefix[mid] <= y) {
+                lo = mid;
+            } else {
+                hi = mid;
+            }
+        }
+        const long long nt = a.prefix[lo + 1] - a.prefix[lo];
+        const long long rem = x - a.prefix[lo] * a.units_per_seq;
+        a.range_start[r] = make_int4(lo, static_cast<int>(rem / nt), static_cast<int>(rem % nt), 0);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Main kernel
+// ---------------------------------------------------------------------------------------
+struct Cursor {
+    int s;   // sequence
+    int j;   // unit within the sequence: kv_head * head_tiles + head_tile
+    int ti;  // tile within the sequence
+    int nt;  // tiles in sequence s
+};
+
+__device__ __forceinline__ void advance(Cursor &c, const StreamArgs &a) {
+    if (++c.ti == c.nt) {
+        c.ti = 0;
+        if (++c.j == a.units_per_seq) {
+            c.j = 0;
+            do {
+                ++c.s;
+                c.nt = (c.s < a.p.num_seqs) ? static_cast<int>(a.prefix[c.s + 1] - a.prefix[c.s]) : 1;
+            } while (c.nt == 0);
+        }
+    }
+}
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(kMaxWarps * 32)
+    pagedDecodeStreamKernel(const __grid_constant__ CUtensorMap tmap_k,
+                            const __grid_constant__ CUtensorMap tmap_v,
+                            const StreamArgs a) {
+    constexpr int kChunks = HD / 64;               // 128-byte column chunks per row
+    constexpr int kBoxBytes = kTileTokens * 128;   // one TMA box
+    constexpr int kTensorBytes = kChunks * kBoxBytes;
+    constexpr int kStageBytes = 2 * kTensorBytes;  // K tile + V tile
+    constexpr int kKSteps = HD / 16;
+    constexpr int kNTiles = HD / 8;
+
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2; // MMA row (q-head within the head tile) / B-fragment column
+    const int t = lane & 3;
+    const int nwarps = blockDim.x >> 5;
+    const int stages = a.stages;
+    const DecodeParams &p = a.p;
+
+    const uint32_t ring = smemAddr(smem_raw) + warp * stages * kStageBytes;
+    const uint32_t bars = smemAddr(smem_raw) + nwarps * stages * kStageBytes + warp * stages * 8;
+
+    if (lane == 0) {
+        for (int i = 0; i < stages; ++i) {
+            mbarInit(bars + i * 8, 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+
+    const int worker = blockIdx.x * nwarps + warp;
+    const int num_ranges = a.header->num_ranges;
+    if (worker >= num_ranges) {
+        return;
+    }
+    const long long total_tiles = a.header->total_tiles;
+    const long long range_len = a.header->range_len;
+    const long long x0 = worker * range_len;
+    const long long count = (total_tiles - x0 < range_len) ? (total_tiles - x0) : range_len;
+
+    const int4 rs = a.range_start[worker];
+    Cursor gen; // next tile to fetch
+    gen.s = rs.x;
+    gen.j = rs.y;
+    gen.ti = rs.z;
+    gen.nt = static_cast<int>(a.prefix[rs.x + 1] - a.prefix[rs.x]);
+    Cursor cur = gen; // next tile to consume
+
+    const int tpp = a.tiles_per_page;
+    const int head_tiles = a.head_tiles;
+
+    auto tableEntry = [&](const Cursor &c) -> long long {
+        return loadIndex(p.block_tables, c.s * p.bt_seq_stride + c.ti / tpp, p.index_is_64);
+    };
+    auto issue = [&](int stage, const Cursor &c, long long block) {
+        const uint32_t bar = bars + stage * 8;
+        const uint32_t dst = ring + stage * kStageBytes;
+        if (lane == 0) {
+            mbarExpectTx(bar, kStageBytes);
+        }
+        if (lane < 2 * kChunks) {
+            const int is_v = lane / kChunks;
+            const int chunk = lane % kChunks;
+            tmaLoadBox(dst + is_v * kTensorBytes + chunk * kBoxBytes, is_v ? &tmap_v : &tmap_k, bar,
+                       chunk * 64, (c.ti % tpp) * kTileTokens, c.j / head_tiles, static_cast<int>(block));
+        }
+    };
+
+    // ---- prologue: fill the ring ------------------------------------------------------
+    long long issued = 0;
+    {
+        Cursor pc[kMaxStages];
+        long long pb[kMaxStages];
+#pragma unroll
+        for (int i = 0; i < kMaxStages; ++i) {
+            if (i < stages && i < count) {
+                pc[i] = gen;
+                pb[i] = tableEntry(gen);
+                if (i + 1 < count) {
+                    advance(gen, a);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kMaxStages; ++i) {
+            if (i < stages && i < count) {
+                issue(i, pc[i], pb[i]);
+                ++issued;
+            }
+        }
+    }
+    // `gen` now names tile number `issued` of the range (when it exists); fetch its table entry early.
+    long long next_block = (issued < count) ? tableEntry(gen) : 0;
+
+    // ---- per-unit state ---------------------------------------------------------------
+    uint32_t qa[kKSteps][2];
+    float o[kNTiles][4];
+    float m_run = -INFINITY;
+    float l_run = 0.f;
+    float slope_log2 = 0.f;
+    int first_ti = cur.ti;
+    int seq_len = 0;
+    bool row_valid = false;
+
+    auto loadUnit = [&]() {
+        const int kv_head = cur.j / head_tiles;
+        const int head_tile = cur.j % head_tiles;
+        const int head_in_group = head_tile * kHeadsPerTile + g;
+        row_valid = head_in_group < p.group_size;
+        const int head = kv_head * p.group_size + (row_valid ? head_in_group : 0);
+        const T *q = static_cast<const T *>(p.q) + cur.s * p.q_seq_stride + head * p.q_head_stride;
+#pragma unroll
+        for (int ks = 0; ks < kKSteps; ++ks) {
+            qa[ks][0] = row_valid ? *reinterpret_cast<const uint32_t *>(q + ks * 16 + 2 * t) : 0u;
+            qa[ks][1] = row_valid ? *reinterpret_cast<const uint32_t *>(q + ks * 16 + 8 + 2 * t) : 0u;
+        }
+        slope_log2 = (p.alibi_slopes != nullptr && row_valid) ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
+        long long len = loadIndex(p.seq_lens, cur.s, p.index_is_64);
+        const long long capacity = static_cast<long long>(p.max_blocks_per_seq) * p.block_size;
+        seq_len = static_cast<int>(len > capacity ? capacity : len);
+#pragma unroll
+        for (int n = 0; n < kNTiles; ++n) {
+            o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+        }
+        m_run = -INFINITY;
+        l_run = 0.f;
+        first_ti = cur.ti;
+    };
+    loadUnit();
+
+    bool failed = false;
+    int stage = 0;
+    uint32_t parity = 0;
+
+    long long i = 0;
+    for (; i < count; ++i) {
+        const uint32_t bar = bars + stage * 8;
+        const uint32_t k_tile = ring + stage * kStageBytes;
+        const uint32_t v_tile = k_tile + kTensorBytes;
+        if (!mbarWait(bar, parity)) {
+            failed = true;
+            break;
+        }
+
+        const int tok0 = cur.ti * kTileTokens;
+        const int valid = seq_len - tok0; // >= 1 by construction
+        if (valid < kTileTokens) {
+            // Rows past the end of the sequence may hold anything (including NaN bit patterns):
+            // K rows are neutralised by the -inf mask below, V rows must be zeroed because
+            // 0 * NaN would poison the accumulators.
+            for (int idx = lane; idx < (kTileTokens - valid) * kChunks * 8; idx += 32) {
+                const int row = valid + idx / (kChunks * 8);
+                const int rest = idx % (kChunks * 8);
+                const uint32_t addr = v_tile + (rest / 8) * kBoxBytes + row * 128 + (rest % 8) * 16;
+                asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+            }
+            // these generic-proxy writes precede the next TMA write into the same slot
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+        }
+
+        // ---- S^T = Q . K^T ------------------------------------------------------------
+        float sc[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+        }
+        {
+            // lane -> (token row, which 16-byte column of the 32-byte k-step)
+            const int row = ((lane >> 4) << 3) + (lane & 7);
+            const int half = (lane >> 3) & 1;
+#pragma unroll
+            for (int ks = 0; ks < kKSteps; ++ks) {
+                const int col = ks * 2 + half; // 16-byte column within the row
+                const uint32_t addr = k_tile + (col >> 3) * kBoxBytes + row * 128 + (((col & 7) ^ (row & 7)) << 4);
+                uint32_t b0, b1, b2, b3;
+                ldmatrixX4(addr, b0, b1, b2, b3);
+                mma16816<T>(sc[0], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+                mma16816<T>(sc[1], qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+            }
+        }
+
+        // ---- online softmax (log2 domain) for q-head g over this tile's 16 tokens -----------
+        float x[4];
+        x[0] = sc[0][0] * p.scale_log2e;
+        x[1] = sc[0][1] * p.scale_log2e;
+        x[2] = sc[1][0] * p.scale_log2e;
+        x[3] = sc[1][1] * p.scale_log2e;
+        if (slope_log2 != 0.f) {
+            const int rel = tok0 + 2 * t - (seq_len - 1);
+            x[0] += slope_log2 * static_cast<float>(rel);
+            x[1] += slope_log2 * static_cast<float>(rel + 1);
+            x[2] += slope_log2 * static_cast<float>(rel + 8);
+            x[3] += slope_log2 * static_cast<float>(rel + 9);
+        }
+        if (valid < kTileTokens) {
+            const int c = 2 * t;
+            x[0] = (c < valid) ? x[0] : -INFINITY;
+            x[1] = (c + 1 < valid) ? x[1] : -INFINITY;
+            x[2] = (c + 8 < valid) ? x[2] : -INFINITY;
+            x[3] = (c + 9 < valid) ? x[3] : -INFINITY;
+        }
+        float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float alpha = fastExp2(m_run - m_new);
+        const float p0 = fastExp2(x[0] - m_new);
+        const float p1 = fastExp2(x[1] - m_new);
+        const float p2 = fastExp2(x[2] - m_new);
+        const float p3 = fastExp2(x[3] - m_new);
+        l_run = l_run * alpha + ((p0 + p1) + (p2 + p3));
+        m_run = m_new;
+        const uint32_t pa0 = packPair(p0, p1, T());
+        const uint32_t pa2 = packPair(p2, p3, T());
+#pragma unroll
+        for (int n = 0; n < kNTiles; ++n) {
+            o[n][0] *= alpha;
+            o[n][1] *= alpha;
+        }
+
+        // ---- O += P . V -----------------------------------------------------------------
+        {
+            const int row = (((lane >> 3) & 1) << 3) + (lane & 7);
+            const int sel = lane >> 4;
+#pragma unroll
+            for (int np = 0; np < kNTiles / 2; ++np) {
+                const int col = np * 2 + sel;
+                const uint32_t addr = v_tile + (col >> 3) * kBoxBytes + row * 128 + (((col & 7) ^ (row & 7)) << 4);
+                uint32_t b0, b1, b2, b3;
+                ldmatrixX4Trans(addr, b0, b1, b2, b3);
+                mma16816<T>(o[2 * np], pa0, 0u, pa2, 0u, b0, b1);
+                mma16816<T>(o[2 * np + 1], pa0, 0u, pa2, 0u, b2, b3);
+            }
+        }
+
+        // ---- the slot is free: refill it with tile i + stages -----------------------------
+        __syncwarp();
+        if (issued < count) {
+            issue(stage, gen, next_block);
+            ++issued;
+            if (issued < count) {
+                advance(gen, a);
+                next_block = tableEntry(gen);
+            }
+        }
+        if (++stage == stages) {
+            stage = 0;
+            parity ^= 1u;
+        }
+
+        // ---- end of unit or end of range: emit --------------------------------------------
+        const bool unit_end = (cur.ti + 1 == cur.nt);
+        if (unit_end || i + 1 == count) {
+            float l_all = l_run;
+            l_all += __shfl_xor_sync(0xffffffffu, l_all, 1);
+            l_all += __shfl_xor_sync(0xffffffffu, l_all, 2);
+            const int kv_head = cur.j / head_tiles;
+            const int head_tile = cur.j % head_tiles;
+            if (first_ti == 0 && unit_end) {
+                if (row_valid) {
+                    const int head = kv_head * p.group_size + head_tile * kHeadsPerTile + g;
+                    T *out = static_cast<T *>(p.out) + cur.s * p.o_seq_stride + head * p.o_head_stride;
+                    const float inv = 1.f / l_all;
+#pragma unroll
+                    for (int n = 0; n < kNTiles; ++n) {
+                        *reinterpret_cast<uint32_t *>(out + n * 8 + 2 * t) = packPair(o[n][0] * inv, o[n][1] * inv, T());
+                    }
+                }
+            } else {
+                const long long unit = static_cast<long long>(cur.s) * a.units_per_seq + cur.j;
+                float *rec = a.partials + (unit + worker) * (kHeadsPerTile * (HD + 2));
+                if (row_valid) {
+#pragma unroll
+                    for (int n = 0; n < kNTiles; ++n) {
+                        *reinterpret_cast<float2 *>(rec + g * HD + n * 8 + 2 * t) = make_float2(o[n][0], o[n][1]);
+                    }
+                }
+                if (t == 0 && row_valid) {
+                    *reinterpret_cast<float2 *>(rec + kHeadsPerTile * HD + g * 2) = make_float2(m_run, l_all);
+                }
+            }
+        }
+        if (i + 1 < count) {
+            advance(cur, a);
+            if (unit_end) {
+                loadUnit();
+            }
+        }
+    }
+
+    if (failed) {
+        if (lane == 0) {
+            atomicExch(&a.header->error, 1);
+        }
+        // Let this worker's copies still in flight land (bounded) before its shared memory is
+        // released: they sit in slots `stage`, `stage + 1`, ... in issue order.
+        int sidx = stage;
+        uint32_t par = parity;
+        for (long long k = i; k < issued; ++k) {
+            (void)mbarWait(bars + sidx * 8, par);
+            if (++sidx == stages) {
+                sidx = 0;
+                par ^= 1u;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Combine kernel: one warp per (sequence, q-head); merges the records of a split unit.
+// ---------------------------------------------------------------------------------------
+template <typename T, int HD>
+__global__ void __launch_bounds__(128)
+    pagedDecodeCombineKernel(const StreamArgs a) {
+    constexpr int kPerLane = HD / 32;
+    const DecodeParams &p = a.p;
+    const int lane = threadIdx.x & 31;
+    const long long pair = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (pair >= static_cast<long long>(p.num_seqs) * p.num_heads) {
+        return;
+    }
+    const int s = static_cast<int>(pair / p.num_heads);
+    const int head = static_cast<int>(pair % p.num_heads);
+    const long long nt = a.prefix[s + 1] - a.prefix[s];
+    if (nt == 0) {
+        return; // empty sequence: output untouched
+    }
+    const int kv_head = head / p.group_size;
+    const int in_group = head % p.group_size;
+    const int j = kv_head * a.head_tiles + in_group / kHeadsPerTile;
+    const int row = in_group % kHeadsPerTile;
+    const long long range_len = a.header->range_len;
+    const long long start = a.prefix[s] * a.units_per_seq + j * nt;
+    const long long r_first = start / range_len;
+    const long long r_last = (start + nt - 1) / range_len;
+    if (r_first == r_last) {
+        return; // the worker that covered the whole unit wrote the output itself
+    }
+    const long long unit = static_cast<long long>(s) * a.units_per_seq + j;
+    constexpr int kRec = kHeadsPerTile * (HD + 2);
+    const float *base = a.partials + (unit + r_first) * kRec;
+    const int n = static_cast<int>(r_last - r_first + 1);
+
+    float m_all = -INFINITY;
+    for (int i = lane; i < n; i += 32) {
+        m_all = fmaxf(m_all, base[static_cast<long long>(i) * kRec + kHeadsPerTile * HD + row * 2]);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, off));
+    }
+    float acc[kPerLane];
+#pragma unroll
+    for (int k = 0; k < kPerLane; ++k) {
+        acc[k] = 0.f;
+    }
+    float l_all = 0.f;
+    for (int i = 0; i < n; ++i) {
+        const float *rec = base + static_cast<long long>(i) * kRec;
+        const float2 ml = *reinterpret_cast<const float2 *>(rec + kHeadsPerTile * HD + row * 2);
+        const float w = exp2f(ml.x - m_all);
+        l_all = fmaf(w, ml.y, l_all);
+        const float *src = rec + row * HD + lane * kPerLane;
+#pragma unroll
+        for (int k = 0; k < kPerLane; ++k) {
+            acc[k] = fmaf(w, src[k], acc[k]);
+        }
+    }
+    const float inv = 1.f / l_all;
+    T *out = static_cast<T *>(p.out) + s * p.o_seq_stride + head * p.o_head_stride + lane * kPerLane;
+#pragma unroll
+    for (int k = 0; k < kPerLane; k += 2) {
+        *reinterpret_cast<uint32_t *>(out + k) = packPair(acc[k] * inv, acc[k + 1] * inv, T());
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encodeTiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess
+            && qres == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        } else {
+            (void)cudaGetLastError();
+        }
+    });
+    return fn;
+}
+
+// 4-D map {head_size, block_size, num_kv_heads, num_blocks} over one cache pool.
+bool encodeCacheMap(CUtensorMap *map, const Info &I, const void *base,
+                    ptrdiff_t row_stride, ptrdiff_t head_stride, ptrdiff_t block_stride, size_t width) {
+    EncodeTiledFn fn = encodeTiled();
+    if (fn == nullptr) {
+        return false;
+    }
+    const cuuint64_t dims[4] = {width, I.block_size, I.num_kv_heads, I.num_blocks};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(row_stride) * 2, static_cast<cuuint64_t>(head_stride) * 2,
+                                   static_cast<cuuint64_t>(block_stride) * 2};
+    const cuuint32_t box[4] = {64, kTileTokens, 1, 1};
+    const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+    const CUtensorMapDataType dt = (I.dtype == INFINI_DTYPE_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const CUresult rc = fn(map, dt, 4, const_cast<void *>(base), dims, strides, box, elem_strides,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS;
+}
+
+int envInt(const char *name, int fallback, int lo, int hi) {
+    const char *v = std::getenv(name);
+    if (v == nullptr || *v == '\0') {
+        return fallback;
+    }
+    const long parsed = std::strtol(v, nullptr, 10);
+    if (parsed < lo || parsed > hi) {
+        return fallback;
+    }
+    return static_cast<int>(parsed);
+}
+
+size_t roundUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct WorkspaceLayout {
+    size_t header_off, prefix_off, range_off, partial_off, total;
+};
+
+WorkspaceLayout workspaceLayout(const Info &I, const StreamPlan &plan) {
+    WorkspaceLayout L;
+    L.header_off = 0;
+    L.prefix_off = 256;
+    L.range_off = roundUp(L.prefix_off + (I.num_seqs + 1) * sizeof(long long), 256);
+    L.partial_off = roundUp(L.range_off + static_cast<size_t>(plan.num_workers) * sizeof(int4), 256);
+    const size_t units = I.num_seqs * I.num_kv_heads * static_cast<size_t>(plan.head_tiles_per_group);
+    const size_t rec = kHeadsPerTile * (I.head_size + 2) * sizeof(float);
+    L.total = roundUp(L.partial_off + (units + plan.num_workers) * rec, 256);
+    return L;
+}
+
+template <typename T, int HD>
+infiniStatus_t launchTyped(const StreamPlan &plan, const StreamArgs &args, const CUtensorMap &mk, const CUtensorMap &mv,
+                           int device_id, cudaStream_t stream) {
+    static bool attr_done[64] = {};
+    auto kernel = pagedDecodeStreamKernel<T, HD>;
+    if (device_id < 0 || device_id >= 64 || !attr_done[device_id]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan.smem_bytes)) != cudaSuccess) {
+            return checkLaunch("cudaFuncSetAttribute(pagedDecodeStreamKernel)");
+        }
+        if (device_id >= 0 && device_id < 64) {
+            attr_done[device_id] = true;
+        }
+    }
+    pagedDecodePlanKernel<<<1, kPlanThreads, 0, stream>>>(args);
+    kernel<<<plan.grid, plan.warps_per_cta * 32, plan.smem_bytes, stream>>>(mk, mv, args);
+    const long long pairs = static_cast<long long>(args.p.num_seqs) * args.p.num_heads;
+    const unsigned combine_blocks = static_cast<unsigned>((pairs + 3) / 4);
+    pagedDecodeCombineKernel<T, HD><<<combine_blocks, 128, 0, stream>>>(args);
+    return checkLaunch("pagedDecodeStream");
+}
+
+} // namespace
+
+StreamPlan planStream(const Info &I, const DeviceProps &props) {
+    StreamPlan plan;
+    const size_t hd = I.head_size;
+    if (I.value_size != hd || (hd != 64 && hd != 128 && hd != 192 && hd != 256)) {
+        return plan;
+    }
+    if (I.block_size % kTileTokens != 0 || I.num_seqs == 0 || I.num_heads == 0) {
+        return plan;
+    }
+    auto even = [](ptrdiff_t v) { return (v & 1) == 0; };
+    auto mult8 = [](ptrdiff_t v) { return v > 0 && (v % 8) == 0; }; // 16 bytes of a 2-byte dtype
+    if (!even(I.q_seq_stride) || !even(I.q_head_stride) || !even(I.o_seq_stride) || !even(I.o_head_stride)) {
+        return plan;
+    }
+    if (!mult8(I.k_row_stride) || !mult8(I.k_head_stride) || !mult8(I.k_block_stride)
+        || !mult8(I.v_row_stride) || !mult8(I.v_head_stride) || !mult8(I.v_block_stride)) {
+        return plan;
+    }
+    if (I.num_blocks == 0) {
+        return plan;
+    }
+    // Total tiles must stay far from 64-bit overflow and per-sequence tiles must fit an int.
+    const unsigned long long tiles_per_seq_max = static_cast<unsigned long long>(I.max_num_blocks_per_seq) * (I.block_size / kTileTokens);
+    if (tiles_per_seq_max > 0x3fffffffull) {
+        return plan;
+    }
+    // Trial encode with a stand-in base address: checks that the driver accepts these strides.
+    CUtensorMap probe;
+    void *fake = reinterpret_cast<void *>(static_cast<uintptr_t>(1) << 30);
+    if (!encodeCacheMap(&probe, I, fake, I.k_row_stride, I.k_head_stride, I.k_block_stride, hd)
+        || !encodeCacheMap(&probe, I, fake, I.v_row_stride, I.v_head_stride, I.v_block_stride, hd)) {
+        return plan;
+    }
+
+    const int group = static_cast<int>(I.num_heads / I.num_kv_heads);
+    plan.head_tiles_per_group = (group + kHeadsPerTile - 1) / kHeadsPerTile;
+
+    const size_t stage_bytes = 2 * (hd / 64) * kTileTokens * 128;
+    const int default_stages = (hd <= 128) ? 3 : 2;
+    plan.warps_per_cta = envInt("INFINIOP_PAGED_DECODE_WARPS", 4, 1, kMaxWarps);
+    plan.stages = envInt("INFINIOP_PAGED_DECODE_STAGES", default_stages, 1, kMaxStages);
+    int ctas_per_sm = envInt("INFINIOP_PAGED_DECODE_CTAS_PER_SM", 2, 1, 8);
+    auto smemFor = [&](int warps, int stages) { return static_cast<size_t>(warps) * stages * (stage_bytes + 8) + 1024; };
+    const size_t budget = props.smem_per_block_optin;
+    while (plan.stages > 1 && smemFor(plan.warps_per_cta, plan.stages) > budget) {
+        --plan.stages;
+    }
+    if (smemFor(plan.warps_per_cta, plan.stages) > budget) {
+        return plan;
+    }
+    plan.smem_bytes = smemFor(plan.warps_per_cta, plan.stages);
+    // Each resident CTA also reserves 1 KiB of system shared memory.
+    while (ctas_per_sm > 1 && ctas_per_sm * (plan.smem_bytes + 1024) > props.smem_per_sm) {
+        --ctas_per_sm;
+    }
+    plan.grid = props.sm_count * ctas_per_sm;
+    plan.num_workers = plan.grid * plan.warps_per_cta;
+    plan.workspace_bytes = workspaceLayout(I, plan).total;
+    plan.eligible = true;
+    return plan;
+}
+
+infiniStatus_t launchDecodeStream(const Info &I, const StreamPlan &plan, const DecodeParams &p,
+                                  void *workspace, size_t workspace_size, cudaStream_t stream) {
+    B200_RETURN_IF(workspace_size < plan.workspace_bytes, INFINI_STATUS_INSUFFICIENT_WORKSPACE);
+    const auto addr = [](const void *ptr) { return reinterpret_cast<uintptr_t>(ptr); };
+    // TMA needs 16-byte aligned pool bases; the fragment loads need 4-byte aligned q/out.
+    if (((addr(p.k_cache) | addr(p.v_cache)) & 15u) != 0 || ((addr(p.q) | addr(p.out)) & 3u) != 0 || (addr(workspace) & 255u) != 0) {
+        return launchDecodeGeneric(I, p, stream);
+    }
+    CUtensorMap mk, mv;
+    B200_RETURN_IF(!encodeCacheMap(&mk, I, p.k_cache, I.k_row_stride, I.k_head_stride, I.k_block_stride, I.head_size), INFINI_STATUS_INTERNAL_ERROR);
+    B200_RETURN_IF(!encodeCacheMap(&mv, I, p.v_cache, I.v_row_stride, I.v_head_stride, I.v_block_stride, I.value_size), INFINI_STATUS_INTERNAL_ERROR);
+
+    const WorkspaceLayout L = workspaceLayout(I, plan);
+    auto *ws = static_cast<unsigned char *>(workspace);
+    StreamArgs a;
+    a.p = p;
+    a.header = reinterpret_cast<PlanHeader *>(ws + L.header_off);
+    a.prefix = reinterpret_cast<long long *>(ws + L.prefix_off);
+    a.range_start = reinterpret_cast<int4 *>(ws + L.range_off);
+    a.partials = reinterpret_cast<float *>(ws + L.partial_off);
+    a.head_tiles = plan.head_tiles_per_group;
+    a.units_per_seq = static_cast<int>(I.num_kv_heads) * plan.head_tiles_per_group;
+    a.tiles_per_page = static_cast<int>(I.block_size / kTileTokens);
+    a.stages = plan.stages;
+    a.num_workers = plan.num_workers;
+
+    int device_id = -1;
+    (void)cudaGetDevice(&device_id);
+    const bool f16 = (I.dtype == INFINI_DTYPE_F16);
+    switch (I.head_size) {
+    case 64:
+        return f16 ? launchTyped<__half, 64>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 64>(plan, a, mk, mv, device_id, stream);
+    case 128:
+        return f16 ? launchTyped<__half, 128>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 128>(plan, a, mk, mv, device_id, stream);
+    case 192:
+        return f16 ? launchTyped<__half, 192>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 192>(plan, a, mk, mv, device_id, stream);
+    case 256:
+        return f16 ? launchTyped<__half, 256>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 256>(plan, a, mk, mv, device_id, stream);
+    default:
+        return INFINI_STATUS_BAD_TENSOR_SHAPE;
+    }
+}
+
+} // namespace b200::paged_attention

@@ -1,0 +1,68 @@
+// Launch interface between the paged-attention descriptor code and its CUDA kernels.
+#ifndef INFINIOP_B200_PAGED_ATTENTION_KERNELS_H
+#define INFINIOP_B200_PAGED_ATTENTION_KERNELS_H
+
+#include "info.h"
+
+#include <cuda.h>
+
+namespace b200::paged_attention {
+
+// Everything a decode kernel needs; strides are in ELEMENTS of the tensor's dtype.
+struct DecodeParams {
+    void *out;
+    const void *q;
+    const void *k_cache;
+    const void *v_cache;
+    const void *block_tables;
+    const void *seq_lens;
+    const float *alibi_slopes; // may be null
+
+    int num_seqs;
+    int num_heads;
+    int num_kv_heads;
+    int group_size; // num_heads / num_kv_heads
+    int head_size;
+    int value_size;
+    int block_size;
+    int max_blocks_per_seq;
+    int index_is_64; // block_tables / seq_lens element width: 1 => 8 bytes, 0 => 4 bytes
+
+    long long q_seq_stride, q_head_stride;
+    long long o_seq_stride, o_head_stride;
+    long long k_block_stride, k_head_stride, k_row_stride;
+    long long v_block_stride, v_head_stride, v_row_stride;
+    long long bt_seq_stride;
+
+    float scale_log2e; // scale * log2(e): scores live in the log2 domain, softmax uses exp2
+};
+
+__host__ __device__ inline long long loadIndex(const void *base, long long i, int is64) {
+    return is64 ? static_cast<const long long *>(base)[i]
+                : static_cast<long long>(static_cast<const int *>(base)[i]);
+}
+
+// ---- generic SIMT path (any supported head/value size, block size and strides) ---------
+infiniStatus_t launchDecodeGeneric(const Info &info, const DecodeParams &p, cudaStream_t stream);
+
+// ---- streaming path: TMA page staging + mma.sync, work split evenly over persistent warps
+struct StreamPlan {
+    bool eligible = false;
+    int head_tiles_per_group = 1; // q-heads of a GQA group are processed 8 at a time
+    int warps_per_cta = 0;
+    int stages = 0;
+    int grid = 0;        // persistent CTAs
+    int num_workers = 0; // grid * warps_per_cta
+    size_t smem_bytes = 0;
+    size_t workspace_bytes = 0;
+};
+
+// Decides at descriptor creation whether the streaming path applies and sizes its workspace.
+StreamPlan planStream(const Info &info, const DeviceProps &props);
+
+infiniStatus_t launchDecodeStream(const Info &info, const StreamPlan &plan, const DecodeParams &p,
+                                  void *workspace, size_t workspace_size, cudaStream_t stream);
+
+} // namespace b200::paged_attention
+
+#endif

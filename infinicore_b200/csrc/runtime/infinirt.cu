@@ -1,0 +1,348 @@
+// libinfinirt: the runtime C API over the CUDA runtime, NVIDIA devices only.
+//
+// Mirrors the behaviour of reference src/infinirt/infinirt.cc (dispatcher, thread-local
+// current device) and src/infinirt/cuda/infinirt_cuda.cu:264-470 (CUDA backend) for the
+// entry points declared in include/infinirt.h.  There is no CPU backend: with the
+// current device left at INFINI_DEVICE_CPU (the initial state of every thread) all
+// stream/event/memory calls return INFINI_STATUS_DEVICE_TYPE_NOT_SUPPORTED.
+#include "infinirt.h"
+
+#include <cuda_runtime.h>
+
+#include <cstdio>
+
+namespace {
+
+thread_local infiniDevice_t t_device_type = INFINI_DEVICE_CPU;
+thread_local int t_device_id = 0;
+
+inline infiniStatus_t fromCuda(cudaError_t err, const char *what) {
+    if (err == cudaSuccess) {
+        return INFINI_STATUS_SUCCESS;
+    }
+    std::fprintf(stderr, "[infinirt] %s failed: %s\n", what, cudaGetErrorString(err));
+    return INFINI_STATUS_INTERNAL_ERROR;
+}
+
+#define RT_CUDA(call) return fromCuda((call), #call)
+
+#define RT_REQUIRE_NVIDIA()                                   \
+    do {                                                      \
+        if (t_device_type != INFINI_DEVICE_NVIDIA) {          \
+            return INFINI_STATUS_DEVICE_TYPE_NOT_SUPPORTED;   \
+        }                                                     \
+    } while (0)
+
+#define RT_REQUIRE_PTR(p)                                     \
+    do {                                                      \
+        if ((p) == nullptr) {                                 \
+            return INFINI_STATUS_NULL_POINTER;                \
+        }                                                     \
+    } while (0)
+
+inline cudaMemcpyKind toCudaKind(infinirtMemcpyKind_t kind) {
+    switch (kind) {
+    case INFINIRT_MEMCPY_H2H:
+        return cudaMemcpyHostToHost;
+    case INFINIRT_MEMCPY_H2D:
+        return cudaMemcpyHostToDevice;
+    case INFINIRT_MEMCPY_D2H:
+        return cudaMemcpyDeviceToHost;
+    case INFINIRT_MEMCPY_D2D:
+        return cudaMemcpyDeviceToDevice;
+    }
+    return cudaMemcpyDefault;
+}
+
+} // namespace
+
+__INFINI_C infiniStatus_t infinirtInit() {
+    return INFINI_STATUS_SUCCESS;
+}
+
+__INFINI_C infiniStatus_t infinirtGetDeviceCount(infiniDevice_t device, int *count) {
+    RT_REQUIRE_PTR(count);
+    if (device == INFINI_DEVICE_CPU) {
+        *count = 1;
+        return INFINI_STATUS_SUCCESS;
+    }
+    if (device != INFINI_DEVICE_NVIDIA) {
+        *count = 0;
+        return INFINI_STATUS_SUCCESS;
+    }
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        (void)cudaGetLastError();
+        n = 0;
+    }
+    *count = n;
+    return INFINI_STATUS_SUCCESS;
+}
+
+__INFINI_C infiniStatus_t infinirtGetAllDeviceCount(int *count_array) {
+    RT_REQUIRE_PTR(count_array);
+    for (int i = 0; i < INFINI_DEVICE_TYPE_COUNT; ++i) {
+        infiniStatus_t st = infinirtGetDeviceCount(static_cast<infiniDevice_t>(i), &count_array[i]);
+        if (st != INFINI_STATUS_SUCCESS) {
+            return st;
+        }
+    }
+    return INFINI_STATUS_SUCCESS;
+}
+
+__INFINI_C infiniStatus_t infinirtSetDevice(infiniDevice_t device, int device_id) {
+    if (device == INFINI_DEVICE_CPU) {
+        t_device_type = device;
+        t_device_id = device_id;
+        return INFINI_STATUS_SUCCESS;
+    }
+    if (device != INFINI_DEVICE_NVIDIA) {
+        return INFINI_STATUS_DEVICE_TYPE_NOT_SUPPORTED;
+    }
+    cudaError_t err = cudaSetDevice(device_id);
+    if (err != cudaSuccess) {
+        (void)cudaGetLastError();
+        std::fprintf(stderr, "[infinirt] cudaSetDevice(%d) failed: %s\n", device_id, cudaGetErrorString(err));
+        return INFINI_STATUS_DEVICE_NOT_FOUND;
+    }
+    t_device_type = device;
+    t_device_id = device_id;
+    return INFINI_STATUS_SUCCESS;
+}
+
+__INFINI_C infiniStatus_t infinirtGetDevice(infiniDevice_t *device_ptr, int *device_id_ptr) {
+    if (device_ptr == nullptr && device_id_ptr == nullptr) {
+        return INFINI_STATUS_NULL_POINTER;
+    }
+    if (device_ptr != nullptr) {
+        *device_ptr = t_device_type;
+    }
+    if (device_id_ptr != nullptr) {
+        *device_id_ptr = t_device_id;
+    }
+    return INFINI_STATUS_SUCCESS;
+}
+
+__INFINI_C infiniStatus_t infinirtGetMemInfo(infiniDevice_t device, int device_id, size_t *free_bytes, size_t *total_bytes) {
+    RT_REQUIRE_PTR(free_bytes);
+    RT_REQUIRE_PTR(total_bytes);
+    if (device != INFINI_DEVICE_NVIDIA) {
+        return INFINI_STATUS_DEVICE_TYPE_NOT_SUPPORTED;
+    }
+    int prev = 0;
+    if (cudaGetDevice(&prev) != cudaSuccess) {
+        return INFINI_STATUS_INTERNAL_ERROR;
+    }
+    if (cudaSetDevice(device_id) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return INFINI_STATUS_DEVICE_NOT_FOUND;
+    }
+    cudaError_t err = cudaMemGetInfo(free_bytes, total_bytes);
+    (void)cudaSetDevice(prev);
+    return fromCuda(err, "cudaMemGetInfo");
+}
+
+__INFINI_C infiniStatus_t infinirtDeviceSynchronize() {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaDeviceSynchronize());
+}
+
+// ---- streams -------------------------------------------------------------------------
+
+__INFINI_C infiniStatus_t infinirtStreamCreate(infinirtStream_t *stream_ptr) {
+    RT_REQUIRE_PTR(stream_ptr);
+    RT_REQUIRE_NVIDIA();
+    cudaStream_t s = nullptr;
+    cudaError_t err = cudaStreamCreate(&s);
+    *stream_ptr = s;
+    return fromCuda(err, "cudaStreamCreate");
+}
+
+__INFINI_C infiniStatus_t infinirtStreamDestroy(infinirtStream_t stream) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
+}
+
+__INFINI_C infiniStatus_t infinirtStreamSynchronize(infinirtStream_t stream) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+}
+
+__INFINI_C infiniStatus_t infinirtStreamWaitEvent(infinirtStream_t stream, infinirtEvent_t event) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(event), 0));
+}
+
+// ---- events --------------------------------------------------------------------------
+
+__INFINI_C infiniStatus_t infinirtEventCreate(infinirtEvent_t *event_ptr) {
+    RT_REQUIRE_PTR(event_ptr);
+    RT_REQUIRE_NVIDIA();
+    cudaEvent_t e = nullptr;
+    cudaError_t err = cudaEventCreate(&e);
+    *event_ptr = e;
+    return fromCuda(err, "cudaEventCreate");
+}
+
+__INFINI_C infiniStatus_t infinirtEventCreateWithFlags(infinirtEvent_t *event_ptr, uint32_t flags) {
+    RT_REQUIRE_PTR(event_ptr);
+    RT_REQUIRE_NVIDIA();
+    unsigned int cuda_flags = cudaEventDefault;
+    if (flags & INFINIRT_EVENT_DISABLE_TIMING) {
+        cuda_flags |= cudaEventDisableTiming;
+    }
+    if (flags & INFINIRT_EVENT_BLOCKING_SYNC) {
+        cuda_flags |= cudaEventBlockingSync;
+    }
+    cudaEvent_t e = nullptr;
+    cudaError_t err = cudaEventCreateWithFlags(&e, cuda_flags);
+    *event_ptr = e;
+    return fromCuda(err, "cudaEventCreateWithFlags");
+}
+
+__INFINI_C infiniStatus_t infinirtEventRecord(infinirtEvent_t event, infinirtStream_t stream) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)));
+}
+
+__INFINI_C infiniStatus_t infinirtEventQuery(infinirtEvent_t event, infinirtEventStatus_t *status_ptr) {
+    RT_REQUIRE_PTR(status_ptr);
+    RT_REQUIRE_NVIDIA();
+    cudaError_t err = cudaEventQuery(static_cast<cudaEvent_t>(event));
+    if (err == cudaSuccess) {
+        *status_ptr = INFINIRT_EVENT_COMPLETE;
+        return INFINI_STATUS_SUCCESS;
+    }
+    if (err == cudaErrorNotReady) {
+        (void)cudaGetLastError();
+        *status_ptr = INFINIRT_EVENT_NOT_READY;
+        return INFINI_STATUS_SUCCESS;
+    }
+    return fromCuda(err, "cudaEventQuery");
+}
+
+__INFINI_C infiniStatus_t infinirtEventSynchronize(infinirtEvent_t event) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaEventSynchronize(static_cast<cudaEvent_t>(event)));
+}
+
+__INFINI_C infiniStatus_t infinirtEventDestroy(infinirtEvent_t event) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+}
+
+__INFINI_C infiniStatus_t infinirtEventElapsedTime(float *ms_ptr, infinirtEvent_t start, infinirtEvent_t end) {
+    RT_REQUIRE_PTR(ms_ptr);
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaEventElapsedTime(ms_ptr, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(end)));
+}
+
+// ---- memory --------------------------------------------------------------------------
+
+__INFINI_C infiniStatus_t infinirtMalloc(void **p_ptr, size_t size) {
+    RT_REQUIRE_PTR(p_ptr);
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaMalloc(p_ptr, size));
+}
+
+__INFINI_C infiniStatus_t infinirtMallocHost(void **p_ptr, size_t size) {
+    RT_REQUIRE_PTR(p_ptr);
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaMallocHost(p_ptr, size));
+}
+
+__INFINI_C infiniStatus_t infinirtFree(void *ptr) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaFree(ptr));
+}
+
+__INFINI_C infiniStatus_t infinirtFreeHost(void *ptr) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaFreeHost(ptr));
+}
+
+__INFINI_C infiniStatus_t infinirtMemcpy(void *dst, const void *src, size_t size, infinirtMemcpyKind_t kind) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaMemcpy(dst, src, size, toCudaKind(kind)));
+}
+
+__INFINI_C infiniStatus_t infinirtMemcpyAsync(void *dst, const void *src, size_t size, infinirtMemcpyKind_t kind, infinirtStream_t stream) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaMemcpyAsync(dst, src, size, toCudaKind(kind), static_cast<cudaStream_t>(stream)));
+}
+
+__INFINI_C infiniStatus_t infinirtMallocAsync(void **p_ptr, size_t size, infinirtStream_t stream) {
+    RT_REQUIRE_PTR(p_ptr);
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaMallocAsync(p_ptr, size, static_cast<cudaStream_t>(stream)));
+}
+
+__INFINI_C infiniStatus_t infinirtFreeAsync(void *ptr, infinirtStream_t stream) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaFreeAsync(ptr, static_cast<cudaStream_t>(stream)));
+}
+
+__INFINI_C infiniStatus_t infinirtMemset(void *ptr, int value, size_t count) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaMemset(ptr, value, count));
+}
+
+__INFINI_C infiniStatus_t infinirtMemsetAsync(void *ptr, int value, size_t count, infinirtStream_t stream) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaMemsetAsync(ptr, value, count, static_cast<cudaStream_t>(stream)));
+}
+
+// ---- graph capture -------------------------------------------------------------------
+
+__INFINI_C infiniStatus_t infinirtStreamBeginCapture(infinirtStream_t stream, infinirtStreamCaptureMode_t mode) {
+    RT_REQUIRE_NVIDIA();
+    cudaStreamCaptureMode cuda_mode = cudaStreamCaptureModeGlobal;
+    if (mode == INFINIRT_STREAM_CAPTURE_MODE_THREAD_LOCAL) {
+        cuda_mode = cudaStreamCaptureModeThreadLocal;
+    } else if (mode == INFINIRT_STREAM_CAPTURE_MODE_RELAXED) {
+        cuda_mode = cudaStreamCaptureModeRelaxed;
+    }
+    RT_CUDA(cudaStreamBeginCapture(static_cast<cudaStream_t>(stream), cuda_mode));
+}
+
+__INFINI_C infiniStatus_t infinirtStreamEndCapture(infinirtStream_t stream, infinirtGraph_t *graph_ptr) {
+    RT_REQUIRE_PTR(graph_ptr);
+    RT_REQUIRE_NVIDIA();
+    cudaGraph_t g = nullptr;
+    cudaError_t err = cudaStreamEndCapture(static_cast<cudaStream_t>(stream), &g);
+    *graph_ptr = g;
+    return fromCuda(err, "cudaStreamEndCapture");
+}
+
+__INFINI_C infiniStatus_t infinirtGraphDestroy(infinirtGraph_t graph) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaGraphDestroy(static_cast<cudaGraph_t>(graph)));
+}
+
+__INFINI_C infiniStatus_t infinirtGraphInstantiate(
+    infinirtGraphExec_t *graph_exec_ptr,
+    infinirtGraph_t graph,
+    infinirtGraphNode_t *node_ptr,
+    char *log_buffer,
+    size_t buffer_size) {
+    RT_REQUIRE_PTR(graph_exec_ptr);
+    RT_REQUIRE_NVIDIA();
+    (void)node_ptr;
+    if (log_buffer != nullptr && buffer_size > 0) {
+        log_buffer[0] = '\0';
+    }
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t err = cudaGraphInstantiate(&exec, static_cast<cudaGraph_t>(graph), 0);
+    *graph_exec_ptr = exec;
+    return fromCuda(err, "cudaGraphInstantiate");
+}
+
+__INFINI_C infiniStatus_t infinirtGraphExecDestroy(infinirtGraphExec_t graph_exec) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph_exec)));
+}
+
+__INFINI_C infiniStatus_t infinirtGraphLuanch(infinirtGraphExec_t graph_exec, infinirtStream_t stream) {
+    RT_REQUIRE_NVIDIA();
+    RT_CUDA(cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph_exec), static_cast<cudaStream_t>(stream)));
+}

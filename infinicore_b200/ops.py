@@ -1,0 +1,148 @@
+"""User-facing operators on torch CUDA tensors, routed through the C ABI.
+
+Same names, argument order and meaning as the reference's Python operators
+(python/infinicore/ops/paged_attention.py:5-41, python/infinicore/ops/paged_caching.py:5-22);
+descriptor reuse follows the reference's per-thread, per-device LRU keyed on tensor metadata
+(src/infinicore/ops/infiniop_impl.hpp:8-78, capacity 100).  torch supplies device memory and the
+current stream; every byte of compute happens inside libinfiniop.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from collections import OrderedDict
+
+import torch
+
+from .libinfiniop import (
+    LIBINFINIOP, InfiniDeviceEnum, InfiniDtype, TestTensor, check_error, create_handle,
+    infiniopOperatorDescriptor_t, to_infini_dtype,
+)
+
+_CACHE_CAPACITY = 100
+_tls = threading.local()
+
+
+def _state(device_index: int):
+    per_dev = getattr(_tls, "per_dev", None)
+    if per_dev is None:
+        per_dev = _tls.per_dev = {}
+    st = per_dev.get(device_index)
+    if st is None:
+        check_error(LIBINFINIOP.infinirtSetDevice(InfiniDeviceEnum.NVIDIA, device_index))
+        st = per_dev[device_index] = {"handle": create_handle(), "cache": OrderedDict(), "workspace": {}}
+    else:
+        # infinirt's current device is per host thread; keep it in step with the tensors' device
+        check_error(LIBINFINIOP.infinirtSetDevice(InfiniDeviceEnum.NVIDIA, device_index))
+    return st
+
+
+def _meta(t, index_dtype=None):
+    if t is None:
+        return None
+    return (index_dtype or str(t.dtype), tuple(t.shape), tuple(t.stride()))
+
+
+def _desc(t: torch.Tensor, dt=None):
+    return TestTensor.from_torch(t, dt if dt is not None else to_infini_dtype(t.dtype), InfiniDeviceEnum.NVIDIA)
+
+
+def _require_cuda(*tensors):
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("infinicore_b200 operators run on CUDA tensors only; there is no CPU fallback")
+        dev = t.device.index if dev is None else dev
+        if t.device.index != dev:
+            raise RuntimeError("all tensors of one call must live on the same GPU")
+    return dev
+
+
+def _lookup(st, key, make):
+    cache = st["cache"]
+    entry = cache.get(key)
+    if entry is None:
+        entry = make()
+        cache[key] = entry
+        if len(cache) > _CACHE_CAPACITY:
+            _, old = cache.popitem(last=False)
+            old["destroy"](old["desc"])
+    else:
+        cache.move_to_end(key)
+    return entry
+
+
+def _workspace(st, nbytes: int, device_index: int):
+    """One grow-only scratch buffer per (thread, device, stream)."""
+    if nbytes == 0:
+        return None
+    stream = torch.cuda.current_stream(device_index).cuda_stream
+    buf = st["workspace"].get(stream)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=f"cuda:{device_index}")
+        st["workspace"][stream] = buf
+    return buf
+
+
+def paged_attention(q, k_cache, v_cache, block_tables, cache_lens, alibi_slopes=None, scale: float = 1.0, *, out=None):
+    """Decode attention of one query token per sequence over a paged KV cache.
+
+    q [num_seqs, num_heads, head_size]; k_cache/v_cache [num_blocks, num_kv_heads, block_size,
+    head_size]; block_tables [num_seqs, max_blocks] and cache_lens [num_seqs] int64 or int32.
+    Returns `out` (allocated when not given)."""
+    dev = _require_cuda(q, k_cache, v_cache, block_tables, cache_lens, alibi_slopes, out)
+    if out is None:
+        out = torch.empty((*q.shape[:-1], v_cache.shape[3]), dtype=q.dtype, device=q.device)
+    st = _state(dev)
+    key = ("paged_attention", _meta(out), _meta(q), _meta(k_cache), _meta(v_cache), _meta(block_tables),
+           _meta(cache_lens), _meta(alibi_slopes), float(scale))
+
+    def make():
+        tensors = [_desc(out), _desc(q), _desc(k_cache), _desc(v_cache), _desc(block_tables), _desc(cache_lens)]
+        alibi = _desc(alibi_slopes) if alibi_slopes is not None else None
+        desc = infiniopOperatorDescriptor_t()
+        check_error(LIBINFINIOP.infiniopCreatePagedAttentionDescriptor(
+            st["handle"], ctypes.byref(desc), *[t.descriptor for t in tensors],
+            alibi.descriptor if alibi is not None else None, scale))
+        size = ctypes.c_size_t(0)
+        check_error(LIBINFINIOP.infiniopGetPagedAttentionWorkspaceSize(desc, ctypes.byref(size)))
+        for t in tensors + ([alibi] if alibi is not None else []):
+            t.destroy_desc()
+        return {"desc": desc, "workspace": size.value, "destroy": LIBINFINIOP.infiniopDestroyPagedAttentionDescriptor}
+
+    entry = _lookup(st, key, make)
+    ws = _workspace(st, entry["workspace"], dev)
+    with torch.cuda.device(dev):
+        check_error(LIBINFINIOP.infiniopPagedAttention(
+            entry["desc"], ws.data_ptr() if ws is not None else None, entry["workspace"],
+            out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            block_tables.data_ptr(), cache_lens.data_ptr(),
+            alibi_slopes.data_ptr() if alibi_slopes is not None else None,
+            torch.cuda.current_stream(dev).cuda_stream))
+    return out
+
+
+def paged_caching(k_cache, v_cache, k, v, slot_mapping):
+    """Scatters k/v rows [num_tokens, num_kv_heads, head_size] into the paged pools at
+    slot_mapping (int64; negative = padding).  Returns (k_cache, v_cache)."""
+    dev = _require_cuda(k_cache, v_cache, k, v, slot_mapping)
+    st = _state(dev)
+    key = ("paged_caching", _meta(k_cache), _meta(v_cache), _meta(k), _meta(v), _meta(slot_mapping))
+
+    def make():
+        tensors = [_desc(k_cache), _desc(v_cache), _desc(k), _desc(v), _desc(slot_mapping)]
+        desc = infiniopOperatorDescriptor_t()
+        check_error(LIBINFINIOP.infiniopCreatePagedCachingDescriptor(
+            st["handle"], ctypes.byref(desc), *[t.descriptor for t in tensors]))
+        for t in tensors:
+            t.destroy_desc()
+        return {"desc": desc, "workspace": 0, "destroy": LIBINFINIOP.infiniopDestroyPagedCachingDescriptor}
+
+    entry = _lookup(st, key, make)
+    with torch.cuda.device(dev):
+        check_error(LIBINFINIOP.infiniopPagedCaching(
+            entry["desc"], None, 0, k_cache.data_ptr(), v_cache.data_ptr(), k.data_ptr(), v.data_ptr(),
+            slot_mapping.data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
+    return (k_cache, v_cache)

@@ -1,0 +1,122 @@
+"""TEST INFRASTRUCTURE - CPU oracle for the paged decode path.
+
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline leg may import this package.
+It wraps oracle/paged_oracle.c (a restatement of the reference's torch checkers, see the
+header of that file) for numpy arrays holding raw 16-bit patterns.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_double, c_float, c_int, c_int64, c_ssize_t, c_uint16, c_void_p
+
+import numpy as np
+
+from .build import build as _build
+
+F16, F32, BF16 = 12, 13, 19
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(str(_build()))
+        _lib.oracle_paged_attention.restype = c_int
+        _lib.oracle_paged_attention.argtypes = [
+            c_int, c_int, c_void_p,
+            c_void_p, c_ssize_t, c_ssize_t,
+            c_void_p, c_ssize_t, c_ssize_t, c_ssize_t,
+            c_void_p, c_ssize_t, c_ssize_t, c_ssize_t,
+            c_void_p, c_ssize_t,
+            c_void_p,
+            c_void_p,
+            c_float,
+            c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+        ]
+        _lib.oracle_paged_caching.restype = c_int
+        _lib.oracle_paged_caching.argtypes = [
+            c_int64,
+            c_void_p, c_ssize_t, c_ssize_t, c_ssize_t,
+            c_void_p, c_ssize_t, c_ssize_t, c_ssize_t,
+            c_void_p, c_ssize_t, c_ssize_t,
+            c_void_p, c_ssize_t, c_ssize_t,
+            c_void_p,
+            c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+        ]
+        _lib.oracle_float_to_f16.restype = c_uint16
+        _lib.oracle_float_to_f16.argtypes = [c_float]
+        _lib.oracle_float_to_bf16.restype = c_uint16
+        _lib.oracle_float_to_bf16.argtypes = [c_float]
+        _lib.oracle_f16_to_float.restype = c_float
+        _lib.oracle_f16_to_float.argtypes = [c_uint16]
+        _lib.oracle_bf16_to_float.restype = c_float
+        _lib.oracle_bf16_to_float.argtypes = [c_uint16]
+        _lib.oracle_num_threads.restype = c_int
+    return _lib
+
+
+def num_threads() -> int:
+    return int(lib().oracle_num_threads())
+
+
+def _elem_strides(a: np.ndarray):
+    assert all(s % a.itemsize == 0 for s in a.strides)
+    return [s // a.itemsize for s in a.strides]
+
+
+def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, scale, dtype, alibi_slopes=None,
+                    mode="exact", out=None) -> np.ndarray:
+    """q/k_cache/v_cache: uint16 arrays of raw F16/BF16 bits (any strides, last dim dense).
+    Returns float64 [num_seqs, num_heads, value_size]; rows of empty sequences keep the
+    values of `out` (NaN when `out` is not given)."""
+    assert q.dtype == np.uint16 and k_cache.dtype == np.uint16 and v_cache.dtype == np.uint16
+    num_seqs, num_heads, head_size = q.shape
+    num_blocks, num_kv_heads, block_size, _ = k_cache.shape
+    value_size = v_cache.shape[3]
+    bt = np.ascontiguousarray(block_tables, dtype=np.int64)
+    sl = np.ascontiguousarray(seq_lens, dtype=np.int64)
+    if out is None:
+        out = np.full((num_seqs, num_heads, value_size), np.nan, dtype=np.float64)
+    assert out.dtype == np.float64 and out.flags.c_contiguous
+    qs, ks, vs = _elem_strides(q), _elem_strides(k_cache), _elem_strides(v_cache)
+    assert qs[2] == 1 and ks[3] == 1 and vs[3] == 1
+    al = None
+    if alibi_slopes is not None:
+        al = np.ascontiguousarray(alibi_slopes, dtype=np.float32)
+    rc = lib().oracle_paged_attention(
+        0 if mode == "exact" else 1, int(dtype), out.ctypes.data,
+        q.ctypes.data, qs[0], qs[1],
+        k_cache.ctypes.data, ks[0], ks[1], ks[2],
+        v_cache.ctypes.data, vs[0], vs[1], vs[2],
+        bt.ctypes.data, bt.shape[1] if bt.ndim == 2 else 0,
+        sl.ctypes.data,
+        al.ctypes.data if al is not None else None,
+        float(scale),
+        num_seqs, num_heads, num_kv_heads, head_size, value_size, block_size, num_blocks, bt.shape[1],
+    )
+    if rc != 0:
+        raise ValueError(f"oracle_paged_attention rejected its input (code {rc})")
+    return out
+
+
+def paged_caching(k_cache, v_cache, k, v, slot_mapping) -> None:
+    """In-place, byte-exact scatter of k/v rows into the pools (arrays of any 2- or 4-byte dtype)."""
+    es = k_cache.itemsize
+    assert v_cache.itemsize == es and k.itemsize == es and v.itemsize == es
+    num_blocks, num_kv_heads, block_size, head_size = k_cache.shape[:4]
+    v_head_size = v_cache.shape[3]
+    sm = np.ascontiguousarray(slot_mapping, dtype=np.int64)
+    kcs, vcs, ks, vs = (_elem_strides(a) for a in (k_cache, v_cache, k, v))
+    assert kcs[3] == 1 and vcs[3] == 1 and ks[2] == 1 and vs[2] == 1
+    rc = lib().oracle_paged_caching(
+        es,
+        k_cache.ctypes.data, kcs[0], kcs[1], kcs[2],
+        v_cache.ctypes.data, vcs[0], vcs[1], vcs[2],
+        k.ctypes.data, ks[0], ks[1],
+        v.ctypes.data, vs[0], vs[1],
+        sm.ctypes.data,
+        sm.shape[0], num_kv_heads, head_size, v_head_size, block_size, num_blocks,
+    )
+    if rc != 0:
+        raise ValueError(f"oracle_paged_caching rejected its input (code {rc})")

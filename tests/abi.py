@@ -1,0 +1,132 @@
+"""Calls the two operators through the C ABI exactly as the reference's own tests do
+(test/infiniop/paged_attention.py:202-251, test/infiniop/paged_caching.py:164-212): build
+tensor descriptors, create the operator descriptor, query the workspace, destroy the tensor
+descriptors BEFORE executing, execute on the NULL stream with a 0x01-filled workspace."""
+from __future__ import annotations
+
+import contextlib
+import ctypes
+import os
+
+import torch
+
+from infinicore_b200.libinfiniop import (
+    LIBINFINIOP, InfiniDeviceEnum, InfiniDtype, TestTensor, TestWorkspace, check_error, create_handle,
+    destroy_handle, infiniopOperatorDescriptor_t, to_infini_dtype,
+)
+
+_handle = None
+
+
+def handle():
+    global _handle
+    if _handle is None:
+        check_error(LIBINFINIOP.infinirtSetDevice(InfiniDeviceEnum.NVIDIA, 0))
+        _handle = create_handle()
+    return _handle
+
+
+@contextlib.contextmanager
+def decode_path(path):
+    """The decode path is chosen when the descriptor is created (INFINIOP_PAGED_DECODE_PATH)."""
+    old = os.environ.get("INFINIOP_PAGED_DECODE_PATH")
+    if path is None:
+        os.environ.pop("INFINIOP_PAGED_DECODE_PATH", None)
+    else:
+        os.environ["INFINIOP_PAGED_DECODE_PATH"] = path
+    try:
+        yield
+    finally:
+        if old is None:
+            os.environ.pop("INFINIOP_PAGED_DECODE_PATH", None)
+        else:
+            os.environ["INFINIOP_PAGED_DECODE_PATH"] = old
+
+
+def _tt(t, dt=None):
+    return TestTensor.from_torch(t, dt if dt is not None else to_infini_dtype(t.dtype), InfiniDeviceEnum.NVIDIA)
+
+
+class AttentionOp:
+    """One created paged-attention descriptor plus its workspace."""
+
+    def __init__(self, out, q, k_cache, v_cache, block_tables, seq_lens, alibi, scale, path=None, index_dtype=None):
+        tensors = [_tt(out), _tt(q), _tt(k_cache), _tt(v_cache), _tt(block_tables, index_dtype), _tt(seq_lens, index_dtype)]
+        al = _tt(alibi) if alibi is not None else None
+        self.desc = infiniopOperatorDescriptor_t()
+        with decode_path(path):
+            self.status = LIBINFINIOP.infiniopCreatePagedAttentionDescriptor(
+                handle(), ctypes.byref(self.desc), *[t.descriptor for t in tensors],
+                al.descriptor if al is not None else None, scale)
+        for t in tensors + ([al] if al is not None else []):
+            t.destroy_desc()
+        self.workspace_size = 0
+        self.workspace = None
+        if self.status == 0:
+            size = ctypes.c_size_t(0)
+            check_error(LIBINFINIOP.infiniopGetPagedAttentionWorkspaceSize(self.desc, ctypes.byref(size)))
+            self.workspace_size = size.value
+            self.workspace = TestWorkspace(size.value, InfiniDeviceEnum.NVIDIA)
+
+    def run(self, out, q, k_cache, v_cache, block_tables, seq_lens, alibi=None, stream=None, workspace_size=None):
+        return LIBINFINIOP.infiniopPagedAttention(
+            self.desc, self.workspace.data(), self.workspace_size if workspace_size is None else workspace_size,
+            out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            block_tables.data_ptr(), seq_lens.data_ptr(), alibi.data_ptr() if alibi is not None else None, stream)
+
+    def error_flag(self) -> int:
+        """First int of the workspace: set non-zero by a worker whose bounded wait ran out."""
+        if self.workspace is None or self.workspace.tensor is None:
+            return 0
+        return int(self.workspace.tensor[:4].view(torch.int32).item())
+
+    def destroy(self):
+        if self.status == 0 and self.desc:
+            check_error(LIBINFINIOP.infiniopDestroyPagedAttentionDescriptor(self.desc))
+            self.desc = None
+
+
+def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, scale, alibi=None, path=None, out=None,
+                    index_dtype=None):
+    """Runs one decode call through the C ABI; returns `out` (synchronised)."""
+    if out is None:
+        out = torch.zeros((*q.shape[:-1], v_cache.shape[3]), dtype=q.dtype, device=q.device)
+    op = AttentionOp(out, q, k_cache, v_cache, block_tables, seq_lens, alibi, scale, path, index_dtype)
+    check_error(op.status)
+    try:
+        check_error(op.run(out, q, k_cache, v_cache, block_tables, seq_lens, alibi))
+        torch.cuda.synchronize()
+        assert op.error_flag() == 0 or op.workspace_size == 0, "a worker's bounded wait ran out"
+    finally:
+        op.destroy()
+    return out
+
+
+def create_caching(k_cache, v_cache, k, v, slot_mapping, slot_dtype=None):
+    tensors = [_tt(k_cache), _tt(v_cache), _tt(k), _tt(v), _tt(slot_mapping, slot_dtype)]
+    desc = infiniopOperatorDescriptor_t()
+    status = LIBINFINIOP.infiniopCreatePagedCachingDescriptor(handle(), ctypes.byref(desc), *[t.descriptor for t in tensors])
+    for t in tensors:
+        t.destroy_desc()
+    return status, desc
+
+
+def paged_caching(k_cache, v_cache, k, v, slot_mapping, stream=None):
+    status, desc = create_caching(k_cache, v_cache, k, v, slot_mapping)
+    check_error(status)
+    size = ctypes.c_size_t(123)
+    check_error(LIBINFINIOP.infiniopGetPagedCachingWorkspaceSize(desc, ctypes.byref(size)))
+    assert size.value == 0
+    try:
+        check_error(LIBINFINIOP.infiniopPagedCaching(desc, None, 0, k_cache.data_ptr(), v_cache.data_ptr(),
+                                                     k.data_ptr(), v.data_ptr(), slot_mapping.data_ptr(), stream))
+        torch.cuda.synchronize()
+    finally:
+        check_error(LIBINFINIOP.infiniopDestroyPagedCachingDescriptor(desc))
+
+
+def shutdown():
+    global _handle
+    if _handle is not None:
+        destroy_handle(_handle)
+        _handle = None

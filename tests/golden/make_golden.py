@@ -1,0 +1,150 @@
+"""Regenerates tests/golden/*.npz by running the REFERENCE's own Python checkers on seeded inputs.
+
+Run in a container that has the reference checkout (it is not needed to run the tests):
+
+    python tests/golden/make_golden.py /path/to/InfiniCore
+
+The two functions executed are imported unmodified from the reference tree:
+  ref_single_query_cached_kv_attention   test/infiniop/paged_attention.py:47-88
+  ref_paged_caching                      test/infiniop/paged_caching.py:25-55
+Those files import the reference's ctypes harness at module level (which would try to load the
+reference's compiled library); a stand-in `libinfiniop` module with empty attributes is put
+in sys.modules first so that only the pure-torch functions are used.
+
+Each .npz stores the inputs as raw bit patterns (uint16 for fp16/bf16) plus the reference's
+output, so the tests need neither torch-specific pickles nor the reference.
+"""
+from __future__ import annotations
+
+import importlib.util
+import sys
+import types
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE.parent.parent))
+
+from infinicore_b200 import workloads  # noqa: E402
+
+
+def load_reference(ref_root: Path):
+    class _Anything(types.ModuleType):
+        def __getattr__(self, name):
+            if name.startswith("__"):
+                raise AttributeError(name)
+            return type(name, (), {"__getattr__": lambda self, n: 0})()
+
+    sys.modules["libinfiniop"] = _Anything("libinfiniop")
+    mods = {}
+    for name in ("paged_attention", "paged_caching"):
+        spec = importlib.util.spec_from_file_location(f"_ref_{name}", ref_root / "test" / "infiniop" / f"{name}.py")
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mods[name] = mod
+    return mods["paged_attention"], mods["paged_caching"]
+
+
+def bits(t: torch.Tensor) -> np.ndarray:
+    if t.dtype in (torch.float16, torch.bfloat16):
+        return t.contiguous().view(torch.int16).numpy().view(np.uint16).copy()
+    return t.contiguous().numpy().copy()
+
+
+DTYPE_CODE = {torch.float16: 12, torch.float32: 13, torch.bfloat16: 19}
+
+
+def attention_cases():
+    g = torch.Generator()
+    g.manual_seed(1234)
+    yield "attn_c1_fp16_gqa4_hd64", workloads.config1_small(seed=1), None
+    yield "attn_bf16_gqa4_hd128", workloads.build_case(
+        "x", dtype=torch.bfloat16, seq_lens=[300, 17, 1, 160], num_heads=8, num_kv_heads=2, head_size=128,
+        block_size=16, num_blocks=40, seed=11), None
+    yield "attn_bf16_gqa8_hd128", workloads.build_case(
+        "x", dtype=torch.bfloat16, seq_lens=[64, 333, 16, 15], num_heads=16, num_kv_heads=2, head_size=128,
+        block_size=16, num_blocks=32, seed=12, std=0.5), None
+    yield "attn_fp16_mha_hd128_alibi", workloads.build_case(
+        "x", dtype=torch.float16, seq_lens=[200, 31], num_heads=4, num_kv_heads=4, head_size=128,
+        block_size=16, num_blocks=16, seed=13), "alibi"
+    yield "attn_fp16_gqa6_hd256", workloads.build_case(
+        "x", dtype=torch.float16, seq_lens=[32, 9], num_heads=12, num_kv_heads=2, head_size=256,
+        block_size=16, num_blocks=4, seed=14), None
+    yield "attn_bf16_mla_hd576_v512", workloads.build_case(
+        "x", dtype=torch.bfloat16, seq_lens=[100, 7], num_heads=16, num_kv_heads=1, head_size=576, value_size=512,
+        block_size=16, num_blocks=8, seed=15, std=0.3), None
+    yield "attn_fp16_gqa2_hd64_bs32", workloads.build_case(
+        "x", dtype=torch.float16, seq_lens=[150, 64, 33], num_heads=4, num_kv_heads=2, head_size=64,
+        block_size=32, num_blocks=10, seed=16), None
+    yield "attn_bf16_mha_hd192", workloads.build_case(
+        "x", dtype=torch.bfloat16, seq_lens=[77], num_heads=3, num_kv_heads=3, head_size=192,
+        block_size=16, num_blocks=6, seed=17), None
+
+
+def make_attention(ref_attn):
+    for name, case, variant in attention_cases():
+        alibi = None
+        if variant == "alibi":
+            alibi = torch.tensor(ref_attn.get_alibi_slopes(case.num_heads), dtype=torch.float32)
+        out = ref_attn.ref_single_query_cached_kv_attention(
+            case.q, case.k_cache, case.v_cache, case.block_tables, case.seq_lens, case.scale, alibi)
+        np.savez_compressed(
+            HERE / f"{name}.npz",
+            dtype=np.int64(DTYPE_CODE[case.dtype]), scale=np.float32(case.scale),
+            q=bits(case.q), k_cache=bits(case.k_cache), v_cache=bits(case.v_cache),
+            block_tables=case.block_tables.numpy(), seq_lens=case.seq_lens.numpy(),
+            alibi=(alibi.numpy() if alibi is not None else np.zeros(0, np.float32)),
+            out=bits(out),
+        )
+        print("wrote", name, tuple(out.shape))
+
+
+def caching_cases():
+    # (name, dtype, num_blocks, kv_heads, block_size, head, v_head, num_tokens, permuted layout)
+    yield "cache_fp16_hd64", torch.float16, 32, 2, 16, 64, 64, 37, False
+    yield "cache_bf16_hd128_bs32", torch.bfloat16, 12, 4, 32, 128, 128, 50, False
+    yield "cache_f32_hd64", torch.float32, 16, 2, 16, 64, 64, 21, False
+    yield "cache_bf16_mla_576_512", torch.bfloat16, 8, 1, 16, 576, 512, 19, False
+    yield "cache_fp16_permuted_layout", torch.float16, 16, 4, 16, 64, 64, 40, True
+
+
+def make_caching(ref_cache):
+    for idx, (name, dtype, nb, kvh, bs, hd, vd, ntok, permuted) in enumerate(caching_cases()):
+        g = torch.Generator()
+        g.manual_seed(100 + idx)
+        if permuted:
+            # allocated [nb, bs, kvh, hd], handed over as the [nb, kvh, bs, hd] view
+            # (reference test/infinicore/ops/paged_caching.py:147-149)
+            k_cache = torch.randn((nb, bs, kvh, hd), generator=g).to(dtype).permute(0, 2, 1, 3)
+            v_cache = torch.randn((nb, bs, kvh, vd), generator=g).to(dtype).permute(0, 2, 1, 3)
+        else:
+            k_cache = torch.randn((nb, kvh, bs, hd), generator=g).to(dtype)
+            v_cache = torch.randn((nb, kvh, bs, vd), generator=g).to(dtype)
+        k = torch.randn((ntok, kvh, hd), generator=g).to(dtype)
+        v = torch.randn((ntok, kvh, vd), generator=g).to(dtype)
+        slots = torch.randperm(nb * bs, generator=g)[:ntok].to(torch.int64)
+        k_after, v_after = ref_cache.ref_paged_caching(k_cache, v_cache, k, v, slots)
+        # pools are stored in their PHYSICAL order; `permuted` tells the test how to view them
+        phys = (lambda t: t.permute(0, 2, 1, 3)) if permuted else (lambda t: t)
+        np.savez_compressed(
+            HERE / f"{name}.npz",
+            dtype=np.int64(DTYPE_CODE[dtype]), permuted=np.int64(permuted),
+            k_cache=bits(phys(k_cache)), v_cache=bits(phys(v_cache)), k=bits(k), v=bits(v),
+            slot_mapping=slots.numpy(),
+            k_cache_after=bits(phys(k_after)), v_cache_after=bits(phys(v_after)),
+        )
+        print("wrote", name)
+
+
+def main():
+    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    ref_attn, ref_cache = load_reference(ref_root)
+    torch.set_num_threads(4)
+    make_attention(ref_attn)
+    make_caching(ref_cache)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,111 @@
+"""CPU-side checks of the C-ABI libraries: they load, export every symbol the public headers
+declare, and the host-only entry points behave (no compute call is made here)."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def declared_symbols():
+    names = {}
+    for header in sorted((ROOT / "include").rglob("*.h")):
+        for m in re.finditer(r"__INFINI_C\s+__export\s+infiniStatus_t\s+(\w+)\s*\(", header.read_text()):
+            names[m.group(1)] = header.name
+    return names
+
+
+def test_headers_declare_the_expected_surface():
+    names = declared_symbols()
+    for must in ("infiniopCreatePagedAttentionDescriptor", "infiniopGetPagedAttentionWorkspaceSize",
+                 "infiniopPagedAttention", "infiniopDestroyPagedAttentionDescriptor",
+                 "infiniopCreatePagedCachingDescriptor", "infiniopGetPagedCachingWorkspaceSize",
+                 "infiniopPagedCaching", "infiniopDestroyPagedCachingDescriptor",
+                 "infiniopCreateHandle", "infiniopCreateTensorDescriptor", "infinirtSetDevice", "infinirtGetDevice"):
+        assert must in names
+
+
+def test_libraries_load_and_export_every_declared_symbol():
+    from infinicore_b200 import libinfiniop as L
+
+    rt_path, op_path = L.library_paths()
+    rt = ctypes.CDLL(str(rt_path), mode=ctypes.RTLD_GLOBAL)
+    op = ctypes.CDLL(str(op_path))
+    for name, header in declared_symbols().items():
+        lib = rt if name.startswith("infinirt") else op
+        assert hasattr(lib, name), f"{name} (declared in {header}) is not exported"
+    # and the binding's own lists are the same set
+    assert set(L.INFINIOP_SYMBOLS) | set(L.INFINIRT_SYMBOLS) == set(declared_symbols())
+
+
+def test_tensor_descriptor_round_trip_needs_no_device():
+    from infinicore_b200.libinfiniop import CTensor, InfiniDtype
+
+    t = CTensor(InfiniDtype.BF16, [4, 8, 128], None)
+    assert bool(t.descriptor)
+    t.destroy_desc()
+    t = CTensor(InfiniDtype.F16, [16, 2, 16, 64], [2048, 64, 128, 1])
+    t.destroy_desc()
+
+
+def test_thread_local_device_defaults_to_cpu_and_handle_creation_is_refused():
+    import threading
+
+    from infinicore_b200.libinfiniop import LIBINFINIOP, InfiniDeviceEnum, infiniopHandle_t
+
+    seen = {}
+
+    def probe():
+        dev, idx = ctypes.c_int(-1), ctypes.c_int(-1)
+        seen["get"] = LIBINFINIOP.infinirtGetDevice(ctypes.byref(dev), ctypes.byref(idx))
+        seen["dev"] = dev.value
+        h = infiniopHandle_t()
+        seen["create"] = LIBINFINIOP.infiniopCreateHandle(ctypes.byref(h))
+
+    th = threading.Thread(target=probe)  # a fresh thread: nothing has selected a device on it
+    th.start()
+    th.join()
+    assert seen["get"] == 0 and seen["dev"] == InfiniDeviceEnum.CPU
+    assert seen["create"] == 5  # INFINI_STATUS_DEVICE_TYPE_NOT_SUPPORTED: there is no CPU backend
+
+
+def test_null_pointers_are_reported():
+    from infinicore_b200.libinfiniop import LIBINFINIOP
+
+    assert LIBINFINIOP.infiniopCreateHandle(None) == 4
+    assert LIBINFINIOP.infinirtGetDevice(None, None) == 4
+    assert LIBINFINIOP.infiniopGetPagedAttentionWorkspaceSize(None, None) == 4
+    assert LIBINFINIOP.infiniopDestroyPagedCachingDescriptor(None) == 4
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU behaviour")
+def test_without_a_gpu_the_runtime_says_so():
+    from infinicore_b200.libinfiniop import LIBINFINIOP, InfiniDeviceEnum
+
+    assert LIBINFINIOP.infinirtSetDevice(InfiniDeviceEnum.NVIDIA, 0) == 6  # DEVICE_NOT_FOUND
+    assert LIBINFINIOP.infinirtSetDevice(InfiniDeviceEnum.ASCEND, 0) == 5
+    n = ctypes.c_int(-1)
+    assert LIBINFINIOP.infinirtGetDeviceCount(InfiniDeviceEnum.NVIDIA, ctypes.byref(n)) == 0 and n.value == 0
+
+
+def test_operators_refuse_cpu_tensors():
+    import infinicore_b200 as ib
+
+    q = torch.zeros(1, 1, 64, dtype=torch.float16)
+    kc = torch.zeros(1, 1, 16, 64, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        ib.paged_attention(q, kc, kc, torch.zeros(1, 1, dtype=torch.int64), torch.ones(1, dtype=torch.int64))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        ib.paged_caching(kc, kc, q, q, torch.zeros(1, dtype=torch.int64))
+
+
+def test_missing_library_fails_loudly(tmp_path, monkeypatch):
+    from infinicore_b200 import libinfiniop as L
+
+    monkeypatch.setenv("INFINI_ROOT", str(tmp_path))
+    monkeypatch.setattr(L, "_PKG", tmp_path)
+    with pytest.raises(FileNotFoundError, match="no non-CUDA fallback"):
+        L.library_paths()

@@ -1,0 +1,97 @@
+"""CPU tests that pin the oracle (oracle/paged_oracle.c) to the reference.
+
+The golden files hold outputs of the reference's own torch checkers
+(ref_single_query_cached_kv_attention, ref_paged_caching) on seeded inputs - see
+tests/golden/make_golden.py.  The oracle's "reference" mode reproduces those roundings and must
+agree to within a couple of output ulps (summation order is the only freedom); its "exact" mode
+must agree within the path's parity tolerance.
+"""
+import numpy as np
+import pytest
+
+import oracle
+from helpers import ATTN_TOL, BF16, F16, bits_to_float, golden_names, load_golden
+
+
+def _ulp(dtype_code, x):
+    mant = 10 if dtype_code == F16 else 7
+    return np.maximum(np.abs(x), 2.0 ** -14) * 2.0 ** -mant
+
+
+@pytest.mark.parametrize("name", golden_names("attn_"))
+def test_attention_reference_mode_matches_reference_output(name):
+    g = load_golden(name)
+    dt = int(g["dtype"])
+    alibi = g["alibi"] if g["alibi"].size else None
+    got = oracle.paged_attention(g["q"], g["k_cache"], g["v_cache"], g["block_tables"], g["seq_lens"],
+                                 float(g["scale"]), dt, alibi, mode="reference")
+    want = bits_to_float(g["out"], dt)
+    # Same roundings, different summation order: a rounded probability or output can flip by one
+    # ulp; allow 3 ulps of the output plus the spread that one-ulp probability flips can cause.
+    err = np.abs(got - want)
+    assert np.all(err <= 4 * _ulp(dt, want) + 1e-3 * np.abs(want).max()), f"max err {err.max():.3e}"
+    assert np.mean(err <= _ulp(dt, want)) > 0.9
+
+
+@pytest.mark.parametrize("name", golden_names("attn_"))
+def test_attention_exact_mode_within_path_tolerance(name):
+    g = load_golden(name)
+    dt = int(g["dtype"])
+    alibi = g["alibi"] if g["alibi"].size else None
+    got = oracle.paged_attention(g["q"], g["k_cache"], g["v_cache"], g["block_tables"], g["seq_lens"],
+                                 float(g["scale"]), dt, alibi, mode="exact")
+    want = bits_to_float(g["out"], dt)
+    atol, rtol = ATTN_TOL[dt]
+    assert np.all(np.abs(got - want) <= atol + rtol * np.abs(want))
+
+
+@pytest.mark.parametrize("name", golden_names("cache_"))
+def test_caching_bit_exact_against_reference_output(name):
+    g = load_golden(name)
+    k_cache, v_cache = g["k_cache"].copy(), g["v_cache"].copy()
+    if int(g["permuted"]):
+        # stored physically as [blocks, slots, heads, dim]; the operator sees [blocks, heads, slots, dim]
+        oracle.paged_caching(k_cache.transpose(0, 2, 1, 3), v_cache.transpose(0, 2, 1, 3), g["k"], g["v"], g["slot_mapping"])
+    else:
+        oracle.paged_caching(k_cache, v_cache, g["k"], g["v"], g["slot_mapping"])
+    assert np.array_equal(k_cache, g["k_cache_after"])
+    assert np.array_equal(v_cache, g["v_cache_after"])
+
+
+def test_caching_skips_negative_slots_and_rejects_out_of_pool():
+    rng = np.random.default_rng(0)
+    k_cache = rng.integers(0, 65536, (4, 2, 16, 64), dtype=np.uint16)
+    v_cache = rng.integers(0, 65536, (4, 2, 16, 64), dtype=np.uint16)
+    k = rng.integers(0, 65536, (3, 2, 64), dtype=np.uint16)
+    v = rng.integers(0, 65536, (3, 2, 64), dtype=np.uint16)
+    before = k_cache.copy()
+    oracle.paged_caching(k_cache, v_cache, k, v, np.array([5, -1, 40]))
+    assert np.array_equal(k_cache[0, :, 5], k[0]) and np.array_equal(k_cache[2, :, 8], k[2])
+    mask = np.ones_like(before, dtype=bool)
+    mask[0, :, 5] = False
+    mask[2, :, 8] = False
+    assert np.array_equal(k_cache[mask], before[mask])
+    with pytest.raises(ValueError):
+        oracle.paged_caching(k_cache, v_cache, k, v, np.array([5, 6, 64]))
+
+
+def test_attention_leaves_empty_sequences_untouched():
+    g = load_golden("attn_bf16_gqa4_hd128")
+    lens = g["seq_lens"].copy()
+    lens[1] = 0
+    out = np.full((4, 8, 128), 7.0)
+    oracle.paged_attention(g["q"], g["k_cache"], g["v_cache"], g["block_tables"], lens, float(g["scale"]), BF16, out=out)
+    assert np.all(out[1] == 7.0) and not np.any(out[0] == 7.0)
+
+
+def test_codecs_round_trip_every_finite_pattern():
+    lib = oracle.lib()
+    for h in list(range(0, 0x7c00, 7)) + [0x7bff, 0x0001, 0x03ff, 0x0400, 0x8001, 0xfbff]:
+        assert lib.oracle_float_to_f16(lib.oracle_f16_to_float(h)) == h
+    for h in list(range(0, 0x7f80, 13)) + [0x7f7f, 0x0001, 0x8001]:
+        assert lib.oracle_float_to_bf16(lib.oracle_bf16_to_float(h)) == h
+    # ties go to even
+    assert lib.oracle_float_to_f16(1.0 + 2.0 ** -11) == 0x3c00
+    assert lib.oracle_float_to_f16(1.0 + 3 * 2.0 ** -11) == 0x3c02
+    assert lib.oracle_float_to_bf16(1.0 + 2.0 ** -8) == 0x3f80
+    assert lib.oracle_float_to_bf16(1.0 + 3 * 2.0 ** -8) == 0x3f82

@@ -1,0 +1,449 @@
+"""GPU parity of infiniopPagedAttention through the C ABI.
+
+Checked against (a) the reference's golden outputs, (b) the CPU oracle in "exact" mode on the same
+seeded inputs, at the parity tolerance of the path: fp16 atol 2e-3 / rtol 2e-3, bf16 atol 1e-2 /
+rtol 1e-2.  Both kernels are covered: the streaming TMA/MMA path (default where eligible) and the
+generic path (forced with INFINIOP_PAGED_DECODE_PATH=generic at descriptor creation)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import ATTN_TOL, TORCH_DTYPE, assert_close, bits_to_float, bits_to_torch, golden_names, load_golden, torch_to_bits
+from infinicore_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+
+PATHS = [None, "generic"]
+
+
+@pytest.fixture(scope="module")
+def abi():
+    import abi as _abi
+
+    yield _abi
+
+
+def oracle_out(case, alibi=None, seq_lens=None, mode="exact"):
+    dt = 12 if case.dtype == torch.float16 else 19
+    lens = case.seq_lens if seq_lens is None else seq_lens
+    return oracle.paged_attention(
+        torch_to_bits(case.q), torch_to_bits(case.k_cache), torch_to_bits(case.v_cache),
+        case.block_tables.cpu().numpy(), lens.cpu().numpy(), case.scale, dt,
+        alibi.cpu().numpy() if alibi is not None else None, mode=mode)
+
+
+def run_case(abi, case, path, alibi=None, index_dtype=None, seq_lens=None, out=None):
+    d = case.to("cuda")
+    lens = d.seq_lens if seq_lens is None else seq_lens.cuda()
+    bt = d.block_tables
+    if index_dtype is not None:
+        bt, lens = bt.to(torch.int32), lens.to(torch.int32)
+    return abi.paged_attention(d.q, d.k_cache, d.v_cache, bt, lens, d.scale,
+                               alibi.cuda() if alibi is not None else None, path=path, out=out, index_dtype=index_dtype)
+
+
+def check(case, got, want):
+    atol, rtol = ATTN_TOL[case.dtype]
+    assert_close(got.float().cpu().numpy(), want, atol, rtol, case.name)
+
+
+# ---- golden vectors produced by the reference's own checker -------------------------------------
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("name", golden_names("attn_"))
+def test_golden(abi, name, path):
+    g = load_golden(name)
+    dt = int(g["dtype"])
+    dev = "cuda"
+    q, kc, vc = (bits_to_torch(g[k], dt).to(dev) for k in ("q", "k_cache", "v_cache"))
+    alibi = torch.from_numpy(g["alibi"]).to(dev) if g["alibi"].size else None
+    got = abi.paged_attention(q, kc, vc, torch.from_numpy(g["block_tables"]).to(dev),
+                              torch.from_numpy(g["seq_lens"]).to(dev), float(g["scale"]), alibi, path=path)
+    atol, rtol = ATTN_TOL[dt]
+    assert_close(got.float().cpu().numpy(), bits_to_float(g["out"], dt), atol, rtol, f"{name} vs reference output")
+    exact = oracle.paged_attention(g["q"], g["k_cache"], g["v_cache"], g["block_tables"], g["seq_lens"],
+                                   float(g["scale"]), dt, g["alibi"] if g["alibi"].size else None)
+    assert_close(got.float().cpu().numpy(), exact, atol, rtol, f"{name} vs exact oracle")
+
+
+# ---- the reference's own case list (U(0,1) data, identity tables) ---------------------------------
+
+# reference test/infiniop/paged_attention.py:95-109 and test/infinicore/ops/paged_attention.py:22-37
+REFERENCE_CASES = [
+    (1, 1, 1, 128, 16, 1024), (4, 40, 40, 128, 16, 1024), (6, 40, 40, 128, 16, 1024), (3, 8, 8, 128, 16, 1024),
+    (3, 8, 8, 64, 16, 1024), (8, 64, 8, 128, 16, 2048), (1, 16, 16, 192, 16, 256), (1, 16, 16, 576, 16, 256),
+    (1, 16, 1, 576, 16, 256, 512), (1, 24, 4, 256, 16, 32), (1, 12, 2, 256, 16, 32), (1, 6, 1, 256, 16, 32),
+    (1, 1, 1, 128, 16, 15),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", REFERENCE_CASES)
+def test_reference_case_list(abi, case, dtype):
+    num_seqs, heads, kvh, hd, bs, max_len = case[:6]
+    vd = case[6] if len(case) > 6 else hd
+    g = torch.Generator().manual_seed(sum(case))
+    max_blocks = (max_len + bs - 1) // bs
+    c = workloads.build_case("ref", dtype=dtype, seq_lens=torch.randint(1, max_len, (num_seqs,), generator=g),
+                             num_heads=heads, num_kv_heads=kvh, head_size=hd, value_size=vd, block_size=bs,
+                             num_blocks=num_seqs * max_blocks, max_blocks_per_seq=max_blocks, shuffle_tables=False,
+                             seed=sum(case))
+    # the reference draws U(0,1)
+    gg = torch.Generator().manual_seed(sum(case) + 1)
+    c.q = torch.rand(c.q.shape, generator=gg).to(dtype)
+    c.k_cache = torch.rand(c.k_cache.shape, generator=gg).to(dtype)
+    c.v_cache = torch.rand(c.v_cache.shape, generator=gg).to(dtype)
+    c.name = f"ref{case}"
+    check(c, run_case(abi, c, None), oracle_out(c))
+
+
+# ---- benchmark configuration 1, as a flow: cache the newest token, then attend ----------------------
+
+@pytest.mark.parametrize("path", PATHS)
+def test_config1_caching_then_attention(abi, path):
+    c = workloads.config1_small(seed=1)
+    d = c.to("cuda")
+    abi.paged_caching(d.k_cache, d.v_cache, d.new_k, d.new_v, d.slot_mapping)
+    kb, vb = torch_to_bits(c.k_cache).copy(), torch_to_bits(c.v_cache).copy()
+    oracle.paged_caching(kb, vb, torch_to_bits(c.new_k), torch_to_bits(c.new_v), c.slot_mapping.numpy())
+    assert np.array_equal(torch_to_bits(d.k_cache), kb) and np.array_equal(torch_to_bits(d.v_cache), vb)
+    got = abi.paged_attention(d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, d.scale, path=path)
+    want = oracle.paged_attention(torch_to_bits(c.q), kb, vb, c.block_tables.numpy(), c.seq_lens.numpy(), c.scale, 12)
+    check(c, got, want)
+
+
+# ---- edge cases ------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("dtype,heads,kvh,hd", [(torch.float16, 4, 1, 64), (torch.bfloat16, 8, 1, 128), (torch.bfloat16, 2, 2, 128),
+                                                (torch.float16, 12, 1, 128), (torch.bfloat16, 20, 2, 64)])
+def test_every_length_across_three_pages(abi, path, dtype, heads, kvh, hd):
+    """Sequence lengths 1..49 in one batch: every position of the ragged last tile, page boundaries,
+    group sizes 1, 4, 8, 10 and 12 (more than one 8-head tile per kv-head)."""
+    lens = torch.arange(1, 50)
+    c = workloads.build_case("lens1to49", dtype=dtype, seq_lens=lens, num_heads=heads, num_kv_heads=kvh, head_size=hd,
+                             block_size=16, seed=21, slack_blocks=7)
+    check(c, run_case(abi, c, path), oracle_out(c))
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_empty_sequences_leave_their_rows_untouched(abi, path):
+    c = workloads.build_case("with_empty", dtype=torch.bfloat16, seq_lens=[40, 0, 17, 0, 0, 300], num_heads=8, num_kv_heads=2,
+                             head_size=128, block_size=16, seed=22)
+    out = torch.full((6, 8, 128), 3.0, dtype=torch.bfloat16, device="cuda")
+    got = run_case(abi, c, path, out=out)
+    want = oracle_out(c)
+    live = [0, 2, 5]
+    atol, rtol = ATTN_TOL[c.dtype]
+    assert_close(got[live].float().cpu().numpy(), want[live], atol, rtol, "live rows")
+    assert bool((got[[1, 3, 4]] == 3.0).all())
+
+
+def test_all_sequences_empty(abi):
+    c = workloads.build_case("all_empty", dtype=torch.float16, seq_lens=[0, 0], num_heads=4, num_kv_heads=2, head_size=64,
+                             block_size=16, num_blocks=2, seed=23)
+    out = torch.full((2, 4, 64), 5.0, dtype=torch.float16, device="cuda")
+    got = run_case(abi, c, None, out=out)
+    assert bool((got == 5.0).all())
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_unused_cache_slots_may_hold_nan(abi, path):
+    """Slots past seq_len in the last page, and blocks no table points at, are never part of the
+    result even when they hold NaN/Inf bit patterns."""
+    c = workloads.build_case("poison", dtype=torch.bfloat16, seq_lens=[5, 33, 47, 16], num_heads=8, num_kv_heads=2, head_size=128,
+                             block_size=16, seed=24, slack_blocks=5)
+    want = oracle_out(c)
+    poison = torch.tensor(float("nan"), dtype=torch.bfloat16)
+    used = torch.zeros(c.k_cache.shape[0], dtype=torch.bool)
+    for i, ln in enumerate(c.seq_lens.tolist()):
+        nblk = (ln + 15) // 16
+        used[c.block_tables[i, :nblk]] = True
+        if ln % 16:
+            last = int(c.block_tables[i, nblk - 1])
+            c.k_cache[last, :, ln % 16:, :] = poison
+            c.v_cache[last, :, ln % 16:, :] = float("inf")
+    c.k_cache[~used] = poison
+    c.v_cache[~used] = poison
+    got = run_case(abi, c, path)
+    assert bool(torch.isfinite(got.float()).all())
+    check(c, got, want)
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("index_dtype", ["I32", "U32"])
+def test_32bit_index_dtypes(abi, path, index_dtype):
+    from infinicore_b200.libinfiniop import InfiniDtype
+
+    c = workloads.build_case("idx32", dtype=torch.float16, seq_lens=[100, 3, 64], num_heads=8, num_kv_heads=2, head_size=128,
+                             block_size=16, seed=25)
+    got = run_case(abi, c, path, index_dtype=getattr(InfiniDtype, index_dtype))
+    check(c, got, oracle_out(c))
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_alibi(abi, path):
+    c = workloads.build_case("alibi", dtype=torch.bfloat16, seq_lens=[130, 48, 1], num_heads=8, num_kv_heads=2, head_size=128,
+                             block_size=16, seed=26)
+    slopes = torch.tensor([2.0 ** (-(i + 1)) for i in range(8)], dtype=torch.float32)
+    slopes[3] = 0.0
+    check(c, run_case(abi, c, path, alibi=slopes), oracle_out(c, alibi=slopes))
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_permuted_cache_layout_and_strided_q_out(abi, path):
+    """Caches allocated [blocks, slots, heads, dim] and passed as the permuted view (reference
+    test/infinicore/ops/paged_caching.py:147-149); q and out are slices of wider buffers."""
+    c = workloads.build_case("permuted", dtype=torch.float16, seq_lens=[70, 129, 16], num_heads=8, num_kv_heads=4, head_size=64,
+                             block_size=16, seed=27)
+    want = oracle_out(c)
+    d = c.to("cuda")
+    kc = d.k_cache.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+    vc = d.v_cache.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+    assert kc.stride() != d.k_cache.stride()
+    q_wide = torch.zeros((3, 8, 96), dtype=torch.float16, device="cuda")
+    q_wide[:, :, 16:80] = d.q
+    out_wide = torch.zeros((3, 16, 64), dtype=torch.float16, device="cuda")
+    got = abi.paged_attention(q_wide[:, :, 16:80], kc, vc, d.block_tables, d.seq_lens, d.scale, path=path, out=out_wide[:, ::2])
+    check(c, got, want)
+    assert bool((out_wide[:, 1::2] == 0).all())
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_block_size_32_and_wide_block_table(abi, path):
+    c = workloads.build_case("bs32", dtype=torch.bfloat16, seq_lens=[200, 31, 97], num_heads=4, num_kv_heads=2, head_size=128,
+                             block_size=32, max_blocks_per_seq=40, seed=28)
+    check(c, run_case(abi, c, path), oracle_out(c))
+
+
+def test_block_size_8_takes_the_generic_path(abi):
+    c = workloads.build_case("bs8", dtype=torch.float16, seq_lens=[50, 9], num_heads=4, num_kv_heads=2, head_size=64,
+                             block_size=8, seed=29)
+    check(c, run_case(abi, c, None), oracle_out(c))
+
+
+# ---- scaled-down versions of the ragged and long-context benchmark configurations ------------------
+
+def test_ragged_lengths_log_uniform(abi):
+    """Shape of benchmark configuration 3 (64/8 heads, N(0, 0.5), log-uniform lengths) at 1/16 scale."""
+    g = torch.Generator().manual_seed(30)
+    u = torch.rand(48, generator=g)
+    lens = torch.exp(math.log(16) + u * (math.log(2048) - math.log(16))).round().long()
+    c = workloads.build_case("ragged", dtype=torch.bfloat16, seq_lens=lens, num_heads=64, num_kv_heads=8, head_size=128,
+                             block_size=16, max_blocks_per_seq=128, std=0.5, seed=30, slack_blocks=16)
+    check(c, run_case(abi, c, None), oracle_out(c))
+
+
+def test_long_context_small_batch_is_split_many_ways(abi):
+    """Shape of benchmark configuration 4 (fp16, 2 sequences, 32/8 heads) at 16384 tokens: each
+    (sequence, kv-head) is spread over dozens of workers and reduced by the combine kernel."""
+    c = workloads.build_case("longctx", dtype=torch.float16, seq_lens=[16384, 16384], num_heads=32, num_kv_heads=8, head_size=128,
+                             block_size=16, seed=31)
+    check(c, run_case(abi, c, None), oracle_out(c))
+
+
+# ---- size-independent properties at the full size of benchmark configuration 2 -----------------------
+
+@pytest.fixture(scope="module")
+def config2():
+    return workloads.config2_llama8b(device="cuda")
+
+
+def test_config2_subset_against_oracle(abi, config2):
+    """Full-size launch (64 x 4096 tokens, 1 GiB of KV); three of the 64 sequences are checked
+    element-wise against the oracle."""
+    d = config2
+    got = abi.paged_attention(d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, d.scale)
+    pick = [0, 31, 63]
+    want = oracle.paged_attention(torch_to_bits(d.q[pick]), torch_to_bits(d.k_cache), torch_to_bits(d.v_cache),
+                                  d.block_tables[pick].cpu().numpy(), d.seq_lens[pick].cpu().numpy(), d.scale, 19)
+    atol, rtol = ATTN_TOL[torch.bfloat16]
+    assert_close(got[pick].float().cpu().numpy(), want, atol, rtol, "config 2 subset")
+    assert bool(torch.isfinite(got.float()).all())
+
+
+def test_config2_is_invariant_under_physical_block_permutation(abi, config2):
+    """Moving every page to a different physical block (and rewriting the tables to match) must not
+    change a single output bit: the result depends on logical content only."""
+    d = config2
+    base = abi.paged_attention(d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, d.scale)
+    nb = d.k_cache.shape[0]
+    perm = torch.randperm(nb, generator=torch.Generator().manual_seed(99)).cuda()  # new_pool[perm[b]] = old_pool[b]
+    k2 = torch.empty_like(d.k_cache)
+    v2 = torch.empty_like(d.v_cache)
+    k2[perm] = d.k_cache
+    v2[perm] = d.v_cache
+    got = abi.paged_attention(d.q, k2, v2, perm[d.block_tables], d.seq_lens, d.scale)
+    assert torch.equal(got.view(torch.int16), base.view(torch.int16))
+
+
+def test_config2_output_is_linear_in_v(abi, config2):
+    """Doubling V doubles the output exactly (power-of-two scaling commutes with every rounding)."""
+    d = config2
+    base = abi.paged_attention(d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, d.scale)
+    got = abi.paged_attention(d.q, d.k_cache, d.v_cache * 2, d.block_tables, d.seq_lens, d.scale)
+    assert torch.equal(got.view(torch.int16), (base * 2).view(torch.int16))
+
+
+def test_config2_repeated_calls_are_deterministic(abi, config2):
+    d = config2
+    a = abi.paged_attention(d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, d.scale)
+    b = abi.paged_attention(d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, d.scale)
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+# ---- ABI behaviour -----------------------------------------------------------------------------------
+
+def _small(dtype=torch.float16, hd=128):
+    return workloads.build_case("abi", dtype=dtype, seq_lens=[20, 5], num_heads=4, num_kv_heads=2, head_size=hd,
+                                block_size=16, seed=40).to("cuda")
+
+
+def test_descriptor_validation_status_codes(abi):
+    d = _small()
+    out = torch.zeros_like(d.q)
+
+    def status(**kw):
+        args = dict(out=out, q=d.q, k_cache=d.k_cache, v_cache=d.v_cache, block_tables=d.block_tables,
+                    seq_lens=d.seq_lens, alibi=None, scale=d.scale)
+        args.update(kw)
+        op = abi.AttentionOp(**args)
+        st = op.status
+        op.destroy()
+        return st
+
+    assert status() == 0
+    assert status(q=d.q.float()) == 10                                   # F32 is not a decode dtype
+    assert status(k_cache=d.k_cache.to(torch.bfloat16)) == 10           # cache dtype must match q
+    assert status(seq_lens=d.seq_lens.to(torch.int32)) == 10            # index dtypes must agree
+    assert status(block_tables=d.block_tables.float()) == 10
+    assert status(q=d.q[0]) == 11                                        # rank
+    assert status(block_tables=d.block_tables[0]) == 11
+    assert status(out=out[:, :2]) == 11                                  # out heads != q heads
+    assert status(q=d.q[:, :3], out=out[:, :3]) == 11                    # 3 q-heads over 2 kv-heads
+    assert status(q=d.q[:, :, :96], out=out[:, :, :96], k_cache=d.k_cache[..., :96], v_cache=d.v_cache[..., :96]) == 11  # head size 96
+    assert status(q=d.q.transpose(1, 2).contiguous().transpose(1, 2)) == 12  # last dim not dense
+    assert status(alibi=torch.zeros(4, dtype=torch.float16, device="cuda")) == 10
+    assert status(seq_lens=d.seq_lens[:1]) == 11
+
+
+def test_insufficient_workspace_is_reported_before_any_launch(abi):
+    d = _small()
+    out = torch.full_like(d.q, 9.0)
+    op = abi.AttentionOp(out, d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, None, d.scale)
+    assert op.status == 0 and op.workspace_size > 0
+    assert op.run(out, d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, workspace_size=op.workspace_size - 1) == 13
+    torch.cuda.synchronize()
+    assert bool((out == 9.0).all())
+    assert op.run(out, d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens) == 0
+    torch.cuda.synchronize()
+    op.destroy()
+
+
+def test_descriptor_reports_its_device(abi):
+    import ctypes
+
+    from infinicore_b200.libinfiniop import LIBINFINIOP
+
+    d = _small()
+    op = abi.AttentionOp(torch.zeros_like(d.q), d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, None, d.scale)
+    dev, idx = ctypes.c_int(-1), ctypes.c_int(-1)
+    assert LIBINFINIOP.infiniopGetDescriptorDeviceType(op.desc, ctypes.byref(dev)) == 0 and dev.value == 1
+    assert LIBINFINIOP.infiniopGetDescriptorDeviceId(op.desc, ctypes.byref(idx)) == 0 and idx.value == 0
+    assert op.desc.contents.device == 1 and op.desc.contents.device_id == 0  # the two leading ints callers read
+    op.destroy()
+
+
+def test_one_descriptor_serves_new_pointers_and_new_lengths(abi):
+    """The descriptor holds shapes and strides only; data pointers, lengths and tables are per call."""
+    c1 = workloads.build_case("a", dtype=torch.bfloat16, seq_lens=[100, 7, 64], num_heads=8, num_kv_heads=2, head_size=128,
+                              block_size=16, num_blocks=32, max_blocks_per_seq=8, seed=41)
+    c2 = workloads.build_case("b", dtype=torch.bfloat16, seq_lens=[1, 128, 33], num_heads=8, num_kv_heads=2, head_size=128,
+                              block_size=16, num_blocks=32, max_blocks_per_seq=8, seed=42)
+    d1, d2 = c1.to("cuda"), c2.to("cuda")
+    out = torch.zeros_like(d1.q)
+    op = abi.AttentionOp(out, d1.q, d1.k_cache, d1.v_cache, d1.block_tables, d1.seq_lens, None, d1.scale)
+    for c, d in ((c1, d1), (c2, d2), (c1, d1)):
+        assert op.run(out, d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens) == 0
+        torch.cuda.synchronize()
+        check(c, out, oracle_out(c))
+    op.destroy()
+
+
+def test_cuda_graph_capture_of_the_decode_step(abi):
+    """caching + attention captured into a CUDA graph through the infinirt API and replayed after the
+    inputs changed in place (execute allocates nothing and never synchronises)."""
+    import ctypes
+
+    from infinicore_b200.libinfiniop import LIBINFINIOP, check_error
+
+    c = workloads.build_case("graph", dtype=torch.bfloat16, seq_lens=[100, 37, 64, 5], num_heads=8, num_kv_heads=2, head_size=128,
+                             block_size=16, seed=43)
+    d = c.to("cuda")
+    out = torch.zeros_like(d.q)
+    op = abi.AttentionOp(out, d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, None, d.scale)
+    st, cdesc = abi.create_caching(d.k_cache, d.v_cache, d.new_k, d.new_v, d.slot_mapping)
+    assert st == 0 and op.status == 0
+
+    stream = ctypes.c_void_p()
+    check_error(LIBINFINIOP.infinirtStreamCreate(ctypes.byref(stream)))
+
+    def step(s):
+        check_error(LIBINFINIOP.infiniopPagedCaching(cdesc, None, 0, d.k_cache.data_ptr(), d.v_cache.data_ptr(),
+                                                     d.new_k.data_ptr(), d.new_v.data_ptr(), d.slot_mapping.data_ptr(), s))
+        check_error(op.run(out, d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, stream=s))
+
+    step(stream)  # warm-up outside capture
+    check_error(LIBINFINIOP.infinirtStreamSynchronize(stream))
+    torch.cuda.synchronize()
+    check_error(LIBINFINIOP.infinirtStreamBeginCapture(stream, 2))  # RELAXED, as infinicore's graph does
+    step(stream)
+    graph = ctypes.c_void_p()
+    check_error(LIBINFINIOP.infinirtStreamEndCapture(stream, ctypes.byref(graph)))
+    gexec = ctypes.c_void_p()
+    check_error(LIBINFINIOP.infinirtGraphInstantiate(ctypes.byref(gexec), graph, None, None, 0))
+
+    # change the inputs in place, replay, compare with the oracle on the new inputs
+    g = torch.Generator().manual_seed(44)
+    c.q = torch.randn(c.q.shape, generator=g).to(torch.bfloat16)
+    c.new_k = torch.randn(c.new_k.shape, generator=g).to(torch.bfloat16)
+    c.new_v = torch.randn(c.new_v.shape, generator=g).to(torch.bfloat16)
+    d.q.copy_(c.q)
+    d.new_k.copy_(c.new_k)
+    d.new_v.copy_(c.new_v)
+    out.zero_()
+    torch.cuda.synchronize()
+    check_error(LIBINFINIOP.infinirtGraphLuanch(gexec, stream))
+    check_error(LIBINFINIOP.infinirtStreamSynchronize(stream))
+
+    kb, vb = torch_to_bits(c.k_cache).copy(), torch_to_bits(c.v_cache).copy()
+    oracle.paged_caching(kb, vb, torch_to_bits(c.new_k), torch_to_bits(c.new_v), c.slot_mapping.numpy())
+    want = oracle.paged_attention(torch_to_bits(c.q), kb, vb, c.block_tables.numpy(), c.seq_lens.numpy(), c.scale, 19)
+    check(c, out, want)
+    assert np.array_equal(torch_to_bits(d.k_cache), kb)
+
+    check_error(LIBINFINIOP.infinirtGraphExecDestroy(gexec))
+    check_error(LIBINFINIOP.infinirtGraphDestroy(graph))
+    check_error(LIBINFINIOP.infinirtStreamDestroy(stream))
+    check_error(LIBINFINIOP.infiniopDestroyPagedCachingDescriptor(cdesc))
+    op.destroy()
+
+
+def test_python_operators_match_the_abi_path(abi):
+    """infinicore_b200.paged_attention / paged_caching (descriptor cache, torch's current stream)."""
+    import infinicore_b200 as ib
+
+    c = workloads.config1_small(seed=3)
+    d = c.to("cuda")
+    ib.paged_caching(d.k_cache, d.v_cache, d.new_k, d.new_v, d.slot_mapping)
+    got = ib.paged_attention(d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, None, d.scale)
+    again = ib.paged_attention(d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, None, d.scale)
+    torch.cuda.synchronize()
+    kb, vb = torch_to_bits(c.k_cache).copy(), torch_to_bits(c.v_cache).copy()
+    oracle.paged_caching(kb, vb, torch_to_bits(c.new_k), torch_to_bits(c.new_v), c.slot_mapping.numpy())
+    want = oracle.paged_attention(torch_to_bits(c.q), kb, vb, c.block_tables.numpy(), c.seq_lens.numpy(), c.scale, 12)
+    check(c, got, want)
+    assert torch.equal(got, again)
