@@ -44,12 +44,13 @@ NCU_TRAFFIC_BYTES = {"c2": None}
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-seqs", type=int, default=0, help="sequences in the CPU sample (0 = the whole batch)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-clocks", action="store_true", help="skip nvidia-smi sampling (for short runs under a profiler)")
     return ap.parse_args()
 
 
@@ -187,6 +188,11 @@ class ClockSampler:
                 stdout=self.file, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
+            return
+        # nvidia-smi needs a moment before its first row; do not start timing before it samples
+        deadline = time.time() + 3.0
+        while time.time() < deadline and os.path.getsize(self.file.name) == 0:
+            time.sleep(0.02)
 
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
@@ -319,7 +325,8 @@ def gpu_arm(args):
         one_step()
     barrier()
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    sample_clocks = rank == 0 and not args.no_clocks
+    if sample_clocks:
         sampler.start()
     K = args.steps
     attn_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
@@ -339,6 +346,15 @@ def gpu_arm(args):
     end.record(stream)
     barrier()
     total_ms = start.elapsed_time(end)
+    clock_window = "timed region"
+    if sample_clocks and total_ms < 400.0:
+        # Too short for nvidia-smi's 100 ms sampling: keep the identical load running (untimed) so the
+        # clocks under this load are still observed.
+        extra = int(600.0 / max(total_ms / K, 1e-3))
+        for _ in range(extra):
+            one_step()
+        torch.cuda.synchronize()
+        clock_window = f"timed region ({total_ms:.1f} ms) + {extra} identical untimed steps"
     if flush is not None:
         # the scrub is not part of the step: subtract its measured share
         flush_ms = sum(start.elapsed_time(cache_events[0]) if i == 0 else attn_events[i - 1][1].elapsed_time(cache_events[i]) for i in range(K))
@@ -346,7 +362,9 @@ def gpu_arm(args):
     attn_ms = statistics.mean(a.elapsed_time(b) for a, b in attn_events)
     attn_ms_min = min(a.elapsed_time(b) for a, b in attn_events)
     cache_ms = statistics.mean(c.elapsed_time(a) for c, (a, _) in zip(cache_events, attn_events))
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop() if sample_clocks else None
+    if clocks is not None:
+        clocks["window"] = clock_window
 
     kv_bytes_all = sum_over_ranks(float(case.kv_bytes))
     seqs_all = sum_over_ranks(float(case.num_seqs))

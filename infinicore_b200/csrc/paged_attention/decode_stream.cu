@@ -72,6 +72,8 @@ struct StreamArgs {
     int tiles_per_page; // block_size / 16
     int stages;
     int num_workers;
+    int probe_copy_only; // measurement aid: stream the tiles but skip the arithmetic (output is garbage)
+    int embedded_plan;   // 1: every CTA derives the plan itself in shared memory (no plan kernel)
 };
 
 // ---------------------------------------------------------------------------------------
@@ -135,17 +137,17 @@ __device__ __forceinline__ void tmaLoadBox(uint32_t dst, const CUtensorMap *map,
 }
 
 __device__ __forceinline__ void ldmatrixX4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    // volatile keeps it after the (volatile) mbarrier wait; no memory clobber, so the compiler
+    // may keep unrelated values in registers across it
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr)
-                 : "memory");
+                 : "r"(addr));
 }
 
 __device__ __forceinline__ void ldmatrixX4Trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr)
-                 : "memory");
+                 : "r"(addr));
 }
 
 template <typename T>
@@ -155,7 +157,7 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
 template <>
 __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                         uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -164,7 +166,7 @@ __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], uint32_t 
 template <>
 __device__ __forceinline__ void mma16816<__half>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                  uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -176,6 +178,18 @@ __device__ __forceinline__ float fastExp2(float x) {
     return y;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute
+// may start while its predecessor in the stream still runs; it must not touch global memory the
+// predecessor may write until gridDependencyWait() returns (which is when the predecessor has
+// completed and its writes are visible).  Every CTA executes the wait before it exits, so the
+// ordering is transitive along a chain of such kernels.  Both are no-ops for a normal launch.
+__device__ __forceinline__ void gridDependencyWait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void gridLaunchDependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ uint32_t packPair(float lo, float hi, __nv_bfloat16) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&v);
@@ -183,6 +197,47 @@ __device__ __forceinline__ uint32_t packPair(float lo, float hi, __nv_bfloat16) 
 __device__ __forceinline__ uint32_t packPair(float lo, float hi, __half) {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// ---------------------------------------------------------------------------------------
+// Walking the linear tile space
+// ---------------------------------------------------------------------------------------
+struct Cursor {
+    int s;   // sequence
+    int j;   // unit within the sequence: kv_head * head_tiles + head_tile
+    int ti;  // tile within the sequence
+    int nt;  // tiles in sequence s
+};
+
+__device__ __forceinline__ void advance(Cursor &c, const long long *prefix, int num_seqs, int units_per_seq) {
+    if (++c.ti == c.nt) {
+        c.ti = 0;
+        if (++c.j == units_per_seq) {
+            c.j = 0;
+            do {
+                ++c.s;
+                c.nt = (c.s < num_seqs) ? static_cast<int>(prefix[c.s + 1] - prefix[c.s]) : 1;
+            } while (c.nt == 0);
+        }
+    }
+}
+
+// Where does linear position x start?  It belongs to the last sequence s with
+// prefix[s] * units_per_seq <= x, i.e. prefix[s] <= x / units_per_seq.
+__device__ __forceinline__ int4 locate(const long long *prefix, int num_seqs, int units_per_seq, long long x) {
+    const long long y = x / units_per_seq;
+    int lo = 0, hi = num_seqs; // invariant: prefix[lo] <= y < prefix[hi]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (prefix[mid] <= y) {
+            lo = mid;
+        } else {
+            hi = mid;
+        }
+    }
+    const long long nt = prefix[lo + 1] - prefix[lo];
+    const long long rem = x - prefix[lo] * units_per_seq;
+    return make_int4(lo, static_cast<int>(rem / nt), static_cast<int>(rem % nt), 0);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -198,6 +253,8 @@ __global__ void __launch_bounds__(kPlanThreads)
     const int num_seqs = a.p.num_seqs;
     const long long capacity = static_cast<long long>(a.p.max_blocks_per_seq) * a.p.block_size;
 
+    gridDependencyWait();
+    gridLaunchDependents();
     if (tid == 0) {
         running_s = 0;
         a.prefix[0] = 0;
@@ -261,49 +318,14 @@ __global__ void __launch_bounds__(kPlanThreads)
         a.header->range_len = range_len;
     }
 
-    // Where does range r start?  Position x belongs to the last sequence s with
-    // prefix[s] * units_per_seq <= x, i.e. prefix[s] <= x / units_per_seq.
     for (int r = tid; r < num_ranges; r += kPlanThreads) {
-        const long long x = r * range_len;
-        const long long y = x / a.units_per_seq;
-        int lo = 0, hi = num_seqs; // invariant: prefix[lo] <= y < prefix[hi] (prefix[num_seqs] = seq_tiles > y)
-        while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (a.prefix[mid] <= y) {
-                lo = mid;
-            } else {
-                hi = mid;
-            }
-        }
-        const long long nt = a.prefix[lo + 1] - a.prefix[lo];
-        const long long rem = x - a.prefix[lo] * a.units_per_seq;
-        a.range_start[r] = make_int4(lo, static_cast<int>(rem / nt), static_cast<int>(rem % nt), 0);
+        a.range_start[r] = locate(a.prefix, num_seqs, a.units_per_seq, r * range_len);
     }
 }
 
 // ---------------------------------------------------------------------------------------
 // Main kernel
 // ---------------------------------------------------------------------------------------
-struct Cursor {
-    int s;   // sequence
-    int j;   // unit within the sequence: kv_head * head_tiles + head_tile
-    int ti;  // tile within the sequence
-    int nt;  // tiles in sequence s
-};
-
-__device__ __forceinline__ void advance(Cursor &c, const StreamArgs &a) {
-    if (++c.ti == c.nt) {
-        c.ti = 0;
-        if (++c.j == a.units_per_seq) {
-            c.j = 0;
-            do {
-                ++c.s;
-                c.nt = (c.s < a.p.num_seqs) ? static_cast<int>(a.prefix[c.s + 1] - a.prefix[c.s]) : 1;
-            } while (c.nt == 0);
-        }
-    }
-}
-
 template <typename T, int HD>
 __global__ void __launch_bounds__(kMaxWarps * 32)
     pagedDecodeStreamKernel(const __grid_constant__ CUtensorMap tmap_k,
@@ -328,6 +350,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
 
     const uint32_t ring = smemAddr(smem_raw) + warp * stages * kStageBytes;
     const uint32_t bars = smemAddr(smem_raw) + nwarps * stages * kStageBytes + warp * stages * 8;
+    // shared-memory copy of the plan (embedded mode): tile prefix per sequence + scan scratch
+    long long *prefix_s = reinterpret_cast<long long *>(smem_raw + nwarps * stages * (kStageBytes + 8));
+    long long *scan_s = prefix_s + (p.num_seqs + 1);
 
     if (lane == 0) {
         for (int i = 0; i < stages; ++i) {
@@ -338,29 +363,100 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     }
     __syncwarp();
 
+    // Everything above touches only this CTA's shared memory; from here on global memory that an
+    // earlier kernel in the stream may have produced is read.
+    gridDependencyWait();
+    gridLaunchDependents();
+
     const int worker = blockIdx.x * nwarps + warp;
-    const int num_ranges = a.header->num_ranges;
+    const long long *prefix;
+    long long total_tiles, range_len;
+    int num_ranges;
+    if (a.embedded_plan) {
+        // Every CTA derives the same plan: per-thread chunk of sequences -> block scan -> prefix.
+        const int tid = threadIdx.x;
+        const int nthreads = blockDim.x;
+        const int per = (p.num_seqs + nthreads - 1) / nthreads;
+        const long long capacity = static_cast<long long>(p.max_blocks_per_seq) * p.block_size;
+        const int s_begin = min(tid * per, p.num_seqs);
+        const int s_end = min(s_begin + per, p.num_seqs);
+        long long mine = 0;
+        for (int s = s_begin; s < s_end; ++s) {
+            long long len = loadIndex(p.seq_lens, s, p.index_is_64);
+            len = len < 0 ? 0 : (len > capacity ? capacity : len);
+            mine += (len + kTileTokens - 1) / kTileTokens;
+        }
+        long long incl = mine;
+#pragma unroll
+        for (int o2 = 1; o2 < 32; o2 <<= 1) {
+            const long long n = __shfl_up_sync(0xffffffffu, incl, o2);
+            if (lane >= o2) {
+                incl += n;
+            }
+        }
+        if (lane == 31) {
+            scan_s[warp] = incl;
+        }
+        __syncthreads();
+        long long before = incl - mine;
+        for (int w = 0; w < warp; ++w) {
+            before += scan_s[w];
+        }
+        for (int s = s_begin; s < s_end; ++s) {
+            long long len = loadIndex(p.seq_lens, s, p.index_is_64);
+            len = len < 0 ? 0 : (len > capacity ? capacity : len);
+            before += (len + kTileTokens - 1) / kTileTokens;
+            prefix_s[s + 1] = before;
+        }
+        if (tid == 0) {
+            prefix_s[0] = 0;
+        }
+        __syncthreads();
+        prefix = prefix_s;
+        total_tiles = prefix_s[p.num_seqs] * a.units_per_seq;
+        range_len = (total_tiles + a.num_workers - 1) / a.num_workers;
+        range_len = range_len < 1 ? 1 : range_len;
+        num_ranges = static_cast<int>((total_tiles + range_len - 1) / range_len);
+        if (blockIdx.x == 0) {
+            // the combine kernel reads the plan from the workspace
+            for (int s = tid; s <= p.num_seqs; s += nthreads) {
+                a.prefix[s] = prefix_s[s];
+            }
+            if (tid == 0) {
+                // A worker can only raise the flag after a 2 s wait ran out; CTA 0 is resident from
+                // the start of the launch, so this store precedes any such write.
+                a.header->error = 0;
+                a.header->num_ranges = num_ranges;
+                a.header->total_tiles = total_tiles;
+                a.header->range_len = range_len;
+            }
+        }
+    } else {
+        prefix = a.prefix;
+        total_tiles = a.header->total_tiles;
+        range_len = a.header->range_len;
+        num_ranges = a.header->num_ranges;
+    }
     if (worker >= num_ranges) {
         return;
     }
-    const long long total_tiles = a.header->total_tiles;
-    const long long range_len = a.header->range_len;
     const long long x0 = worker * range_len;
     const long long count = (total_tiles - x0 < range_len) ? (total_tiles - x0) : range_len;
 
-    const int4 rs = a.range_start[worker];
+    const int4 rs = a.embedded_plan ? locate(prefix, p.num_seqs, a.units_per_seq, x0) : a.range_start[worker];
     Cursor gen; // next tile to fetch
     gen.s = rs.x;
     gen.j = rs.y;
     gen.ti = rs.z;
-    gen.nt = static_cast<int>(a.prefix[rs.x + 1] - a.prefix[rs.x]);
+    gen.nt = static_cast<int>(prefix[rs.x + 1] - prefix[rs.x]);
     Cursor cur = gen; // next tile to consume
 
     const int tpp = a.tiles_per_page;
     const int head_tiles = a.head_tiles;
 
     auto tableEntry = [&](const Cursor &c) -> long long {
-        return loadIndex(p.block_tables, c.s * p.bt_seq_stride + c.ti / tpp, p.index_is_64);
+        const int page = (tpp == 1) ? c.ti : c.ti / tpp;
+        return loadIndex(p.block_tables, c.s * p.bt_seq_stride + page, p.index_is_64);
     };
     auto issue = [&](int stage, const Cursor &c, long long block) {
         const uint32_t bar = bars + stage * 8;
@@ -371,8 +467,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
         if (lane < 2 * kChunks) {
             const int is_v = lane / kChunks;
             const int chunk = lane % kChunks;
+            const int row0 = (tpp == 1) ? 0 : (c.ti % tpp) * kTileTokens;
+            const int kv_head = (head_tiles == 1) ? c.j : c.j / head_tiles;
             tmaLoadBox(dst + is_v * kTensorBytes + chunk * kBoxBytes, is_v ? &tmap_v : &tmap_k, bar,
-                       chunk * 64, (c.ti % tpp) * kTileTokens, c.j / head_tiles, static_cast<int>(block));
+                       chunk * 64, row0, kv_head, static_cast<int>(block));
         }
     };
 
@@ -387,7 +485,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
                 pc[i] = gen;
                 pb[i] = tableEntry(gen);
                 if (i + 1 < count) {
-                    advance(gen, a);
+                    advance(gen, prefix, p.num_seqs, a.units_per_seq);
                 }
             }
         }
@@ -452,6 +550,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
             break;
         }
 
+        if (!a.probe_copy_only) {
         const int tok0 = cur.ti * kTileTokens;
         const int valid = seq_len - tok0; // >= 1 by construction
         if (valid < kTileTokens) {
@@ -469,33 +568,63 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
             __syncwarp();
         }
 
-        // ---- S^T = Q . K^T ------------------------------------------------------------
-        float sc[2][4];
+        // Operand loads are issued ahead of the math that needs them: all K fragments, then (for
+        // head sizes up to 128) all V fragments, so their shared-memory latency overlaps the QK
+        // MMAs and the softmax instead of sitting in front of every MMA.
+        const int k_row = ((lane >> 4) << 3) + (lane & 7);     // token row this lane addresses for K
+        const int k_half = (lane >> 3) & 1;                     // which 16-byte column of the 32-byte k-step
+        const int v_row = (((lane >> 3) & 1) << 3) + (lane & 7);
+        const int v_sel = lane >> 4;
+        auto kAddr = [&](int ks) {
+            const int col = ks * 2 + k_half;
+            return k_tile + (col >> 3) * kBoxBytes + k_row * 128 + (((col & 7) ^ (k_row & 7)) << 4);
+        };
+        auto vAddr = [&](int np) {
+            const int col = np * 2 + v_sel;
+            return v_tile + (col >> 3) * kBoxBytes + v_row * 128 + (((col & 7) ^ (v_row & 7)) << 4);
+        };
+        constexpr int kKChunk = (kKSteps <= 8) ? kKSteps : ((kKSteps % 8 == 0) ? 8 : 6); // divides kKSteps, even
+        constexpr bool kPrefetchV = (HD <= 128);
+        constexpr int kVFrags = kPrefetchV ? kNTiles / 2 : 1;
+
+        // ---- S^T = Q . K^T: two accumulator chains per 8-token n-tile -----------------------
+        float sa[2][4], sb[2][4];
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
-            sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+            sa[n][0] = sa[n][1] = sa[n][2] = sa[n][3] = 0.f;
+            sb[n][0] = sb[n][1] = sb[n][2] = sb[n][3] = 0.f;
         }
-        {
-            // lane -> (token row, which 16-byte column of the 32-byte k-step)
-            const int row = ((lane >> 4) << 3) + (lane & 7);
-            const int half = (lane >> 3) & 1;
+        uint32_t vb[kVFrags][4];
 #pragma unroll
-            for (int ks = 0; ks < kKSteps; ++ks) {
-                const int col = ks * 2 + half; // 16-byte column within the row
-                const uint32_t addr = k_tile + (col >> 3) * kBoxBytes + row * 128 + (((col & 7) ^ (row & 7)) << 4);
-                uint32_t b0, b1, b2, b3;
-                ldmatrixX4(addr, b0, b1, b2, b3);
-                mma16816<T>(sc[0], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
-                mma16816<T>(sc[1], qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+        for (int c0 = 0; c0 < kKSteps; c0 += kKChunk) {
+            uint32_t kb[kKChunk][4];
+#pragma unroll
+            for (int ks = 0; ks < kKChunk; ++ks) {
+                ldmatrixX4(kAddr(c0 + ks), kb[ks][0], kb[ks][1], kb[ks][2], kb[ks][3]);
+            }
+            if constexpr (kPrefetchV) {
+                if (c0 == 0) {
+#pragma unroll
+                for (int np = 0; np < kVFrags; ++np) {
+                    ldmatrixX4Trans(vAddr(np), vb[np][0], vb[np][1], vb[np][2], vb[np][3]);
+                }
+                }
+            }
+#pragma unroll
+            for (int ks = 0; ks < kKChunk; ks += 2) {
+                mma16816<T>(sa[0], qa[c0 + ks][0], 0u, qa[c0 + ks][1], 0u, kb[ks][0], kb[ks][1]);
+                mma16816<T>(sa[1], qa[c0 + ks][0], 0u, qa[c0 + ks][1], 0u, kb[ks][2], kb[ks][3]);
+                mma16816<T>(sb[0], qa[c0 + ks + 1][0], 0u, qa[c0 + ks + 1][1], 0u, kb[ks + 1][0], kb[ks + 1][1]);
+                mma16816<T>(sb[1], qa[c0 + ks + 1][0], 0u, qa[c0 + ks + 1][1], 0u, kb[ks + 1][2], kb[ks + 1][3]);
             }
         }
 
         // ---- online softmax (log2 domain) for q-head g over this tile's 16 tokens -----------
         float x[4];
-        x[0] = sc[0][0] * p.scale_log2e;
-        x[1] = sc[0][1] * p.scale_log2e;
-        x[2] = sc[1][0] * p.scale_log2e;
-        x[3] = sc[1][1] * p.scale_log2e;
+        x[0] = (sa[0][0] + sb[0][0]) * p.scale_log2e;
+        x[1] = (sa[0][1] + sb[0][1]) * p.scale_log2e;
+        x[2] = (sa[1][0] + sb[1][0]) * p.scale_log2e;
+        x[3] = (sa[1][1] + sb[1][1]) * p.scale_log2e;
         if (slope_log2 != 0.f) {
             const int rel = tok0 + 2 * t - (seq_len - 1);
             x[0] += slope_log2 * static_cast<float>(rel);
@@ -530,19 +659,22 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
         }
 
         // ---- O += P . V -----------------------------------------------------------------
-        {
-            const int row = (((lane >> 3) & 1) << 3) + (lane & 7);
-            const int sel = lane >> 4;
 #pragma unroll
-            for (int np = 0; np < kNTiles / 2; ++np) {
-                const int col = np * 2 + sel;
-                const uint32_t addr = v_tile + (col >> 3) * kBoxBytes + row * 128 + (((col & 7) ^ (row & 7)) << 4);
-                uint32_t b0, b1, b2, b3;
-                ldmatrixX4Trans(addr, b0, b1, b2, b3);
-                mma16816<T>(o[2 * np], pa0, 0u, pa2, 0u, b0, b1);
-                mma16816<T>(o[2 * np + 1], pa0, 0u, pa2, 0u, b2, b3);
+        for (int np = 0; np < kNTiles / 2; ++np) {
+            uint32_t b0, b1, b2, b3;
+            if constexpr (kPrefetchV) {
+                b0 = vb[np][0];
+                b1 = vb[np][1];
+                b2 = vb[np][2];
+                b3 = vb[np][3];
+            } else {
+                ldmatrixX4Trans(vAddr(np), b0, b1, b2, b3);
             }
+            mma16816<T>(o[2 * np], pa0, 0u, pa2, 0u, b0, b1);
+            mma16816<T>(o[2 * np + 1], pa0, 0u, pa2, 0u, b2, b3);
         }
+
+        } // !probe_copy_only
 
         // ---- the slot is free: refill it with tile i + stages -----------------------------
         __syncwarp();
@@ -550,7 +682,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
             issue(stage, gen, next_block);
             ++issued;
             if (issued < count) {
-                advance(gen, a);
+                advance(gen, prefix, p.num_seqs, a.units_per_seq);
                 next_block = tableEntry(gen);
             }
         }
@@ -592,7 +724,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
             }
         }
         if (i + 1 < count) {
-            advance(cur, a);
+            advance(cur, prefix, p.num_seqs, a.units_per_seq);
             if (unit_end) {
                 loadUnit();
             }
@@ -626,6 +758,8 @@ __global__ void __launch_bounds__(128)
     constexpr int kPerLane = HD / 32;
     const DecodeParams &p = a.p;
     const int lane = threadIdx.x & 31;
+    gridDependencyWait(); // the records, the plan and `out` rows written by the main kernel
+    gridLaunchDependents();
     const long long pair = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (pair >= static_cast<long long>(p.num_seqs) * p.num_heads) {
         return;
@@ -760,21 +894,55 @@ WorkspaceLayout workspaceLayout(const Info &I, const StreamPlan &plan) {
 template <typename T, int HD>
 infiniStatus_t launchTyped(const StreamPlan &plan, const StreamArgs &args, const CUtensorMap &mk, const CUtensorMap &mv,
                            int device_id, cudaStream_t stream) {
-    static bool attr_done[64] = {};
+    // The opt-in shared memory limit is a per-device, per-kernel attribute; raise it whenever a plan
+    // needs more than any earlier plan on that device did.
+    static std::mutex attr_mutex;
+    static size_t attr_bytes[64] = {};
     auto kernel = pagedDecodeStreamKernel<T, HD>;
-    if (device_id < 0 || device_id >= 64 || !attr_done[device_id]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan.smem_bytes)) != cudaSuccess) {
-            return checkLaunch("cudaFuncSetAttribute(pagedDecodeStreamKernel)");
-        }
-        if (device_id >= 0 && device_id < 64) {
-            attr_done[device_id] = true;
+    {
+        std::lock_guard<std::mutex> lock(attr_mutex);
+        const bool tracked = device_id >= 0 && device_id < 64;
+        if (!tracked || attr_bytes[device_id] < plan.smem_bytes) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan.smem_bytes)) != cudaSuccess) {
+                return checkLaunch("cudaFuncSetAttribute(pagedDecodeStreamKernel)");
+            }
+            if (tracked) {
+                attr_bytes[device_id] = plan.smem_bytes;
+            }
         }
     }
-    pagedDecodePlanKernel<<<1, kPlanThreads, 0, stream>>>(args);
-    kernel<<<plan.grid, plan.warps_per_cta * 32, plan.smem_bytes, stream>>>(mk, mv, args);
+    // All launches carry the programmatic-serialization attribute: each kernel's prologue overlaps
+    // the tail of whatever precedes it in the stream, and each kernel waits (griddepcontrol.wait)
+    // before it reads anything a predecessor may have written.
+    cudaLaunchAttribute pdl;
+    pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl.val.programmaticStreamSerializationAllowed = plan.use_pdl ? 1 : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = stream;
+    cfg.attrs = &pdl;
+    cfg.numAttrs = 1;
+
+    if (!plan.embedded_plan) {
+        cfg.gridDim = dim3(1);
+        cfg.blockDim = dim3(kPlanThreads);
+        cfg.dynamicSmemBytes = 0;
+        if (cudaLaunchKernelEx(&cfg, pagedDecodePlanKernel, args) != cudaSuccess) {
+            return checkLaunch("pagedDecodePlanKernel");
+        }
+    }
+    cfg.gridDim = dim3(plan.grid);
+    cfg.blockDim = dim3(plan.warps_per_cta * 32);
+    cfg.dynamicSmemBytes = plan.smem_bytes;
+    if (cudaLaunchKernelEx(&cfg, kernel, mk, mv, args) != cudaSuccess) {
+        return checkLaunch("pagedDecodeStreamKernel");
+    }
     const long long pairs = static_cast<long long>(args.p.num_seqs) * args.p.num_heads;
-    const unsigned combine_blocks = static_cast<unsigned>((pairs + 3) / 4);
-    pagedDecodeCombineKernel<T, HD><<<combine_blocks, 128, 0, stream>>>(args);
+    cfg.gridDim = dim3(static_cast<unsigned>((pairs + 3) / 4));
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, HD>, args) != cudaSuccess) {
+        return checkLaunch("pagedDecodeCombineKernel");
+    }
     return checkLaunch("pagedDecodeStream");
 }
 
@@ -818,11 +986,16 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
     plan.head_tiles_per_group = (group + kHeadsPerTile - 1) / kHeadsPerTile;
 
     const size_t stage_bytes = 2 * (hd / 64) * kTileTokens * 128;
-    const int default_stages = (hd <= 128) ? 3 : 2;
+    const int default_stages = 2;
     plan.warps_per_cta = envInt("INFINIOP_PAGED_DECODE_WARPS", 4, 1, kMaxWarps);
     plan.stages = envInt("INFINIOP_PAGED_DECODE_STAGES", default_stages, 1, kMaxStages);
     int ctas_per_sm = envInt("INFINIOP_PAGED_DECODE_CTAS_PER_SM", 2, 1, 8);
-    auto smemFor = [&](int warps, int stages) { return static_cast<size_t>(warps) * stages * (stage_bytes + 8) + 1024; };
+    // The plan is derived inside the main kernel (one launch fewer) when the per-sequence prefix fits
+    // a modest slice of shared memory; larger batches use the separate one-CTA plan kernel.
+    plan.embedded_plan = envInt("INFINIOP_PAGED_DECODE_EMBEDDED_PLAN", 1, 0, 1) != 0 && I.num_seqs <= 4095;
+    plan.use_pdl = envInt("INFINIOP_PAGED_DECODE_PDL", 1, 0, 1) != 0;
+    const size_t plan_bytes = plan.embedded_plan ? (I.num_seqs + 1 + kMaxWarps) * sizeof(long long) : 0;
+    auto smemFor = [&](int warps, int stages) { return static_cast<size_t>(warps) * stages * (stage_bytes + 8) + plan_bytes + 1024; };
     const size_t budget = props.smem_per_block_optin;
     while (plan.stages > 1 && smemFor(plan.warps_per_cta, plan.stages) > budget) {
         --plan.stages;
@@ -835,6 +1008,7 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
     while (ctas_per_sm > 1 && ctas_per_sm * (plan.smem_bytes + 1024) > props.smem_per_sm) {
         --ctas_per_sm;
     }
+    plan.probe_copy_only = envInt("INFINIOP_PAGED_DECODE_PROBE_COPY_ONLY", 0, 0, 1) != 0;
     plan.grid = props.sm_count * ctas_per_sm;
     plan.num_workers = plan.grid * plan.warps_per_cta;
     plan.workspace_bytes = workspaceLayout(I, plan).total;
@@ -867,6 +1041,8 @@ infiniStatus_t launchDecodeStream(const Info &I, const StreamPlan &plan, const D
     a.tiles_per_page = static_cast<int>(I.block_size / kTileTokens);
     a.stages = plan.stages;
     a.num_workers = plan.num_workers;
+    a.probe_copy_only = plan.probe_copy_only ? 1 : 0;
+    a.embedded_plan = plan.embedded_plan ? 1 : 0;
 
     int device_id = -1;
     (void)cudaGetDevice(&device_id);

@@ -55,6 +55,9 @@ struct StreamPlan {
     int num_workers = 0; // grid * warps_per_cta
     size_t smem_bytes = 0;
     size_t workspace_bytes = 0;
+    bool embedded_plan = false;   // the main kernel derives the plan itself (no plan kernel)
+    bool use_pdl = true;          // launches carry the programmatic-serialization attribute
+    bool probe_copy_only = false; // measurement aid (INFINIOP_PAGED_DECODE_PROBE_COPY_ONLY=1): tiles are streamed, math skipped
 };
 
 // Decides at descriptor creation whether the streaming path applies and sizes its workspace.

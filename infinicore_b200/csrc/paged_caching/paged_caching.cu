@@ -14,6 +14,7 @@
 // 256 KiB in, 256 KiB out) and launch-latency bound; the grid is sized to the row count.
 #include "../common.h"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace b200::paged_caching {
@@ -37,6 +38,7 @@ struct Info {
 struct Descriptor {
     OpDescriptorBase base;
     Info info;
+    bool use_pdl; // INFINIOP_PAGED_DECODE_PDL (default 1), read when the descriptor is created
 };
 
 static infiniStatus_t makeInfo(Info &out,
@@ -118,6 +120,11 @@ constexpr int kWarpsPerBlock = 8;
 template <typename Vec>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
     pagedCachingScatterKernel(const KernelArgs a) {
+    // Launched with the programmatic-serialization attribute: wait for the preceding kernel in the
+    // stream (which may still be reading the pools or producing k/v), then let the next one start
+    // its prologue.  Both are no-ops for a normal launch.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const long long row = static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
     if (row >= a.num_rows) {
         return;
@@ -192,13 +199,24 @@ static infiniStatus_t launch(const Descriptor &desc,
 
     auto aligned16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     const bool vec16 = I.strides_vec16 && aligned16(k_cache) && aligned16(v_cache) && aligned16(k) && aligned16(v);
+    cudaLaunchAttribute pdl;
+    pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl.val.programmaticStreamSerializationAllowed = desc.use_pdl ? 1 : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = stream;
+    cfg.attrs = &pdl;
+    cfg.numAttrs = 1;
+    cudaError_t err;
     if (vec16) {
-        pagedCachingScatterKernel<uint4><<<grid, block, 0, stream>>>(a);
+        err = cudaLaunchKernelEx(&cfg, pagedCachingScatterKernel<uint4>, a);
     } else if (I.elem_size == 4) {
-        pagedCachingScatterKernel<uint32_t><<<grid, block, 0, stream>>>(a);
+        err = cudaLaunchKernelEx(&cfg, pagedCachingScatterKernel<uint32_t>, a);
     } else {
-        pagedCachingScatterKernel<uint16_t><<<grid, block, 0, stream>>>(a);
+        err = cudaLaunchKernelEx(&cfg, pagedCachingScatterKernel<uint16_t>, a);
     }
+    (void)err;
     return checkLaunch("pagedCachingScatterKernel");
 }
 
@@ -224,7 +242,9 @@ __INFINI_C infiniStatus_t infiniopCreatePagedCachingDescriptor(
     B200_RETURN_IF(st != INFINI_STATUS_SUCCESS, st);
 
     auto *h = reinterpret_cast<b200::Handle *>(handle);
-    auto *d = new Descriptor{{handle->device, handle->device_id, b200::OpKind::PagedCaching, h->props}, info};
+    const char *pdl_env = std::getenv("INFINIOP_PAGED_DECODE_PDL");
+    const bool use_pdl = !(pdl_env != nullptr && pdl_env[0] == '0');
+    auto *d = new Descriptor{{handle->device, handle->device_id, b200::OpKind::PagedCaching, h->props}, info, use_pdl};
     *desc_ptr = reinterpret_cast<infiniopPagedCachingDescriptor_t>(d);
     return INFINI_STATUS_SUCCESS;
 }
