@@ -66,6 +66,7 @@ struct StreamArgs {
     PlanHeader *header;
     long long *prefix;  // [num_seqs + 1] tiles before each sequence (one kv-head, one head tile)
     int4 *range_start;  // [workers] (sequence, unit-within-sequence, tile) where a range begins
+    int4 *tasks;        // [workers] combine tasks: (sequence, unit-within-sequence, first range, records)
     float *partials;    // [(units + workers)] records of 8 * (HD + 2) floats
     int units_per_seq;  // num_kv_heads * head_tiles
     int head_tiles;
@@ -451,6 +452,21 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     gen.nt = static_cast<int>(prefix[rs.x + 1] - prefix[rs.x]);
     Cursor cur = gen; // next tile to consume
 
+    if (lane == 0) {
+        // This range starts mid-unit when rs.z != 0; if it is the first range to do so for that
+        // unit, it owns the unit's combine task.
+        int4 task = make_int4(-1, -1, 0, 0);
+        if (rs.z != 0) {
+            const long long unit_start = x0 - rs.z;
+            const long long r_first = unit_start / range_len;
+            if (worker == r_first + 1) {
+                const long long r_last = (unit_start + gen.nt - 1) / range_len;
+                task = make_int4(rs.x, rs.y, static_cast<int>(r_first), static_cast<int>(r_last - r_first + 1));
+            }
+        }
+        a.tasks[worker] = task;
+    }
+
     const int tpp = a.tiles_per_page;
     const int head_tiles = a.head_tiles;
 
@@ -750,72 +766,127 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
 }
 
 // ---------------------------------------------------------------------------------------
-// Combine kernel: one warp per (sequence, q-head); merges the records of a split unit.
+// Combine kernel.  A unit is split exactly when a range boundary falls inside it, so there are
+// fewer split units than workers.  The worker whose range starts at the FIRST boundary inside a
+// unit leaves a task (sequence, unit, first range, number of records) in tasks[worker]; CTA r of
+// this kernel executes tasks[r].  Its warps share out the unit's records, each warp merges its
+// share with a warp-local running maximum, and the per-warp results are merged through shared
+// memory - the same (m, l, acc) algebra at both levels.
 // ---------------------------------------------------------------------------------------
+template <int HD>
+struct CombineShape {
+    static constexpr int kWarps = (HD <= 128) ? 8 : 4;
+    static constexpr int kFloats = kHeadsPerTile * HD;       // accumulator floats per record
+    static constexpr int kVec = kFloats / 4 / 32;             // float4 per lane per record
+    static constexpr int kRec = kHeadsPerTile * (HD + 2);
+};
+
 template <typename T, int HD>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(CombineShape<HD>::kWarps * 32)
     pagedDecodeCombineKernel(const StreamArgs a) {
-    constexpr int kPerLane = HD / 32;
+    using S = CombineShape<HD>;
+    __shared__ float4 acc_s[S::kWarps][S::kFloats / 4];
+    __shared__ float m_s[S::kWarps][kHeadsPerTile];
+    __shared__ float l_s[S::kWarps][kHeadsPerTile];
+
     const DecodeParams &p = a.p;
+    const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    gridDependencyWait(); // the records, the plan and `out` rows written by the main kernel
+    gridDependencyWait(); // records, plan, tasks and directly written `out` rows come from the main kernel
     gridLaunchDependents();
-    const long long pair = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (pair >= static_cast<long long>(p.num_seqs) * p.num_heads) {
+    const int r = blockIdx.x;
+    if (r >= a.header->num_ranges) {
         return;
     }
-    const int s = static_cast<int>(pair / p.num_heads);
-    const int head = static_cast<int>(pair % p.num_heads);
-    const long long nt = a.prefix[s + 1] - a.prefix[s];
-    if (nt == 0) {
-        return; // empty sequence: output untouched
+    const int4 task = a.tasks[r];
+    const int n = task.w;
+    if (n <= 0) {
+        return;
     }
-    const int kv_head = head / p.group_size;
-    const int in_group = head % p.group_size;
-    const int j = kv_head * a.head_tiles + in_group / kHeadsPerTile;
-    const int row = in_group % kHeadsPerTile;
-    const long long range_len = a.header->range_len;
-    const long long start = a.prefix[s] * a.units_per_seq + j * nt;
-    const long long r_first = start / range_len;
-    const long long r_last = (start + nt - 1) / range_len;
-    if (r_first == r_last) {
-        return; // the worker that covered the whole unit wrote the output itself
-    }
+    const int s = task.x, j = task.y;
+    const int kv_head = j / a.head_tiles;
+    const int head_tile = j % a.head_tiles;
+    const int heads_valid = min(kHeadsPerTile, p.group_size - head_tile * kHeadsPerTile);
     const long long unit = static_cast<long long>(s) * a.units_per_seq + j;
-    constexpr int kRec = kHeadsPerTile * (HD + 2);
-    const float *base = a.partials + (unit + r_first) * kRec;
-    const int n = static_cast<int>(r_last - r_first + 1);
+    const float *base = a.partials + (unit + task.z) * S::kRec;
 
-    float m_all = -INFINITY;
-    for (int i = lane; i < n; i += 32) {
-        m_all = fmaxf(m_all, base[static_cast<long long>(i) * kRec + kHeadsPerTile * HD + row * 2]);
-    }
+    // vector v of this lane covers floats [4 * (v * 32 + lane), +4) of the record's accumulator block
+    int head_of[S::kVec];
+    float m_loc[S::kVec], l_loc[S::kVec];
+    float4 acc[S::kVec];
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, off));
+    for (int v = 0; v < S::kVec; ++v) {
+        head_of[v] = (v * 32 + lane) / (HD / 4);
+        m_loc[v] = -INFINITY;
+        l_loc[v] = 0.f;
+        acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    float acc[kPerLane];
+    for (int i = warp; i < n; i += S::kWarps) {
+        const float *ml = base + static_cast<long long>(i) * S::kRec + S::kFloats;
 #pragma unroll
-    for (int k = 0; k < kPerLane; ++k) {
-        acc[k] = 0.f;
-    }
-    float l_all = 0.f;
-    for (int i = 0; i < n; ++i) {
-        const float *rec = base + static_cast<long long>(i) * kRec;
-        const float2 ml = *reinterpret_cast<const float2 *>(rec + kHeadsPerTile * HD + row * 2);
-        const float w = exp2f(ml.x - m_all);
-        l_all = fmaf(w, ml.y, l_all);
-        const float *src = rec + row * HD + lane * kPerLane;
-#pragma unroll
-        for (int k = 0; k < kPerLane; ++k) {
-            acc[k] = fmaf(w, src[k], acc[k]);
+        for (int v = 0; v < S::kVec; ++v) {
+            if (head_of[v] < heads_valid) {
+                m_loc[v] = fmaxf(m_loc[v], ml[head_of[v] * 2]);
+            }
         }
     }
-    const float inv = 1.f / l_all;
-    T *out = static_cast<T *>(p.out) + s * p.o_seq_stride + head * p.o_head_stride + lane * kPerLane;
+    for (int i = warp; i < n; i += S::kWarps) {
+        const float *rec = base + static_cast<long long>(i) * S::kRec;
+        const float4 *rec4 = reinterpret_cast<const float4 *>(rec);
 #pragma unroll
-    for (int k = 0; k < kPerLane; k += 2) {
-        *reinterpret_cast<uint32_t *>(out + k) = packPair(acc[k] * inv, acc[k + 1] * inv, T());
+        for (int v = 0; v < S::kVec; ++v) {
+            if (head_of[v] < heads_valid) {
+                const float2 ml = *reinterpret_cast<const float2 *>(rec + S::kFloats + head_of[v] * 2);
+                const float w = exp2f(ml.x - m_loc[v]);
+                const float4 x = rec4[v * 32 + lane];
+                acc[v].x = fmaf(w, x.x, acc[v].x);
+                acc[v].y = fmaf(w, x.y, acc[v].y);
+                acc[v].z = fmaf(w, x.z, acc[v].z);
+                acc[v].w = fmaf(w, x.w, acc[v].w);
+                l_loc[v] = fmaf(w, ml.y, l_loc[v]);
+            }
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < S::kVec; ++v) {
+        acc_s[warp][v * 32 + lane] = acc[v];
+        if ((v * 32 + lane) % (HD / 4) == 0) {
+            m_s[warp][head_of[v]] = m_loc[v];
+            l_s[warp][head_of[v]] = l_loc[v];
+        }
+    }
+    __syncthreads();
+
+    for (int f = threadIdx.x; f < S::kFloats / 4; f += S::kWarps * 32) {
+        const int head = f / (HD / 4);
+        if (head >= heads_valid) {
+            continue;
+        }
+        float m_all = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < S::kWarps; ++w) {
+            m_all = fmaxf(m_all, m_s[w][head]);
+        }
+        float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        float l_all = 0.f;
+#pragma unroll
+        for (int w = 0; w < S::kWarps; ++w) {
+            const float mw = m_s[w][head];
+            if (mw != -INFINITY) {
+                const float wgt = exp2f(mw - m_all);
+                const float4 x = acc_s[w][f];
+                o4.x = fmaf(wgt, x.x, o4.x);
+                o4.y = fmaf(wgt, x.y, o4.y);
+                o4.z = fmaf(wgt, x.z, o4.z);
+                o4.w = fmaf(wgt, x.w, o4.w);
+                l_all = fmaf(wgt, l_s[w][head], l_all);
+            }
+        }
+        const float inv = 1.f / l_all;
+        const int q_head = kv_head * p.group_size + head_tile * kHeadsPerTile + head;
+        T *out = static_cast<T *>(p.out) + s * p.o_seq_stride + q_head * p.o_head_stride + (f % (HD / 4)) * 4;
+        *reinterpret_cast<uint32_t *>(out) = packPair(o4.x * inv, o4.y * inv, T());
+        *reinterpret_cast<uint32_t *>(out + 2) = packPair(o4.z * inv, o4.w * inv, T());
     }
 }
 
@@ -876,7 +947,7 @@ int envInt(const char *name, int fallback, int lo, int hi) {
 size_t roundUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct WorkspaceLayout {
-    size_t header_off, prefix_off, range_off, partial_off, total;
+    size_t header_off, prefix_off, range_off, task_off, partial_off, total;
 };
 
 WorkspaceLayout workspaceLayout(const Info &I, const StreamPlan &plan) {
@@ -884,7 +955,8 @@ WorkspaceLayout workspaceLayout(const Info &I, const StreamPlan &plan) {
     L.header_off = 0;
     L.prefix_off = 256;
     L.range_off = roundUp(L.prefix_off + (I.num_seqs + 1) * sizeof(long long), 256);
-    L.partial_off = roundUp(L.range_off + static_cast<size_t>(plan.num_workers) * sizeof(int4), 256);
+    L.task_off = roundUp(L.range_off + static_cast<size_t>(plan.num_workers) * sizeof(int4), 256);
+    L.partial_off = roundUp(L.task_off + static_cast<size_t>(plan.num_workers) * sizeof(int4), 256);
     const size_t units = I.num_seqs * I.num_kv_heads * static_cast<size_t>(plan.head_tiles_per_group);
     const size_t rec = kHeadsPerTile * (I.head_size + 2) * sizeof(float);
     L.total = roundUp(L.partial_off + (units + plan.num_workers) * rec, 256);
@@ -936,9 +1008,8 @@ infiniStatus_t launchTyped(const StreamPlan &plan, const StreamArgs &args, const
     if (cudaLaunchKernelEx(&cfg, kernel, mk, mv, args) != cudaSuccess) {
         return checkLaunch("pagedDecodeStreamKernel");
     }
-    const long long pairs = static_cast<long long>(args.p.num_seqs) * args.p.num_heads;
-    cfg.gridDim = dim3(static_cast<unsigned>((pairs + 3) / 4));
-    cfg.blockDim = dim3(128);
+    cfg.gridDim = dim3(plan.num_workers);
+    cfg.blockDim = dim3(CombineShape<HD>::kWarps * 32);
     cfg.dynamicSmemBytes = 0;
     if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, HD>, args) != cudaSuccess) {
         return checkLaunch("pagedDecodeCombineKernel");
@@ -1035,6 +1106,7 @@ infiniStatus_t launchDecodeStream(const Info &I, const StreamPlan &plan, const D
     a.header = reinterpret_cast<PlanHeader *>(ws + L.header_off);
     a.prefix = reinterpret_cast<long long *>(ws + L.prefix_off);
     a.range_start = reinterpret_cast<int4 *>(ws + L.range_off);
+    a.tasks = reinterpret_cast<int4 *>(ws + L.task_off);
     a.partials = reinterpret_cast<float *>(ws + L.partial_off);
     a.head_tiles = plan.head_tiles_per_group;
     a.units_per_seq = static_cast<int>(I.num_kv_heads) * plan.head_tiles_per_group;
