@@ -1,0 +1,64 @@
+"""Times this library's paged attention against the reference's own kernels (oracle/_ref, built
+by oracle/build_ref.py) on the benchmark configurations, each in a child process.  Prints one
+JSON line per (configuration, library, environment).
+
+    python tests/compare_reference_kernels.py [c2 c3 c4]
+"""
+import json
+import os
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+REF_ROOT = ROOT / "oracle" / "_ref"
+
+SPECS = {
+    "c2": {"builder": "config2_llama8b", "kwargs": {"device": "cuda"}},
+    "c3": {"builder": "config3_ragged72b", "kwargs": {"device": "cuda"}},
+    "c4": {"builder": "config4_longctx", "kwargs": {"device": "cuda"}},
+}
+
+
+def run(spec, env_extra, reference):
+    env = dict(os.environ)
+    env.pop("INFINI_ROOT", None)
+    if reference:
+        env["INFINI_ROOT"] = str(REF_ROOT)
+    env.update(env_extra)
+    with tempfile.TemporaryDirectory() as tmp:
+        out = Path(tmp) / "o.pt"
+        res = subprocess.run([sys.executable, str(ROOT / "tests" / "ref_runner.py"), json.dumps(spec), str(out)],
+                             env=env, capture_output=True, text=True, timeout=900)
+        if res.returncode != 0:
+            return {"error": (res.stdout + res.stderr)[-500:]}
+        return torch.load(out)
+
+
+def main():
+    names = sys.argv[1:] or ["c2", "c3", "c4"]
+    for name in names:
+        spec = dict(SPECS[name], iters=30, caching=False)
+        runs = [("this library", False, {}),
+                ("reference kernels, default (split-KV CTA, 4 splits)", True, {}),
+                ("reference kernels, INFINIOP_FLASH_DECODE_SPLITKV=0", True, {"INFINIOP_FLASH_DECODE_SPLITKV": "0"})]
+        base = None
+        for label, reference, env in runs:
+            r = run(spec, env, reference)
+            line = {"config": name, "library": label}
+            if "error" in r:
+                line["error"] = r["error"]
+            else:
+                line.update(attn_ms=r["attn_ms"], kv_GBps=r["kv_bytes"] / r["attn_ms"] / 1e6, workspace_bytes=r["workspace"])
+                if base is None:
+                    base = r["out"].float()
+                else:
+                    line["max_abs_diff_vs_this_library"] = float((r["out"].float() - base).abs().max())
+            print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,69 @@
+"""Runs one decode step (paged_caching, then paged_attention) through the C ABI of whichever
+libinfiniop the loader finds, in a process of its own.
+
+Used with INFINI_ROOT=oracle/_ref (the reference's own CUDA sources compiled for sm_100a by
+oracle/build_ref.py) to obtain the REFERENCE KERNELS' results and timings on identical seeded
+inputs, without ever loading both libraries into one process (they export the same symbols).
+
+    INFINI_ROOT=... python tests/ref_runner.py '<json spec>' out.pt
+
+spec = {"builder": "<function in infinicore_b200.workloads>", "kwargs": {...}, "iters": N}
+The inputs are rebuilt from the spec (seeded), so nothing large crosses the process boundary.
+"""
+import json
+import statistics
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+
+def main():
+    spec = json.loads(sys.argv[1])
+    out_path = sys.argv[2]
+    from infinicore_b200 import workloads
+    from infinicore_b200.libinfiniop import LIBINFINIOP, check_error, library_paths
+
+    import abi
+
+    kwargs = dict(spec.get("kwargs", {}))
+    if "dtype" in kwargs:
+        kwargs["dtype"] = getattr(torch, kwargs["dtype"])
+    case = getattr(workloads, spec["builder"])(**kwargs)
+    d = case.to("cuda")
+    out = torch.zeros((d.num_seqs, d.num_heads, d.v_cache.shape[3]), dtype=d.dtype, device="cuda")
+    if spec.get("caching", True):
+        abi.paged_caching(d.k_cache, d.v_cache, d.new_k, d.new_v, d.slot_mapping)
+    op = abi.AttentionOp(out, d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, None, d.scale)
+    check_error(op.status)
+    check_error(op.run(out, d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens))
+    torch.cuda.synchronize()
+    result = {"out": out.cpu(), "library": str(library_paths()[1]), "workspace": op.workspace_size}
+    if spec.get("return_cache", False):
+        result["k_cache"] = d.k_cache.cpu()
+        result["v_cache"] = d.v_cache.cpu()
+
+    iters = int(spec.get("iters", 0))
+    if iters:
+        stream = torch.cuda.current_stream().cuda_stream
+        for _ in range(5):
+            check_error(op.run(out, d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, stream=stream))
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            check_error(op.run(out, d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, stream=stream))
+        b.record()
+        torch.cuda.synchronize()
+        result["attn_ms"] = a.elapsed_time(b) / iters
+        result["kv_bytes"] = case.kv_bytes
+    op.destroy()
+    torch.save(result, out_path)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,57 @@
+"""GPU parity against the REFERENCE'S OWN KERNELS: the reference's CUDA sources for this path,
+compiled for sm_100a into oracle/_ref by oracle/build_ref.py, run in a child process on the same
+seeded inputs as this library.  paged_caching must agree bit for bit; attention within the path's
+tolerance (fp16 2e-3 / 2e-3, bf16 1e-2 / 1e-2).  Skipped when oracle/_ref was not built."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from helpers import ATTN_TOL, assert_close
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+REF_ROOT = ROOT / "oracle" / "_ref"
+
+
+def run(spec, tmp_path, reference: bool):
+    env = dict(os.environ)
+    env.pop("INFINI_ROOT", None)
+    if reference:
+        env["INFINI_ROOT"] = str(REF_ROOT)
+    out = tmp_path / ("ref.pt" if reference else "mine.pt")
+    res = subprocess.run([sys.executable, str(ROOT / "tests" / "ref_runner.py"), json.dumps(spec), str(out)],
+                         env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    return torch.load(out)
+
+
+SPECS = [
+    {"builder": "config1_small", "kwargs": {"seed": 1, "device": "cpu"}},
+    {"builder": "build_case", "kwargs": {"name": "gqa4", "dtype": "bfloat16", "seq_lens": [300, 17, 1, 160, 1000], "num_heads": 32,
+                                          "num_kv_heads": 8, "head_size": 128, "block_size": 16, "seed": 51}},
+    {"builder": "build_case", "kwargs": {"name": "gqa8", "dtype": "float16", "seq_lens": [64, 333, 16, 15, 2047], "num_heads": 64,
+                                          "num_kv_heads": 8, "head_size": 128, "block_size": 16, "seed": 52, "std": 0.5}},
+    {"builder": "build_case", "kwargs": {"name": "mha64", "dtype": "float16", "seq_lens": [77, 500], "num_heads": 8,
+                                          "num_kv_heads": 8, "head_size": 64, "block_size": 16, "seed": 53}},
+    {"builder": "config2_llama8b", "kwargs": {"seed": 2, "device": "cuda", "num_seqs": 16}},
+]
+
+
+@pytest.mark.skipif(not (REF_ROOT / "lib" / "libinfiniop.so").is_file(), reason="oracle/_ref not built")
+@pytest.mark.parametrize("spec", SPECS, ids=lambda s: s["kwargs"].get("name", s["builder"]))
+def test_same_inputs_same_results_as_the_reference_kernels(spec, tmp_path):
+    spec = dict(spec, return_cache=spec["builder"] != "config2_llama8b")
+    ref = run(spec, tmp_path, reference=True)
+    mine = run(spec, tmp_path, reference=False)
+    assert "oracle/_ref" in ref["library"] and "oracle/_ref" not in mine["library"]
+    if spec["return_cache"]:
+        assert torch.equal(ref["k_cache"].view(torch.int16), mine["k_cache"].view(torch.int16)), "paged_caching differs"
+        assert torch.equal(ref["v_cache"].view(torch.int16), mine["v_cache"].view(torch.int16)), "paged_caching differs"
+    atol, rtol = ATTN_TOL[ref["out"].dtype]
+    assert_close(mine["out"].float().numpy(), ref["out"].float().numpy(), atol, rtol, "vs reference kernels")
