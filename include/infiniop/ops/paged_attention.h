@@ -59,6 +59,28 @@ __INFINI_C __export infiniStatus_t infiniopPagedAttention(
     const void *alibi_slopes,
     void *stream);
 
+/*
+ * No counterpart in the reference.  Same operation as infiniopPagedAttention, for callers that
+ * cannot provide a workspace because they cannot allocate device memory (all of HBM already given
+ * to the KV pool, a frozen allocator, a host framework that owns every buffer): the scratch is a
+ * 16 MiB array inside this library (INFINIOP_PAGED_ATTENTION_STATIC_WORKSPACE_BYTES), resident on
+ * every GPU that loads the library.  Descriptors that need more are refused with
+ * INFINI_STATUS_INSUFFICIENT_WORKSPACE.  The first call on a device resolves the array's address
+ * and should be made before any stream capture.  All calls on a device share the array: calls that
+ * overlap on the GPU race.  Allocates nothing.
+ */
+#define INFINIOP_PAGED_ATTENTION_STATIC_WORKSPACE_BYTES (16u << 20)
+__INFINI_C __export infiniStatus_t infiniopPagedAttentionStaticWorkspace(
+    infiniopPagedAttentionDescriptor_t desc,
+    void *out,
+    const void *q,
+    const void *k_cache,
+    const void *v_cache,
+    const void *block_tables,
+    const void *seq_lens,
+    const void *alibi_slopes,
+    void *stream);
+
 /* reference include/infiniop/ops/paged_attention.h:90-91 */
 __INFINI_C __export infiniStatus_t infiniopDestroyPagedAttentionDescriptor(
     infiniopPagedAttentionDescriptor_t desc);

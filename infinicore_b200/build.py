@@ -44,6 +44,7 @@ OP_SOURCES = [
     "paged_attention/operator.cu",
     "paged_attention/decode_generic.cu",
     "paged_attention/decode_stream.cu",
+    "paged_attention/static_workspace.cu",
 ]
 
 

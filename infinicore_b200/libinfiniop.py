@@ -82,7 +82,7 @@ INFINIOP_SYMBOLS = [
     "infiniopCreateTensorDescriptor", "infiniopDestroyTensorDescriptor",
     "infiniopGetDescriptorDeviceType", "infiniopGetDescriptorDeviceId",
     "infiniopCreatePagedAttentionDescriptor", "infiniopGetPagedAttentionWorkspaceSize",
-    "infiniopPagedAttention", "infiniopDestroyPagedAttentionDescriptor",
+    "infiniopPagedAttention", "infiniopPagedAttentionStaticWorkspace", "infiniopDestroyPagedAttentionDescriptor",
     "infiniopCreatePagedCachingDescriptor", "infiniopGetPagedCachingWorkspaceSize",
     "infiniopPagedCaching", "infiniopDestroyPagedCachingDescriptor",
 ]
@@ -159,6 +159,15 @@ def _bind(lib: InfiniLib) -> None:
         infiniopOperatorDescriptor_t, c_void_p, c_size_t,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
     ]
+    # No reference counterpart: same call without workspace arguments (scratch lives inside the
+    # library).  Bound only where present, so this binding can also drive a build of the reference's
+    # own library (which the parity tests do through $INFINI_ROOT).
+    if hasattr(op, "infiniopPagedAttentionStaticWorkspace"):
+        op.infiniopPagedAttentionStaticWorkspace.restype = c_int32
+        op.infiniopPagedAttentionStaticWorkspace.argtypes = [
+            infiniopOperatorDescriptor_t,
+            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        ]
     op.infiniopDestroyPagedAttentionDescriptor.restype = c_int32
     op.infiniopDestroyPagedAttentionDescriptor.argtypes = [infiniopOperatorDescriptor_t]
 
