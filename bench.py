@@ -48,6 +48,9 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--mode", default="seq", choices=["seq", "head"],
+                    help="seq: shard by sequence, no collective (default); head: optional KV-head-sharded mode, "
+                         "every rank holds all sequences for its kv-heads and outputs are all-gathered over NCCL")
     ap.add_argument("--cpu-seqs", type=int, default=0, help="sequences in the CPU sample (0 = the whole batch)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-clocks", action="store_true", help="skip nvidia-smi sampling (for short runs under a profiler)")
@@ -64,7 +67,7 @@ def measured_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
-def workload_config(name, case, n_gpus):
+def workload_config(name, case, n_gpus, mode="seq"):
     return {
         "workload": {
             "c2": "configs[1]: Llama-3-8B-shape decode, bf16, batch 64 per GPU, 32/8 heads, head 128, block 16, every seq_len 4096, "
@@ -76,13 +79,26 @@ def workload_config(name, case, n_gpus):
         "num_seqs_per_gpu": case.num_seqs,
         "tokens_per_gpu": case.total_tokens,
         "kv_bytes_per_gpu": case.kv_bytes,
-        "parallelism": f"sequence-sharded x{n_gpus}, no collective",
+        "parallelism": (f"kv-head-sharded x{n_gpus}, one NCCL all-gather of the outputs per step" if mode == "head" and n_gpus > 1
+                        else f"sequence-sharded x{n_gpus}, no collective"),
         "l2": "inputs larger than L2 (KV working set per step >> 126 MB)" if case.kv_bytes > (256 << 20) else "L2 flushed between steps",
     }
 
 
-def make_case(name, rank, world, device):
+def make_case(name, rank, world, device, mode="seq"):
+    import torch
+
     from infinicore_b200 import workloads
+
+    if mode == "head" and world > 1:
+        # every rank: all sequences, its slice of the kv-heads (and of the q-heads that read them)
+        heads, kvh = (32, 8) if name in ("c2", "c4") else (64, 8)
+        lens = {"c2": lambda: torch.full((64,), 4096), "c3": workloads.config3_lengths,
+                "c4": lambda: torch.full((2,), 131072), "c5": workloads.config5_lengths}[name]()
+        assert kvh % world == 0, "kv-heads must divide over the ranks"
+        return workloads.build_case(f"{name}_headshard{rank}of{world}", dtype=torch.float16 if name == "c4" else torch.bfloat16,
+                                    seq_lens=lens, num_heads=heads // world, num_kv_heads=kvh // world, head_size=128,
+                                    block_size=16, seed=7, device=device)
 
     if name == "c2":
         return workloads.config2_llama8b(seed=2 + rank, device=device)
@@ -290,7 +306,10 @@ def gpu_arm(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+
+        # a short collective timeout: a rank mismatch should fail in a minute, not hold the GPUs
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=90))
 
     def barrier():
         if world > 1:
@@ -311,16 +330,25 @@ def gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
 
-    case = make_case(args.workload, rank, world, device)
+    head_mode = args.mode == "head" and world > 1
+    case = make_case(args.workload, rank, world, device, args.mode)
     step = AbiStep(case)
     stream = torch.cuda.current_stream(device)
     sptr = stream.cuda_stream
     small_ws = case.kv_bytes <= (256 << 20)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device) if small_ws else None
 
+    gather_staging = None
+    if head_mode:
+        from infinicore_b200 import sharding
+
+        gather_staging = torch.empty((world, *step.out.shape), dtype=step.out.dtype, device=device)
+
     def one_step():
         step.caching(sptr)
         step.attention(sptr)
+        if head_mode:
+            sharding.gather_head_sharded(step.out, world, staging=gather_staging)
 
     # ---- device-resident timing -------------------------------------------------------------
     for _ in range(max(args.warmup, 3)):
@@ -354,16 +382,17 @@ def gpu_arm(args):
             flush.fill_(i & 0xff)
             total_ms += timed(one_step, 1)
         flush_ms = 0.0
+    ms_per_step = max_over_ranks((total_ms - flush_ms) / K)
     clock_window = "timed region"
-    if sample_clocks and total_ms < 400.0:
+    if not args.no_clocks and ms_per_step * K < 400.0:
         # Too short for nvidia-smi's 100 ms sampling: keep the identical load running (untimed) so the
-        # clocks under this load are still observed.
-        extra = int(600.0 / max(total_ms / K, 1e-3))
+        # clocks under this load are still observed.  Every rank runs the same number of extra steps
+        # (the count derives from the rank-agreed step time), because a step may contain a collective.
+        extra = int(600.0 / max(ms_per_step, 1e-3))
         for _ in range(extra):
             one_step()
         torch.cuda.synchronize()
-        clock_window = f"timed region ({total_ms:.1f} ms) + {extra} identical untimed steps"
-    ms_per_step = max_over_ranks((total_ms - flush_ms) / K)
+        clock_window = f"timed region ({ms_per_step * K:.1f} ms) + {extra} identical untimed steps"
     clocks = sampler.stop() if sample_clocks else None
     if clocks is not None:
         clocks["window"] = clock_window
@@ -377,35 +406,32 @@ def gpu_arm(args):
     value = kv_bytes_all / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end through the public Python API, host buffers in and out ---------------------
-    # One pinned host arena and one device arena with the same layout: the step's inputs travel in a
-    # single host->device copy; the operators see views into the device arena.
-    names = ("q", "new_k", "new_v", "slot_mapping", "block_tables", "seq_lens")
-    offsets, cursor = {}, 0
-    for k in names:
-        t = getattr(case, k)
-        offsets[k] = cursor
-        cursor += (t.numel() * t.element_size() + 255) // 256 * 256
-    host_arena = torch.empty(cursor, dtype=torch.uint8).pin_memory()
-    dev_arena = torch.empty(cursor, dtype=torch.uint8, device=device)
-
-    def view(arena, k):
-        t = getattr(case, k)
-        n = t.numel() * t.element_size()
-        return arena[offsets[k]:offsets[k] + n].view(t.dtype).view(t.shape)
-
-    for k in names:
-        view(host_arena, k).copy_(getattr(case, k).cpu())
-    dev_in = {k: view(dev_arena, k) for k in names}
-    host_out = torch.empty(step.out.shape, dtype=step.out.dtype).pin_memory()
-    h2d = cursor
-    d2h = host_out.numel() * host_out.element_size()
+    # The public call for a whole step: DecodeStep keeps one pinned host arena (q, new K/V rows, slots,
+    # block tables, lengths), copies it to the device in one transfer, runs caching + attention and
+    # copies the output back, all replayed from one CUDA graph.
+    estep = ib.DecodeStep(case.k_cache, case.v_cache, num_seqs=case.num_seqs, num_heads=case.num_heads,
+                          max_blocks_per_seq=case.block_tables.shape[1], scale=case.scale)
+    for k in ("q", "new_k", "new_v", "slot_mapping", "block_tables", "seq_lens"):
+        estep.host[k].copy_(getattr(case, k).cpu())
+    estep.capture()
+    h2d, d2h = estep.h2d_bytes, estep.d2h_bytes
 
     def e2e_step():
-        dev_arena.copy_(host_arena, non_blocking=True)
-        ib.paged_caching(case.k_cache, case.v_cache, dev_in["new_k"], dev_in["new_v"], dev_in["slot_mapping"])
-        out = ib.paged_attention(dev_in["q"], case.k_cache, case.v_cache, dev_in["block_tables"], dev_in["seq_lens"], None, case.scale)
-        host_out.copy_(out, non_blocking=True)
-        stream.synchronize()  # the host reads the step's result before it issues the next step
+        estep.run(sync=True)  # the host reads the step's result before it issues the next step
+
+    if head_mode:
+        # NCCL inside the step: issue the calls directly instead of replaying a graph
+        host_full = torch.empty((case.num_seqs, case.num_heads * world, step.out.shape[2]), dtype=step.out.dtype).pin_memory()
+        d2h = host_full.numel() * host_full.element_size()
+
+        def e2e_step():  # noqa: F811
+            estep._dev_arena.copy_(estep._host_arena, non_blocking=True)
+            ib.paged_caching(case.k_cache, case.v_cache, estep.dev["new_k"], estep.dev["new_v"], estep.dev["slot_mapping"])
+            o = ib.paged_attention(estep.dev["q"], case.k_cache, case.v_cache, estep.dev["block_tables"], estep.dev["seq_lens"],
+                                   None, case.scale, out=estep.out)
+            full = sharding.gather_head_sharded(o, world, staging=gather_staging)
+            host_full.copy_(full, non_blocking=True)
+            stream.synchronize()
 
     for _ in range(3):
         e2e_step()
@@ -434,7 +460,7 @@ def gpu_arm(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if args.workload == "c5" else "weak",
             "vs_baseline": None, "dtype": "f16" if case.dtype == torch.float16 else "bf16", "data": "synthetic",
-            "config": workload_config(args.workload, case, world),
+            "config": workload_config(args.workload, case, world, args.mode),
             "seqs_per_s": seqs_all / (ms_per_step * 1e-3),
             "frac_of_hbm_peak": value / (peak * world),
             "roofline": {

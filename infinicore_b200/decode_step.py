@@ -1,0 +1,95 @@
+"""A whole decode step as one replayable CUDA graph.
+
+The reference's infinicore layer records operators and replays them as CUDA graphs
+(src/infinicore/graph/graph.cc:97-171: warm up, capture the capture-safe segment, replay).  This is
+the same idea for the one segment this library owns: copy the step's small inputs from pinned host
+memory, scatter the new K/V rows into the paged pools (paged_caching), attend (paged_attention),
+copy the output back.  Capturing it once removes the per-step host work of five API calls; the
+operators themselves allocate nothing and never synchronise, which is what makes them capturable.
+
+    step = DecodeStep(k_cache, v_cache, num_seqs=64, num_heads=32, max_blocks_per_seq=256, scale=s)
+    step.host["q"][...] = ...            # fill the pinned inputs: q, new_k, new_v, slot_mapping,
+    out = step.run()                     #   block_tables, seq_lens; run() returns the pinned output
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+_INPUTS = ("q", "new_k", "new_v", "slot_mapping", "block_tables", "seq_lens")
+
+
+class DecodeStep:
+    def __init__(self, k_cache: torch.Tensor, v_cache: torch.Tensor, *, num_seqs: int, num_heads: int,
+                 max_blocks_per_seq: int, scale: float, index_dtype: torch.dtype = torch.int64,
+                 alibi_slopes: torch.Tensor | None = None):
+        if not (k_cache.is_cuda and v_cache.is_cuda):
+            raise RuntimeError("DecodeStep needs the cache pools on a GPU; there is no CPU fallback")
+        self.k_cache, self.v_cache = k_cache, v_cache
+        self.scale = float(scale)
+        self.alibi = alibi_slopes
+        self.device = k_cache.device
+        _, kvh, _, hd = k_cache.shape
+        vd = v_cache.shape[3]
+        dt = k_cache.dtype
+        layout = {
+            "q": ((num_seqs, num_heads, hd), dt),
+            "new_k": ((num_seqs, kvh, hd), dt),
+            "new_v": ((num_seqs, kvh, vd), dt),
+            "slot_mapping": ((num_seqs,), torch.int64),
+            "block_tables": ((num_seqs, max_blocks_per_seq), index_dtype),
+            "seq_lens": ((num_seqs,), index_dtype),
+        }
+        offsets, cursor = {}, 0
+        for name in _INPUTS:
+            shape, dtype = layout[name]
+            nbytes = torch.empty((), dtype=dtype).element_size()
+            for s in shape:
+                nbytes *= s
+            offsets[name] = (cursor, nbytes, shape, dtype)
+            cursor += (nbytes + 255) // 256 * 256
+        self.h2d_bytes = cursor
+        self._host_arena = torch.empty(cursor, dtype=torch.uint8).pin_memory()
+        self._dev_arena = torch.empty(cursor, dtype=torch.uint8, device=self.device)
+
+        def views(arena):
+            return {n: arena[o:o + b].view(d).view(s) for n, (o, b, s, d) in offsets.items()}
+
+        self.host = views(self._host_arena)   # fill these before run()
+        self.dev = views(self._dev_arena)
+        self.out = torch.empty((num_seqs, num_heads, vd), dtype=dt, device=self.device)
+        self.host_out = torch.empty((num_seqs, num_heads, vd), dtype=dt).pin_memory()
+        self.d2h_bytes = self.host_out.numel() * self.host_out.element_size()
+        self._graph = None
+        self._stream = torch.cuda.Stream(device=self.device)
+
+    def _issue(self):
+        self._dev_arena.copy_(self._host_arena, non_blocking=True)
+        ops.paged_caching(self.k_cache, self.v_cache, self.dev["new_k"], self.dev["new_v"], self.dev["slot_mapping"])
+        ops.paged_attention(self.dev["q"], self.k_cache, self.v_cache, self.dev["block_tables"], self.dev["seq_lens"],
+                            self.alibi, self.scale, out=self.out)
+        self.host_out.copy_(self.out, non_blocking=True)
+
+    def capture(self):
+        """Warm up (creates descriptors and the workspace outside the capture), then record the step."""
+        with torch.cuda.stream(self._stream):
+            for _ in range(3):
+                self._issue()
+            self._stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=self._stream):
+                self._issue()
+        self._graph = graph
+        return self
+
+    def run(self, sync: bool = True) -> torch.Tensor:
+        """Replays the captured step with whatever the pinned inputs hold now; returns the pinned
+        output (valid once the replay has completed - immediately when sync=True)."""
+        if self._graph is None:
+            self.capture()
+        self._graph.replay()
+        if sync:
+            # replay() enqueues on the current stream
+            torch.cuda.current_stream(self.device).synchronize()
+        return self.host_out

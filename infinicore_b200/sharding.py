@@ -49,3 +49,34 @@ def kv_bytes(seq_lens: Sequence[int], num_kv_heads: int, head_size: int, value_s
 def job_throughput(bytes_per_rank: Sequence[float], ms_per_rank: Sequence[float]) -> float:
     """GB/s of the whole job: all ranks' bytes over the slowest rank's time."""
     return sum(bytes_per_rank) / (max(ms_per_rank) * 1e-3) / 1e9
+
+
+# ---- optional KV-head-sharded mode -------------------------------------------------------------
+# Rank r holds kv-heads [r * kvh / world, (r + 1) * kvh / world) of EVERY sequence and the q-heads
+# that read them; its attention output is [num_seqs, num_heads / world, head_size].  The only
+# exchange on the path is one all-gather of those outputs (reference collective:
+# infinicclAllGather -> ncclAllGather, src/infiniccl/cuda/infiniccl_cuda.cu:219-234).
+
+def head_slices(num_heads: int, num_kv_heads: int, rank: int, world: int):
+    """(q-head slice, kv-head slice) owned by `rank`."""
+    if num_kv_heads % world != 0:
+        raise ValueError(f"{num_kv_heads} kv-heads do not divide over {world} ranks")
+    group = num_heads // num_kv_heads
+    per = num_kv_heads // world
+    return slice(rank * per * group, (rank + 1) * per * group), slice(rank * per, (rank + 1) * per)
+
+
+def gather_head_sharded(out_local, world: int, group=None, staging=None):
+    """All-gathers per-rank outputs [num_seqs, heads_per_rank, d] into [num_seqs, heads, d].
+
+    NCCL concatenates rank-major, so the gathered buffer is [world, num_seqs, heads_per_rank, d]; the
+    head order of the full tensor is restored with a permuted view (no extra copy is made here; a
+    consumer that needs contiguity pays one).  `staging` may hold a preallocated gather buffer."""
+    import torch
+    import torch.distributed as dist
+
+    num_seqs, hpr, d = out_local.shape
+    if staging is None:
+        staging = torch.empty((world, num_seqs, hpr, d), dtype=out_local.dtype, device=out_local.device)
+    dist.all_gather_into_tensor(staging.view(-1), out_local.contiguous().view(-1), group=group)
+    return staging.permute(1, 0, 2, 3).reshape(num_seqs, world * hpr, d)

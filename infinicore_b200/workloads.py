@@ -136,10 +136,15 @@ def config2_llama8b(seed=2, device="cuda", num_seqs=64, seq_len=4096) -> DecodeC
                       head_size=128, block_size=16, num_blocks=num_seqs * ((seq_len + 15) // 16), seed=seed, device=device)
 
 
+def config3_lengths(seed=3, num_seqs=256, lo=16, hi=32768) -> torch.Tensor:
+    """Log-uniform sequence lengths of the ragged configuration."""
+    u = torch.rand(num_seqs, generator=_cpu_gen(seed))
+    return torch.exp(math.log(lo) + u * (math.log(hi) - math.log(lo))).round().to(torch.int64).clamp(lo, hi)
+
+
 def config3_ragged72b(seed=3, device="cuda", num_seqs=256, lo=16, hi=32768) -> DecodeCase:
     """bf16, batch 256, 64/8 heads, head 128, lengths log-uniform in [16, 32768], N(0, 0.5) data."""
-    u = torch.rand(num_seqs, generator=_cpu_gen(seed))
-    lens = torch.exp(math.log(lo) + u * (math.log(hi) - math.log(lo))).round().to(torch.int64).clamp(lo, hi)
+    lens = config3_lengths(seed, num_seqs, lo, hi)
     return build_case("c3_ragged_72b_bf16", dtype=torch.bfloat16, seq_lens=lens, num_heads=64, num_kv_heads=8,
                       head_size=128, block_size=16, max_blocks_per_seq=(hi + 15) // 16, std=0.5, seed=seed,
                       device=device, slack_blocks=64)

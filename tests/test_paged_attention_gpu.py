@@ -447,3 +447,32 @@ def test_python_operators_match_the_abi_path(abi):
     want = oracle.paged_attention(torch_to_bits(c.q), kb, vb, c.block_tables.numpy(), c.seq_lens.numpy(), c.scale, 12)
     check(c, got, want)
     assert torch.equal(got, again)
+
+
+def test_decode_step_graph_replay_matches_direct_calls(abi):
+    """infinicore_b200.DecodeStep: host inputs -> H2D -> caching -> attention -> D2H captured once and
+    replayed; two replays with different inputs, each checked against the oracle."""
+    import infinicore_b200 as ib
+
+    base = workloads.build_case("step", dtype=torch.bfloat16, seq_lens=[100, 37, 64, 5, 900, 16], num_heads=32, num_kv_heads=8,
+                                head_size=128, block_size=16, seed=61)
+    d = base.to("cuda")
+    step = ib.DecodeStep(d.k_cache, d.v_cache, num_seqs=6, num_heads=32, max_blocks_per_seq=base.block_tables.shape[1],
+                         scale=base.scale)
+    kb, vb = torch_to_bits(base.k_cache).copy(), torch_to_bits(base.v_cache).copy()
+    g = torch.Generator().manual_seed(62)
+    for round_ in range(2):
+        q = torch.randn(base.q.shape, generator=g).to(torch.bfloat16)
+        nk = torch.randn(base.new_k.shape, generator=g).to(torch.bfloat16)
+        nv = torch.randn(base.new_v.shape, generator=g).to(torch.bfloat16)
+        step.host["q"].copy_(q)
+        step.host["new_k"].copy_(nk)
+        step.host["new_v"].copy_(nv)
+        step.host["slot_mapping"].copy_(base.slot_mapping)
+        step.host["block_tables"].copy_(base.block_tables)
+        step.host["seq_lens"].copy_(base.seq_lens)
+        got = step.run().clone()
+        oracle.paged_caching(kb, vb, torch_to_bits(nk), torch_to_bits(nv), base.slot_mapping.numpy())
+        want = oracle.paged_attention(torch_to_bits(q), kb, vb, base.block_tables.numpy(), base.seq_lens.numpy(), base.scale, 19)
+        check(base, got, want)
+        assert np.array_equal(torch_to_bits(d.k_cache), kb), f"round {round_}: pools differ"

@@ -105,3 +105,53 @@ def test_a_rank_that_dies_before_the_step_is_reported_by_the_parent():
 
 def _dies():
     raise SystemExit(3)
+
+
+# ---- optional KV-head-sharded mode: slices + all-gather reproduce the unsharded result ----------
+
+def _head_worker(rank, world, port, out):
+    import numpy as np
+
+    import oracle
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        c = workloads.build_case("hs", dtype=torch.float16, seq_lens=[40, 7, 129], num_heads=8, num_kv_heads=4,
+                                 head_size=64, block_size=16, seed=81)  # same seed: every rank sees the same full problem
+
+        def bits(t):
+            return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+        qs, ks = sharding.head_slices(8, 4, rank, world)
+        local = oracle.paged_attention(bits(c.q[:, qs]), bits(c.k_cache[:, ks]), bits(c.v_cache[:, ks]),
+                                       c.block_tables.numpy(), c.seq_lens.numpy(), c.scale, 12)
+        full = sharding.gather_head_sharded(torch.from_numpy(local), world)
+        if rank == 0:
+            want = oracle.paged_attention(bits(c.q), bits(c.k_cache), bits(c.v_cache), c.block_tables.numpy(),
+                                          c.seq_lens.numpy(), c.scale, 12)
+            out.put(bool(np.array_equal(full.numpy(), want)))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_head_sharded_outputs_all_gather_to_the_unsharded_result():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_head_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    assert out.get(timeout=180) is True
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+
+
+def test_head_slices():
+    assert sharding.head_slices(64, 8, 3, 8) == (slice(24, 32), slice(3, 4))
+    assert sharding.head_slices(32, 8, 1, 2) == (slice(16, 32), slice(4, 8))
+    with pytest.raises(ValueError):
+        sharding.head_slices(32, 8, 0, 3)
