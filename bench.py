@@ -38,7 +38,7 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one pagedDecodeStreamKernel launch, from the ncu
 # capture summarised under profiles/ (None until a capture exists for that workload).
-NCU_TRAFFIC_BYTES = {"c2": None}
+NCU_TRAFFIC_BYTES = {"c2": 1074814000 + 5161000}  # profiles/pagedDecodeStreamKernel_c2.md, launch 1
 
 
 def parse_args():
@@ -458,7 +458,7 @@ def gpu_arm(args):
         achieved = case.kv_bytes / (attn_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if args.workload == "c5" else "weak",
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if (args.workload == "c5" or head_mode) else "weak",
             "vs_baseline": None, "dtype": "f16" if case.dtype == torch.float16 else "bf16", "data": "synthetic",
             "config": workload_config(args.workload, case, world, args.mode),
             "seqs_per_s": seqs_all / (ms_per_step * 1e-3),

@@ -14,6 +14,7 @@ _LAZY = {
     "library_paths": "libinfiniop",
     "paged_attention": "ops",
     "paged_caching": "ops",
+    "paged_attention_prefill": "ops",
     "DecodeStep": "decode_step",
 }
 

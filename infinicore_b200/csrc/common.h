@@ -88,6 +88,7 @@ inline size_t dtypeSize(infiniDtype_t dt) {
 enum class OpKind : int {
     PagedAttention = 1,
     PagedCaching = 2,
+    PagedAttentionPrefill = 3,
 };
 
 struct OpDescriptorBase {

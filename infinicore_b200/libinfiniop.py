@@ -83,6 +83,8 @@ INFINIOP_SYMBOLS = [
     "infiniopGetDescriptorDeviceType", "infiniopGetDescriptorDeviceId",
     "infiniopCreatePagedAttentionDescriptor", "infiniopGetPagedAttentionWorkspaceSize",
     "infiniopPagedAttention", "infiniopPagedAttentionStaticWorkspace", "infiniopDestroyPagedAttentionDescriptor",
+    "infiniopCreatePagedAttentionPrefillDescriptor", "infiniopGetPagedAttentionPrefillWorkspaceSize",
+    "infiniopPagedAttentionPrefill", "infiniopDestroyPagedAttentionPrefillDescriptor",
     "infiniopCreatePagedCachingDescriptor", "infiniopGetPagedCachingWorkspaceSize",
     "infiniopPagedCaching", "infiniopDestroyPagedCachingDescriptor",
 ]
@@ -170,6 +172,24 @@ def _bind(lib: InfiniLib) -> None:
         ]
     op.infiniopDestroyPagedAttentionDescriptor.restype = c_int32
     op.infiniopDestroyPagedAttentionDescriptor.argtypes = [infiniopOperatorDescriptor_t]
+
+    # reference test/infiniop/libinfiniop/op_register.py:2272-2320
+    if hasattr(op, "infiniopCreatePagedAttentionPrefillDescriptor"):
+        op.infiniopCreatePagedAttentionPrefillDescriptor.restype = c_int32
+        op.infiniopCreatePagedAttentionPrefillDescriptor.argtypes = [
+            infiniopHandle_t, POINTER(infiniopOperatorDescriptor_t),
+            infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t,
+            infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, c_void_p, c_float,
+        ]
+        op.infiniopGetPagedAttentionPrefillWorkspaceSize.restype = c_int32
+        op.infiniopGetPagedAttentionPrefillWorkspaceSize.argtypes = [infiniopOperatorDescriptor_t, POINTER(c_size_t)]
+        op.infiniopPagedAttentionPrefill.restype = c_int32
+        op.infiniopPagedAttentionPrefill.argtypes = [
+            infiniopOperatorDescriptor_t, c_void_p, c_size_t,
+            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        ]
+        op.infiniopDestroyPagedAttentionPrefillDescriptor.restype = c_int32
+        op.infiniopDestroyPagedAttentionPrefillDescriptor.argtypes = [infiniopOperatorDescriptor_t]
 
     # reference test/infiniop/libinfiniop/op_register.py:2231-2269
     op.infiniopCreatePagedCachingDescriptor.restype = c_int32

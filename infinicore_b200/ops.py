@@ -124,6 +124,44 @@ def paged_attention(q, k_cache, v_cache, block_tables, cache_lens, alibi_slopes=
     return out
 
 
+def paged_attention_prefill(q, k_cache, v_cache, block_tables, history_lens, cu_seqlens_q, alibi_slopes=None,
+                            scale: float = 1.0, *, out=None):
+    """Causal attention of packed new tokens q [total_q, num_heads, head_size] over each sequence's paged
+    KV cache (which already holds the new tokens).  `history_lens` [num_seqs] is the total KV length per
+    sequence, `cu_seqlens_q` [num_seqs + 1] the prefix sum of new-token counts; same argument order as
+    the reference's python/infinicore/ops/paged_attention_prefill.py:5-46."""
+    dev = _require_cuda(q, k_cache, v_cache, block_tables, history_lens, cu_seqlens_q, alibi_slopes, out)
+    if out is None:
+        out = torch.empty((*q.shape[:-1], v_cache.shape[3]), dtype=q.dtype, device=q.device)
+    st = _state(dev)
+    key = ("paged_attention_prefill", _meta(out), _meta(q), _meta(k_cache), _meta(v_cache), _meta(block_tables),
+           _meta(history_lens), _meta(cu_seqlens_q), _meta(alibi_slopes), float(scale))
+
+    def make():
+        tensors = [_desc(out), _desc(q), _desc(k_cache), _desc(v_cache), _desc(block_tables), _desc(history_lens), _desc(cu_seqlens_q)]
+        alibi = _desc(alibi_slopes) if alibi_slopes is not None else None
+        desc = infiniopOperatorDescriptor_t()
+        check_error(LIBINFINIOP.infiniopCreatePagedAttentionPrefillDescriptor(
+            st["handle"], ctypes.byref(desc), *[t.descriptor for t in tensors],
+            alibi.descriptor if alibi is not None else None, scale))
+        size = ctypes.c_size_t(0)
+        check_error(LIBINFINIOP.infiniopGetPagedAttentionPrefillWorkspaceSize(desc, ctypes.byref(size)))
+        for t in tensors + ([alibi] if alibi is not None else []):
+            t.destroy_desc()
+        return {"desc": desc, "workspace": size.value, "destroy": LIBINFINIOP.infiniopDestroyPagedAttentionPrefillDescriptor}
+
+    entry = _lookup(st, key, make)
+    ws = _workspace(st, entry["workspace"], dev)
+    with torch.cuda.device(dev):
+        check_error(LIBINFINIOP.infiniopPagedAttentionPrefill(
+            entry["desc"], ws.data_ptr() if ws is not None else None, entry["workspace"],
+            out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(),
+            history_lens.data_ptr(), cu_seqlens_q.data_ptr(),
+            alibi_slopes.data_ptr() if alibi_slopes is not None else None,
+            torch.cuda.current_stream(dev).cuda_stream))
+    return out
+
+
 def paged_caching(k_cache, v_cache, k, v, slot_mapping):
     """Scatters k/v rows [num_tokens, num_kv_heads, head_size] into the paged pools at
     slot_mapping (int64; negative = padding).  Returns (k_cache, v_cache)."""

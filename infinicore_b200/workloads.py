@@ -169,3 +169,65 @@ def config5_shard(rank=0, world=1, seed=5, device="cuda", num_seqs=2048) -> Deco
     return build_case(f"c5_shard{rank}of{world}_bf16", dtype=torch.bfloat16, seq_lens=lens, num_heads=64,
                       num_kv_heads=8, head_size=128, block_size=16, max_blocks_per_seq=8192 // 16,
                       seed=seed * 1000 + rank, device=device)
+
+
+# ---- prefill ------------------------------------------------------------------------------------
+
+@dataclass
+class PrefillCase:
+    name: str
+    dtype: torch.dtype
+    num_heads: int
+    num_kv_heads: int
+    head_size: int
+    block_size: int
+    scale: float
+    q: torch.Tensor               # [total_q, num_heads, head_size], packed over sequences
+    k_cache: torch.Tensor         # pools already hold every token, the new ones included
+    v_cache: torch.Tensor
+    block_tables: torch.Tensor    # [num_seqs, max_blocks_per_seq]
+    seq_lens: torch.Tensor        # [num_seqs] total KV length (cached + new)
+    cum_seq_lens_q: torch.Tensor  # [num_seqs + 1]
+
+    @property
+    def num_seqs(self) -> int:
+        return self.seq_lens.numel()
+
+    @property
+    def flops(self) -> int:
+        """2 * 2 * heads * head_size * (number of (query, key) pairs the causal mask keeps)."""
+        new = (self.cum_seq_lens_q[1:] - self.cum_seq_lens_q[:-1]).double()
+        total = self.seq_lens.double()
+        pairs = (new * (total - new) + new * (new + 1) / 2).sum().item()
+        return int(4 * self.num_heads * self.head_size * pairs)
+
+    def to(self, device) -> "PrefillCase":
+        moved = {k: (v.to(device) if isinstance(v, torch.Tensor) else v) for k, v in self.__dict__.items()}
+        return PrefillCase(**moved)
+
+
+def build_prefill_case(name, *, dtype, new_lens, cached_lens, num_heads, num_kv_heads, head_size, block_size,
+                       std=1.0, seed=0, device="cpu", value_size=None, index_dtype=torch.int64) -> PrefillCase:
+    """One prefill problem: sequence i has cached_lens[i] tokens in the cache and new_lens[i] new query
+    tokens (whose K/V are in the cache as well, as after paged_caching)."""
+    new_lens = torch.as_tensor(new_lens, dtype=torch.int64)
+    cached_lens = torch.as_tensor(cached_lens, dtype=torch.int64)
+    base = build_case(name, dtype=dtype, seq_lens=new_lens + cached_lens, num_heads=num_heads, num_kv_heads=num_kv_heads,
+                      head_size=head_size, block_size=block_size, std=std, seed=seed, device=device, value_size=value_size)
+    gen = torch.Generator(device=torch.device(device))
+    gen.manual_seed(seed + 17)
+    total_q = int(new_lens.sum())
+    q = _randn((total_q, num_heads, head_size), dtype, std, gen, torch.device(device))
+    cum = torch.zeros(new_lens.numel() + 1, dtype=torch.int64)
+    cum[1:] = torch.cumsum(new_lens, 0)
+    return PrefillCase(name=name, dtype=dtype, num_heads=num_heads, num_kv_heads=num_kv_heads, head_size=head_size,
+                       block_size=block_size, scale=base.scale, q=q, k_cache=base.k_cache, v_cache=base.v_cache,
+                       block_tables=base.block_tables.to(index_dtype), seq_lens=base.seq_lens.to(index_dtype),
+                       cum_seq_lens_q=cum.to(index_dtype).to(device))
+
+
+def prefill_llama8b(seed=6, device="cuda", num_seqs=8, new_len=2048, cached_len=0) -> PrefillCase:
+    """Llama-3-8B-shape prefill: bf16, 32/8 heads, head 128, block 16, `num_seqs` prompts of `new_len` tokens."""
+    return build_prefill_case("prefill_llama3_8b_bf16", dtype=torch.bfloat16, new_lens=[new_len] * num_seqs,
+                              cached_lens=[cached_len] * num_seqs, num_heads=32, num_kv_heads=8, head_size=128,
+                              block_size=16, seed=seed, device=device)

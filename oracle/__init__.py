@@ -34,6 +34,18 @@ def lib() -> ctypes.CDLL:
             c_float,
             c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
         ]
+        _lib.oracle_paged_attention_prefill.restype = c_int
+        _lib.oracle_paged_attention_prefill.argtypes = [
+            c_int, c_int, c_void_p,
+            c_void_p, c_ssize_t, c_ssize_t,
+            c_void_p, c_ssize_t, c_ssize_t, c_ssize_t,
+            c_void_p, c_ssize_t, c_ssize_t, c_ssize_t,
+            c_void_p, c_ssize_t,
+            c_void_p, c_void_p,
+            c_void_p,
+            c_float,
+            c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+        ]
         _lib.oracle_paged_caching.restype = c_int
         _lib.oracle_paged_caching.argtypes = [
             c_int64,
@@ -97,6 +109,42 @@ def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, scale, dtype, a
     )
     if rc != 0:
         raise ValueError(f"oracle_paged_attention rejected its input (code {rc})")
+    return out
+
+
+def paged_attention_prefill(q, k_cache, v_cache, block_tables, seq_lens, cum_seq_lens_q, scale, dtype,
+                            alibi_slopes=None, mode="exact", out=None) -> np.ndarray:
+    """q: uint16 [total_q, num_heads, head_size] packed over sequences.  Returns float64
+    [total_q, num_heads, value_size]; rows outside every chunk keep `out` (NaN when not given)."""
+    assert q.dtype == np.uint16 and k_cache.dtype == np.uint16 and v_cache.dtype == np.uint16
+    total_q, num_heads, head_size = q.shape
+    num_blocks, num_kv_heads, block_size, _ = k_cache.shape
+    value_size = v_cache.shape[3]
+    bt = np.ascontiguousarray(block_tables, dtype=np.int64)
+    sl = np.ascontiguousarray(seq_lens, dtype=np.int64)
+    cq = np.ascontiguousarray(cum_seq_lens_q, dtype=np.int64)
+    assert cq.shape[0] == sl.shape[0] + 1
+    if out is None:
+        out = np.full((total_q, num_heads, value_size), np.nan, dtype=np.float64)
+    assert out.dtype == np.float64 and out.flags.c_contiguous
+    qs, ks, vs = _elem_strides(q), _elem_strides(k_cache), _elem_strides(v_cache)
+    assert qs[2] == 1 and ks[3] == 1 and vs[3] == 1
+    al = None
+    if alibi_slopes is not None:
+        al = np.ascontiguousarray(alibi_slopes, dtype=np.float32)
+    rc = lib().oracle_paged_attention_prefill(
+        0 if mode == "exact" else 1, int(dtype), out.ctypes.data,
+        q.ctypes.data, qs[0], qs[1],
+        k_cache.ctypes.data, ks[0], ks[1], ks[2],
+        v_cache.ctypes.data, vs[0], vs[1], vs[2],
+        bt.ctypes.data, bt.shape[1],
+        sl.ctypes.data, cq.ctypes.data,
+        al.ctypes.data if al is not None else None,
+        float(scale),
+        sl.shape[0], num_heads, num_kv_heads, head_size, value_size, block_size, num_blocks, bt.shape[1],
+    )
+    if rc != 0:
+        raise ValueError(f"oracle_paged_attention_prefill rejected its input (code {rc})")
     return out
 
 

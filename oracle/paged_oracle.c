@@ -11,6 +11,10 @@
  *   oracle_paged_attention   test/infiniop/paged_attention.py:38-88
  *                            (ref_masked_attention, ref_single_query_cached_kv_attention)
  *   oracle_paged_caching     test/infiniop/paged_caching.py:25-55 (ref_paged_caching)
+ *   oracle_paged_attention_prefill
+ *                            test/infiniop/paged_attention_prefill.py:96-140
+ *                            (ref_paged_attention_multi_turn: new token t of a chunk of n in a
+ *                            sequence of total length L attends KV positions 0 .. L - n + t)
  *
  * plus the two edge cases those functions leave undefined and the reference kernels define:
  * a sequence with seq_len <= 0 leaves its output rows untouched
@@ -151,6 +155,105 @@ int oracle_num_threads(void) {
 #endif
 }
 
+/* One query row (one q-head) against the first `len` tokens of one paged sequence.  `o` receives
+ * value_size doubles.  Returns 0 or -5 (out of memory). */
+static int attend_row(
+    int mode, int dtype, double *o, const uint16_t *qv, int64_t len, int64_t kvh, int64_t h,
+    const uint16_t *k_cache, ptrdiff_t k_block_stride, ptrdiff_t k_head_stride, ptrdiff_t k_row_stride,
+    const uint16_t *v_cache, ptrdiff_t v_block_stride, ptrdiff_t v_head_stride, ptrdiff_t v_row_stride,
+    const int64_t *block_table, const float *alibi_slopes, float scale,
+    int64_t head_size, int64_t value_size, int64_t block_size) {
+    float *qf = (float *)malloc(sizeof(float) * (size_t)head_size);
+    double *logit = (double *)malloc(sizeof(double) * (size_t)len);
+    double *acc = (double *)malloc(sizeof(double) * (size_t)value_size);
+    if (!qf || !logit || !acc) {
+        free(qf);
+        free(logit);
+        free(acc);
+        return -5;
+    }
+    for (int64_t d = 0; d < head_size; ++d) {
+        qf[d] = load16(qv + d, dtype);
+    }
+
+    /* logits = scale * (q . k) [+ slope * (t - (len - 1))] */
+    double mx = -INFINITY;
+    for (int64_t t = 0; t < len; ++t) {
+        const int64_t blk = block_table[t / block_size];
+        const uint16_t *kr = k_cache + blk * k_block_stride + kvh * k_head_stride + (t % block_size) * k_row_stride;
+        double lg;
+        if (mode == 0) {
+            double dot = 0.0;
+            for (int64_t d = 0; d < head_size; ++d) {
+                dot += (double)qf[d] * (double)load16(kr + d, dtype);
+            }
+            lg = (double)scale * dot;
+            if (alibi_slopes) {
+                lg += (double)alibi_slopes[h] * (double)(t - len + 1);
+            }
+        } else {
+            float dot = 0.f;
+            for (int64_t d = 0; d < head_size; ++d) {
+                dot += qf[d] * load16(kr + d, dtype);
+            }
+            float l32 = scale * round16(dot, dtype); /* einsum result is in the tensor dtype */
+            if (alibi_slopes) {
+                l32 += alibi_slopes[h] * (float)(t - len + 1);
+            }
+            lg = (double)l32;
+        }
+        logit[t] = lg;
+        if (lg > mx) {
+            mx = lg;
+        }
+    }
+
+    /* softmax, then probabilities (rounded to the tensor dtype in mode 1) times V */
+    double denom = 0.0;
+    if (mode == 0) {
+        for (int64_t t = 0; t < len; ++t) {
+            logit[t] = exp(logit[t] - mx);
+            denom += logit[t];
+        }
+    } else {
+        float d32 = 0.f;
+        for (int64_t t = 0; t < len; ++t) {
+            const float e = expf((float)logit[t] - (float)mx);
+            logit[t] = (double)e;
+            d32 += e;
+        }
+        denom = (double)d32;
+    }
+    for (int64_t d = 0; d < value_size; ++d) {
+        acc[d] = 0.0;
+    }
+    for (int64_t t = 0; t < len; ++t) {
+        const int64_t blk = block_table[t / block_size];
+        const uint16_t *vr = v_cache + blk * v_block_stride + kvh * v_head_stride + (t % block_size) * v_row_stride;
+        if (mode == 0) {
+            const double pw = logit[t] / denom;
+            for (int64_t d = 0; d < value_size; ++d) {
+                acc[d] += pw * (double)load16(vr + d, dtype);
+            }
+        } else {
+            const float pw = round16((float)logit[t] / (float)denom, dtype);
+            if (pw == 0.f) {
+                continue;
+            }
+            for (int64_t d = 0; d < value_size; ++d) {
+                acc[d] = (double)((float)acc[d] + pw * load16(vr + d, dtype));
+            }
+        }
+    }
+    for (int64_t d = 0; d < value_size; ++d) {
+        o[d] = (mode == 0) ? acc[d] : (double)round16((float)acc[d], dtype);
+    }
+    free(qf);
+    free(logit);
+    free(acc);
+    return 0;
+}
+
 /* ---- paged attention (decode) ----------------------------------------------------------
  * All strides are in elements.  out is dense double [num_seqs][num_heads][value_size]; rows of
  * sequences with seq_len <= 0 are not written.  Returns 0, or a negative code for a table
@@ -200,98 +303,76 @@ int oracle_paged_attention(
                 continue; /* output row untouched */
             }
             const int64_t kvh = h / group; /* repeat_interleave(keys, group, dim=1) */
-            const uint16_t *qv = q + s * q_seq_stride + h * q_head_stride;
-            double *o = out + (s * num_heads + h) * value_size;
+            const int rc = attend_row(mode, dtype, out + (s * num_heads + h) * value_size,
+                                      q + s * q_seq_stride + h * q_head_stride, len, kvh, h,
+                                      k_cache, k_block_stride, k_head_stride, k_row_stride,
+                                      v_cache, v_block_stride, v_head_stride, v_row_stride,
+                                      block_tables + s * bt_seq_stride, alibi_slopes, scale,
+                                      head_size, value_size, block_size);
+            if (rc != 0) {
+                status = rc;
+            }
+        }
+    }
+    return status;
+}
 
-            float *qf = (float *)malloc(sizeof(float) * (size_t)head_size);
-            double *logit = (double *)malloc(sizeof(double) * (size_t)len);
-            double *acc = (double *)malloc(sizeof(double) * (size_t)value_size);
-            if (!qf || !logit || !acc) {
-                status = -5;
-                free(qf);
-                free(logit);
-                free(acc);
-                continue;
+/* ---- paged attention (prefill) -----------------------------------------------------------
+ * q and out are packed over sequences: rows cum_q[i] .. cum_q[i+1]-1 are the new tokens of
+ * sequence i, whose KV (new tokens included) is already in the cache and seq_lens[i] long.
+ * out is dense double [total_q][num_heads][value_size]; rows no chunk covers are not written.
+ */
+int oracle_paged_attention_prefill(
+    int mode, int dtype,
+    double *out,
+    const uint16_t *q, ptrdiff_t q_token_stride, ptrdiff_t q_head_stride,
+    const uint16_t *k_cache, ptrdiff_t k_block_stride, ptrdiff_t k_head_stride, ptrdiff_t k_row_stride,
+    const uint16_t *v_cache, ptrdiff_t v_block_stride, ptrdiff_t v_head_stride, ptrdiff_t v_row_stride,
+    const int64_t *block_tables, ptrdiff_t bt_seq_stride,
+    const int64_t *seq_lens, const int64_t *cum_q,
+    const float *alibi_slopes, float scale,
+    int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads,
+    int64_t head_size, int64_t value_size, int64_t block_size,
+    int64_t num_blocks, int64_t max_blocks_per_seq) {
+    if (dtype != ORACLE_DTYPE_F16 && dtype != ORACLE_DTYPE_BF16) {
+        return -1;
+    }
+    if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || block_size <= 0) {
+        return -2;
+    }
+    const int64_t group = num_heads / num_kv_heads;
+    int status = 0;
+    ensure_f16_table();
+    for (int64_t s = 0; s < num_seqs; ++s) {
+        const int64_t len = seq_lens[s];
+        const int64_t n_new = cum_q[s + 1] - cum_q[s];
+        if (n_new < 0 || len < n_new || len > max_blocks_per_seq * block_size) {
+            return -3;
+        }
+        for (int64_t b = 0; b * block_size < len; ++b) {
+            const int64_t blk = block_tables[s * bt_seq_stride + b];
+            if (blk < 0 || blk >= num_blocks) {
+                return -4;
             }
-            for (int64_t d = 0; d < head_size; ++d) {
-                qf[d] = load16(qv + d, dtype);
-            }
-
-            /* logits = scale * (q . k) [+ slope * (t - (len - 1))] */
-            double mx = -INFINITY;
-            for (int64_t t = 0; t < len; ++t) {
-                const int64_t blk = block_tables[s * bt_seq_stride + t / block_size];
-                const uint16_t *kr = k_cache + blk * k_block_stride + kvh * k_head_stride + (t % block_size) * k_row_stride;
-                double lg;
-                if (mode == 0) {
-                    double dot = 0.0;
-                    for (int64_t d = 0; d < head_size; ++d) {
-                        dot += (double)qf[d] * (double)load16(kr + d, dtype);
-                    }
-                    lg = (double)scale * dot;
-                    if (alibi_slopes) {
-                        lg += (double)alibi_slopes[h] * (double)(t - len + 1);
-                    }
-                } else {
-                    float dot = 0.f;
-                    for (int64_t d = 0; d < head_size; ++d) {
-                        dot += qf[d] * load16(kr + d, dtype);
-                    }
-                    float l32 = scale * round16(dot, dtype); /* einsum result is in the tensor dtype */
-                    if (alibi_slopes) {
-                        l32 += alibi_slopes[h] * (float)(t - len + 1);
-                    }
-                    lg = (double)l32;
-                }
-                logit[t] = lg;
-                if (lg > mx) {
-                    mx = lg;
-                }
-            }
-
-            /* softmax, then probabilities (rounded to the tensor dtype in mode 1) times V */
-            double denom = 0.0;
-            if (mode == 0) {
-                for (int64_t t = 0; t < len; ++t) {
-                    logit[t] = exp(logit[t] - mx);
-                    denom += logit[t];
-                }
-            } else {
-                float d32 = 0.f;
-                for (int64_t t = 0; t < len; ++t) {
-                    const float e = expf((float)logit[t] - (float)mx);
-                    logit[t] = (double)e;
-                    d32 += e;
-                }
-                denom = (double)d32;
-            }
-            for (int64_t d = 0; d < value_size; ++d) {
-                acc[d] = 0.0;
-            }
-            for (int64_t t = 0; t < len; ++t) {
-                const int64_t blk = block_tables[s * bt_seq_stride + t / block_size];
-                const uint16_t *vr = v_cache + blk * v_block_stride + kvh * v_head_stride + (t % block_size) * v_row_stride;
-                if (mode == 0) {
-                    const double pw = logit[t] / denom;
-                    for (int64_t d = 0; d < value_size; ++d) {
-                        acc[d] += pw * (double)load16(vr + d, dtype);
-                    }
-                } else {
-                    const float pw = round16((float)logit[t] / (float)denom, dtype);
-                    if (pw == 0.f) {
-                        continue;
-                    }
-                    for (int64_t d = 0; d < value_size; ++d) {
-                        acc[d] = (double)((float)acc[d] + pw * load16(vr + d, dtype));
-                    }
+        }
+    }
+    for (int64_t s = 0; s < num_seqs; ++s) {
+        const int64_t n_new = cum_q[s + 1] - cum_q[s];
+        const int64_t cache_len = seq_lens[s] - n_new;
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+        for (int64_t t = 0; t < n_new; ++t) {
+            for (int64_t h = 0; h < num_heads; ++h) {
+                const int64_t row = cum_q[s] + t;
+                const int rc = attend_row(mode, dtype, out + (row * num_heads + h) * value_size,
+                                          q + row * q_token_stride + h * q_head_stride, cache_len + t + 1, h / group, h,
+                                          k_cache, k_block_stride, k_head_stride, k_row_stride,
+                                          v_cache, v_block_stride, v_head_stride, v_row_stride,
+                                          block_tables + s * bt_seq_stride, alibi_slopes, scale,
+                                          head_size, value_size, block_size);
+                if (rc != 0) {
+                    status = rc;
                 }
             }
-            for (int64_t d = 0; d < value_size; ++d) {
-                o[d] = (mode == 0) ? acc[d] : (double)round16((float)acc[d], dtype);
-            }
-            free(qf);
-            free(logit);
-            free(acc);
         }
     }
     return status;

@@ -26,21 +26,36 @@ def handle():
     return _handle
 
 
+# Named variants of the decode path.  Every knob is read when the descriptor is created.
+PATH_ENV = {
+    None: {},
+    "generic": {"INFINIOP_PAGED_DECODE_PATH": "generic"},
+    "stream": {"INFINIOP_PAGED_DECODE_PATH": "stream"},
+    # plan computed by the separate one-CTA kernel instead of inside the main kernel, plain launches
+    "stream-plan-kernel": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_DECODE_EMBEDDED_PLAN": "0",
+                           "INFINIOP_PAGED_DECODE_PDL": "0"},
+    # other ring geometry: 3 warps per CTA, 4 slots
+    "stream-3x4": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_DECODE_WARPS": "3", "INFINIOP_PAGED_DECODE_STAGES": "4"},
+}
+
+
 @contextlib.contextmanager
 def decode_path(path):
-    """The decode path is chosen when the descriptor is created (INFINIOP_PAGED_DECODE_PATH)."""
-    old = os.environ.get("INFINIOP_PAGED_DECODE_PATH")
-    if path is None:
-        os.environ.pop("INFINIOP_PAGED_DECODE_PATH", None)
-    else:
-        os.environ["INFINIOP_PAGED_DECODE_PATH"] = path
+    """Sets the environment of one named path variant for the duration of a descriptor creation."""
+    env = PATH_ENV[path]
+    keys = {k for v in PATH_ENV.values() for k in v}
+    old = {k: os.environ.get(k) for k in keys}
+    for k in keys:
+        os.environ.pop(k, None)
+    os.environ.update(env)
     try:
         yield
     finally:
-        if old is None:
-            os.environ.pop("INFINIOP_PAGED_DECODE_PATH", None)
-        else:
-            os.environ["INFINIOP_PAGED_DECODE_PATH"] = old
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
 
 
 def _tt(t, dt=None):
@@ -99,6 +114,56 @@ def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, scale, alibi=No
         assert op.error_flag() == 0 or op.workspace_size == 0, "a worker's bounded wait ran out"
     finally:
         op.destroy()
+    return out
+
+
+@contextlib.contextmanager
+def prefill_path(path):
+    """INFINIOP_PAGED_PREFILL_PATH (auto | tiles | generic) is read when the descriptor is created."""
+    old = os.environ.get("INFINIOP_PAGED_PREFILL_PATH")
+    if path is None:
+        os.environ.pop("INFINIOP_PAGED_PREFILL_PATH", None)
+    else:
+        os.environ["INFINIOP_PAGED_PREFILL_PATH"] = path
+    try:
+        yield
+    finally:
+        if old is None:
+            os.environ.pop("INFINIOP_PAGED_PREFILL_PATH", None)
+        else:
+            os.environ["INFINIOP_PAGED_PREFILL_PATH"] = old
+
+
+def create_prefill(out, q, k_cache, v_cache, block_tables, seq_lens, cum_q, alibi, scale, path=None, index_dtype=None):
+    tensors = [_tt(out), _tt(q), _tt(k_cache), _tt(v_cache), _tt(block_tables, index_dtype), _tt(seq_lens, index_dtype),
+               _tt(cum_q, index_dtype)]
+    al = _tt(alibi) if alibi is not None else None
+    desc = infiniopOperatorDescriptor_t()
+    with prefill_path(path):
+        status = LIBINFINIOP.infiniopCreatePagedAttentionPrefillDescriptor(
+            handle(), ctypes.byref(desc), *[t.descriptor for t in tensors], al.descriptor if al is not None else None, scale)
+    for t in tensors + ([al] if al is not None else []):
+        t.destroy_desc()
+    return status, desc
+
+
+def paged_attention_prefill(q, k_cache, v_cache, block_tables, seq_lens, cum_q, scale, alibi=None, path=None, out=None,
+                            index_dtype=None, stream=None):
+    """Runs one prefill call through the C ABI (descriptors destroyed before execute); returns `out`."""
+    if out is None:
+        out = torch.zeros((*q.shape[:-1], v_cache.shape[3]), dtype=q.dtype, device=q.device)
+    status, desc = create_prefill(out, q, k_cache, v_cache, block_tables, seq_lens, cum_q, alibi, scale, path, index_dtype)
+    check_error(status)
+    size = ctypes.c_size_t(99)
+    check_error(LIBINFINIOP.infiniopGetPagedAttentionPrefillWorkspaceSize(desc, ctypes.byref(size)))
+    ws = TestWorkspace(size.value, InfiniDeviceEnum.NVIDIA)
+    try:
+        check_error(LIBINFINIOP.infiniopPagedAttentionPrefill(
+            desc, ws.data(), size.value, out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            block_tables.data_ptr(), seq_lens.data_ptr(), cum_q.data_ptr(), alibi.data_ptr() if alibi is not None else None, stream))
+        torch.cuda.synchronize()
+    finally:
+        check_error(LIBINFINIOP.infiniopDestroyPagedAttentionPrefillDescriptor(desc))
     return out
 
 

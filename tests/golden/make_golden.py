@@ -7,6 +7,7 @@ Run in a container that has the reference checkout (it is not needed to run the 
 The two functions executed are imported unmodified from the reference tree:
   ref_single_query_cached_kv_attention   test/infiniop/paged_attention.py:47-88
   ref_paged_caching                      test/infiniop/paged_caching.py:25-55
+  ref_paged_attention_multi_turn         test/infiniop/paged_attention_prefill.py:96-140
 Those files import the reference's ctypes harness at module level (which would try to load the
 reference's compiled library); a stand-in `libinfiniop` module with empty attributes is put
 in sys.modules first so that only the pure-torch functions are used.
@@ -39,12 +40,12 @@ def load_reference(ref_root: Path):
 
     sys.modules["libinfiniop"] = _Anything("libinfiniop")
     mods = {}
-    for name in ("paged_attention", "paged_caching"):
+    for name in ("paged_attention", "paged_caching", "paged_attention_prefill"):
         spec = importlib.util.spec_from_file_location(f"_ref_{name}", ref_root / "test" / "infiniop" / f"{name}.py")
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
         mods[name] = mod
-    return mods["paged_attention"], mods["paged_caching"]
+    return mods["paged_attention"], mods["paged_caching"], mods["paged_attention_prefill"]
 
 
 def bits(t: torch.Tensor) -> np.ndarray:
@@ -138,12 +139,41 @@ def make_caching(ref_cache):
         print("wrote", name)
 
 
+def prefill_cases():
+    # (name, dtype, new_lens, cached_lens, heads, kv_heads, head, block, value)
+    # The reference's checker has no repeat_interleave: it covers MHA (and kv_heads == 1, which
+    # broadcasts), as do the reference's own prefill test cases.
+    yield "prefill_bf16_mha_hd128", torch.bfloat16, [70, 5, 130], [0, 33, 64], 4, 4, 128, 16, None
+    yield "prefill_fp16_mha_hd128_bs8", torch.float16, [16, 9, 64, 1], [0, 7, 30, 100], 4, 4, 128, 8, None
+    yield "prefill_fp16_mha_hd64", torch.float16, [100, 65], [28, 0], 3, 3, 64, 16, None
+    yield "prefill_bf16_mqa_hd128", torch.bfloat16, [40, 17], [9, 0], 8, 1, 128, 16, None
+    yield "prefill_bf16_mla_576_512", torch.bfloat16, [8, 3], [0, 8], 16, 1, 576, 16, 512
+
+
+def make_prefill(ref_prefill):
+    for idx, (name, dtype, new, cached, heads, kvh, hd, bs, vd) in enumerate(prefill_cases()):
+        c = workloads.build_prefill_case(name, dtype=dtype, new_lens=new, cached_lens=cached, num_heads=heads,
+                                         num_kv_heads=kvh, head_size=hd, block_size=bs, seed=200 + idx, value_size=vd,
+                                         std=0.5 if hd == 576 else 1.0)
+        out = ref_prefill.ref_paged_attention_multi_turn(c.q, c.k_cache, c.v_cache, c.block_tables, c.seq_lens,
+                                                         c.cum_seq_lens_q, c.scale)
+        np.savez_compressed(
+            HERE / f"{name}.npz",
+            dtype=np.int64(DTYPE_CODE[dtype]), scale=np.float32(c.scale),
+            q=bits(c.q), k_cache=bits(c.k_cache), v_cache=bits(c.v_cache),
+            block_tables=c.block_tables.numpy(), seq_lens=c.seq_lens.numpy(), cum_seq_lens_q=c.cum_seq_lens_q.numpy(),
+            out=bits(out),
+        )
+        print("wrote", name, tuple(out.shape))
+
+
 def main():
     ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
-    ref_attn, ref_cache = load_reference(ref_root)
+    ref_attn, ref_cache, ref_prefill = load_reference(ref_root)
     torch.set_num_threads(4)
     make_attention(ref_attn)
     make_caching(ref_cache)
+    make_prefill(ref_prefill)
 
 
 if __name__ == "__main__":

@@ -95,3 +95,44 @@ def test_codecs_round_trip_every_finite_pattern():
     assert lib.oracle_float_to_f16(1.0 + 3 * 2.0 ** -11) == 0x3c02
     assert lib.oracle_float_to_bf16(1.0 + 2.0 ** -8) == 0x3f80
     assert lib.oracle_float_to_bf16(1.0 + 3 * 2.0 ** -8) == 0x3f82
+
+
+# ---- prefill ------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("name", golden_names("prefill_"))
+def test_prefill_reference_mode_matches_reference_output(name):
+    g = load_golden(name)
+    dt = int(g["dtype"])
+    got = oracle.paged_attention_prefill(g["q"], g["k_cache"], g["v_cache"], g["block_tables"], g["seq_lens"],
+                                         g["cum_seq_lens_q"], float(g["scale"]), dt, mode="reference")
+    want = bits_to_float(g["out"], dt)
+    err = np.abs(got - want)
+    assert np.all(err <= 4 * _ulp(dt, want) + 1e-3 * np.abs(want).max()), f"max err {err.max():.3e}"
+    assert np.mean(err <= _ulp(dt, want)) > 0.9
+
+
+@pytest.mark.parametrize("name", golden_names("prefill_"))
+def test_prefill_exact_mode_within_path_tolerance(name):
+    g = load_golden(name)
+    dt = int(g["dtype"])
+    got = oracle.paged_attention_prefill(g["q"], g["k_cache"], g["v_cache"], g["block_tables"], g["seq_lens"],
+                                         g["cum_seq_lens_q"], float(g["scale"]), dt, mode="exact")
+    want = bits_to_float(g["out"], dt)
+    atol, rtol = ATTN_TOL[dt]
+    assert np.all(np.abs(got - want) <= atol + rtol * np.abs(want))
+
+
+def test_prefill_row_equals_decode_with_the_causal_length():
+    """A new token is a decode query against the first cached + t + 1 tokens: the two oracles agree bit for bit."""
+    g = load_golden("prefill_bf16_mha_hd128")
+    dt = int(g["dtype"])
+    full = oracle.paged_attention_prefill(g["q"], g["k_cache"], g["v_cache"], g["block_tables"], g["seq_lens"],
+                                          g["cum_seq_lens_q"], float(g["scale"]), dt)
+    cum, lens = g["cum_seq_lens_q"], g["seq_lens"]
+    for s in range(len(lens)):
+        n = cum[s + 1] - cum[s]
+        for t in (0, n // 2, n - 1):
+            row = cum[s] + t
+            dec = oracle.paged_attention(g["q"][row:row + 1], g["k_cache"], g["v_cache"], g["block_tables"][s:s + 1],
+                                         np.array([lens[s] - n + t + 1]), float(g["scale"]), dt)
+            assert np.array_equal(dec[0], full[row])

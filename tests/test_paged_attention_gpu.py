@@ -219,6 +219,37 @@ def test_block_size_32_and_wide_block_table(abi, path):
     check(c, run_case(abi, c, path), oracle_out(c))
 
 
+@pytest.mark.parametrize("path", ["stream-plan-kernel", "stream-3x4"])
+def test_stream_path_variants(abi, path):
+    """The separate plan kernel with plain (non-programmatic) launches, and another ring geometry,
+    on ragged lengths with empty sequences and a split long sequence."""
+    c = workloads.build_case("variants", dtype=torch.bfloat16, seq_lens=[1, 0, 47, 5000, 16, 333, 0, 2049], num_heads=32, num_kv_heads=8,
+                             head_size=128, block_size=16, seed=33)
+    out = torch.full((8, 32, 128), 2.0, dtype=torch.bfloat16, device="cuda")
+    got = run_case(abi, c, path, out=out)
+    want = oracle_out(c)
+    live = [0, 2, 3, 4, 5, 7]
+    atol, rtol = ATTN_TOL[c.dtype]
+    assert_close(got[live].float().cpu().numpy(), want[live], atol, rtol, path)
+    assert bool((got[[1, 6]] == 2.0).all())
+
+
+def test_more_sequences_than_the_embedded_plan_holds(abi):
+    """5000 short sequences: beyond 4095 the plan comes from the separate plan kernel."""
+    g = torch.Generator().manual_seed(34)
+    lens = torch.randint(0, 40, (5000,), generator=g)
+    c = workloads.build_case("many", dtype=torch.float16, seq_lens=lens, num_heads=4, num_kv_heads=1, head_size=64,
+                             block_size=16, seed=34, max_blocks_per_seq=3)
+    out = torch.full((5000, 4, 64), 6.0, dtype=torch.float16, device="cuda")
+    got = run_case(abi, c, "stream", out=out)
+    want = oracle_out(c)
+    live = (lens > 0).nonzero().flatten().tolist()
+    dead = (lens == 0).nonzero().flatten().tolist()
+    atol, rtol = ATTN_TOL[c.dtype]
+    assert_close(got[live].float().cpu().numpy(), want[live], atol, rtol, "5000 sequences")
+    assert bool((got[dead] == 6.0).all())
+
+
 def test_block_size_8_takes_the_generic_path(abi):
     c = workloads.build_case("bs8", dtype=torch.float16, seq_lens=[50, 9], num_heads=4, num_kv_heads=2, head_size=64,
                              block_size=8, seed=29)
