@@ -46,7 +46,7 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5", "prefill"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--mode", default="seq", choices=["seq", "head"],
                     help="seq: shard by sequence, no collective (default); head: optional KV-head-sharded mode, "
@@ -482,9 +482,70 @@ def gpu_arm(args):
         dist.destroy_process_group()
 
 
+def prefill_arm(args):
+    """Secondary benchmark (the path's upstream neighbour): infiniopPagedAttentionPrefill at the
+    Llama-3-8B head shape, 8 prompts x 2048 new tokens, bf16.  Tensor-bound: reported in TFLOP/s of
+    the causal attention flops against the measured dense bf16 peak."""
+    import torch
+
+    import infinicore_b200 as ib
+    from infinicore_b200 import workloads
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    torch.cuda.set_device(0)
+    case = workloads.prefill_llama8b(device="cuda")
+    out = torch.empty((case.q.shape[0], case.num_heads, case.head_size), dtype=case.dtype, device="cuda")
+    stream = torch.cuda.current_stream()
+
+    def call():
+        ib.paged_attention_prefill(case.q, case.k_cache, case.v_cache, case.block_tables, case.seq_lens, case.cum_seq_lens_q,
+                                   None, case.scale, out=out)
+
+    K = min(args.steps, 200)
+    for _ in range(max(args.warmup, 3)):
+        call()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    if not args.no_clocks:
+        sampler.start()
+    a_ev, b_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a_ev.record(stream)
+    for _ in range(K):
+        call()
+    b_ev.record(stream)
+    torch.cuda.synchronize()
+    ms = a_ev.elapsed_time(b_ev) / K
+    clocks = sampler.stop() if not args.no_clocks else None
+    peak = 1590.0
+    kind = "fallback"
+    pth = ROOT / "MEASURED_PEAKS.json"
+    if pth.is_file():
+        try:
+            peak, kind = float(json.loads(pth.read_text())["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    tflops = case.flops / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "paged_attn_prefill_throughput", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": K, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "prefill, Llama-3-8B head shape: bf16, 8 prompts x 2048 new tokens, 32/8 heads, head 128, block 16 "
+                               "(not a BASELINE config: the decode path's upstream neighbour)",
+                   "l2": "K/V of one prompt (8 MiB per kv-head group) is re-read from L2 by design; q/out stream once"},
+        "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak, "traffic": None,
+                     "peak_kind": f"of {kind}", "kernel": "pagedPrefillTileKernel", "algorithmic_flops_per_launch": case.flops},
+        "gpu_launches": K, "clocks": clocks,
+    }), flush=True)
+
+
 def main():
     args = parse_args()
-    if args.impl == "reference":
+    if args.workload == "prefill":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the prefill workload has no CPU reference arm; use the decode workloads"}))
+            return
+        prefill_arm(args)
+    elif args.impl == "reference":
         reference_arm(args)
     else:
         gpu_arm(args)

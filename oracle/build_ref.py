@@ -37,6 +37,8 @@ OP_SOURCES = [
     "src/infiniop/ops/paged_attention/nvidia/paged_attention_hd256.cu",
     "src/infiniop/ops/paged_attention/nvidia/paged_attention_hd576.cu",
     "src/infiniop/ops/paged_attention/nvidia/paged_attention_mla_hd576_v512.cu",
+    "src/infiniop/ops/paged_attention_prefill/operator.cc",
+    "src/infiniop/ops/paged_attention_prefill/nvidia/paged_attention_prefill_nvidia.cu",
     "src/infiniop/ops/paged_caching/operator.cc",
     "src/infiniop/ops/paged_caching/nvidia/paged_caching_nvidia.cu",
     "src/utils/custom_types.cc",

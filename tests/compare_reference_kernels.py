@@ -20,6 +20,9 @@ SPECS = {
     "c2": {"builder": "config2_llama8b", "kwargs": {"device": "cuda"}},
     "c3": {"builder": "config3_ragged72b", "kwargs": {"device": "cuda"}},
     "c4": {"builder": "config4_longctx", "kwargs": {"device": "cuda"}},
+    # prefill, Llama-3-8B head shape: 8 prompts x 2048 new tokens; and 4 x 1024 new over 3072 cached
+    "p1": {"builder": "prefill_llama8b", "kwargs": {"device": "cuda", "num_seqs": 8, "new_len": 2048, "cached_len": 0}},
+    "p2": {"builder": "prefill_llama8b", "kwargs": {"device": "cuda", "num_seqs": 4, "new_len": 1024, "cached_len": 3072}},
 }
 
 
@@ -42,9 +45,13 @@ def main():
     names = sys.argv[1:] or ["c2", "c3", "c4"]
     for name in names:
         spec = dict(SPECS[name], iters=30, caching=False)
-        runs = [("this library", False, {}),
-                ("reference kernels, default (split-KV CTA, 4 splits)", True, {}),
-                ("reference kernels, INFINIOP_FLASH_DECODE_SPLITKV=0", True, {"INFINIOP_FLASH_DECODE_SPLITKV": "0"})]
+        if name.startswith("p"):
+            runs = [("this library", False, {}), ("this library, row-wise generic kernel", False, {"INFINIOP_PAGED_PREFILL_PATH": "generic"}),
+                    ("reference kernels, default", True, {})]
+        else:
+            runs = [("this library", False, {}),
+                    ("reference kernels, default (split-KV CTA, 4 splits)", True, {}),
+                    ("reference kernels, INFINIOP_FLASH_DECODE_SPLITKV=0", True, {"INFINIOP_FLASH_DECODE_SPLITKV": "0"})]
         base = None
         for label, reference, env in runs:
             r = run(spec, env, reference)
@@ -52,7 +59,11 @@ def main():
             if "error" in r:
                 line["error"] = r["error"]
             else:
-                line.update(attn_ms=r["attn_ms"], kv_GBps=r["kv_bytes"] / r["attn_ms"] / 1e6, workspace_bytes=r["workspace"])
+                line.update(attn_ms=r["attn_ms"], workspace_bytes=r["workspace"])
+                if "kv_bytes" in r:
+                    line["kv_GBps"] = r["kv_bytes"] / r["attn_ms"] / 1e6
+                if "flops" in r:
+                    line["TFLOPs"] = r["flops"] / r["attn_ms"] / 1e9
                 if base is None:
                     base = r["out"].float()
                 else:

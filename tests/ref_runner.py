@@ -11,6 +11,7 @@ spec = {"builder": "<function in infinicore_b200.workloads>", "kwargs": {...}, "
 The inputs are rebuilt from the spec (seeded), so nothing large crosses the process boundary.
 """
 import json
+import os
 import statistics
 import sys
 from pathlib import Path
@@ -20,6 +21,46 @@ import torch
 ROOT = Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(ROOT / "tests"))
+
+
+def run_prefill(spec, case, d, out_path):
+    import ctypes
+
+    import abi
+    from infinicore_b200.libinfiniop import LIBINFINIOP, InfiniDeviceEnum, TestWorkspace, check_error, library_paths
+
+    out = torch.zeros((d.q.shape[0], d.num_heads, d.v_cache.shape[3]), dtype=d.dtype, device="cuda")
+    status, desc = abi.create_prefill(out, d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, d.cum_seq_lens_q, None, d.scale,
+                                      path=os.environ.get("INFINIOP_PAGED_PREFILL_PATH"))
+    check_error(status)
+    size = ctypes.c_size_t(0)
+    check_error(LIBINFINIOP.infiniopGetPagedAttentionPrefillWorkspaceSize(desc, ctypes.byref(size)))
+    ws = TestWorkspace(size.value, InfiniDeviceEnum.NVIDIA)
+
+    def call(stream=None):
+        check_error(LIBINFINIOP.infiniopPagedAttentionPrefill(
+            desc, ws.data(), size.value, out.data_ptr(), d.q.data_ptr(), d.k_cache.data_ptr(), d.v_cache.data_ptr(),
+            d.block_tables.data_ptr(), d.seq_lens.data_ptr(), d.cum_seq_lens_q.data_ptr(), None, stream))
+
+    call()
+    torch.cuda.synchronize()
+    result = {"out": out.cpu(), "library": str(library_paths()[1]), "workspace": size.value}
+    iters = int(spec.get("iters", 0))
+    if iters:
+        stream = torch.cuda.current_stream().cuda_stream
+        for _ in range(3):
+            call(stream)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            call(stream)
+        b.record()
+        torch.cuda.synchronize()
+        result["attn_ms"] = a.elapsed_time(b) / iters
+        result["flops"] = case.flops
+    check_error(LIBINFINIOP.infiniopDestroyPagedAttentionPrefillDescriptor(desc))
+    torch.save(result, out_path)
 
 
 def main():
@@ -35,6 +76,8 @@ def main():
         kwargs["dtype"] = getattr(torch, kwargs["dtype"])
     case = getattr(workloads, spec["builder"])(**kwargs)
     d = case.to("cuda")
+    if isinstance(case, workloads.PrefillCase):
+        return run_prefill(spec, case, d, out_path)
     out = torch.zeros((d.num_seqs, d.num_heads, d.v_cache.shape[3]), dtype=d.dtype, device="cuda")
     if spec.get("caching", True):
         abi.paged_caching(d.k_cache, d.v_cache, d.new_k, d.new_v, d.slot_mapping)

@@ -55,3 +55,23 @@ def test_same_inputs_same_results_as_the_reference_kernels(spec, tmp_path):
         assert torch.equal(ref["v_cache"].view(torch.int16), mine["v_cache"].view(torch.int16)), "paged_caching differs"
     atol, rtol = ATTN_TOL[ref["out"].dtype]
     assert_close(mine["out"].float().numpy(), ref["out"].float().numpy(), atol, rtol, "vs reference kernels")
+
+
+PREFILL_SPECS = [
+    {"builder": "build_prefill_case", "kwargs": {"name": "pf_mha", "dtype": "bfloat16", "new_lens": [70, 5, 130], "cached_lens": [0, 33, 64],
+                                                  "num_heads": 8, "num_kv_heads": 8, "head_size": 128, "block_size": 16, "seed": 54}},
+    {"builder": "build_prefill_case", "kwargs": {"name": "pf_gqa4", "dtype": "float16", "new_lens": [200, 64, 1], "cached_lens": [17, 0, 300],
+                                                  "num_heads": 32, "num_kv_heads": 8, "head_size": 128, "block_size": 16, "seed": 55}},
+    {"builder": "build_prefill_case", "kwargs": {"name": "pf_bs8", "dtype": "bfloat16", "new_lens": [16, 9, 64], "cached_lens": [0, 7, 30],
+                                                  "num_heads": 4, "num_kv_heads": 4, "head_size": 128, "block_size": 8, "seed": 56}},
+]
+
+
+@pytest.mark.skipif(not (REF_ROOT / "lib" / "libinfiniop.so").is_file(), reason="oracle/_ref not built")
+@pytest.mark.parametrize("spec", PREFILL_SPECS, ids=lambda s: s["kwargs"]["name"])
+def test_prefill_same_results_as_the_reference_kernels(spec, tmp_path):
+    ref = run(spec, tmp_path, reference=True)
+    mine = run(spec, tmp_path, reference=False)
+    assert "oracle/_ref" in ref["library"] and "oracle/_ref" not in mine["library"]
+    atol, rtol = ATTN_TOL[ref["out"].dtype]
+    assert_close(mine["out"].float().numpy(), ref["out"].float().numpy(), atol, rtol, "prefill vs reference kernels")
