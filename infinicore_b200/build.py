@@ -48,6 +48,7 @@ OP_SOURCES = [
     "paged_attention_prefill/operator.cu",
     "paged_attention_prefill/prefill_generic.cu",
     "paged_attention_prefill/prefill_tiles.cu",
+    "paged_attention_prefill/prefill_umma.cu",
 ]
 
 

@@ -13,6 +13,7 @@ struct Descriptor {
     OpDescriptorBase base;
     Info info;
     TilePlan tiles;
+    UmmaPlan umma;
 };
 
 } // namespace b200::paged_attention_prefill
@@ -47,12 +48,24 @@ __INFINI_C infiniStatus_t infiniopCreatePagedAttentionPrefillDescriptor(
                    INFINI_STATUS_BAD_TENSOR_SHAPE);
 
     auto *h = reinterpret_cast<b200::Handle *>(handle);
-    auto *d = new Descriptor{{handle->device, handle->device_id, b200::OpKind::PagedAttentionPrefill, h->props}, info, {}};
-    // INFINIOP_PAGED_PREFILL_PATH = auto (default) | tiles | generic
+    auto *d = new Descriptor{{handle->device, handle->device_id, b200::OpKind::PagedAttentionPrefill, h->props}, info, {}, {}};
+    // INFINIOP_PAGED_PREFILL_PATH = auto (default) | umma | tiles | generic
     const char *path = std::getenv("INFINIOP_PAGED_PREFILL_PATH");
-    if (!(path != nullptr && std::strcmp(path, "generic") == 0)) {
+    const bool want_generic = path != nullptr && std::strcmp(path, "generic") == 0;
+    const bool want_tiles = path != nullptr && std::strcmp(path, "tiles") == 0;
+    const bool want_umma = path != nullptr && std::strcmp(path, "umma") == 0;
+    if (!want_generic) {
         d->tiles = b200::paged_attention_prefill::planPrefillTiles(info, *h->props);
     }
+    if (want_umma || path == nullptr || std::strcmp(path, "auto") == 0) {
+        d->umma = b200::paged_attention_prefill::planPrefillUmma(info, *h->props);
+        if (want_umma && !d->umma.eligible) {
+            std::fprintf(stderr, "[infiniop] INFINIOP_PAGED_PREFILL_PATH=umma but this problem is not eligible for the tcgen05 kernel\n");
+            delete d;
+            return INFINI_STATUS_BAD_PARAM;
+        }
+    }
+    (void)want_tiles;
     if (path != nullptr && std::strcmp(path, "tiles") == 0 && !d->tiles.eligible) {
         std::fprintf(stderr, "[infiniop] INFINIOP_PAGED_PREFILL_PATH=tiles but this problem is not eligible for the tensor-core kernel\n");
         delete d;
@@ -130,6 +143,9 @@ __INFINI_C infiniStatus_t infiniopPagedAttentionPrefill(
     pp.total_q = static_cast<int>(d->info.total_q_tokens);
 
     auto cuda_stream = static_cast<cudaStream_t>(stream);
+    if (d->umma.eligible) {
+        return b200::paged_attention_prefill::launchPrefillUmma(d->info, d->umma, pp, cuda_stream);
+    }
     if (d->tiles.eligible) {
         return b200::paged_attention_prefill::launchPrefillTiles(d->info, d->tiles, pp, cuda_stream);
     }

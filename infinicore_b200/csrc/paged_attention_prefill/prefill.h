@@ -113,6 +113,14 @@ struct TilePlan {
 TilePlan planPrefillTiles(const Info &info, const DeviceProps &props);
 infiniStatus_t launchPrefillTiles(const Info &info, const TilePlan &plan, const PrefillParams &p, cudaStream_t stream);
 
+// Blackwell tensor-core path (tcgen05.mma, TMEM accumulators); head size 128.
+struct UmmaPlan {
+    bool eligible = false;
+    int box_rows = 16;
+};
+UmmaPlan planPrefillUmma(const Info &info, const DeviceProps &props);
+infiniStatus_t launchPrefillUmma(const Info &info, const UmmaPlan &plan, const PrefillParams &p, cudaStream_t stream);
+
 } // namespace b200::paged_attention_prefill
 
 #endif

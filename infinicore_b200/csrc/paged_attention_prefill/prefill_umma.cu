@@ -1,0 +1,723 @@
+// Blackwell tensor-core prefill kernel: tcgen05.mma with TMEM accumulators, operands staged by TMA.
+//
+// Same result as prefill_tiles.cu (and the reference's prefill kernels,
+// src/infiniop/ops/paged_attention_prefill/cuda/kernel_v2.cuh), different machine mapping:
+//
+//  * one CTA = one (sequence, q-head, tile of 128 new tokens).  Q tile [128 x 128] and the KV tiles
+//    [64 tokens x 128] land in shared memory through non-multicast `cp.async.bulk.tensor` boxes with
+//    the 128-byte swizzle, which is exactly the canonical K-major (Q, K) / MN-major (V) operand layout
+//    of `tcgen05.mma`, so the MMA reads them through shared-memory descriptors with no repacking.
+//  * S[128 x 64] = Q.K^T is 8 `tcgen05.mma.cta_group::1.kind::f16` (M=128, N=64, K=16) issued by one
+//    thread into TMEM columns [0, 64); completion reaches the other threads through `tcgen05.commit`
+//    on an mbarrier.
+//  * thread r of the four softmax warps owns query row r: it reads its S row with `tcgen05.ld`
+//    (32x32b: TMEM lane = row), does the fp32 online softmax without any cross-thread traffic, rounds
+//    P to the cache dtype and writes its row into a swizzled K-major shared-memory tile.
+//  * O[128 x 128] += P.V is 4 more `tcgen05.mma` (M=128, N=128, K=16) accumulating in TMEM columns
+//    [64, 192) across all KV tiles.  The running maximum used for the exponentials is only raised
+//    when a row's true maximum exceeds it by more than 2^8 (the result is unchanged: numerator and
+//    denominator share the same reference); only then does a warp read its O rows back, scale them
+//    and store them (`tcgen05.ld` / `tcgen05.st`).  O is read once more at the end for the
+//    normalised store.  The same commit that publishes O also releases the KV stage to the producer,
+//    and P.V of tile i overlaps the S MMA and softmax arithmetic of tile i + 1.
+//  * a fifth warp is the TMA producer (block-table lookups, K/V boxes) and owns the TMEM allocation.
+//
+// Every wait is an mbarrier wait with a time limit; on every path the CTA reaches the common exit,
+// where the TMEM columns are released.
+#include "prefill.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <mutex>
+#include <type_traits>
+
+namespace b200::paged_attention_prefill {
+
+namespace {
+
+using paged_attention::DecodeParams;
+using paged_attention::loadIndex;
+
+constexpr int kHD = 128;
+constexpr int kBM = 128;                 // query rows per CTA = MMA M
+constexpr int kBN = 64;                  // KV tokens per stage = MMA N of S, K extent of P.V
+constexpr int kSoftmaxWarps = 4;
+constexpr int kThreads = (kSoftmaxWarps + 1) * 32;
+constexpr int kStages = 2;
+constexpr int kChunks = kHD / 64;        // 128-byte column chunks per row
+constexpr int kQBytes = kChunks * kBM * 128;        // 32 KiB
+constexpr int kTensorBytes = kChunks * kBN * 128;   // one K (or V) tile: 16 KiB
+constexpr int kStageBytes = 2 * kTensorBytes;
+constexpr int kPBytes = kBM * kBN * 2;              // 16 KiB
+constexpr int kTmemCols = 256;           // S: [0,64)  O_tile: [64,192)
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+// ---- PTX wrappers -------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smemAddr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbarInit(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbarExpectTx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbarTryWait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ unsigned long long globalTimerNs() {
+    unsigned long long v;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(v));
+    return v;
+}
+__device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity) {
+    if (mbarTryWait(bar, parity)) {
+        return true;
+    }
+    const unsigned long long t0 = globalTimerNs();
+    while (!mbarTryWait(bar, parity)) {
+        if (globalTimerNs() - t0 > kWaitLimitNs) {
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tmaLoad4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tmaLoad3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tcgenFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgenFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgenCommit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]; one thread issues it
+__device__ __forceinline__ void ummaF16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmemLoad32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        v[i] = __uint_as_float(r[i]);
+    }
+}
+__device__ __forceinline__ void tmemStore32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr),
+          "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float fastExp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t packPair(float lo, float hi, __nv_bfloat16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+__device__ __forceinline__ uint32_t packPair(float lo, float hi, __half) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+// Barrier among the four softmax warps that also ORs a per-thread "my bounded wait ran out" flag, so
+// that all 128 threads leave the main loop together and nobody is left waiting at a later barrier.
+__device__ __forceinline__ bool softmaxWarpsSyncAnyFailed(bool failed) {
+    uint32_t any;
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        "setp.ne.u32 q, %1, 0;\n"
+        "bar.red.or.pred p, 1, %2, q;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(any)
+        : "r"(static_cast<uint32_t>(failed)), "n"(kSoftmaxWarps * 32)
+        : "memory");
+    return any != 0;
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+// Offsets are in bytes; the hardware fields drop the 4 low bits.
+__device__ __forceinline__ uint64_t smemDesc(uint32_t addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((leading_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((stride_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+// Instruction descriptor of kind::f16: fp32 accumulate, A/B both `fmt` (0 = f16, 1 = bf16).
+__host__ __device__ constexpr uint32_t instrDesc(uint32_t fmt, uint32_t a_mn_major, uint32_t b_mn_major, uint32_t m, uint32_t n) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+struct UmmaArgs {
+    PrefillParams pp;
+    int box_rows; // rows of one K/V TMA box: 16 when block_size % 16 == 0, else 8
+};
+
+// smem layout (dynamic, 1024-aligned):
+//   [Q 32 KiB][stage 0: K 16 KiB | V 16 KiB][stage 1 ...][P 16 KiB][barriers][tmem base][scan scratch]
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+    pagedPrefillUmmaKernel(const __grid_constant__ CUtensorMap tmap_q,
+                           const __grid_constant__ CUtensorMap tmap_k,
+                           const __grid_constant__ CUtensorMap tmap_v,
+                           const UmmaArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    constexpr int kRingOff = kQBytes;
+    constexpr int kPOff = kRingOff + kStages * kStageBytes;
+    constexpr int kBarOff = kPOff + kPBytes;
+    const uint32_t smem0 = smemAddr(smem_raw);
+    const uint32_t q_tile = smem0;
+    const uint32_t ring = smem0 + kRingOff;
+    const uint32_t p_tile = smem0 + kPOff;
+    const uint32_t full_bar = smem0 + kBarOff;            // [kStages]
+    const uint32_t empty_bar = full_bar + kStages * 8;    // [kStages]
+    const uint32_t q_bar = empty_bar + kStages * 8;
+    const uint32_t s_bar = q_bar + 8;
+    const uint32_t o_bar = s_bar + 8;
+    const uint32_t drain_bar = o_bar + 8;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + kBarOff + (2 * kStages + 4) * 8);
+    int *scratch = reinterpret_cast<int *>(tmem_slot + 2);
+    int &sh_seq = scratch[0];
+    int &sh_t0 = scratch[1];
+    int &sh_found = scratch[2];
+    int &sh_failed = scratch[3];
+    int *sh_warp_tot = scratch + 4;
+
+    const DecodeParams &p = a.pp.d;
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int head = blockIdx.y;
+    const int tile_id = blockIdx.x;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbarInit(full_bar + s * 8, 1);
+            mbarInit(empty_bar + s * 8, 1);
+        }
+        mbarInit(q_bar, 1);
+        mbarInit(s_bar, 1);
+        mbarInit(o_bar, 1);
+        mbarInit(drain_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        sh_found = 0;
+        sh_failed = 0;
+    }
+    __syncthreads();
+
+    // ---- which (sequence, first new token) is this tile? (before any TMEM is held) ----------------
+    {
+        int carry = 0;
+        for (int base = 0; base < p.num_seqs; base += kThreads) {
+            const int i = base + tid;
+            int tiles = 0;
+            if (i < p.num_seqs) {
+                const long long n = loadIndex(a.pp.cum_seq_lens_q, i + 1, p.index_is_64) - loadIndex(a.pp.cum_seq_lens_q, i, p.index_is_64);
+                tiles = n > 0 ? static_cast<int>((n + kBM - 1) / kBM) : 0;
+            }
+            int incl = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) {
+                    incl += v;
+                }
+            }
+            if (lane == 31) {
+                sh_warp_tot[warp] = incl;
+            }
+            __syncthreads();
+            int prev = 0, total = 0;
+#pragma unroll
+            for (int w = 0; w < kThreads / 32; ++w) {
+                prev += (w < warp) ? sh_warp_tot[w] : 0;
+                total += sh_warp_tot[w];
+            }
+            const int excl = carry + prev + incl - tiles;
+            if (tiles > 0 && tile_id >= excl && tile_id < excl + tiles) {
+                sh_seq = i;
+                sh_t0 = (tile_id - excl) * kBM;
+                sh_found = 1;
+            }
+            __syncthreads();
+            if (sh_found) {
+                break;
+            }
+            carry += total;
+        }
+    }
+    if (!sh_found) {
+        return;
+    }
+    const int seq = sh_seq;
+    const int t0 = sh_t0;
+    const long long q_begin = loadIndex(a.pp.cum_seq_lens_q, seq, p.index_is_64);
+    const int n_new = static_cast<int>(loadIndex(a.pp.cum_seq_lens_q, seq + 1, p.index_is_64) - q_begin);
+    const long long capacity = static_cast<long long>(p.max_blocks_per_seq) * p.block_size;
+    long long total_ll = loadIndex(p.seq_lens, seq, p.index_is_64);
+    total_ll = total_ll > capacity ? capacity : total_ll;
+    const int total_len = static_cast<int>(total_ll);
+    const int cache_len = total_len - n_new;
+    const int rows_valid = min(kBM, n_new - t0);
+    const int kv_end = min(total_len, cache_len + t0 + rows_valid);
+    if (kv_end <= 0) {
+        return;
+    }
+    const int num_kv_tiles = (kv_end + kBN - 1) / kBN;
+    const int kv_head = head / p.group_size;
+
+    // ---- TMEM: the producer warp allocates, everyone reads the base address -----------------------
+    if (warp == kSoftmaxWarps) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgenFenceBefore();
+    __syncthreads();
+    tcgenFenceAfter();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base;       // 64 columns
+    const uint32_t tmem_o = tmem_base + 64;  // 128 columns
+
+    if (warp == kSoftmaxWarps) {
+        // ================================ producer warp ==========================================
+        if (lane == 0) {
+            mbarExpectTx(q_bar, kQBytes);
+            for (int c = 0; c < kChunks; ++c) {
+                tmaLoad3d(q_tile + c * (kBM * 128), &tmap_q, q_bar, c * 64, head, static_cast<int>(q_begin + t0));
+            }
+        }
+        const int box_rows = a.box_rows;
+        const int boxes_per_tensor = (kBN / box_rows) * kChunks;
+        const int box_bytes = box_rows * 128;
+        int issued = 0;
+        for (int kt = 0; kt < num_kv_tiles; ++kt) {
+            const int stage = kt % kStages;
+            const uint32_t parity = (kt / kStages) & 1;
+            if (kt >= kStages) {
+                if (!mbarWait(empty_bar + stage * 8, parity ^ 1u)) {
+                    sh_failed = 1;
+                    break;
+                }
+            }
+            const int kv0 = kt * kBN;
+            const int live_sub = min(kBN / box_rows, (kv_end - kv0 + box_rows - 1) / box_rows);
+            const uint32_t dst = ring + stage * kStageBytes;
+            if (lane == 0) {
+                mbarExpectTx(full_bar + stage * 8, static_cast<uint32_t>(2 * live_sub * kChunks * box_bytes));
+            }
+            __syncwarp();
+            for (int b = lane; b < 2 * boxes_per_tensor; b += 32) {
+                const int is_v = b / boxes_per_tensor;
+                const int r = (b % boxes_per_tensor) / kChunks;
+                const int c = b % kChunks;
+                if (r < live_sub) {
+                    const int j0 = kv0 + r * box_rows;
+                    const int page = j0 / p.block_size;
+                    const int row0 = j0 - page * p.block_size;
+                    const long long block = loadIndex(p.block_tables, seq * p.bt_seq_stride + page, p.index_is_64);
+                    tmaLoad4d(dst + is_v * kTensorBytes + c * (kBN * 128) + r * box_bytes, is_v ? &tmap_v : &tmap_k,
+                              full_bar + stage * 8, c * 64, row0, kv_head, static_cast<int>(block));
+                }
+            }
+            issued = kt + 1;
+        }
+        if (sh_failed) {
+            // bounded wait for the copies of the last (up to kStages) tiles this warp issued
+            for (int kt = max(0, issued - kStages); kt < issued; ++kt) {
+                (void)mbarWait(full_bar + (kt % kStages) * 8, (kt / kStages) & 1);
+            }
+        }
+    } else {
+        // ================================ softmax warps ==========================================
+        constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u; // 0 = f16, 1 = bf16
+        constexpr uint32_t kIdescS = instrDesc(kFmt, 0, 0, kBM, kBN);  // Q (K-major) x K (K-major)
+        constexpr uint32_t kIdescO = instrDesc(kFmt, 0, 1, kBM, kHD);  // P (K-major) x V (MN-major)
+        const int row = tid;                                           // tile-local query row = TMEM lane
+        const int limit = cache_len + t0 + row;                        // last KV position this row may see
+        const float slope_log2 = (p.alibi_slopes != nullptr) ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
+        const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
+
+        // Running reference maximum used for the exponentials (log2 domain) and the row sum.  The
+        // reference is raised lazily, so p can reach 2^kLazyBits: far inside fp32 / bf16 / fp16 range
+        // for the products that follow (fp16 P is bounded by 2^8 * 1 = 256).
+        constexpr float kLazyBits = 8.f;
+        float m_used = 0.f, l_run = 0.f;
+        bool failed = false;
+
+        if (!mbarWait(q_bar, 0)) {
+            failed = true;
+        }
+        for (int kt = 0; kt < num_kv_tiles; ++kt) {
+            const int stage = kt % kStages;
+            const uint32_t parity = (kt / kStages) & 1;
+            const uint32_t k_tile = ring + stage * kStageBytes;
+            const uint32_t v_tile = k_tile + kTensorBytes;
+            const int kv0 = kt * kBN;
+            const int valid = kv_end - kv0;
+
+            failed = failed || !mbarWait(full_bar + stage * 8, parity);
+            if (!failed && valid < kBN) {
+                // V rows past the end may hold anything: zero them so that 0 * garbage stays 0
+                for (int idx = tid; idx < (kBN - valid) * kChunks * 8; idx += kSoftmaxWarps * 32) {
+                    const int vrow = valid + idx / (kChunks * 8);
+                    const int rest = idx % (kChunks * 8);
+                    const uint32_t addr = v_tile + (rest / 8) * (kBN * 128) + vrow * 128 + (rest % 8) * 16;
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            // every thread has read the previous tile's S by now (it passed the P barrier below)
+            tcgenFenceBefore();
+            failed = softmaxWarpsSyncAnyFailed(failed);
+            if (failed) {
+                break;
+            }
+
+            // ---- S = Q . K^T ------------------------------------------------------------------------
+            if (tid == 0) {
+                tcgenFenceAfter();
+#pragma unroll
+                for (int ks = 0; ks < kHD / 16; ++ks) {
+                    const uint32_t koff = (ks % 4) * 32; // 16 elements = 32 bytes inside the 128-byte swizzled row
+                    const uint64_t da = smemDesc(q_tile + (ks / 4) * (kBM * 128) + koff, 16, 1024);
+                    const uint64_t db = smemDesc(k_tile + (ks / 4) * (kBN * 128) + koff, 16, 1024);
+                    ummaF16(tmem_s, da, db, kIdescS, ks > 0 ? 1u : 0u);
+                }
+                tcgenCommit(s_bar);
+            }
+            failed = !mbarWait(s_bar, kt & 1);
+            uint32_t pw[kBN / 2];
+            float alpha = 1.f;
+            bool rescale = false;
+            if (!failed) {
+                tcgenFenceAfter();
+                // ---- softmax of this thread's row (log2 domain) ---------------------------------------
+                float s[kBN];
+                {
+                    float lo[32], hi[32];
+                    tmemLoad32(tmem_s + lane_field, lo);
+                    tmemLoad32(tmem_s + lane_field + 32, hi);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        s[i] = lo[i];
+                        s[32 + i] = hi[i];
+                    }
+                }
+                const bool need_mask = (kv0 + kBN - 1 > limit) || (valid < kBN);
+                float mx = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < kBN; ++j) {
+                    float x = s[j] * p.scale_log2e;
+                    if (slope_log2 != 0.f) {
+                        x += slope_log2 * static_cast<float>(kv0 + j - limit);
+                    }
+                    if (need_mask) {
+                        x = (kv0 + j <= limit && j < valid) ? x : -INFINITY;
+                    }
+                    s[j] = x;
+                    mx = fmaxf(mx, x);
+                }
+                if (kt == 0) {
+                    m_used = (mx == -INFINITY) ? 0.f : mx; // nothing accumulated yet: no rescale needed
+                } else if (mx > m_used + kLazyBits) {
+                    alpha = fastExp2(m_used - mx);
+                    m_used = mx;
+                    rescale = true;
+                }
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < kBN; j += 2) {
+                    const float p0 = fastExp2(s[j] - m_used);
+                    const float p1 = fastExp2(s[j + 1] - m_used);
+                    sum += p0 + p1;
+                    pw[j / 2] = packPair(p0, p1, T());
+                }
+                l_run = l_run * alpha + sum;
+            }
+            // The previous tile's P.V must have retired before P (shared memory) is overwritten and
+            // before O (TMEM) is rescaled.
+            if (kt > 0) {
+                failed = failed || !mbarWait(o_bar, (kt - 1) & 1);
+            }
+            if (!failed) {
+                tcgenFenceAfter();
+                if (__any_sync(0xffffffffu, rescale)) {
+                    // warp-collective: every lane scales its own row (alpha = 1 where nothing changed)
+#pragma unroll
+                    for (int c = 0; c < kHD / 32; ++c) {
+                        float o[32];
+                        tmemLoad32(tmem_o + lane_field + c * 32, o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            o[i] *= alpha;
+                        }
+                        tmemStore32(tmem_o + lane_field + c * 32, o);
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < kBN / 8; ++c) {
+                    const uint32_t addr = p_tile + row * 128 + ((c ^ (row & 7)) << 4);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pw[c * 4]), "r"(pw[c * 4 + 1]),
+                                 "r"(pw[c * 4 + 2]), "r"(pw[c * 4 + 3]) : "memory");
+                }
+            }
+            // P (generic-proxy writes) must be visible to the tensor core's async-proxy reads; the TMEM
+            // stores above must be ordered before the MMA that accumulates into O
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tcgenFenceBefore();
+            failed = softmaxWarpsSyncAnyFailed(failed);
+            if (failed) {
+                break;
+            }
+
+            // ---- O += P . V ----------------------------------------------------------------------------
+            if (tid == 0) {
+                tcgenFenceAfter();
+#pragma unroll
+                for (int kk = 0; kk < kBN / 16; ++kk) {
+                    const uint64_t da = smemDesc(p_tile + kk * 32, 16, 1024);
+                    const uint64_t db = smemDesc(v_tile + kk * (16 * 128), kBN * 128, 1024);
+                    ummaF16(tmem_o, da, db, kIdescO, (kt > 0 || kk > 0) ? 1u : 0u);
+                }
+                tcgenCommit(o_bar);
+                tcgenCommit(empty_bar + stage * 8); // K and V of this stage are free once these MMAs retire
+            }
+        }
+
+        if (!failed) {
+            failed = !mbarWait(o_bar, (num_kv_tiles - 1) & 1);
+        }
+        if (failed) {
+            sh_failed = 1;
+        } else {
+            tcgenFenceAfter();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            T *out = static_cast<T *>(p.out) + (q_begin + t0 + row) * p.o_seq_stride + head * p.o_head_stride;
+#pragma unroll
+            for (int c = 0; c < kHD / 32; ++c) {
+                float o[32];
+                tmemLoad32(tmem_o + lane_field + c * 32, o); // warp-collective: rows past the chunk load too
+                if (row < rows_valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        v.x = packPair(o[i] * inv, o[i + 1] * inv, T());
+                        v.y = packPair(o[i + 2] * inv, o[i + 3] * inv, T());
+                        v.z = packPair(o[i + 4] * inv, o[i + 5] * inv, T());
+                        v.w = packPair(o[i + 6] * inv, o[i + 7] * inv, T());
+                        *reinterpret_cast<uint4 *>(out + c * 32 + i) = v;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- common exit ------------------------------------------------------------------------------
+    // On the normal path every MMA and every copy has been waited for.  After a failed wait something
+    // may still be in flight: give the tensor core (bounded) time to retire what was issued and let the
+    // producer's last copies land before TMEM and shared memory are given back.
+    if (tid == 0) {
+        tcgenCommit(drain_bar);
+        (void)mbarWait(drain_bar, 0);
+    }
+    tcgenFenceBefore();
+    __syncthreads();
+    if (warp == kSoftmaxWarps) {
+        tcgenFenceAfter();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- host -------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encodeTiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess
+            && qres == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        } else {
+            (void)cudaGetLastError();
+        }
+    });
+    return fn;
+}
+
+CUtensorMapDataType mapDtype(infiniDtype_t dt) {
+    return dt == INFINI_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+}
+
+bool encodeCacheMap(CUtensorMap *map, const paged_attention::Info &A, const void *base, ptrdiff_t row_stride,
+                    ptrdiff_t head_stride, ptrdiff_t block_stride, int box_rows) {
+    EncodeTiledFn fn = encodeTiled();
+    if (fn == nullptr) {
+        return false;
+    }
+    const cuuint64_t dims[4] = {A.head_size, A.block_size, A.num_kv_heads, A.num_blocks};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(row_stride) * 2, static_cast<cuuint64_t>(head_stride) * 2,
+                                   static_cast<cuuint64_t>(block_stride) * 2};
+    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+    const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+    return fn(map, mapDtype(A.dtype), 4, const_cast<void *>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// q as {head_size, num_heads, total_q}: one box = 64 elements x 1 head x 128 tokens
+bool encodeQueryMap(CUtensorMap *map, const Info &info, const void *base) {
+    EncodeTiledFn fn = encodeTiled();
+    if (fn == nullptr) {
+        return false;
+    }
+    const auto &A = info.attn;
+    const cuuint64_t dims[3] = {A.head_size, A.num_heads, info.total_q_tokens};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(A.q_head_stride) * 2, static_cast<cuuint64_t>(A.q_seq_stride) * 2};
+    const cuuint32_t box[3] = {64, 1, kBM};
+    const cuuint32_t elem_strides[3] = {1, 1, 1};
+    return fn(map, mapDtype(A.dtype), 3, const_cast<void *>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+constexpr size_t kSmemBytes = kQBytes + kStages * kStageBytes + kPBytes + 256 + 1024;
+
+template <typename T>
+infiniStatus_t launchTyped(const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv,
+                           unsigned tiles, int device_id, cudaStream_t stream) {
+    static std::mutex attr_mutex;
+    static bool attr_done[64] = {};
+    auto kernel = pagedPrefillUmmaKernel<T>;
+    {
+        std::lock_guard<std::mutex> lock(attr_mutex);
+        const bool tracked = device_id >= 0 && device_id < 64;
+        if (!tracked || !attr_done[device_id]) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes)) != cudaSuccess) {
+                return checkLaunch("cudaFuncSetAttribute(pagedPrefillUmmaKernel)");
+            }
+            if (tracked) {
+                attr_done[device_id] = true;
+            }
+        }
+    }
+    const dim3 grid(tiles, args.pp.d.num_heads);
+    kernel<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, args);
+    return checkLaunch("pagedPrefillUmmaKernel");
+}
+
+} // namespace
+
+UmmaPlan planPrefillUmma(const Info &info, const DeviceProps &props) {
+    UmmaPlan plan;
+    const auto &A = info.attn;
+    if (A.head_size != kHD || A.value_size != kHD) {
+        return plan;
+    }
+    if (A.block_size % 8 != 0 || A.num_seqs == 0 || A.num_seqs > 65536 || info.total_q_tokens == 0 || A.num_blocks == 0) {
+        return plan;
+    }
+    plan.box_rows = (A.block_size % 16 == 0) ? 16 : 8;
+    auto mult8 = [](ptrdiff_t v) { return v > 0 && (v % 8) == 0; }; // 16 bytes of a 2-byte dtype
+    if (!mult8(A.q_seq_stride) || !mult8(A.q_head_stride) || !mult8(A.o_seq_stride) || !mult8(A.o_head_stride)) {
+        return plan;
+    }
+    if (!mult8(A.k_row_stride) || !mult8(A.k_head_stride) || !mult8(A.k_block_stride)
+        || !mult8(A.v_row_stride) || !mult8(A.v_head_stride) || !mult8(A.v_block_stride)) {
+        return plan;
+    }
+    CUtensorMap probe;
+    void *fake = reinterpret_cast<void *>(static_cast<uintptr_t>(1) << 30);
+    if (!encodeCacheMap(&probe, A, fake, A.k_row_stride, A.k_head_stride, A.k_block_stride, plan.box_rows)
+        || !encodeCacheMap(&probe, A, fake, A.v_row_stride, A.v_head_stride, A.v_block_stride, plan.box_rows)
+        || !encodeQueryMap(&probe, info, fake)) {
+        return plan;
+    }
+    if (kSmemBytes > props.smem_per_block_optin) {
+        return plan;
+    }
+    plan.eligible = true;
+    return plan;
+}
+
+infiniStatus_t launchPrefillUmma(const Info &info, const UmmaPlan &plan, const PrefillParams &pp, cudaStream_t stream) {
+    const auto &A = info.attn;
+    const auto &p = pp.d;
+    const auto addr = [](const void *ptr) { return reinterpret_cast<uintptr_t>(ptr); };
+    if (((addr(p.k_cache) | addr(p.v_cache) | addr(p.q) | addr(p.out)) & 15u) != 0) {
+        return launchPrefillGeneric(info, pp, stream);
+    }
+    CUtensorMap mq, mk, mv;
+    B200_RETURN_IF(!encodeQueryMap(&mq, info, p.q), INFINI_STATUS_INTERNAL_ERROR);
+    B200_RETURN_IF(!encodeCacheMap(&mk, A, p.k_cache, A.k_row_stride, A.k_head_stride, A.k_block_stride, plan.box_rows), INFINI_STATUS_INTERNAL_ERROR);
+    B200_RETURN_IF(!encodeCacheMap(&mv, A, p.v_cache, A.v_row_stride, A.v_head_stride, A.v_block_stride, plan.box_rows), INFINI_STATUS_INTERNAL_ERROR);
+    UmmaArgs args;
+    args.pp = pp;
+    args.box_rows = plan.box_rows;
+    const unsigned tiles = static_cast<unsigned>((info.total_q_tokens + kBM - 1) / kBM + A.num_seqs);
+    int device_id = -1;
+    (void)cudaGetDevice(&device_id);
+    return A.dtype == INFINI_DTYPE_F16 ? launchTyped<__half>(args, mq, mk, mv, tiles, device_id, stream)
+                                       : launchTyped<__nv_bfloat16>(args, mq, mk, mv, tiles, device_id, stream);
+}
+
+} // namespace b200::paged_attention_prefill

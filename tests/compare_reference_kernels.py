@@ -46,7 +46,10 @@ def main():
     for name in names:
         spec = dict(SPECS[name], iters=30, caching=False)
         if name.startswith("p"):
-            runs = [("this library", False, {}), ("this library, row-wise generic kernel", False, {"INFINIOP_PAGED_PREFILL_PATH": "generic"}),
+            runs = [("this library (default path)", False, {}),
+                    ("this library, tcgen05 kernel", False, {"INFINIOP_PAGED_PREFILL_PATH": "umma"}),
+                    ("this library, mma.sync tile kernel", False, {"INFINIOP_PAGED_PREFILL_PATH": "tiles"}),
+                    ("this library, row-wise generic kernel", False, {"INFINIOP_PAGED_PREFILL_PATH": "generic"}),
                     ("reference kernels, default", True, {})]
         else:
             runs = [("this library", False, {}),

@@ -14,7 +14,8 @@ from infinicore_b200 import workloads
 
 pytestmark = pytest.mark.gpu
 
-PATHS = [None, "generic"]
+PATHS = [None, "generic", "tiles"]
+PATHS_HD128 = [None, "generic", "tiles", "umma"]  # the tcgen05 kernel takes head size 128 (and is the default there)
 
 
 @pytest.fixture(scope="module")
@@ -43,9 +44,13 @@ def check(c, got, want):
     assert_close(got.float().cpu().numpy(), want, atol, rtol, c.name)
 
 
-@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("path", PATHS_HD128)
 @pytest.mark.parametrize("name", golden_names("prefill_"))
 def test_golden(abi, name, path):
+    if path == "umma" and "hd128" not in name:
+        pytest.skip("tcgen05 kernel: head size 128 only")
+    if path == "tiles" and "576" in name:
+        pytest.skip("tile kernel: head sizes 64 and 128")
     g = load_golden(name)
     dt = int(g["dtype"])
     q, kc, vc = (bits_to_torch(g[k], dt).cuda() for k in ("q", "k_cache", "v_cache"))
@@ -85,10 +90,12 @@ def test_reference_case_list_multi_round(abi, case, dtype, index_dtype):
         cached = cached + new
 
 
-@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("path", PATHS_HD128)
 @pytest.mark.parametrize("dtype,heads,kvh,hd,bs", [(torch.bfloat16, 8, 2, 128, 16), (torch.float16, 4, 1, 64, 16),
                                                    (torch.bfloat16, 4, 4, 128, 8), (torch.float16, 8, 2, 128, 32)])
 def test_gqa_ragged_chunks_and_tile_boundaries(abi, path, dtype, heads, kvh, hd, bs):
+    if path == "umma" and hd != 128:
+        pytest.skip("tcgen05 kernel: head size 128 only")
     """Chunk lengths around the 64-row tile and the page size, cached prefixes of every alignment,
     one sequence with no new tokens."""
     new = [1, 63, 64, 65, 127, 128, 129, 0, 200, 17]
@@ -98,7 +105,7 @@ def test_gqa_ragged_chunks_and_tile_boundaries(abi, path, dtype, heads, kvh, hd,
     check(c, run_case(abi, c, path), oracle_out(c))
 
 
-@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("path", PATHS_HD128)
 def test_alibi(abi, path):
     c = workloads.build_prefill_case("alibi", dtype=torch.bfloat16, new_lens=[70, 9], cached_lens=[30, 0], num_heads=8,
                                      num_kv_heads=2, head_size=128, block_size=16, seed=92)
@@ -107,7 +114,7 @@ def test_alibi(abi, path):
     check(c, run_case(abi, c, path, alibi=slopes), oracle_out(c, alibi=slopes))
 
 
-@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("path", PATHS_HD128)
 def test_unused_cache_slots_may_hold_nan_and_untouched_rows_stay(abi, path):
     c = workloads.build_prefill_case("poison", dtype=torch.float16, new_lens=[37, 80], cached_lens=[5, 0], num_heads=4,
                                      num_kv_heads=2, head_size=128, block_size=16, seed=93)
@@ -133,11 +140,12 @@ def test_unused_cache_slots_may_hold_nan_and_untouched_rows_stay(abi, path):
     assert bool((got[-3:] == 8.0).all())
 
 
-def test_long_prompt_against_oracle(abi):
+@pytest.mark.parametrize("path", ["tiles", "umma"])
+def test_long_prompt_against_oracle(abi, path):
     """2 prompts x 1024 new tokens over 512 cached, Llama-3-8B head shape."""
     c = workloads.build_prefill_case("long", dtype=torch.bfloat16, new_lens=[1024, 1000], cached_lens=[512, 0], num_heads=32,
                                      num_kv_heads=8, head_size=128, block_size=16, seed=94)
-    check(c, run_case(abi, c, None), oracle_out(c))
+    check(c, run_case(abi, c, path), oracle_out(c))
 
 
 def test_prefill_of_one_token_equals_decode(abi):
