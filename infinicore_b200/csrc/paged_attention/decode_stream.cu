@@ -52,7 +52,7 @@ constexpr int kHeadsPerTile = 8;
 constexpr int kMaxStages = 8;
 constexpr int kMaxWarps = 8;
 constexpr int kPlanThreads = 1024;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull; // an mbarrier wait gives up after 2 s
+constexpr long long kWaitLimitCycles = 4000000000ll; // an mbarrier wait gives up after ~2 s
 
 struct PlanHeader {
     int error;      // set non-zero by a worker whose bounded wait ran out
@@ -106,20 +106,15 @@ __device__ __forceinline__ bool mbarTryWait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
-__device__ __forceinline__ unsigned long long globalTimerNs() {
-    unsigned long long v;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(v));
-    return v;
-}
-
-// Bounded wait: false means the time limit ran out (the copy it waits for never landed).
+// Bounded wait: false means the limit ran out (the copy or MMA it waits for never completed).  The
+// bound is counted on the SM's cycle counter, which is cheap to read; roughly 2 s at 2 GHz.
 __device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity) {
     if (mbarTryWait(bar, parity)) {
         return true;
     }
-    const unsigned long long t0 = globalTimerNs();
+    const long long t0 = clock64();
     while (!mbarTryWait(bar, parity)) {
-        if (globalTimerNs() - t0 > kWaitLimitNs) {
+        if (clock64() - t0 > kWaitLimitCycles) {
             return false;
         }
     }

@@ -38,7 +38,7 @@ constexpr int kBN = 64;              // KV tokens per stage
 constexpr int kConsumerWarps = 4;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kStages = 2;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr long long kWaitLimitCycles = 4000000000ll; // an mbarrier wait gives up after ~2 s
 
 __device__ __forceinline__ uint32_t smemAddr(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -65,19 +65,15 @@ __device__ __forceinline__ bool mbarTryWait(uint32_t bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-__device__ __forceinline__ unsigned long long globalTimerNs() {
-    unsigned long long v;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(v));
-    return v;
-}
-// Bounded wait: false means the time limit ran out.
+// Bounded wait: false means the limit ran out (the copy or MMA it waits for never completed).  The
+// bound is counted on the SM's cycle counter, which is cheap to read; roughly 2 s at 2 GHz.
 __device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity) {
     if (mbarTryWait(bar, parity)) {
         return true;
     }
-    const unsigned long long t0 = globalTimerNs();
+    const long long t0 = clock64();
     while (!mbarTryWait(bar, parity)) {
-        if (globalTimerNs() - t0 > kWaitLimitNs) {
+        if (clock64() - t0 > kWaitLimitCycles) {
             return false;
         }
     }

@@ -51,7 +51,7 @@ constexpr int kTensorBytes = kChunks * kBN * 128;   // one K (or V) tile: 16 KiB
 constexpr int kStageBytes = 2 * kTensorBytes;
 constexpr int kPBytes = kBM * kBN * 2;              // 16 KiB
 constexpr int kTmemCols = 256;           // S: [0,64)  O_tile: [64,192)
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr long long kWaitLimitCycles = 4000000000ll; // an mbarrier wait gives up after ~2 s
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smemAddr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -74,18 +74,15 @@ __device__ __forceinline__ bool mbarTryWait(uint32_t bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-__device__ __forceinline__ unsigned long long globalTimerNs() {
-    unsigned long long v;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(v));
-    return v;
-}
+// Bounded wait: false means the limit ran out (the copy or MMA it waits for never completed).  The
+// bound is counted on the SM's cycle counter, which is cheap to read; roughly 2 s at 2 GHz.
 __device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity) {
     if (mbarTryWait(bar, parity)) {
         return true;
     }
-    const unsigned long long t0 = globalTimerNs();
+    const long long t0 = clock64();
     while (!mbarTryWait(bar, parity)) {
-        if (globalTimerNs() - t0 > kWaitLimitNs) {
+        if (clock64() - t0 > kWaitLimitCycles) {
             return false;
         }
     }
@@ -210,7 +207,7 @@ struct UmmaArgs {
 };
 
 // smem layout (dynamic, 1024-aligned):
-//   [Q 32 KiB][stage 0: K 16 KiB | V 16 KiB][stage 1 ...][P 16 KiB][barriers][tmem base][scan scratch]
+//   [Q 32 KiB][K ring: stages x 16 KiB][V ring: stages x 16 KiB][P 16 KiB][barriers][tmem base][scan scratch]
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
     pagedPrefillUmmaKernel(const __grid_constant__ CUtensorMap tmap_q,
@@ -225,13 +222,17 @@ __global__ void __launch_bounds__(kThreads)
     const uint32_t q_tile = smem0;
     const uint32_t ring = smem0 + kRingOff;
     const uint32_t p_tile = smem0 + kPOff;
-    const uint32_t full_bar = smem0 + kBarOff;            // [kStages]
-    const uint32_t empty_bar = full_bar + kStages * 8;    // [kStages]
-    const uint32_t q_bar = empty_bar + kStages * 8;
+    // K and V travel in separate rings: a K slot is handed back as soon as S = Q.K^T has retired, a V
+    // slot only after P.V, so the next K tile is in flight a whole softmax earlier.
+    const uint32_t k_full = smem0 + kBarOff;              // [kStages]
+    const uint32_t k_empty = k_full + kStages * 8;        // [kStages]
+    const uint32_t v_full = k_empty + kStages * 8;        // [kStages]
+    const uint32_t v_empty = v_full + kStages * 8;        // [kStages]
+    const uint32_t q_bar = v_empty + kStages * 8;
     const uint32_t s_bar = q_bar + 8;
     const uint32_t o_bar = s_bar + 8;
     const uint32_t drain_bar = o_bar + 8;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + kBarOff + (2 * kStages + 4) * 8);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + kBarOff + (4 * kStages + 4) * 8);
     int *scratch = reinterpret_cast<int *>(tmem_slot + 2);
     int &sh_seq = scratch[0];
     int &sh_t0 = scratch[1];
@@ -248,8 +249,10 @@ __global__ void __launch_bounds__(kThreads)
 
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbarInit(full_bar + s * 8, 1);
-            mbarInit(empty_bar + s * 8, 1);
+            mbarInit(k_full + s * 8, 1);
+            mbarInit(k_empty + s * 8, 1);
+            mbarInit(v_full + s * 8, 1);
+            mbarInit(v_empty + s * 8, 1);
         }
         mbarInit(q_bar, 1);
         mbarInit(s_bar, 1);
@@ -350,38 +353,63 @@ __global__ void __launch_bounds__(kThreads)
         for (int kt = 0; kt < num_kv_tiles; ++kt) {
             const int stage = kt % kStages;
             const uint32_t parity = (kt / kStages) & 1;
-            if (kt >= kStages) {
-                if (!mbarWait(empty_bar + stage * 8, parity ^ 1u)) {
-                    sh_failed = 1;
-                    break;
-                }
-            }
             const int kv0 = kt * kBN;
             const int live_sub = min(kBN / box_rows, (kv_end - kv0 + box_rows - 1) / box_rows);
-            const uint32_t dst = ring + stage * kStageBytes;
-            if (lane == 0) {
-                mbarExpectTx(full_bar + stage * 8, static_cast<uint32_t>(2 * live_sub * kChunks * box_bytes));
-            }
-            __syncwarp();
-            for (int b = lane; b < 2 * boxes_per_tensor; b += 32) {
-                const int is_v = b / boxes_per_tensor;
+            // this lane's boxes (at most 2 per lane: 2 tensors x (64 / box_rows) x 2 chunks <= 32 .. 64):
+            // resolve their block-table entries first, so the lookup latency hides behind the wait below
+            long long blocks[2];
+            int rows0[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int b = lane + u * 32;
                 const int r = (b % boxes_per_tensor) / kChunks;
-                const int c = b % kChunks;
-                if (r < live_sub) {
+                blocks[u] = 0;
+                rows0[u] = 0;
+                if (b < 2 * boxes_per_tensor && r < live_sub) {
                     const int j0 = kv0 + r * box_rows;
                     const int page = j0 / p.block_size;
-                    const int row0 = j0 - page * p.block_size;
-                    const long long block = loadIndex(p.block_tables, seq * p.bt_seq_stride + page, p.index_is_64);
-                    tmaLoad4d(dst + is_v * kTensorBytes + c * (kBN * 128) + r * box_bytes, is_v ? &tmap_v : &tmap_k,
-                              full_bar + stage * 8, c * 64, row0, kv_head, static_cast<int>(block));
+                    rows0[u] = j0 - page * p.block_size;
+                    blocks[u] = loadIndex(p.block_tables, seq * p.bt_seq_stride + page, p.index_is_64);
                 }
+            }
+            // K first (its slot frees after S of tile kt - kStages), then V (frees after that tile's P.V):
+            // the same order in which the two slots become free.
+            bool ok = true;
+#pragma unroll
+            for (int is_v = 0; is_v < 2; ++is_v) {
+                const uint32_t full = (is_v ? v_full : k_full) + stage * 8;
+                const uint32_t empty = (is_v ? v_empty : k_empty) + stage * 8;
+                if (kt >= kStages && !mbarWait(empty, parity ^ 1u)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t dst = ring + (is_v * kStages + stage) * kTensorBytes;
+                if (lane == 0) {
+                    mbarExpectTx(full, static_cast<uint32_t>(live_sub * kChunks * box_bytes));
+                }
+                __syncwarp();
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int b = lane + u * 32;
+                    const int r = (b % boxes_per_tensor) / kChunks;
+                    const int c = b % kChunks;
+                    if (b < 2 * boxes_per_tensor && b / boxes_per_tensor == is_v && r < live_sub) {
+                        tmaLoad4d(dst + c * (kBN * 128) + r * box_bytes, is_v ? &tmap_v : &tmap_k, full, c * 64, rows0[u],
+                                  kv_head, static_cast<int>(blocks[u]));
+                    }
+                }
+            }
+            if (!ok) {
+                sh_failed = 1;
+                break;
             }
             issued = kt + 1;
         }
         if (sh_failed) {
             // bounded wait for the copies of the last (up to kStages) tiles this warp issued
             for (int kt = max(0, issued - kStages); kt < issued; ++kt) {
-                (void)mbarWait(full_bar + (kt % kStages) * 8, (kt / kStages) & 1);
+                (void)mbarWait(k_full + (kt % kStages) * 8, (kt / kStages) & 1);
+                (void)mbarWait(v_full + (kt % kStages) * 8, (kt / kStages) & 1);
             }
         }
     } else {
@@ -407,12 +435,15 @@ __global__ void __launch_bounds__(kThreads)
         for (int kt = 0; kt < num_kv_tiles; ++kt) {
             const int stage = kt % kStages;
             const uint32_t parity = (kt / kStages) & 1;
-            const uint32_t k_tile = ring + stage * kStageBytes;
-            const uint32_t v_tile = k_tile + kTensorBytes;
+            const uint32_t k_tile = ring + stage * kTensorBytes;
+            const uint32_t v_tile = ring + (kStages + stage) * kTensorBytes;
             const int kv0 = kt * kBN;
             const int valid = kv_end - kv0;
 
-            failed = failed || !mbarWait(full_bar + stage * 8, parity);
+            failed = failed || !mbarWait(k_full + stage * 8, parity);
+            if (!failed && valid < kBN) {
+                failed = !mbarWait(v_full + stage * 8, parity);
+            }
             if (!failed && valid < kBN) {
                 // V rows past the end may hold anything: zero them so that 0 * garbage stays 0
                 for (int idx = tid; idx < (kBN - valid) * kChunks * 8; idx += kSoftmaxWarps * 32) {
@@ -441,6 +472,7 @@ __global__ void __launch_bounds__(kThreads)
                     ummaF16(tmem_s, da, db, kIdescS, ks > 0 ? 1u : 0u);
                 }
                 tcgenCommit(s_bar);
+                tcgenCommit(k_empty + stage * 8); // the K slot is free once S has retired
             }
             failed = !mbarWait(s_bar, kt & 1);
             uint32_t pw[kBN / 2];
@@ -496,6 +528,7 @@ __global__ void __launch_bounds__(kThreads)
             if (kt > 0) {
                 failed = failed || !mbarWait(o_bar, (kt - 1) & 1);
             }
+            failed = failed || !mbarWait(v_full + stage * 8, parity); // V of this tile has landed
             if (!failed) {
                 tcgenFenceAfter();
                 if (__any_sync(0xffffffffu, rescale)) {
@@ -537,7 +570,7 @@ __global__ void __launch_bounds__(kThreads)
                     ummaF16(tmem_o, da, db, kIdescO, (kt > 0 || kk > 0) ? 1u : 0u);
                 }
                 tcgenCommit(o_bar);
-                tcgenCommit(empty_bar + stage * 8); // K and V of this stage are free once these MMAs retire
+                tcgenCommit(v_empty + stage * 8); // the V slot is free once P.V has retired
             }
         }
 
@@ -640,7 +673,8 @@ bool encodeQueryMap(CUtensorMap *map, const Info &info, const void *base) {
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-constexpr size_t kSmemBytes = kQBytes + kStages * kStageBytes + kPBytes + 256 + 1024;
+// tiles + barriers/TMEM slot/scan scratch; two CTAs (plus 1 KiB of system shared memory each) fit one SM
+constexpr size_t kSmemBytes = kQBytes + kStages * kStageBytes + kPBytes + 256;
 
 template <typename T>
 infiniStatus_t launchTyped(const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv,
