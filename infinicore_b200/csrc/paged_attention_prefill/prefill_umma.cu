@@ -29,6 +29,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -43,14 +44,14 @@ constexpr int kHD = 128;
 constexpr int kBM = 128;                 // query rows per CTA = MMA M
 constexpr int kBN = 64;                  // KV tokens per stage = MMA N of S, K extent of P.V
 constexpr int kSoftmaxWarps = 4;
-constexpr int kThreads = (kSoftmaxWarps + 1) * 32;
-constexpr int kStages = 2;
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
+constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
 constexpr int kChunks = kHD / 64;        // 128-byte column chunks per row
 constexpr int kQBytes = kChunks * kBM * 128;        // 32 KiB
 constexpr int kTensorBytes = kChunks * kBN * 128;   // one K (or V) tile: 16 KiB
-constexpr int kStageBytes = 2 * kTensorBytes;
 constexpr int kPBytes = kBM * kBN * 2;              // 16 KiB
-constexpr int kTmemCols = 256;           // S: [0,64)  O_tile: [64,192)
+constexpr int kTmemCols = 256;           // S buffers: [0,64) [64,128)   O: [128,256)
 constexpr long long kWaitLimitCycles = 4000000000ll; // an mbarrier wait gives up after ~2 s
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -60,6 +61,9 @@ __device__ __forceinline__ void mbarInit(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbarExpectTx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbarArrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbarTryWait(uint32_t bar, uint32_t parity) {
     uint32_t done;
@@ -167,23 +171,6 @@ __device__ __forceinline__ uint32_t packPair(float lo, float hi, __half) {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&v);
 }
-// Barrier among the four softmax warps that also ORs a per-thread "my bounded wait ran out" flag, so
-// that all 128 threads leave the main loop together and nobody is left waiting at a later barrier.
-__device__ __forceinline__ bool softmaxWarpsSyncAnyFailed(bool failed) {
-    uint32_t any;
-    asm volatile(
-        "{\n"
-        ".reg .pred p, q;\n"
-        "setp.ne.u32 q, %1, 0;\n"
-        "bar.red.or.pred p, 1, %2, q;\n"
-        "selp.u32 %0, 1, 0, p;\n"
-        "}\n"
-        : "=r"(any)
-        : "r"(static_cast<uint32_t>(failed)), "n"(kSoftmaxWarps * 32)
-        : "memory");
-    return any != 0;
-}
-
 // Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
 // Offsets are in bytes; the hardware fields drop the 4 low bits.
 __device__ __forceinline__ uint64_t smemDesc(uint32_t addr, uint32_t leading_bytes, uint32_t stride_bytes) {
@@ -208,7 +195,16 @@ struct UmmaArgs {
 
 // smem layout (dynamic, 1024-aligned):
 //   [Q 32 KiB][K ring: stages x 16 KiB][V ring: stages x 16 KiB][P 16 KiB][barriers][tmem base][scan scratch]
-template <typename T>
+// TMEM columns: S buffer 0 [0,64)  S buffer 1 [64,128)  O [128,256)
+//
+// Warp roles: 0-3 softmax (thread r owns query row r = TMEM lane r), 4 TMA producer (also owns the
+// TMEM allocation), 5 MMA issuer.  They talk through mbarriers only:
+//   k_full/v_full[stage]   producer -> MMA (bytes landed)        k_empty/v_empty[stage]  MMA -> producer (tcgen05.commit)
+//   s_ready[buf]           MMA -> softmax (S retired)            s_free[buf]             softmax -> MMA (S read, 4 arrivals)
+//   p_ready                softmax -> MMA (P stored, 4 arrivals) o_done                  MMA -> softmax (P.V retired)
+// The MMA warp runs one S ahead: S(i+1) is issued before it waits for P(i), so the tensor core works on
+// the next scores while the softmax warps are busy with the current ones.
+template <typename T, int kStages>
 __global__ void __launch_bounds__(kThreads)
     pagedPrefillUmmaKernel(const __grid_constant__ CUtensorMap tmap_q,
                            const __grid_constant__ CUtensorMap tmap_k,
@@ -216,23 +212,24 @@ __global__ void __launch_bounds__(kThreads)
                            const UmmaArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr int kRingOff = kQBytes;
-    constexpr int kPOff = kRingOff + kStages * kStageBytes;
+    constexpr int kPOff = kRingOff + kStages * 2 * kTensorBytes;
     constexpr int kBarOff = kPOff + kPBytes;
     const uint32_t smem0 = smemAddr(smem_raw);
     const uint32_t q_tile = smem0;
     const uint32_t ring = smem0 + kRingOff;
     const uint32_t p_tile = smem0 + kPOff;
-    // K and V travel in separate rings: a K slot is handed back as soon as S = Q.K^T has retired, a V
-    // slot only after P.V, so the next K tile is in flight a whole softmax earlier.
     const uint32_t k_full = smem0 + kBarOff;              // [kStages]
     const uint32_t k_empty = k_full + kStages * 8;        // [kStages]
     const uint32_t v_full = k_empty + kStages * 8;        // [kStages]
     const uint32_t v_empty = v_full + kStages * 8;        // [kStages]
-    const uint32_t q_bar = v_empty + kStages * 8;
-    const uint32_t s_bar = q_bar + 8;
-    const uint32_t o_bar = s_bar + 8;
-    const uint32_t drain_bar = o_bar + 8;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + kBarOff + (4 * kStages + 4) * 8);
+    const uint32_t s_ready = v_empty + kStages * 8;       // [2]
+    const uint32_t s_free = s_ready + 16;                 // [2]
+    const uint32_t q_bar = s_free + 16;
+    const uint32_t p_ready = q_bar + 8;
+    const uint32_t o_done = p_ready + 8;
+    const uint32_t drain_bar = o_done + 8;
+    constexpr int kNumBars = 4 * kStages + 8;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + kBarOff + kNumBars * 8);
     int *scratch = reinterpret_cast<int *>(tmem_slot + 2);
     int &sh_seq = scratch[0];
     int &sh_t0 = scratch[1];
@@ -254,9 +251,13 @@ __global__ void __launch_bounds__(kThreads)
             mbarInit(v_full + s * 8, 1);
             mbarInit(v_empty + s * 8, 1);
         }
+        for (int b = 0; b < 2; ++b) {
+            mbarInit(s_ready + b * 8, 1);
+            mbarInit(s_free + b * 8, kSoftmaxWarps);
+        }
         mbarInit(q_bar, 1);
-        mbarInit(s_bar, 1);
-        mbarInit(o_bar, 1);
+        mbarInit(p_ready, kSoftmaxWarps);
+        mbarInit(o_done, 1);
         mbarInit(drain_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -327,7 +328,7 @@ __global__ void __launch_bounds__(kThreads)
     const int kv_head = head / p.group_size;
 
     // ---- TMEM: the producer warp allocates, everyone reads the base address -----------------------
-    if (warp == kSoftmaxWarps) {
+    if (warp == kProducerWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -335,11 +336,10 @@ __global__ void __launch_bounds__(kThreads)
     __syncthreads();
     tcgenFenceAfter();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base;       // 64 columns
-    const uint32_t tmem_o = tmem_base + 64;  // 128 columns
+    const uint32_t tmem_o = tmem_base + 128; // 128 columns; S buffers are columns [0,64) and [64,128)
 
-    if (warp == kSoftmaxWarps) {
-        // ================================ producer warp ==========================================
+    if (warp == kProducerWarp) {
+        // ================================ TMA producer ===========================================
         if (lane == 0) {
             mbarExpectTx(q_bar, kQBytes);
             for (int c = 0; c < kChunks; ++c) {
@@ -349,28 +349,42 @@ __global__ void __launch_bounds__(kThreads)
         const int box_rows = a.box_rows;
         const int boxes_per_tensor = (kBN / box_rows) * kChunks;
         const int box_bytes = box_rows * 128;
+        // The sequence's block-table row is read 32 entries at a time, one entry per lane, one window
+        // ahead of use, and handed to the lane that needs it with a shuffle: no table load sits
+        // between a free slot and the copies that fill it.
+        const long long bt_row = seq * p.bt_seq_stride;
+        const int last_page = (kv_end - 1) / p.block_size;
+        auto loadWindow = [&](int base) -> long long {
+            const int page = base + lane;
+            return (page <= last_page) ? loadIndex(p.block_tables, bt_row + page, p.index_is_64) : 0;
+        };
+        int win_base = 0;
+        long long win_cur = loadWindow(0);
+        long long win_next = loadWindow(32);
         int issued = 0;
         for (int kt = 0; kt < num_kv_tiles; ++kt) {
             const int stage = kt % kStages;
             const uint32_t parity = (kt / kStages) & 1;
             const int kv0 = kt * kBN;
             const int live_sub = min(kBN / box_rows, (kv_end - kv0 + box_rows - 1) / box_rows);
-            // this lane's boxes (at most 2 per lane: 2 tensors x (64 / box_rows) x 2 chunks <= 32 .. 64):
-            // resolve their block-table entries first, so the lookup latency hides behind the wait below
+            while (kv0 / p.block_size >= win_base + 32) {
+                win_base += 32;
+                win_cur = win_next;
+                win_next = loadWindow(win_base + 32);
+            }
             long long blocks[2];
             int rows0[2];
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
                 const int b = lane + u * 32;
                 const int r = (b % boxes_per_tensor) / kChunks;
-                blocks[u] = 0;
-                rows0[u] = 0;
-                if (b < 2 * boxes_per_tensor && r < live_sub) {
-                    const int j0 = kv0 + r * box_rows;
-                    const int page = j0 / p.block_size;
-                    rows0[u] = j0 - page * p.block_size;
-                    blocks[u] = loadIndex(p.block_tables, seq * p.bt_seq_stride + page, p.index_is_64);
-                }
+                const int j0 = kv0 + r * box_rows;
+                const int page = j0 / p.block_size;
+                rows0[u] = j0 - page * p.block_size;
+                const int rel = min(max(page - win_base, 0), 63);
+                const long long from_cur = __shfl_sync(0xffffffffu, win_cur, rel & 31);
+                const long long from_next = __shfl_sync(0xffffffffu, win_next, rel & 31);
+                blocks[u] = rel < 32 ? from_cur : from_next;
             }
             // K first (its slot frees after S of tile kt - kStages), then V (frees after that tile's P.V):
             // the same order in which the two slots become free.
@@ -412,172 +426,231 @@ __global__ void __launch_bounds__(kThreads)
                 (void)mbarWait(v_full + (kt % kStages) * 8, (kt / kStages) & 1);
             }
         }
+    } else if (warp == kMmaWarp) {
+        // ================================ MMA issuer (one thread) ==================================
+        if (lane == 0) {
+            constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u; // 0 = f16, 1 = bf16
+            constexpr uint32_t kIdescS = instrDesc(kFmt, 0, 0, kBM, kBN);  // Q (K-major) x K (K-major)
+            constexpr uint32_t kIdescO = instrDesc(kFmt, 0, 1, kBM, kHD);  // P (K-major) x V (MN-major)
+            // descriptors differ only in their start-address field: build one per operand and add
+            const uint64_t q_desc = smemDesc(q_tile, 16, 1024);
+            const uint64_t k_desc = smemDesc(ring, 16, 1024);
+            const uint64_t p_desc = smemDesc(p_tile, 16, 1024);
+            const uint64_t v_desc = smemDesc(ring + kStages * kTensorBytes, kBN * 128, 1024);
+            bool ok = mbarWait(q_bar, 0);
+
+            auto issueS = [&](int kt) {
+                const int stage = kt % kStages;
+                const uint32_t d = tmem_base + (kt & 1) * kBN;
+                const uint64_t kd = k_desc + ((stage * kTensorBytes) >> 4);
+#pragma unroll
+                for (int ks = 0; ks < kHD / 16; ++ks) {
+                    // 16 elements = 32 bytes inside the 128-byte swizzled row; 4 k-steps per 64-wide chunk
+                    const uint32_t qo = ((ks / 4) * (kBM * 128) + (ks % 4) * 32) >> 4;
+                    const uint32_t ko = ((ks / 4) * (kBN * 128) + (ks % 4) * 32) >> 4;
+                    ummaF16(d, q_desc + qo, kd + ko, kIdescS, ks > 0 ? 1u : 0u);
+                }
+                tcgenCommit(s_ready + (kt & 1) * 8);
+                tcgenCommit(k_empty + stage * 8); // the K slot is free once S has retired
+            };
+
+            if (ok) {
+                ok = mbarWait(k_full, 0);
+            }
+            if (ok) {
+                tcgenFenceAfter();
+                issueS(0);
+            }
+            for (int kt = 0; kt < num_kv_tiles && ok; ++kt) {
+                if (kt + 1 < num_kv_tiles) {
+                    const int nx = kt + 1;
+                    ok = mbarWait(k_full + (nx % kStages) * 8, (nx / kStages) & 1);
+                    if (ok && nx >= 2) {
+                        ok = mbarWait(s_free + (nx & 1) * 8, ((nx >> 1) - 1) & 1); // S buffer read by tile nx - 2
+                    }
+                    if (!ok) {
+                        break;
+                    }
+                    tcgenFenceAfter();
+                    issueS(nx);
+                }
+                const int stage = kt % kStages;
+                ok = mbarWait(p_ready, kt & 1) && mbarWait(v_full + stage * 8, (kt / kStages) & 1);
+                if (!ok) {
+                    break;
+                }
+                tcgenFenceAfter();
+                const uint64_t vd = v_desc + ((stage * kTensorBytes) >> 4);
+#pragma unroll
+                for (int kk = 0; kk < kBN / 16; ++kk) {
+                    ummaF16(tmem_o, p_desc + ((kk * 32) >> 4), vd + ((kk * 16 * 128) >> 4), kIdescO, (kt > 0 || kk > 0) ? 1u : 0u);
+                }
+                tcgenCommit(o_done);
+                tcgenCommit(v_empty + stage * 8); // the V slot is free once P.V has retired
+            }
+            if (!ok) {
+                sh_failed = 1;
+            }
+            // whatever was issued must retire before TMEM and shared memory are given back
+            tcgenCommit(drain_bar);
+            (void)mbarWait(drain_bar, 0);
+        }
     } else {
         // ================================ softmax warps ==========================================
-        constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u; // 0 = f16, 1 = bf16
-        constexpr uint32_t kIdescS = instrDesc(kFmt, 0, 0, kBM, kBN);  // Q (K-major) x K (K-major)
-        constexpr uint32_t kIdescO = instrDesc(kFmt, 0, 1, kBM, kHD);  // P (K-major) x V (MN-major)
         const int row = tid;                                           // tile-local query row = TMEM lane
         const int limit = cache_len + t0 + row;                        // last KV position this row may see
         const float slope_log2 = (p.alibi_slopes != nullptr) ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
         const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
+        const float c_log2 = p.scale_log2e;
 
         // Running reference maximum used for the exponentials (log2 domain) and the row sum.  The
         // reference is raised lazily, so p can reach 2^kLazyBits: far inside fp32 / bf16 / fp16 range
-        // for the products that follow (fp16 P is bounded by 2^8 * 1 = 256).
+        // for the products that follow (fp16 P is bounded by 2^8).
         constexpr float kLazyBits = 8.f;
         float m_used = 0.f, l_run = 0.f;
-        bool failed = false;
+        bool ok = true;
 
-        if (!mbarWait(q_bar, 0)) {
-            failed = true;
-        }
         for (int kt = 0; kt < num_kv_tiles; ++kt) {
             const int stage = kt % kStages;
-            const uint32_t parity = (kt / kStages) & 1;
-            const uint32_t k_tile = ring + stage * kTensorBytes;
-            const uint32_t v_tile = ring + (kStages + stage) * kTensorBytes;
             const int kv0 = kt * kBN;
             const int valid = kv_end - kv0;
+            const uint32_t tmem_s = tmem_base + (kt & 1) * kBN;
+            const uint32_t v_tile = ring + (kStages + stage) * kTensorBytes;
 
-            failed = failed || !mbarWait(k_full + stage * 8, parity);
-            if (!failed && valid < kBN) {
-                failed = !mbarWait(v_full + stage * 8, parity);
+            ok = mbarWait(s_ready + (kt & 1) * 8, (kt >> 1) & 1);
+            if (!ok) {
+                break;
             }
-            if (!failed && valid < kBN) {
+            tcgenFenceAfter();
+            float s[kBN];
+            {
+                float lo[32], hi[32];
+                tmemLoad32(tmem_s + lane_field, lo);
+                tmemLoad32(tmem_s + lane_field + 32, hi);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    s[i] = lo[i];
+                    s[32 + i] = hi[i];
+                }
+            }
+            // this warp is done with the S buffer: the MMA warp may overwrite it (tile kt + 2)
+            tcgenFenceBefore();
+            __syncwarp();
+            if (lane == 0) {
+                mbarArrive(s_free + (kt & 1) * 8);
+            }
+
+            // ---- softmax of this thread's row (log2 domain) -------------------------------------------
+            // "plain" tile: no causal cut, no ragged end, no ALiBi - the row maximum can be taken on the
+            // raw scores (scale > 0) and the scale folded into one fma per element
+            const bool plain = (kv0 + kBN - 1 <= limit) && (valid >= kBN) && (slope_log2 == 0.f) && (c_log2 > 0.f);
+            float mx;
+            if (plain) {
+                float raw = s[0];
+#pragma unroll
+                for (int j = 1; j < kBN; ++j) {
+                    raw = fmaxf(raw, s[j]);
+                }
+                mx = raw * c_log2;
+            } else {
+                mx = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < kBN; ++j) {
+                    float x = s[j] * c_log2;
+                    if (slope_log2 != 0.f) {
+                        x += slope_log2 * static_cast<float>(kv0 + j - limit);
+                    }
+                    x = (kv0 + j <= limit && j < valid) ? x : -INFINITY;
+                    s[j] = x; // already in the log2 domain
+                    mx = fmaxf(mx, x);
+                }
+            }
+            float alpha = 1.f;
+            bool rescale = false;
+            if (kt == 0) {
+                m_used = (mx == -INFINITY) ? 0.f : mx; // nothing accumulated yet: no rescale needed
+            } else if (mx > m_used + kLazyBits) {
+                alpha = fastExp2(m_used - mx);
+                m_used = mx;
+                rescale = true;
+            }
+            uint32_t pw[kBN / 2];
+            float sum = 0.f;
+            const float neg_m = -m_used;
+            if (plain) {
+#pragma unroll
+                for (int j = 0; j < kBN; j += 2) {
+                    const float p0 = fastExp2(fmaf(s[j], c_log2, neg_m));
+                    const float p1 = fastExp2(fmaf(s[j + 1], c_log2, neg_m));
+                    sum += p0 + p1;
+                    pw[j / 2] = packPair(p0, p1, T());
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < kBN; j += 2) {
+                    const float p0 = fastExp2(s[j] + neg_m);
+                    const float p1 = fastExp2(s[j + 1] + neg_m);
+                    sum += p0 + p1;
+                    pw[j / 2] = packPair(p0, p1, T());
+                }
+            }
+            l_run = l_run * alpha + sum;
+
+            // The previous tile's P.V must have retired before P (shared memory) is overwritten and
+            // before O (TMEM) is rescaled.
+            if (kt > 0) {
+                ok = mbarWait(o_done, (kt - 1) & 1);
+                if (!ok) {
+                    break;
+                }
+                tcgenFenceAfter();
+            }
+            if (__any_sync(0xffffffffu, rescale)) {
+                // warp-collective: every lane scales its own row (alpha = 1 where nothing changed)
+#pragma unroll
+                for (int c = 0; c < kHD / 32; ++c) {
+                    float o[32];
+                    tmemLoad32(tmem_o + lane_field + c * 32, o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        o[i] *= alpha;
+                    }
+                    tmemStore32(tmem_o + lane_field + c * 32, o);
+                }
+            }
+            if (valid < kBN) {
                 // V rows past the end may hold anything: zero them so that 0 * garbage stays 0
+                ok = mbarWait(v_full + stage * 8, (kt / kStages) & 1);
+                if (!ok) {
+                    break;
+                }
                 for (int idx = tid; idx < (kBN - valid) * kChunks * 8; idx += kSoftmaxWarps * 32) {
                     const int vrow = valid + idx / (kChunks * 8);
                     const int rest = idx % (kChunks * 8);
                     const uint32_t addr = v_tile + (rest / 8) * (kBN * 128) + vrow * 128 + (rest % 8) * 16;
                     asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-            // every thread has read the previous tile's S by now (it passed the P barrier below)
-            tcgenFenceBefore();
-            failed = softmaxWarpsSyncAnyFailed(failed);
-            if (failed) {
-                break;
+#pragma unroll
+            for (int c = 0; c < kBN / 8; ++c) {
+                const uint32_t addr = p_tile + row * 128 + ((c ^ (row & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pw[c * 4]), "r"(pw[c * 4 + 1]),
+                             "r"(pw[c * 4 + 2]), "r"(pw[c * 4 + 3]) : "memory");
             }
-
-            // ---- S = Q . K^T ------------------------------------------------------------------------
-            if (tid == 0) {
-                tcgenFenceAfter();
-#pragma unroll
-                for (int ks = 0; ks < kHD / 16; ++ks) {
-                    const uint32_t koff = (ks % 4) * 32; // 16 elements = 32 bytes inside the 128-byte swizzled row
-                    const uint64_t da = smemDesc(q_tile + (ks / 4) * (kBM * 128) + koff, 16, 1024);
-                    const uint64_t db = smemDesc(k_tile + (ks / 4) * (kBN * 128) + koff, 16, 1024);
-                    ummaF16(tmem_s, da, db, kIdescS, ks > 0 ? 1u : 0u);
-                }
-                tcgenCommit(s_bar);
-                tcgenCommit(k_empty + stage * 8); // the K slot is free once S has retired
-            }
-            failed = !mbarWait(s_bar, kt & 1);
-            uint32_t pw[kBN / 2];
-            float alpha = 1.f;
-            bool rescale = false;
-            if (!failed) {
-                tcgenFenceAfter();
-                // ---- softmax of this thread's row (log2 domain) ---------------------------------------
-                float s[kBN];
-                {
-                    float lo[32], hi[32];
-                    tmemLoad32(tmem_s + lane_field, lo);
-                    tmemLoad32(tmem_s + lane_field + 32, hi);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        s[i] = lo[i];
-                        s[32 + i] = hi[i];
-                    }
-                }
-                const bool need_mask = (kv0 + kBN - 1 > limit) || (valid < kBN);
-                float mx = -INFINITY;
-#pragma unroll
-                for (int j = 0; j < kBN; ++j) {
-                    float x = s[j] * p.scale_log2e;
-                    if (slope_log2 != 0.f) {
-                        x += slope_log2 * static_cast<float>(kv0 + j - limit);
-                    }
-                    if (need_mask) {
-                        x = (kv0 + j <= limit && j < valid) ? x : -INFINITY;
-                    }
-                    s[j] = x;
-                    mx = fmaxf(mx, x);
-                }
-                if (kt == 0) {
-                    m_used = (mx == -INFINITY) ? 0.f : mx; // nothing accumulated yet: no rescale needed
-                } else if (mx > m_used + kLazyBits) {
-                    alpha = fastExp2(m_used - mx);
-                    m_used = mx;
-                    rescale = true;
-                }
-                float sum = 0.f;
-#pragma unroll
-                for (int j = 0; j < kBN; j += 2) {
-                    const float p0 = fastExp2(s[j] - m_used);
-                    const float p1 = fastExp2(s[j + 1] - m_used);
-                    sum += p0 + p1;
-                    pw[j / 2] = packPair(p0, p1, T());
-                }
-                l_run = l_run * alpha + sum;
-            }
-            // The previous tile's P.V must have retired before P (shared memory) is overwritten and
-            // before O (TMEM) is rescaled.
-            if (kt > 0) {
-                failed = failed || !mbarWait(o_bar, (kt - 1) & 1);
-            }
-            failed = failed || !mbarWait(v_full + stage * 8, parity); // V of this tile has landed
-            if (!failed) {
-                tcgenFenceAfter();
-                if (__any_sync(0xffffffffu, rescale)) {
-                    // warp-collective: every lane scales its own row (alpha = 1 where nothing changed)
-#pragma unroll
-                    for (int c = 0; c < kHD / 32; ++c) {
-                        float o[32];
-                        tmemLoad32(tmem_o + lane_field + c * 32, o);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            o[i] *= alpha;
-                        }
-                        tmemStore32(tmem_o + lane_field + c * 32, o);
-                    }
-                }
-#pragma unroll
-                for (int c = 0; c < kBN / 8; ++c) {
-                    const uint32_t addr = p_tile + row * 128 + ((c ^ (row & 7)) << 4);
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pw[c * 4]), "r"(pw[c * 4 + 1]),
-                                 "r"(pw[c * 4 + 2]), "r"(pw[c * 4 + 3]) : "memory");
-                }
-            }
-            // P (generic-proxy writes) must be visible to the tensor core's async-proxy reads; the TMEM
-            // stores above must be ordered before the MMA that accumulates into O
+            // P and the zeroed V rows (generic-proxy writes) must be visible to the tensor core's
+            // async-proxy reads; the TMEM stores must be ordered before the MMA that accumulates into O
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tcgenFenceBefore();
-            failed = softmaxWarpsSyncAnyFailed(failed);
-            if (failed) {
-                break;
-            }
-
-            // ---- O += P . V ----------------------------------------------------------------------------
-            if (tid == 0) {
-                tcgenFenceAfter();
-#pragma unroll
-                for (int kk = 0; kk < kBN / 16; ++kk) {
-                    const uint64_t da = smemDesc(p_tile + kk * 32, 16, 1024);
-                    const uint64_t db = smemDesc(v_tile + kk * (16 * 128), kBN * 128, 1024);
-                    ummaF16(tmem_o, da, db, kIdescO, (kt > 0 || kk > 0) ? 1u : 0u);
-                }
-                tcgenCommit(o_bar);
-                tcgenCommit(v_empty + stage * 8); // the V slot is free once P.V has retired
+            __syncwarp();
+            if (lane == 0) {
+                mbarArrive(p_ready);
             }
         }
 
-        if (!failed) {
-            failed = !mbarWait(o_bar, (num_kv_tiles - 1) & 1);
+        if (ok) {
+            ok = mbarWait(o_done, (num_kv_tiles - 1) & 1);
         }
-        if (failed) {
+        if (!ok) {
             sh_failed = 1;
         } else {
             tcgenFenceAfter();
@@ -602,17 +675,10 @@ __global__ void __launch_bounds__(kThreads)
         }
     }
 
-    // ---- common exit ------------------------------------------------------------------------------
-    // On the normal path every MMA and every copy has been waited for.  After a failed wait something
-    // may still be in flight: give the tensor core (bounded) time to retire what was issued and let the
-    // producer's last copies land before TMEM and shared memory are given back.
-    if (tid == 0) {
-        tcgenCommit(drain_bar);
-        (void)mbarWait(drain_bar, 0);
-    }
+    // ---- common exit: every role gets here on every path; TMEM reads and MMAs are done ------------
     tcgenFenceBefore();
     __syncthreads();
-    if (warp == kSoftmaxWarps) {
+    if (warp == kProducerWarp) {
         tcgenFenceAfter();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
@@ -673,20 +739,20 @@ bool encodeQueryMap(CUtensorMap *map, const Info &info, const void *base) {
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// tiles + barriers/TMEM slot/scan scratch; two CTAs (plus 1 KiB of system shared memory each) fit one SM
-constexpr size_t kSmemBytes = kQBytes + kStages * kStageBytes + kPBytes + 256;
+// tiles + barriers / TMEM slot / scan scratch
+constexpr size_t smemBytes(int stages) { return kQBytes + static_cast<size_t>(stages) * 2 * kTensorBytes + kPBytes + 512; }
 
-template <typename T>
+template <typename T, int STAGES>
 infiniStatus_t launchTyped(const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv,
                            unsigned tiles, int device_id, cudaStream_t stream) {
     static std::mutex attr_mutex;
     static bool attr_done[64] = {};
-    auto kernel = pagedPrefillUmmaKernel<T>;
+    auto kernel = pagedPrefillUmmaKernel<T, STAGES>;
     {
         std::lock_guard<std::mutex> lock(attr_mutex);
         const bool tracked = device_id >= 0 && device_id < 64;
         if (!tracked || !attr_done[device_id]) {
-            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes)) != cudaSuccess) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes(STAGES))) != cudaSuccess) {
                 return checkLaunch("cudaFuncSetAttribute(pagedPrefillUmmaKernel)");
             }
             if (tracked) {
@@ -695,8 +761,23 @@ infiniStatus_t launchTyped(const UmmaArgs &args, const CUtensorMap &mq, const CU
         }
     }
     const dim3 grid(tiles, args.pp.d.num_heads);
-    kernel<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, args);
+    kernel<<<grid, kThreads, smemBytes(STAGES), stream>>>(mq, mk, mv, args);
     return checkLaunch("pagedPrefillUmmaKernel");
+}
+
+template <typename T>
+infiniStatus_t launchStages(int stages, const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv,
+                            unsigned tiles, int device_id, cudaStream_t stream) {
+    switch (stages) {
+    case 2:
+        return launchTyped<T, 2>(args, mq, mk, mv, tiles, device_id, stream);
+    case 3:
+        return launchTyped<T, 3>(args, mq, mk, mv, tiles, device_id, stream);
+    case 4:
+        return launchTyped<T, 4>(args, mq, mk, mv, tiles, device_id, stream);
+    default:
+        return launchTyped<T, 5>(args, mq, mk, mv, tiles, device_id, stream);
+    }
 }
 
 } // namespace
@@ -726,7 +807,15 @@ UmmaPlan planPrefillUmma(const Info &info, const DeviceProps &props) {
         || !encodeQueryMap(&probe, info, fake)) {
         return plan;
     }
-    if (kSmemBytes > props.smem_per_block_optin) {
+    // KV ring depth: 2 slots let two CTAs share an SM, 5 slots give one CTA the whole SM
+    plan.stages = 2;
+    if (const char *env = std::getenv("INFINIOP_PAGED_PREFILL_STAGES")) {
+        const int v = std::atoi(env);
+        if (v >= 2 && v <= 5) {
+            plan.stages = v;
+        }
+    }
+    if (smemBytes(plan.stages) > props.smem_per_block_optin) {
         return plan;
     }
     plan.eligible = true;
@@ -750,8 +839,8 @@ infiniStatus_t launchPrefillUmma(const Info &info, const UmmaPlan &plan, const P
     const unsigned tiles = static_cast<unsigned>((info.total_q_tokens + kBM - 1) / kBM + A.num_seqs);
     int device_id = -1;
     (void)cudaGetDevice(&device_id);
-    return A.dtype == INFINI_DTYPE_F16 ? launchTyped<__half>(args, mq, mk, mv, tiles, device_id, stream)
-                                       : launchTyped<__nv_bfloat16>(args, mq, mk, mv, tiles, device_id, stream);
+    return A.dtype == INFINI_DTYPE_F16 ? launchStages<__half>(plan.stages, args, mq, mk, mv, tiles, device_id, stream)
+                                       : launchStages<__nv_bfloat16>(plan.stages, args, mq, mk, mv, tiles, device_id, stream);
 }
 
 } // namespace b200::paged_attention_prefill
