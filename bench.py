@@ -533,7 +533,7 @@ def prefill_arm(args):
                                "(not a BASELINE config: the decode path's upstream neighbour)",
                    "l2": "K/V of one prompt (8 MiB per kv-head group) is re-read from L2 by design; q/out stream once"},
         "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak, "traffic": None,
-                     "peak_kind": f"of {kind}", "kernel": "pagedPrefillTileKernel", "algorithmic_flops_per_launch": case.flops},
+                     "peak_kind": f"of {kind}", "kernel": "pagedPrefillUmmaKernel", "algorithmic_flops_per_launch": case.flops},
         "gpu_launches": K, "clocks": clocks,
     }), flush=True)
 

@@ -43,15 +43,10 @@ using paged_attention::loadIndex;
 constexpr int kHD = 128;
 constexpr int kBM = 128;                 // query rows per CTA = MMA M
 constexpr int kBN = 64;                  // KV tokens per stage = MMA N of S, K extent of P.V
-constexpr int kSoftmaxWarps = 4;
-constexpr int kProducerWarp = 4;
-constexpr int kMmaWarp = 5;
-constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
 constexpr int kChunks = kHD / 64;        // 128-byte column chunks per row
 constexpr int kQBytes = kChunks * kBM * 128;        // 32 KiB
 constexpr int kTensorBytes = kChunks * kBN * 128;   // one K (or V) tile: 16 KiB
 constexpr int kPBytes = kBM * kBN * 2;              // 16 KiB
-constexpr int kTmemCols = 256;           // S buffers: [0,64) [64,128)   O: [128,256)
 constexpr long long kWaitLimitCycles = 4000000000ll; // an mbarrier wait gives up after ~2 s
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -106,10 +101,37 @@ __device__ __forceinline__ void tmaLoad3d(uint32_t dst, const CUtensorMap *map, 
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
 }
+// Shared memory -> global through a tensor map (clipped at the tensor's bounds); completion is tracked
+// by the issuing thread's bulk-async group.
+__device__ __forceinline__ void tmaStore3d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tmaStoreCommitAndWaitRead() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void prefetchTensorMap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
 __device__ __forceinline__ void tcgenFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgenFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgenCommit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool electOne() {
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
 }
 // D[tmem] (+)= A[smem desc] * B[smem desc]; one thread issues it
 __device__ __forceinline__ void ummaF16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -158,6 +180,61 @@ __device__ __forceinline__ void tmemStore32(uint32_t taddr, const float (&v)[32]
         : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+// 64 consecutive fp32 columns of this thread's TMEM lane: both loads in flight, then one wait.  The
+// wait names the registers so that nothing reads them before it.
+__device__ __forceinline__ void tmemLoad64(uint32_t taddr, float (&v)[64]) {
+    uint32_t r[64];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t *q = r + 32 * h;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3]), "=r"(q[4]), "=r"(q[5]), "=r"(q[6]), "=r"(q[7]),
+              "=r"(q[8]), "=r"(q[9]), "=r"(q[10]), "=r"(q[11]), "=r"(q[12]), "=r"(q[13]), "=r"(q[14]), "=r"(q[15]),
+              "=r"(q[16]), "=r"(q[17]), "=r"(q[18]), "=r"(q[19]), "=r"(q[20]), "=r"(q[21]), "=r"(q[22]), "=r"(q[23]),
+              "=r"(q[24]), "=r"(q[25]), "=r"(q[26]), "=r"(q[27]), "=r"(q[28]), "=r"(q[29]), "=r"(q[30]), "=r"(q[31])
+            : "r"(taddr + 32 * h)
+            : "memory");
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t *q = r + 32 * h;
+        asm volatile(
+            "tcgen05.wait::ld.sync.aligned;"
+            : "+r"(q[0]), "+r"(q[1]), "+r"(q[2]), "+r"(q[3]), "+r"(q[4]), "+r"(q[5]), "+r"(q[6]), "+r"(q[7]),
+              "+r"(q[8]), "+r"(q[9]), "+r"(q[10]), "+r"(q[11]), "+r"(q[12]), "+r"(q[13]), "+r"(q[14]), "+r"(q[15]),
+              "+r"(q[16]), "+r"(q[17]), "+r"(q[18]), "+r"(q[19]), "+r"(q[20]), "+r"(q[21]), "+r"(q[22]), "+r"(q[23]),
+              "+r"(q[24]), "+r"(q[25]), "+r"(q[26]), "+r"(q[27]), "+r"(q[28]), "+r"(q[29]), "+r"(q[30]), "+r"(q[31])
+            :
+            : "memory");
+    }
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+        v[i] = __uint_as_float(r[i]);
+    }
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// Maximum of 64 values in 32 three-input instructions, 5 levels deep.
+__device__ __forceinline__ float rowMax64(const float (&s)[64]) {
+    float a[22], b[8];
+#pragma unroll
+    for (int j = 0; j < 21; ++j) {
+        a[j] = max3(s[3 * j], s[3 * j + 1], s[3 * j + 2]);
+    }
+    a[21] = s[63];
+#pragma unroll
+    for (int j = 0; j < 7; ++j) {
+        b[j] = max3(a[3 * j], a[3 * j + 1], a[3 * j + 2]);
+    }
+    b[7] = a[21];
+    return max3(max3(b[0], b[1], b[2]), max3(b[3], b[4], b[5]), fmaxf(b[6], b[7]));
+}
 __device__ __forceinline__ float fastExp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -190,45 +267,62 @@ __host__ __device__ constexpr uint32_t instrDesc(uint32_t fmt, uint32_t a_mn_maj
 
 struct UmmaArgs {
     PrefillParams pp;
-    int box_rows; // rows of one K/V TMA box: 16 when block_size % 16 == 0, else 8
+    int box_rows;  // rows of one K/V TMA box: the largest of 64, 32, 16, 8 that divides block_size
+    int tma_store; // out's strides allow a tensor map: full tiles leave through shared memory and one bulk store
 };
 
 // smem layout (dynamic, 1024-aligned):
-//   [Q 32 KiB][K ring: stages x 16 KiB][V ring: stages x 16 KiB][P 16 KiB][barriers][tmem base][scan scratch]
-// TMEM columns: S buffer 0 [0,64)  S buffer 1 [64,128)  O [128,256)
+//   [Q: kQ x 32 KiB][K ring: stages x 16 KiB][V ring: stages x 16 KiB][P: kQ x 16 KiB][barriers][tmem base][scratch]
+// TMEM columns of q-tile i (base + i * 256): S buffer 0 [0,64)  S buffer 1 [64,128)  O [128,256)
 //
-// Warp roles: 0-3 softmax (thread r owns query row r = TMEM lane r), 4 TMA producer (also owns the
-// TMEM allocation), 5 MMA issuer.  They talk through mbarriers only:
-//   k_full/v_full[stage]   producer -> MMA (bytes landed)        k_empty/v_empty[stage]  MMA -> producer (tcgen05.commit)
-//   s_ready[buf]           MMA -> softmax (S retired)            s_free[buf]             softmax -> MMA (S read, 4 arrivals)
-//   p_ready                softmax -> MMA (P stored, 4 arrivals) o_done                  MMA -> softmax (P.V retired)
-// The MMA warp runs one S ahead: S(i+1) is issued before it waits for P(i), so the tensor core works on
+// kQ q-heads of one GQA group (same 128 token rows) share every staged KV tile: with kQ = 2 each
+// byte brought in from L2 feeds twice the math and eight softmax warps keep the special-function
+// units busy while the tensor core works.  kQ = 1 is the same kernel for odd group sizes.
+//
+// Warp roles: softmax warps [0, 4 kQ) (warp w serves q-tile w / 4; thread owns query row
+// (w % 4) * 32 + lane = its TMEM lane), then kQ MMA-issuing warps (one per q-tile; the first also owns
+// the TMEM allocation) and 2 kQ TMA producer warps (each stages its share of every K/V tile's pages, so
+// neither the copies' issue cost nor the tensor-core instructions' issue cost sits in one warp).
+// They talk through mbarriers only:
+//   k_full/v_full[stage]   producers -> MMA (bytes landed; one arrival per producer warp)
+//   k_empty/v_empty[stage] MMA -> producers (tcgen05.commit, one per MMA warp)
+//   s_ready[i][buf]        MMA i -> softmax i (S retired)           s_free[i][buf]  softmax i -> MMA i (S read, 4 arrivals)
+//   p_ready[i]             softmax i -> MMA i (P stored, 4 arrivals) o_done[i]      MMA i -> softmax i (P.V retired)
+// An MMA warp runs one S ahead: S(t+1) is issued before it waits for P(t), so the tensor core works on
 // the next scores while the softmax warps are busy with the current ones.
-template <typename T, int kStages>
-__global__ void __launch_bounds__(kThreads)
+template <typename T, int kStages, int kQ>
+__global__ void __launch_bounds__((7 * kQ) * 32)
     pagedPrefillUmmaKernel(const __grid_constant__ CUtensorMap tmap_q,
                            const __grid_constant__ CUtensorMap tmap_k,
                            const __grid_constant__ CUtensorMap tmap_v,
+                           const __grid_constant__ CUtensorMap tmap_o,
                            const UmmaArgs a) {
+    constexpr int kSoftmaxWarpsAll = 4 * kQ;
+    constexpr int kMmaWarp0 = kSoftmaxWarpsAll;      // MMA warps [4 kQ, 5 kQ)
+    constexpr int kProducers = 2 * kQ;
+    constexpr int kProducerWarp0 = 5 * kQ;           // producer warps [5 kQ, 7 kQ)
+    constexpr int kNT = 7 * kQ * 32;
+    constexpr int kTmemCols = 256 * kQ;
+
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    constexpr int kRingOff = kQBytes;
+    constexpr int kRingOff = kQ * kQBytes;
     constexpr int kPOff = kRingOff + kStages * 2 * kTensorBytes;
-    constexpr int kBarOff = kPOff + kPBytes;
+    constexpr int kBarOff = kPOff + kQ * kPBytes;
     const uint32_t smem0 = smemAddr(smem_raw);
-    const uint32_t q_tile = smem0;
+    const uint32_t q_tiles = smem0;
     const uint32_t ring = smem0 + kRingOff;
-    const uint32_t p_tile = smem0 + kPOff;
+    const uint32_t p_tiles = smem0 + kPOff;
     const uint32_t k_full = smem0 + kBarOff;              // [kStages]
     const uint32_t k_empty = k_full + kStages * 8;        // [kStages]
     const uint32_t v_full = k_empty + kStages * 8;        // [kStages]
     const uint32_t v_empty = v_full + kStages * 8;        // [kStages]
-    const uint32_t s_ready = v_empty + kStages * 8;       // [2]
-    const uint32_t s_free = s_ready + 16;                 // [2]
-    const uint32_t q_bar = s_free + 16;
-    const uint32_t p_ready = q_bar + 8;
-    const uint32_t o_done = p_ready + 8;
-    const uint32_t drain_bar = o_done + 8;
-    constexpr int kNumBars = 4 * kStages + 8;
+    const uint32_t s_ready = v_empty + kStages * 8;       // [kQ][2]
+    const uint32_t s_free = s_ready + kQ * 16;            // [kQ][2]
+    const uint32_t p_ready = s_free + kQ * 16;            // [kQ]
+    const uint32_t o_done = p_ready + kQ * 8;             // [kQ]
+    const uint32_t drain_bar = o_done + kQ * 8;           // [kQ]
+    const uint32_t q_bar = drain_bar + kQ * 8;
+    constexpr int kNumBars = 4 * kStages + 7 * kQ + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + kBarOff + kNumBars * 8);
     int *scratch = reinterpret_cast<int *>(tmem_slot + 2);
     int &sh_seq = scratch[0];
@@ -241,24 +335,29 @@ __global__ void __launch_bounds__(kThreads)
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const int head = blockIdx.y;
+    const int head0 = blockIdx.y * kQ; // first q-head of this CTA; all kQ heads read the same kv-head
     const int tile_id = blockIdx.x;
 
     if (tid == 0) {
+        prefetchTensorMap(&tmap_q);
+        prefetchTensorMap(&tmap_k);
+        prefetchTensorMap(&tmap_v);
         for (int s = 0; s < kStages; ++s) {
-            mbarInit(k_full + s * 8, 1);
-            mbarInit(k_empty + s * 8, 1);
-            mbarInit(v_full + s * 8, 1);
-            mbarInit(v_empty + s * 8, 1);
+            mbarInit(k_full + s * 8, kProducers);
+            mbarInit(k_empty + s * 8, kQ);
+            mbarInit(v_full + s * 8, kProducers);
+            mbarInit(v_empty + s * 8, kQ);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbarInit(s_ready + b * 8, 1);
-            mbarInit(s_free + b * 8, kSoftmaxWarps);
+        for (int i = 0; i < kQ; ++i) {
+            for (int b = 0; b < 2; ++b) {
+                mbarInit(s_ready + (i * 2 + b) * 8, 1);
+                mbarInit(s_free + (i * 2 + b) * 8, 4);
+            }
+            mbarInit(p_ready + i * 8, 4);
+            mbarInit(o_done + i * 8, 1);
+            mbarInit(drain_bar + i * 8, 1);
         }
         mbarInit(q_bar, 1);
-        mbarInit(p_ready, kSoftmaxWarps);
-        mbarInit(o_done, 1);
-        mbarInit(drain_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         sh_found = 0;
@@ -269,7 +368,7 @@ __global__ void __launch_bounds__(kThreads)
     // ---- which (sequence, first new token) is this tile? (before any TMEM is held) ----------------
     {
         int carry = 0;
-        for (int base = 0; base < p.num_seqs; base += kThreads) {
+        for (int base = 0; base < p.num_seqs; base += kNT) {
             const int i = base + tid;
             int tiles = 0;
             if (i < p.num_seqs) {
@@ -290,7 +389,7 @@ __global__ void __launch_bounds__(kThreads)
             __syncthreads();
             int prev = 0, total = 0;
 #pragma unroll
-            for (int w = 0; w < kThreads / 32; ++w) {
+            for (int w = 0; w < kNT / 32; ++w) {
                 prev += (w < warp) ? sh_warp_tot[w] : 0;
                 total += sh_warp_tot[w];
             }
@@ -325,10 +424,10 @@ __global__ void __launch_bounds__(kThreads)
         return;
     }
     const int num_kv_tiles = (kv_end + kBN - 1) / kBN;
-    const int kv_head = head / p.group_size;
+    const int kv_head = head0 / p.group_size;
 
-    // ---- TMEM: the producer warp allocates, everyone reads the base address -----------------------
-    if (warp == kProducerWarp) {
+    // ---- TMEM: the first MMA warp allocates, everyone reads the base address ----------------------
+    if (warp == kMmaWarp0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -336,171 +435,184 @@ __global__ void __launch_bounds__(kThreads)
     __syncthreads();
     tcgenFenceAfter();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_o = tmem_base + 128; // 128 columns; S buffers are columns [0,64) and [64,128)
 
-    if (warp == kProducerWarp) {
-        // ================================ TMA producer ===========================================
-        if (lane == 0) {
-            mbarExpectTx(q_bar, kQBytes);
-            for (int c = 0; c < kChunks; ++c) {
-                tmaLoad3d(q_tile + c * (kBM * 128), &tmap_q, q_bar, c * 64, head, static_cast<int>(q_begin + t0));
+    if (warp >= kProducerWarp0) {
+        // ================================ TMA producers ==========================================
+        // A K/V tile is kBN / box_rows boxes of rows (one page or part of one) times kChunks column
+        // chunks, per tensor.  Producer r takes row groups r, r + kProducers, ...; inside the warp one
+        // lane owns one (row group, chunk) box, looks its page up in the block table one tile ahead
+        // and issues the K copy and the V copy of that box.
+        const int r = warp - kProducerWarp0;
+        if (r == 0 && lane == 0) {
+            mbarExpectTx(q_bar, kQ * kQBytes);
+            for (int i = 0; i < kQ; ++i) {
+                for (int c = 0; c < kChunks; ++c) {
+                    tmaLoad3d(q_tiles + i * kQBytes + c * (kBM * 128), &tmap_q, q_bar, c * 64, head0 + i, static_cast<int>(q_begin + t0));
+                }
             }
         }
         const int box_rows = a.box_rows;
-        const int boxes_per_tensor = (kBN / box_rows) * kChunks;
-        const int box_bytes = box_rows * 128;
-        // The sequence's block-table row is read 32 entries at a time, one entry per lane, one window
-        // ahead of use, and handed to the lane that needs it with a shuffle: no table load sits
-        // between a free slot and the copies that fill it.
+        const int groups = kBN / box_rows;                   // row groups per tile
+        const uint32_t box_bytes = static_cast<uint32_t>(box_rows) * 128u;
+        const int my_group = r + (lane / kChunks) * kProducers;
+        const int my_chunk = lane % kChunks;
+        const bool has_box = my_group < groups;
         const long long bt_row = seq * p.bt_seq_stride;
-        const int last_page = (kv_end - 1) / p.block_size;
-        auto loadWindow = [&](int base) -> long long {
-            const int page = base + lane;
-            return (page <= last_page) ? loadIndex(p.block_tables, bt_row + page, p.index_is_64) : 0;
+        // (block, first row inside it) of this lane's box in tile kt; block < 0: nothing to copy
+        auto locateBox = [&](int kt, long long &block, int &row0) {
+            const int j0 = kt * kBN + my_group * box_rows;
+            block = -1;
+            row0 = 0;
+            if (has_box && kt < num_kv_tiles && j0 < kv_end) {
+                const int page = j0 / p.block_size;
+                row0 = j0 - page * p.block_size;
+                block = loadIndex(p.block_tables, bt_row + page, p.index_is_64);
+            }
         };
-        int win_base = 0;
-        long long win_cur = loadWindow(0);
-        long long win_next = loadWindow(32);
+        long long block_next;
+        int row0_next;
+        locateBox(0, block_next, row0_next);
         int issued = 0;
+        bool ok = true;
         for (int kt = 0; kt < num_kv_tiles; ++kt) {
             const int stage = kt % kStages;
             const uint32_t parity = (kt / kStages) & 1;
-            const int kv0 = kt * kBN;
-            const int live_sub = min(kBN / box_rows, (kv_end - kv0 + box_rows - 1) / box_rows);
-            while (kv0 / p.block_size >= win_base + 32) {
-                win_base += 32;
-                win_cur = win_next;
-                win_next = loadWindow(win_base + 32);
-            }
-            long long blocks[2];
-            int rows0[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int b = lane + u * 32;
-                const int r = (b % boxes_per_tensor) / kChunks;
-                const int j0 = kv0 + r * box_rows;
-                const int page = j0 / p.block_size;
-                rows0[u] = j0 - page * p.block_size;
-                const int rel = min(max(page - win_base, 0), 63);
-                const long long from_cur = __shfl_sync(0xffffffffu, win_cur, rel & 31);
-                const long long from_next = __shfl_sync(0xffffffffu, win_next, rel & 31);
-                blocks[u] = rel < 32 ? from_cur : from_next;
-            }
+            const long long block = block_next;
+            const int row0 = row0_next;
+            locateBox(kt + 1, block_next, row0_next);       // in flight while this tile's copies are issued
+            const bool live = block >= 0;
+            const uint32_t bytes = static_cast<uint32_t>(__popc(__ballot_sync(0xffffffffu, live))) * box_bytes;
             // K first (its slot frees after S of tile kt - kStages), then V (frees after that tile's P.V):
             // the same order in which the two slots become free.
-            bool ok = true;
 #pragma unroll
             for (int is_v = 0; is_v < 2; ++is_v) {
                 const uint32_t full = (is_v ? v_full : k_full) + stage * 8;
                 const uint32_t empty = (is_v ? v_empty : k_empty) + stage * 8;
-                if (kt >= kStages && !mbarWait(empty, parity ^ 1u)) {
-                    ok = false;
-                    break;
+                if (kt >= kStages) {
+                    ok = __all_sync(0xffffffffu, mbarWait(empty, parity ^ 1u));
+                    if (!ok) {
+                        break;
+                    }
                 }
-                const uint32_t dst = ring + (is_v * kStages + stage) * kTensorBytes;
                 if (lane == 0) {
-                    mbarExpectTx(full, static_cast<uint32_t>(live_sub * kChunks * box_bytes));
+                    mbarExpectTx(full, bytes); // this warp's arrival, announcing its share of the tile
                 }
                 __syncwarp();
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int b = lane + u * 32;
-                    const int r = (b % boxes_per_tensor) / kChunks;
-                    const int c = b % kChunks;
-                    if (b < 2 * boxes_per_tensor && b / boxes_per_tensor == is_v && r < live_sub) {
-                        tmaLoad4d(dst + c * (kBN * 128) + r * box_bytes, is_v ? &tmap_v : &tmap_k, full, c * 64, rows0[u],
-                                  kv_head, static_cast<int>(blocks[u]));
-                    }
+                if (live) {
+                    const uint32_t dst = ring + (is_v * kStages + stage) * kTensorBytes + my_chunk * (kBN * 128)
+                                         + my_group * box_bytes;
+                    tmaLoad4d(dst, is_v ? &tmap_v : &tmap_k, full, my_chunk * 64, row0, kv_head, static_cast<int>(block));
                 }
             }
             if (!ok) {
-                sh_failed = 1;
                 break;
             }
             issued = kt + 1;
         }
-        if (sh_failed) {
+        if (!ok) {
+            sh_failed = 1;
             // bounded wait for the copies of the last (up to kStages) tiles this warp issued
             for (int kt = max(0, issued - kStages); kt < issued; ++kt) {
                 (void)mbarWait(k_full + (kt % kStages) * 8, (kt / kStages) & 1);
                 (void)mbarWait(v_full + (kt % kStages) * 8, (kt / kStages) & 1);
             }
         }
-    } else if (warp == kMmaWarp) {
-        // ================================ MMA issuer (one thread) ==================================
-        if (lane == 0) {
+    } else if (warp >= kMmaWarp0) {
+        // ================================ MMA issuers ==============================================
+        // One warp per q-tile.  The whole warp walks the loop in step and waits on the barriers; one
+        // elected lane issues the tensor-core instructions.
+        {
+            const int i = warp - kMmaWarp0;
             constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u; // 0 = f16, 1 = bf16
             constexpr uint32_t kIdescS = instrDesc(kFmt, 0, 0, kBM, kBN);  // Q (K-major) x K (K-major)
             constexpr uint32_t kIdescO = instrDesc(kFmt, 0, 1, kBM, kHD);  // P (K-major) x V (MN-major)
             // descriptors differ only in their start-address field: build one per operand and add
-            const uint64_t q_desc = smemDesc(q_tile, 16, 1024);
+            const uint64_t q_desc = smemDesc(q_tiles + i * kQBytes, 16, 1024);
             const uint64_t k_desc = smemDesc(ring, 16, 1024);
-            const uint64_t p_desc = smemDesc(p_tile, 16, 1024);
+            const uint64_t p_desc = smemDesc(p_tiles + i * kPBytes, 16, 1024);
             const uint64_t v_desc = smemDesc(ring + kStages * kTensorBytes, kBN * 128, 1024);
-            bool ok = mbarWait(q_bar, 0);
+            const uint32_t tmem_q = __shfl_sync(0xffffffffu, tmem_base, 0) + i * 256;
+            const uint32_t my_s_ready = s_ready + i * 16, my_s_free = s_free + i * 16;
+            auto waitAll = [&](uint32_t bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbarWait(bar, parity)); };
+            bool ok = waitAll(q_bar, 0);
 
-            auto issueS = [&](int kt) {
+            // S(kt); false if a bounded wait ran out
+            auto issueS = [&](int kt) -> bool {
                 const int stage = kt % kStages;
-                const uint32_t d = tmem_base + (kt & 1) * kBN;
-                const uint64_t kd = k_desc + ((stage * kTensorBytes) >> 4);
-#pragma unroll
-                for (int ks = 0; ks < kHD / 16; ++ks) {
-                    // 16 elements = 32 bytes inside the 128-byte swizzled row; 4 k-steps per 64-wide chunk
-                    const uint32_t qo = ((ks / 4) * (kBM * 128) + (ks % 4) * 32) >> 4;
-                    const uint32_t ko = ((ks / 4) * (kBN * 128) + (ks % 4) * 32) >> 4;
-                    ummaF16(d, q_desc + qo, kd + ko, kIdescS, ks > 0 ? 1u : 0u);
+                if (!waitAll(k_full + stage * 8, (kt / kStages) & 1)) {
+                    return false;
                 }
-                tcgenCommit(s_ready + (kt & 1) * 8);
-                tcgenCommit(k_empty + stage * 8); // the K slot is free once S has retired
+                if (kt >= 2 && !waitAll(my_s_free + (kt & 1) * 8, ((kt >> 1) - 1) & 1)) { // S buffer read by tile kt - 2
+                    return false;
+                }
+                tcgenFenceAfter();
+                const uint64_t kd = k_desc + ((stage * kTensorBytes) >> 4);
+                const uint32_t d = tmem_q + (kt & 1) * kBN;
+                if (electOne()) {
+#pragma unroll
+                    for (int ks = 0; ks < kHD / 16; ++ks) {
+                        // 16 elements = 32 bytes inside the 128-byte swizzled row; 4 k-steps per 64-wide chunk
+                        const uint32_t qo = ((ks / 4) * (kBM * 128) + (ks % 4) * 32) >> 4;
+                        const uint32_t ko = ((ks / 4) * (kBN * 128) + (ks % 4) * 32) >> 4;
+                        ummaF16(d, q_desc + qo, kd + ko, kIdescS, ks > 0 ? 1u : 0u);
+                    }
+                    tcgenCommit(my_s_ready + (kt & 1) * 8);
+                    tcgenCommit(k_empty + stage * 8); // the K slot is free once every q-tile's S has retired
+                }
+                __syncwarp();
+                return true;
             };
 
-            if (ok) {
-                ok = mbarWait(k_full, 0);
-            }
-            if (ok) {
-                tcgenFenceAfter();
-                issueS(0);
-            }
+            ok = ok && issueS(0);
             for (int kt = 0; kt < num_kv_tiles && ok; ++kt) {
                 if (kt + 1 < num_kv_tiles) {
-                    const int nx = kt + 1;
-                    ok = mbarWait(k_full + (nx % kStages) * 8, (nx / kStages) & 1);
-                    if (ok && nx >= 2) {
-                        ok = mbarWait(s_free + (nx & 1) * 8, ((nx >> 1) - 1) & 1); // S buffer read by tile nx - 2
-                    }
+                    ok = issueS(kt + 1);
                     if (!ok) {
                         break;
                     }
-                    tcgenFenceAfter();
-                    issueS(nx);
                 }
                 const int stage = kt % kStages;
-                ok = mbarWait(p_ready, kt & 1) && mbarWait(v_full + stage * 8, (kt / kStages) & 1);
+                ok = waitAll(v_full + stage * 8, (kt / kStages) & 1) && waitAll(p_ready + i * 8, kt & 1);
                 if (!ok) {
                     break;
                 }
                 tcgenFenceAfter();
                 const uint64_t vd = v_desc + ((stage * kTensorBytes) >> 4);
+                if (electOne()) {
 #pragma unroll
-                for (int kk = 0; kk < kBN / 16; ++kk) {
-                    ummaF16(tmem_o, p_desc + ((kk * 32) >> 4), vd + ((kk * 16 * 128) >> 4), kIdescO, (kt > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < kBN / 16; ++kk) {
+                        ummaF16(tmem_q + 128, p_desc + ((kk * 32) >> 4), vd + ((kk * 16 * 128) >> 4), kIdescO,
+                                (kt > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    tcgenCommit(o_done + i * 8);
+                    tcgenCommit(v_empty + stage * 8); // the V slot is free once every q-tile's P.V has retired
                 }
-                tcgenCommit(o_done);
-                tcgenCommit(v_empty + stage * 8); // the V slot is free once P.V has retired
+                __syncwarp();
             }
             if (!ok) {
                 sh_failed = 1;
             }
-            // whatever was issued must retire before TMEM and shared memory are given back
-            tcgenCommit(drain_bar);
-            (void)mbarWait(drain_bar, 0);
+            // whatever this warp issued must retire before TMEM and shared memory are given back
+            if (electOne()) {
+                tcgenCommit(drain_bar + i * 8);
+            }
+            __syncwarp();
+            (void)waitAll(drain_bar + i * 8, 0);
         }
     } else {
         // ================================ softmax warps ==========================================
-        const int row = tid;                                           // tile-local query row = TMEM lane
+        const int qi = warp >> 2;                                      // q-tile (= q-head of the pair) this warp serves
+        const int row = (warp & 3) * 32 + lane;                        // tile-local query row = TMEM lane
+        const int head = head0 + qi;
         const int limit = cache_len + t0 + row;                        // last KV position this row may see
         const float slope_log2 = (p.alibi_slopes != nullptr) ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
-        const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
+        const uint32_t lane_field = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t tmem_q = tmem_base + qi * 256;
+        const uint32_t tmem_o = tmem_q + 128;
+        const uint32_t p_tile = p_tiles + qi * kPBytes;
+        const uint32_t my_s_ready = s_ready + qi * 16, my_s_free = s_free + qi * 16;
+        const uint32_t my_p_ready = p_ready + qi * 8, my_o_done = o_done + qi * 8;
+        const int gtid = tid & 127;                                    // thread index within this q-tile's four warps
         const float c_log2 = p.scale_log2e;
 
         // Running reference maximum used for the exponentials (log2 domain) and the row sum.  The
@@ -514,44 +626,31 @@ __global__ void __launch_bounds__(kThreads)
             const int stage = kt % kStages;
             const int kv0 = kt * kBN;
             const int valid = kv_end - kv0;
-            const uint32_t tmem_s = tmem_base + (kt & 1) * kBN;
+            const uint32_t tmem_s = tmem_q + (kt & 1) * kBN;
             const uint32_t v_tile = ring + (kStages + stage) * kTensorBytes;
 
-            ok = mbarWait(s_ready + (kt & 1) * 8, (kt >> 1) & 1);
+            ok = mbarWait(my_s_ready + (kt & 1) * 8, (kt >> 1) & 1);
             if (!ok) {
                 break;
             }
             tcgenFenceAfter();
             float s[kBN];
-            {
-                float lo[32], hi[32];
-                tmemLoad32(tmem_s + lane_field, lo);
-                tmemLoad32(tmem_s + lane_field + 32, hi);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    s[i] = lo[i];
-                    s[32 + i] = hi[i];
-                }
-            }
+            tmemLoad64(tmem_s + lane_field, s);
             // this warp is done with the S buffer: the MMA warp may overwrite it (tile kt + 2)
             tcgenFenceBefore();
             __syncwarp();
             if (lane == 0) {
-                mbarArrive(s_free + (kt & 1) * 8);
+                mbarArrive(my_s_free + (kt & 1) * 8);
             }
 
             // ---- softmax of this thread's row (log2 domain) -------------------------------------------
-            // "plain" tile: no causal cut, no ragged end, no ALiBi - the row maximum can be taken on the
-            // raw scores (scale > 0) and the scale folded into one fma per element
-            const bool plain = (kv0 + kBN - 1 <= limit) && (valid >= kBN) && (slope_log2 == 0.f) && (c_log2 > 0.f);
+            // "plain" tile (the same answer for every row of the CTA): no causal cut, no ragged end, no
+            // ALiBi - the scale (> 0) folds into one fma per element and the row maximum can be taken on
+            // the raw scores.
+            const bool plain = (kv0 + kBN - 1 <= cache_len + t0) && (valid >= kBN) && (slope_log2 == 0.f) && (c_log2 > 0.f);
             float mx;
             if (plain) {
-                float raw = s[0];
-#pragma unroll
-                for (int j = 1; j < kBN; ++j) {
-                    raw = fmaxf(raw, s[j]);
-                }
-                mx = raw * c_log2;
+                mx = rowMax64(s) * c_log2;
             } else {
                 mx = -INFINITY;
 #pragma unroll
@@ -574,32 +673,23 @@ __global__ void __launch_bounds__(kThreads)
                 m_used = mx;
                 rescale = true;
             }
+            // p_j = 2^(x_j - m); x_j = s_j * scale (plain) or s_j already transformed
             uint32_t pw[kBN / 2];
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             const float neg_m = -m_used;
-            if (plain) {
 #pragma unroll
-                for (int j = 0; j < kBN; j += 2) {
-                    const float p0 = fastExp2(fmaf(s[j], c_log2, neg_m));
-                    const float p1 = fastExp2(fmaf(s[j + 1], c_log2, neg_m));
-                    sum += p0 + p1;
-                    pw[j / 2] = packPair(p0, p1, T());
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < kBN; j += 2) {
-                    const float p0 = fastExp2(s[j] + neg_m);
-                    const float p1 = fastExp2(s[j + 1] + neg_m);
-                    sum += p0 + p1;
-                    pw[j / 2] = packPair(p0, p1, T());
-                }
+            for (int j = 0; j < kBN; j += 2) {
+                const float p0 = fastExp2(plain ? fmaf(s[j], c_log2, neg_m) : s[j] + neg_m);
+                const float p1 = fastExp2(plain ? fmaf(s[j + 1], c_log2, neg_m) : s[j + 1] + neg_m);
+                sum4[(j >> 1) & 3] += p0 + p1;
+                pw[j / 2] = packPair(p0, p1, T());
             }
-            l_run = l_run * alpha + sum;
+            l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
 
             // The previous tile's P.V must have retired before P (shared memory) is overwritten and
             // before O (TMEM) is rescaled.
             if (kt > 0) {
-                ok = mbarWait(o_done, (kt - 1) & 1);
+                ok = mbarWait(my_o_done, (kt - 1) & 1);
                 if (!ok) {
                     break;
                 }
@@ -619,12 +709,13 @@ __global__ void __launch_bounds__(kThreads)
                 }
             }
             if (valid < kBN) {
-                // V rows past the end may hold anything: zero them so that 0 * garbage stays 0
+                // V rows past the end may hold anything: zero them so that 0 * garbage stays 0.  Every
+                // q-tile's warps zero all of them (the tiles do not wait for one another).
                 ok = mbarWait(v_full + stage * 8, (kt / kStages) & 1);
                 if (!ok) {
                     break;
                 }
-                for (int idx = tid; idx < (kBN - valid) * kChunks * 8; idx += kSoftmaxWarps * 32) {
+                for (int idx = gtid; idx < (kBN - valid) * kChunks * 8; idx += 128) {
                     const int vrow = valid + idx / (kChunks * 8);
                     const int rest = idx % (kChunks * 8);
                     const uint32_t addr = v_tile + (rest / 8) * (kBN * 128) + vrow * 128 + (rest % 8) * 16;
@@ -643,34 +734,55 @@ __global__ void __launch_bounds__(kThreads)
             tcgenFenceBefore();
             __syncwarp();
             if (lane == 0) {
-                mbarArrive(p_ready);
+                mbarArrive(my_p_ready);
             }
         }
 
         if (ok) {
-            ok = mbarWait(o_done, (num_kv_tiles - 1) & 1);
+            ok = mbarWait(my_o_done, (num_kv_tiles - 1) & 1);
         }
         if (!ok) {
             sh_failed = 1;
-        } else {
-            tcgenFenceAfter();
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            T *out = static_cast<T *>(p.out) + (q_begin + t0 + row) * p.o_seq_stride + head * p.o_head_stride;
+        }
+        tcgenFenceAfter();
+        const float inv = (ok && l_run > 0.f) ? 1.f / l_run : 0.f;
+        // A tile whose 128 rows all belong to this sequence (or run past the end of the tensor, where
+        // the store is clipped) leaves through shared memory - the Q tile's, free by now, in the same
+        // swizzled layout - and one bulk tensor store per 64 columns: full lines instead of 16 bytes
+        // per row per instruction.  A partial tile is written row by row.
+        const bool bulk = a.tma_store != 0 && (rows_valid == kBM || q_begin + t0 + rows_valid == a.pp.total_q);
+        T *out = static_cast<T *>(p.out) + (q_begin + t0 + row) * p.o_seq_stride + head * p.o_head_stride;
+        const uint32_t o_stage = q_tiles + qi * kQBytes;
 #pragma unroll
-            for (int c = 0; c < kHD / 32; ++c) {
-                float o[32];
-                tmemLoad32(tmem_o + lane_field + c * 32, o); // warp-collective: rows past the chunk load too
-                if (row < rows_valid) {
+        for (int c = 0; c < kHD / 32; ++c) {
+            float o[32];
+            tmemLoad32(tmem_o + lane_field + c * 32, o); // warp-collective: rows past the chunk load too
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 v;
-                        v.x = packPair(o[i] * inv, o[i + 1] * inv, T());
-                        v.y = packPair(o[i + 2] * inv, o[i + 3] * inv, T());
-                        v.z = packPair(o[i + 4] * inv, o[i + 5] * inv, T());
-                        v.w = packPair(o[i + 6] * inv, o[i + 7] * inv, T());
-                        *reinterpret_cast<uint4 *>(out + c * 32 + i) = v;
-                    }
+            for (int i = 0; i < 32; i += 8) {
+                uint4 v;
+                v.x = packPair(o[i] * inv, o[i + 1] * inv, T());
+                v.y = packPair(o[i + 2] * inv, o[i + 3] * inv, T());
+                v.z = packPair(o[i + 4] * inv, o[i + 5] * inv, T());
+                v.w = packPair(o[i + 6] * inv, o[i + 7] * inv, T());
+                if (bulk) {
+                    const int col = c * 32 + i; // 8 columns = one 16-byte piece of the 128-byte swizzled row
+                    const uint32_t addr = o_stage + (col / 64) * (kBM * 128) + row * 128 + ((((col % 64) / 8) ^ (row & 7)) << 4);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                } else if (ok && row < rows_valid) {
+                    *reinterpret_cast<uint4 *>(out + c * 32 + i) = v;
                 }
+            }
+        }
+        if (bulk) {
+            // every warp of the q-tile gets here (a failed wait only zeroes what it wrote)
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + qi) : "memory");
+            if ((warp & 3) == 0 && lane == 0 && sh_failed == 0) {
+#pragma unroll
+                for (int c = 0; c < kChunks; ++c) {
+                    tmaStore3d(&tmap_o, o_stage + c * (kBM * 128), c * 64, head, static_cast<int>(q_begin + t0));
+                }
+                tmaStoreCommitAndWaitRead();
             }
         }
     }
@@ -678,7 +790,7 @@ __global__ void __launch_bounds__(kThreads)
     // ---- common exit: every role gets here on every path; TMEM reads and MMAs are done ------------
     tcgenFenceBefore();
     __syncthreads();
-    if (warp == kProducerWarp) {
+    if (warp == kMmaWarp0) {
         tcgenFenceAfter();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
@@ -739,20 +851,38 @@ bool encodeQueryMap(CUtensorMap *map, const Info &info, const void *base) {
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// tiles + barriers / TMEM slot / scan scratch
-constexpr size_t smemBytes(int stages) { return kQBytes + static_cast<size_t>(stages) * 2 * kTensorBytes + kPBytes + 512; }
+// out as {head_size, num_heads, total_q}, same box as q; false when its strides do not fit a tensor map
+bool encodeOutMap(CUtensorMap *map, const Info &info, const void *base) {
+    EncodeTiledFn fn = encodeTiled();
+    if (fn == nullptr) {
+        return false;
+    }
+    const auto &A = info.attn;
+    if (A.o_head_stride <= 0 || A.o_seq_stride <= 0 || (A.o_head_stride % 8) != 0 || (A.o_seq_stride % 8) != 0) {
+        return false;
+    }
+    const cuuint64_t dims[3] = {A.head_size, A.num_heads, info.total_q_tokens};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(A.o_head_stride) * 2, static_cast<cuuint64_t>(A.o_seq_stride) * 2};
+    const cuuint32_t box[3] = {64, 1, kBM};
+    const cuuint32_t elem_strides[3] = {1, 1, 1};
+    return fn(map, mapDtype(A.dtype), 3, const_cast<void *>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
-template <typename T, int STAGES>
-infiniStatus_t launchTyped(const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv,
+// tiles + barriers / TMEM slot / scan scratch
+constexpr size_t smemBytes(int stages, int nq) { return static_cast<size_t>(nq) * (kQBytes + kPBytes) + static_cast<size_t>(stages) * 2 * kTensorBytes + 512; }
+
+template <typename T, int STAGES, int NQ>
+infiniStatus_t launchTyped(const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mo,
                            unsigned tiles, int device_id, cudaStream_t stream) {
     static std::mutex attr_mutex;
     static bool attr_done[64] = {};
-    auto kernel = pagedPrefillUmmaKernel<T, STAGES>;
+    auto kernel = pagedPrefillUmmaKernel<T, STAGES, NQ>;
     {
         std::lock_guard<std::mutex> lock(attr_mutex);
         const bool tracked = device_id >= 0 && device_id < 64;
         if (!tracked || !attr_done[device_id]) {
-            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes(STAGES))) != cudaSuccess) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes(STAGES, NQ))) != cudaSuccess) {
                 return checkLaunch("cudaFuncSetAttribute(pagedPrefillUmmaKernel)");
             }
             if (tracked) {
@@ -760,23 +890,31 @@ infiniStatus_t launchTyped(const UmmaArgs &args, const CUtensorMap &mq, const CU
             }
         }
     }
-    const dim3 grid(tiles, args.pp.d.num_heads);
-    kernel<<<grid, kThreads, smemBytes(STAGES), stream>>>(mq, mk, mv, args);
+    const dim3 grid(tiles, args.pp.d.num_heads / NQ);
+    kernel<<<grid, 7 * NQ * 32, smemBytes(STAGES, NQ), stream>>>(mq, mk, mv, mo, args);
     return checkLaunch("pagedPrefillUmmaKernel");
 }
 
 template <typename T>
-infiniStatus_t launchStages(int stages, const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv,
-                            unsigned tiles, int device_id, cudaStream_t stream) {
+infiniStatus_t launchShape(int stages, int nq, const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mo,
+                           unsigned tiles, int device_id, cudaStream_t stream) {
+    if (nq == 2) {
+        switch (stages) {
+        case 2:
+            return launchTyped<T, 2, 2>(args, mq, mk, mv, mo, tiles, device_id, stream);
+        case 3:
+            return launchTyped<T, 3, 2>(args, mq, mk, mv, mo, tiles, device_id, stream);
+        default:
+            return launchTyped<T, 4, 2>(args, mq, mk, mv, mo, tiles, device_id, stream);
+        }
+    }
     switch (stages) {
     case 2:
-        return launchTyped<T, 2>(args, mq, mk, mv, tiles, device_id, stream);
+        return launchTyped<T, 2, 1>(args, mq, mk, mv, mo, tiles, device_id, stream);
     case 3:
-        return launchTyped<T, 3>(args, mq, mk, mv, tiles, device_id, stream);
-    case 4:
-        return launchTyped<T, 4>(args, mq, mk, mv, tiles, device_id, stream);
+        return launchTyped<T, 3, 1>(args, mq, mk, mv, mo, tiles, device_id, stream);
     default:
-        return launchTyped<T, 5>(args, mq, mk, mv, tiles, device_id, stream);
+        return launchTyped<T, 4, 1>(args, mq, mk, mv, mo, tiles, device_id, stream);
     }
 }
 
@@ -791,7 +929,8 @@ UmmaPlan planPrefillUmma(const Info &info, const DeviceProps &props) {
     if (A.block_size % 8 != 0 || A.num_seqs == 0 || A.num_seqs > 65536 || info.total_q_tokens == 0 || A.num_blocks == 0) {
         return plan;
     }
-    plan.box_rows = (A.block_size % 16 == 0) ? 16 : 8;
+    // rows of one K/V copy: the largest of 64, 32, 16, 8 that divides the page, so a copy never crosses a page
+    plan.box_rows = (A.block_size % 64 == 0) ? 64 : (A.block_size % 32 == 0) ? 32 : (A.block_size % 16 == 0) ? 16 : 8;
     auto mult8 = [](ptrdiff_t v) { return v > 0 && (v % 8) == 0; }; // 16 bytes of a 2-byte dtype
     if (!mult8(A.q_seq_stride) || !mult8(A.q_head_stride) || !mult8(A.o_seq_stride) || !mult8(A.o_head_stride)) {
         return plan;
@@ -807,15 +946,29 @@ UmmaPlan planPrefillUmma(const Info &info, const DeviceProps &props) {
         || !encodeQueryMap(&probe, info, fake)) {
         return plan;
     }
-    // KV ring depth: 2 slots let two CTAs share an SM, 5 slots give one CTA the whole SM
+    // One q-head per CTA, two CTAs per SM, measured fastest.  INFINIOP_PAGED_PREFILL_QTILES=2 (even GQA
+    // groups only) lets the two q-heads of a pair share each staged KV tile in one CTA per SM instead:
+    // half the L2 traffic for about 10% less throughput at the Llama-3-8B shape.
+    const size_t group = A.num_heads / A.num_kv_heads;
+    plan.q_tiles = 1;
+    if (const char *env = std::getenv("INFINIOP_PAGED_PREFILL_QTILES")) {
+        const int v = std::atoi(env);
+        if (v == 1 || (v == 2 && group % 2 == 0)) {
+            plan.q_tiles = v;
+        }
+    }
+    // Two ring slots per tensor measured fastest in both shapes (and let two one-head CTAs share an SM).
     plan.stages = 2;
     if (const char *env = std::getenv("INFINIOP_PAGED_PREFILL_STAGES")) {
         const int v = std::atoi(env);
-        if (v >= 2 && v <= 5) {
+        if (v >= 2 && v <= 4) {
             plan.stages = v;
         }
     }
-    if (smemBytes(plan.stages) > props.smem_per_block_optin) {
+    while (plan.stages > 2 && smemBytes(plan.stages, plan.q_tiles) > props.smem_per_block_optin) {
+        --plan.stages;
+    }
+    if (smemBytes(plan.stages, plan.q_tiles) > props.smem_per_block_optin) {
         return plan;
     }
     plan.eligible = true;
@@ -836,11 +989,16 @@ infiniStatus_t launchPrefillUmma(const Info &info, const UmmaPlan &plan, const P
     UmmaArgs args;
     args.pp = pp;
     args.box_rows = plan.box_rows;
+    CUtensorMap mo;
+    args.tma_store = encodeOutMap(&mo, info, p.out) ? 1 : 0;
+    if (!args.tma_store) {
+        mo = mq; // never dereferenced
+    }
     const unsigned tiles = static_cast<unsigned>((info.total_q_tokens + kBM - 1) / kBM + A.num_seqs);
     int device_id = -1;
     (void)cudaGetDevice(&device_id);
-    return A.dtype == INFINI_DTYPE_F16 ? launchStages<__half>(plan.stages, args, mq, mk, mv, tiles, device_id, stream)
-                                       : launchStages<__nv_bfloat16>(plan.stages, args, mq, mk, mv, tiles, device_id, stream);
+    return A.dtype == INFINI_DTYPE_F16 ? launchShape<__half>(plan.stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream)
+                                       : launchShape<__nv_bfloat16>(plan.stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream);
 }
 
 } // namespace b200::paged_attention_prefill

@@ -117,21 +117,35 @@ def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, scale, alibi=No
     return out
 
 
+# Prefill variants: name -> environment read when the descriptor is created.  The tcgen05 kernel
+# serves two q-heads of an even GQA group per CTA by default; "umma-q1" pins one q-head per CTA.
+PREFILL_ENV = {
+    None: {},
+    "generic": {"INFINIOP_PAGED_PREFILL_PATH": "generic"},
+    "tiles": {"INFINIOP_PAGED_PREFILL_PATH": "tiles"},
+    "umma": {"INFINIOP_PAGED_PREFILL_PATH": "umma"},
+    "umma-q1": {"INFINIOP_PAGED_PREFILL_PATH": "umma", "INFINIOP_PAGED_PREFILL_QTILES": "1"},
+    "umma-q2-s3": {"INFINIOP_PAGED_PREFILL_PATH": "umma", "INFINIOP_PAGED_PREFILL_QTILES": "2", "INFINIOP_PAGED_PREFILL_STAGES": "3"},
+}
+_PREFILL_KEYS = ("INFINIOP_PAGED_PREFILL_PATH", "INFINIOP_PAGED_PREFILL_QTILES", "INFINIOP_PAGED_PREFILL_STAGES")
+
+
 @contextlib.contextmanager
 def prefill_path(path):
-    """INFINIOP_PAGED_PREFILL_PATH (auto | tiles | generic) is read when the descriptor is created."""
-    old = os.environ.get("INFINIOP_PAGED_PREFILL_PATH")
-    if path is None:
-        os.environ.pop("INFINIOP_PAGED_PREFILL_PATH", None)
-    else:
-        os.environ["INFINIOP_PAGED_PREFILL_PATH"] = path
+    """The INFINIOP_PAGED_PREFILL_* variables are read when the descriptor is created."""
+    env = PREFILL_ENV[path] if path in PREFILL_ENV else {"INFINIOP_PAGED_PREFILL_PATH": path}
+    old = {k: os.environ.get(k) for k in _PREFILL_KEYS}
+    for k in _PREFILL_KEYS:
+        os.environ.pop(k, None)
+    os.environ.update(env)
     try:
         yield
     finally:
-        if old is None:
-            os.environ.pop("INFINIOP_PAGED_PREFILL_PATH", None)
-        else:
-            os.environ["INFINIOP_PAGED_PREFILL_PATH"] = old
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
 
 
 def create_prefill(out, q, k_cache, v_cache, block_tables, seq_lens, cum_q, alibi, scale, path=None, index_dtype=None):

@@ -15,7 +15,7 @@ from infinicore_b200 import workloads
 pytestmark = pytest.mark.gpu
 
 PATHS = [None, "generic", "tiles"]
-PATHS_HD128 = [None, "generic", "tiles", "umma"]  # the tcgen05 kernel takes head size 128 (and is the default there)
+PATHS_HD128 = [None, "generic", "tiles", "umma", "umma-q1", "umma-q2-s3"]  # the tcgen05 kernel takes head size 128 (and is the default there)
 
 
 @pytest.fixture(scope="module")
@@ -47,7 +47,7 @@ def check(c, got, want):
 @pytest.mark.parametrize("path", PATHS_HD128)
 @pytest.mark.parametrize("name", golden_names("prefill_"))
 def test_golden(abi, name, path):
-    if path == "umma" and "hd128" not in name:
+    if path is not None and path.startswith("umma") and "hd128" not in name:
         pytest.skip("tcgen05 kernel: head size 128 only")
     if path == "tiles" and "576" in name:
         pytest.skip("tile kernel: head sizes 64 and 128")
@@ -94,7 +94,7 @@ def test_reference_case_list_multi_round(abi, case, dtype, index_dtype):
 @pytest.mark.parametrize("dtype,heads,kvh,hd,bs", [(torch.bfloat16, 8, 2, 128, 16), (torch.float16, 4, 1, 64, 16),
                                                    (torch.bfloat16, 4, 4, 128, 8), (torch.float16, 8, 2, 128, 32)])
 def test_gqa_ragged_chunks_and_tile_boundaries(abi, path, dtype, heads, kvh, hd, bs):
-    if path == "umma" and hd != 128:
+    if path is not None and path.startswith("umma") and hd != 128:
         pytest.skip("tcgen05 kernel: head size 128 only")
     """Chunk lengths around the 64-row tile and the page size, cached prefixes of every alignment,
     one sequence with no new tokens."""
@@ -140,7 +140,7 @@ def test_unused_cache_slots_may_hold_nan_and_untouched_rows_stay(abi, path):
     assert bool((got[-3:] == 8.0).all())
 
 
-@pytest.mark.parametrize("path", ["tiles", "umma"])
+@pytest.mark.parametrize("path", ["tiles", "umma", "umma-q1", "umma-q2-s3"])
 def test_long_prompt_against_oracle(abi, path):
     """2 prompts x 1024 new tokens over 512 cached, Llama-3-8B head shape."""
     c = workloads.build_prefill_case("long", dtype=torch.bfloat16, new_lens=[1024, 1000], cached_lens=[512, 0], num_heads=32,
