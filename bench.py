@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5", "prefill"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--collective", default="infiniccl", choices=["infiniccl", "torch"],
+                    help="head mode only: the all-gather goes through libinfiniccl.so (default) or torch.distributed")
     ap.add_argument("--mode", default="seq", choices=["seq", "head"],
                     help="seq: shard by sequence, no collective (default); head: optional KV-head-sharded mode, "
                          "every rank holds all sequences for its kv-heads and outputs are all-gathered over NCCL")
@@ -339,16 +341,21 @@ def gpu_arm(args):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device) if small_ws else None
 
     gather_staging = None
+    ccl_comm = None  # infinicclAllGather through libinfiniccl.so; None: torch.distributed's all-gather
     if head_mode:
         from infinicore_b200 import sharding
 
         gather_staging = torch.empty((world, *step.out.shape), dtype=step.out.dtype, device=device)
+        if args.collective == "infiniccl":
+            from infinicore_b200 import ccl
+
+            ccl_comm = ccl.init_from_process_group()
 
     def one_step():
         step.caching(sptr)
         step.attention(sptr)
         if head_mode:
-            sharding.gather_head_sharded(step.out, world, staging=gather_staging)
+            sharding.gather_head_sharded(step.out, world, staging=gather_staging, comm=ccl_comm)
 
     # ---- device-resident timing -------------------------------------------------------------
     for _ in range(max(args.warmup, 3)):
@@ -429,7 +436,7 @@ def gpu_arm(args):
             ib.paged_caching(case.k_cache, case.v_cache, estep.dev["new_k"], estep.dev["new_v"], estep.dev["slot_mapping"])
             o = ib.paged_attention(estep.dev["q"], case.k_cache, case.v_cache, estep.dev["block_tables"], estep.dev["seq_lens"],
                                    None, case.scale, out=estep.out)
-            full = sharding.gather_head_sharded(o, world, staging=gather_staging)
+            full = sharding.gather_head_sharded(o, world, staging=gather_staging, comm=ccl_comm)
             host_full.copy_(full, non_blocking=True)
             stream.synchronize()
 
@@ -478,6 +485,9 @@ def gpu_arm(args):
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
+    if ccl_comm is not None:
+        torch.cuda.synchronize()
+        ccl_comm.destroy()
     if world > 1:
         dist.destroy_process_group()
 

@@ -25,6 +25,38 @@ __INFINI_C __export infiniStatus_t infinirtGetDeviceCount(infiniDevice_t device,
 __INFINI_C __export infiniStatus_t infinirtSetDevice(infiniDevice_t device, int device_id);
 __INFINI_C __export infiniStatus_t infinirtGetDevice(infiniDevice_t *device_ptr, int *device_id_ptr);
 __INFINI_C __export infiniStatus_t infinirtGetMemInfo(infiniDevice_t device, int device_id, size_t *free_bytes, size_t *total_bytes);
+
+/* Resource snapshot (reference include/infinirt.h:13-60).  `valid_fields` says which members the
+ * backend filled; a consumer must test the bit before it reads a member.  This library fills the
+ * memory-capacity members from the driver; the utilisation and communication members stay clear -
+ * they need the management library and a collective-timing store, which this path does not carry. */
+typedef enum {
+    INFINIRT_RESOURCE_FIELD_NONE = 0,
+    INFINIRT_RESOURCE_FIELD_MEMORY_CAPACITY = 1ull << 0,
+    INFINIRT_RESOURCE_FIELD_COMPUTE_UTILIZATION = 1ull << 1,
+    INFINIRT_RESOURCE_FIELD_MEMORY_BANDWIDTH_UTILIZATION = 1ull << 2,
+    INFINIRT_RESOURCE_FIELD_KERNEL_TIME_RATIO = 1ull << 3,
+    INFINIRT_RESOURCE_FIELD_COMMUNICATION = 1ull << 4,
+} infinirtResourceField_t;
+
+typedef struct {
+    infiniDevice_t device_type;
+    int device_id;
+    uint64_t valid_fields;
+    uint64_t estimated_fields;
+    size_t free_bytes;
+    size_t total_bytes;
+    size_t used_bytes;
+    size_t reserved_bytes;
+    float compute_utilization;
+    float memory_bandwidth_utilization;
+    float kernel_time_ratio;
+    float communication_time_ratio;
+    uint64_t communication_bytes;
+} infinirtDeviceResourceSnapshot_t;
+
+__INFINI_C __export infiniStatus_t infinirtGetDeviceResourceSnapshot(infiniDevice_t device, int device_id,
+                                                                    infinirtDeviceResourceSnapshot_t *snapshot);
 __INFINI_C __export infiniStatus_t infinirtDeviceSynchronize();
 
 /* Stream */

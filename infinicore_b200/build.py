@@ -52,6 +52,10 @@ OP_SOURCES = [
 ]
 
 
+# libinfiniccl: the InfiniCCL C ABI over NCCL (system libnccl: /usr/include/nccl.h, -lnccl)
+CCL_SOURCES = ["ccl/infiniccl.cu"]
+
+
 def nvcc() -> str:
     exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(exe):
@@ -104,7 +108,7 @@ def _link(objs, out: Path, extra, verbose: bool) -> None:
 
 
 def build(force: bool = False, verbose: bool = False) -> dict:
-    """Compiles what is stale and returns {"infinirt": path, "infiniop": path}."""
+    """Compiles what is stale and returns {"infinirt": path, "infiniop": path, "infiniccl": path}."""
     LIB.mkdir(exist_ok=True)
     OBJ.mkdir(exist_ok=True)
     if force:
@@ -113,14 +117,18 @@ def build(force: bool = False, verbose: bool = False) -> dict:
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
         rt_objs = list(pool.map(lambda s: _compile(s, verbose), RT_SOURCES))
         op_objs = list(pool.map(lambda s: _compile(s, verbose), OP_SOURCES))
+        ccl_objs = list(pool.map(lambda s: _compile(s, verbose), CCL_SOURCES))
     librt = LIB / "libinfinirt.so"
     libop = LIB / "libinfiniop.so"
-    newest_obj = max(o.stat().st_mtime for o in rt_objs + op_objs)
+    libccl = LIB / "libinfiniccl.so"
+    newest_obj = max(o.stat().st_mtime for o in rt_objs + op_objs + ccl_objs)
     if force or not librt.exists() or librt.stat().st_mtime < newest_obj:
         _link(rt_objs, librt, [], verbose)
     if force or not libop.exists() or libop.stat().st_mtime < newest_obj:
         _link(op_objs, libop, [f"-L{LIB}", "-linfinirt", "-Xlinker", "-rpath=$ORIGIN"], verbose)
-    return {"infinirt": librt, "infiniop": libop}
+    if force or not libccl.exists() or libccl.stat().st_mtime < newest_obj:
+        _link(ccl_objs, libccl, [f"-L{LIB}", "-linfinirt", "-lnccl", "-Xlinker", "-rpath=$ORIGIN"], verbose)
+    return {"infinirt": librt, "infiniop": libop, "infiniccl": libccl}
 
 
 def main() -> None:

@@ -7,6 +7,7 @@
 // stream/event/memory calls return INFINI_STATUS_DEVICE_TYPE_NOT_SUPPORTED.
 #include "infinirt.h"
 
+#include <cstring>
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -140,6 +141,25 @@ __INFINI_C infiniStatus_t infinirtGetMemInfo(infiniDevice_t device, int device_i
     cudaError_t err = cudaMemGetInfo(free_bytes, total_bytes);
     (void)cudaSetDevice(prev);
     return fromCuda(err, "cudaMemGetInfo");
+}
+
+// Only the capacity members are filled (and flagged); the rest of the snapshot is zero with its bits clear.
+__INFINI_C infiniStatus_t infinirtGetDeviceResourceSnapshot(infiniDevice_t device, int device_id,
+                                                           infinirtDeviceResourceSnapshot_t *snapshot) {
+    RT_REQUIRE_PTR(snapshot);
+    std::memset(snapshot, 0, sizeof(*snapshot));
+    snapshot->device_type = device;
+    snapshot->device_id = device_id;
+    size_t free_bytes = 0, total_bytes = 0;
+    const infiniStatus_t st = infinirtGetMemInfo(device, device_id, &free_bytes, &total_bytes);
+    if (st != INFINI_STATUS_SUCCESS) {
+        return st;
+    }
+    snapshot->free_bytes = free_bytes;
+    snapshot->total_bytes = total_bytes;
+    snapshot->used_bytes = total_bytes - free_bytes;
+    snapshot->valid_fields = INFINIRT_RESOURCE_FIELD_MEMORY_CAPACITY;
+    return INFINI_STATUS_SUCCESS;
 }
 
 __INFINI_C infiniStatus_t infinirtDeviceSynchronize() {

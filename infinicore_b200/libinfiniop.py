@@ -90,7 +90,7 @@ INFINIOP_SYMBOLS = [
 ]
 INFINIRT_SYMBOLS = [
     "infinirtInit", "infinirtGetAllDeviceCount", "infinirtGetDeviceCount", "infinirtSetDevice",
-    "infinirtGetDevice", "infinirtGetMemInfo", "infinirtDeviceSynchronize",
+    "infinirtGetDevice", "infinirtGetMemInfo", "infinirtGetDeviceResourceSnapshot", "infinirtDeviceSynchronize",
     "infinirtStreamCreate", "infinirtStreamDestroy", "infinirtStreamSynchronize", "infinirtStreamWaitEvent",
     "infinirtEventCreate", "infinirtEventCreateWithFlags", "infinirtEventRecord", "infinirtEventQuery",
     "infinirtEventSynchronize", "infinirtEventDestroy", "infinirtEventElapsedTime",

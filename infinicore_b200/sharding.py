@@ -66,17 +66,24 @@ def head_slices(num_heads: int, num_kv_heads: int, rank: int, world: int):
     return slice(rank * per * group, (rank + 1) * per * group), slice(rank * per, (rank + 1) * per)
 
 
-def gather_head_sharded(out_local, world: int, group=None, staging=None):
+def gather_head_sharded(out_local, world: int, group=None, staging=None, comm=None):
     """All-gathers per-rank outputs [num_seqs, heads_per_rank, d] into [num_seqs, heads, d].
 
     NCCL concatenates rank-major, so the gathered buffer is [world, num_seqs, heads_per_rank, d]; the
     head order of the full tensor is restored with a permuted view (no extra copy is made here; a
-    consumer that needs contiguity pays one).  `staging` may hold a preallocated gather buffer."""
+    consumer that needs contiguity pays one).  `staging` may hold a preallocated gather buffer.
+    `comm` is an infinicore_b200.ccl.Communicator: the gather then goes through infinicclAllGather
+    (the reference's route, src/infiniccl/cuda/infiniccl_cuda.cu:219-234) on the current stream;
+    without it, through torch.distributed on `group`."""
     import torch
-    import torch.distributed as dist
 
     num_seqs, hpr, d = out_local.shape
     if staging is None:
         staging = torch.empty((world, num_seqs, hpr, d), dtype=out_local.dtype, device=out_local.device)
-    dist.all_gather_into_tensor(staging.view(-1), out_local.contiguous().view(-1), group=group)
+    if comm is not None:
+        comm.all_gather(out_local.contiguous().view(-1), staging.view(-1))
+    else:
+        import torch.distributed as dist
+
+        dist.all_gather_into_tensor(staging.view(-1), out_local.contiguous().view(-1), group=group)
     return staging.permute(1, 0, 2, 3).reshape(num_seqs, world * hpr, d)

@@ -32,13 +32,28 @@ def test_libraries_load_and_export_every_declared_symbol():
     from infinicore_b200 import libinfiniop as L
 
     rt_path, op_path = L.library_paths()
+    from infinicore_b200 import ccl
+
     rt = ctypes.CDLL(str(rt_path), mode=ctypes.RTLD_GLOBAL)
     op = ctypes.CDLL(str(op_path))
+    cc = ctypes.CDLL(str(ccl.library_path()))
     for name, header in declared_symbols().items():
-        lib = rt if name.startswith("infinirt") else op
+        lib = rt if name.startswith("infinirt") else cc if name.startswith("infiniccl") else op
         assert hasattr(lib, name), f"{name} (declared in {header}) is not exported"
-    # and the binding's own lists are the same set
-    assert set(L.INFINIOP_SYMBOLS) | set(L.INFINIRT_SYMBOLS) == set(declared_symbols())
+    # and the bindings' own lists are the same set
+    assert set(L.INFINIOP_SYMBOLS) | set(L.INFINIRT_SYMBOLS) | set(ccl.INFINICCL_SYMBOLS) == set(declared_symbols())
+
+
+def test_infiniccl_argument_checks_need_no_device():
+    """Host-side refusals of libinfiniccl.so (reference src/infiniccl/infiniccl.cc: NULL checks first)."""
+    from infinicore_b200 import ccl
+
+    l = ccl.lib()
+    assert l.infinicclGetUniqueId(None) == 4           # INFINI_STATUS_NULL_POINTER
+    assert l.infinicclCommInitRank(None, 2, ccl.UniqueId(), 0) == 4
+    assert l.infinicclCommDestroy(None) == 0            # NULL communicator: nothing to do
+    assert l.infinicclGroupStart(None) == 4
+    assert l.infinicclCommInitAll(0, None, 1, None) == 5  # CPU device type: not supported
 
 
 def test_tensor_descriptor_round_trip_needs_no_device():
