@@ -15,6 +15,7 @@ _LAZY = {
     "paged_attention": "ops",
     "paged_caching": "ops",
     "paged_attention_prefill": "ops",
+    "paged_decode_step": "ops",
     "DecodeStep": "decode_step",
 }
 

@@ -89,6 +89,7 @@ enum class OpKind : int {
     PagedAttention = 1,
     PagedCaching = 2,
     PagedAttentionPrefill = 3,
+    PagedDecodeStep = 4,
 };
 
 struct OpDescriptorBase {

@@ -1,0 +1,221 @@
+// infiniopPagedDecodeStep: append the newest K/V row of every sequence, then attend - the work of
+// infiniopPagedCaching + infiniopPagedAttention for one decode layer behind one entry point.
+//
+// The reference has no such operator (its callers issue the two separately:
+// src/infinicore/ops/paged_caching/paged_caching_infiniop.cc:38-51 then
+// src/infinicore/ops/paged_attention/paged_attention_infiniop.cc:47-64).  When the streaming kernel
+// takes the problem, the append rides inside it: the warp that reaches a sequence's last tile swaps
+// the new row into its staged copy and stores it into the cache, so no separate launch is needed
+// and no other CTA has to see the cache write.  Otherwise a small append kernel runs first and the
+// generic attention kernel follows in stream order.
+#include "kernels.h"
+
+#include <cstdlib>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cstring>
+
+namespace b200::paged_attention {
+
+namespace {
+
+struct StepDescriptor {
+    OpDescriptorBase base;
+    Info info;
+    StreamPlan stream;
+    size_t workspace_bytes;
+    ptrdiff_t new_k_seq_stride, new_v_seq_stride;
+    bool rows_vectorisable; // row starts stay 16-byte aligned given aligned bases
+};
+
+// One warp per (sequence, kv-head, K | V) row.
+template <typename T>
+__global__ void __launch_bounds__(128) pagedAppendRowsKernel(const DecodeParams p, int vec_ok) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int rows = p.num_seqs * p.num_kv_heads * 2;
+    if (warp >= rows) {
+        return;
+    }
+    const int is_v = warp & 1;
+    const int kv_head = (warp >> 1) % p.num_kv_heads;
+    const int seq = (warp >> 1) / p.num_kv_heads;
+    long long len = loadIndex(p.seq_lens, seq, p.index_is_64);
+    const long long capacity = static_cast<long long>(p.max_blocks_per_seq) * p.block_size;
+    len = len > capacity ? capacity : len;
+    if (len <= 0) {
+        return;
+    }
+    const long long n = len - 1;
+    const long long block = loadIndex(p.block_tables, seq * p.bt_seq_stride + n / p.block_size, p.index_is_64);
+    const int row = static_cast<int>(n % p.block_size);
+    const int width = is_v ? p.value_size : p.head_size;
+    const T *src = is_v ? static_cast<const T *>(p.new_v) + seq * p.new_v_seq_stride + kv_head * p.value_size
+                        : static_cast<const T *>(p.new_k) + seq * p.new_k_seq_stride + kv_head * p.head_size;
+    T *dst = is_v ? static_cast<T *>(const_cast<void *>(p.v_cache)) + block * p.v_block_stride + kv_head * p.v_head_stride + row * p.v_row_stride
+                  : static_cast<T *>(const_cast<void *>(p.k_cache)) + block * p.k_block_stride + kv_head * p.k_head_stride + row * p.k_row_stride;
+    if (vec_ok) {
+        for (int i = lane * 8; i < width; i += 256) {
+            *reinterpret_cast<uint4 *>(dst + i) = *reinterpret_cast<const uint4 *>(src + i);
+        }
+    } else {
+        for (int i = lane; i < width; i += 32) {
+            dst[i] = src[i];
+        }
+    }
+}
+
+} // namespace
+
+infiniStatus_t launchAppendNewRows(const Info &info, const DecodeParams &p, cudaStream_t stream) {
+    const long long rows = static_cast<long long>(p.num_seqs) * p.num_kv_heads * 2;
+    if (rows == 0) {
+        return INFINI_STATUS_SUCCESS;
+    }
+    const auto addr = [](const void *ptr) { return reinterpret_cast<uintptr_t>(ptr); };
+    const auto mult8 = [](long long v) { return (v % 8) == 0; };
+    const int vec_ok = ((addr(p.k_cache) | addr(p.v_cache) | addr(p.new_k) | addr(p.new_v)) & 15u) == 0 && mult8(p.head_size) && mult8(p.value_size)
+                       && mult8(p.new_k_seq_stride) && mult8(p.new_v_seq_stride) && mult8(p.k_block_stride) && mult8(p.k_head_stride)
+                       && mult8(p.k_row_stride) && mult8(p.v_block_stride) && mult8(p.v_head_stride) && mult8(p.v_row_stride);
+    const unsigned blocks = static_cast<unsigned>((rows * 32 + 127) / 128);
+    if (info.dtype == INFINI_DTYPE_F16) {
+        pagedAppendRowsKernel<__half><<<blocks, 128, 0, stream>>>(p, vec_ok);
+    } else {
+        pagedAppendRowsKernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(p, vec_ok);
+    }
+    return checkLaunch("pagedAppendRowsKernel");
+}
+
+// defined in operator.cu
+DecodeParams makeDecodeParams(const Info &I, void *out, const void *q, const void *k_cache, const void *v_cache,
+                              const void *block_tables, const void *seq_lens, const void *alibi_slopes);
+
+} // namespace b200::paged_attention
+
+using b200::paged_attention::StepDescriptor;
+
+__INFINI_C infiniStatus_t infiniopCreatePagedDecodeStepDescriptor(
+    infiniopHandle_t handle,
+    infiniopPagedDecodeStepDescriptor_t *desc_ptr,
+    infiniopTensorDescriptor_t out_desc,
+    infiniopTensorDescriptor_t q_desc,
+    infiniopTensorDescriptor_t k_cache_desc,
+    infiniopTensorDescriptor_t v_cache_desc,
+    infiniopTensorDescriptor_t new_k_desc,
+    infiniopTensorDescriptor_t new_v_desc,
+    infiniopTensorDescriptor_t block_tables_desc,
+    infiniopTensorDescriptor_t seq_lens_desc,
+    infiniopTensorDescriptor_t alibi_slopes_desc,
+    float scale) {
+    B200_RETURN_IF(handle == nullptr || desc_ptr == nullptr, INFINI_STATUS_NULL_POINTER);
+    B200_RETURN_IF(out_desc == nullptr || q_desc == nullptr || k_cache_desc == nullptr || v_cache_desc == nullptr
+                       || new_k_desc == nullptr || new_v_desc == nullptr || block_tables_desc == nullptr || seq_lens_desc == nullptr,
+                   INFINI_STATUS_NULL_POINTER);
+    B200_RETURN_IF(handle->device != INFINI_DEVICE_NVIDIA, INFINI_STATUS_DEVICE_TYPE_NOT_SUPPORTED);
+
+    b200::paged_attention::Info info;
+    infiniStatus_t st = b200::paged_attention::makeInfo(info, out_desc, q_desc, k_cache_desc, v_cache_desc,
+                                                        block_tables_desc, seq_lens_desc, alibi_slopes_desc, scale);
+    B200_RETURN_IF(st != INFINI_STATUS_SUCCESS, st);
+    B200_RETURN_IF(info.num_seqs > 0x7fffffffu || info.num_heads > 65535u || info.max_num_blocks_per_seq > 0x7fffffffu
+                       || info.block_size > 65536u || info.num_blocks > 0x7fffffffu,
+                   INFINI_STATUS_BAD_TENSOR_SHAPE);
+    // the new rows: one token per sequence, the cache's dtype, dense heads
+    B200_RETURN_IF(new_k_desc->dtype != info.dtype || new_v_desc->dtype != info.dtype, INFINI_STATUS_BAD_TENSOR_DTYPE);
+    B200_RETURN_IF(new_k_desc->ndim() != 3 || new_v_desc->ndim() != 3, INFINI_STATUS_BAD_TENSOR_SHAPE);
+    B200_RETURN_IF(new_k_desc->dim(0) != info.num_seqs || new_k_desc->dim(1) != info.num_kv_heads || new_k_desc->dim(2) != info.head_size,
+                   INFINI_STATUS_BAD_TENSOR_SHAPE);
+    B200_RETURN_IF(new_v_desc->dim(0) != info.num_seqs || new_v_desc->dim(1) != info.num_kv_heads || new_v_desc->dim(2) != info.value_size,
+                   INFINI_STATUS_BAD_TENSOR_SHAPE);
+    B200_RETURN_IF(new_k_desc->stride(2) != 1 || new_v_desc->stride(2) != 1, INFINI_STATUS_BAD_TENSOR_STRIDES);
+    B200_RETURN_IF(new_k_desc->stride(1) != static_cast<ptrdiff_t>(info.head_size)
+                       || new_v_desc->stride(1) != static_cast<ptrdiff_t>(info.value_size),
+                   INFINI_STATUS_BAD_TENSOR_STRIDES);
+
+    auto *h = reinterpret_cast<b200::Handle *>(handle);
+    auto *d = new StepDescriptor{{handle->device, handle->device_id, b200::OpKind::PagedDecodeStep, h->props}, info, {}, 0,
+                                 new_k_desc->stride(0), new_v_desc->stride(0), false};
+    d->rows_vectorisable = (d->new_k_seq_stride % 8) == 0 && (d->new_v_seq_stride % 8) == 0;
+
+    // the same path selection as infiniopPagedAttention (INFINIOP_PAGED_DECODE_PATH = auto | stream | generic)
+    const char *path = std::getenv("INFINIOP_PAGED_DECODE_PATH");
+    const bool force_generic = (path != nullptr) && std::strcmp(path, "generic") == 0;
+    if (!force_generic) {
+        d->stream = b200::paged_attention::planStream(info, *h->props);
+    }
+    if (path != nullptr && std::strcmp(path, "stream") == 0 && !d->stream.eligible) {
+        std::fprintf(stderr, "[infiniop] INFINIOP_PAGED_DECODE_PATH=stream but this problem is not eligible for the streaming kernel\n");
+        delete d;
+        return INFINI_STATUS_BAD_PARAM;
+    }
+    d->workspace_bytes = d->stream.eligible ? d->stream.workspace_bytes : 0;
+    *desc_ptr = reinterpret_cast<infiniopPagedDecodeStepDescriptor_t>(d);
+    return INFINI_STATUS_SUCCESS;
+}
+
+__INFINI_C infiniStatus_t infiniopGetPagedDecodeStepWorkspaceSize(infiniopPagedDecodeStepDescriptor_t desc, size_t *size) {
+    B200_RETURN_IF(desc == nullptr || size == nullptr, INFINI_STATUS_NULL_POINTER);
+    auto *d = reinterpret_cast<StepDescriptor *>(desc);
+    B200_RETURN_IF(d->base.kind != b200::OpKind::PagedDecodeStep, INFINI_STATUS_BAD_PARAM);
+    *size = d->workspace_bytes;
+    return INFINI_STATUS_SUCCESS;
+}
+
+__INFINI_C infiniStatus_t infiniopPagedDecodeStep(
+    infiniopPagedDecodeStepDescriptor_t desc,
+    void *workspace,
+    size_t workspace_size,
+    void *out,
+    const void *q,
+    void *k_cache,
+    void *v_cache,
+    const void *new_k,
+    const void *new_v,
+    const void *block_tables,
+    const void *seq_lens,
+    const void *alibi_slopes,
+    void *stream) {
+    B200_RETURN_IF(desc == nullptr, INFINI_STATUS_NULL_POINTER);
+    auto *d = reinterpret_cast<StepDescriptor *>(desc);
+    B200_RETURN_IF(d->base.kind != b200::OpKind::PagedDecodeStep, INFINI_STATUS_BAD_PARAM);
+    const auto &I = d->info;
+    if (I.num_seqs == 0 || I.num_heads == 0) {
+        return INFINI_STATUS_SUCCESS;
+    }
+    B200_RETURN_IF(out == nullptr || q == nullptr || k_cache == nullptr || v_cache == nullptr || new_k == nullptr || new_v == nullptr
+                       || block_tables == nullptr || seq_lens == nullptr,
+                   INFINI_STATUS_NULL_POINTER);
+    B200_RETURN_IF(I.has_alibi && alibi_slopes == nullptr, INFINI_STATUS_NULL_POINTER);
+    B200_RETURN_IF(workspace_size < d->workspace_bytes, INFINI_STATUS_INSUFFICIENT_WORKSPACE);
+    B200_RETURN_IF(d->workspace_bytes > 0 && workspace == nullptr, INFINI_STATUS_NULL_POINTER);
+
+    auto p = b200::paged_attention::makeDecodeParams(I, out, q, k_cache, v_cache, block_tables, seq_lens, alibi_slopes);
+    p.new_k = new_k;
+    p.new_v = new_v;
+    p.new_k_seq_stride = d->new_k_seq_stride;
+    p.new_v_seq_stride = d->new_v_seq_stride;
+    auto cuda_stream = static_cast<cudaStream_t>(stream);
+    const auto addr = [](const void *ptr) { return reinterpret_cast<uintptr_t>(ptr); };
+    const bool fused = d->stream.eligible && b200::paged_attention::streamTakesPointers(p, workspace) && d->rows_vectorisable
+                       && ((addr(new_k) | addr(new_v)) & 15u) == 0;
+    if (fused) {
+        return b200::paged_attention::launchDecodeStream(I, d->stream, p, workspace, workspace_size, cuda_stream);
+    }
+    // append first, then the attention kernels without the row hand-over
+    const infiniStatus_t st = b200::paged_attention::launchAppendNewRows(I, p, cuda_stream);
+    B200_RETURN_IF(st != INFINI_STATUS_SUCCESS, st);
+    p.new_k = nullptr;
+    p.new_v = nullptr;
+    if (d->stream.eligible) {
+        return b200::paged_attention::launchDecodeStream(I, d->stream, p, workspace, workspace_size, cuda_stream);
+    }
+    return b200::paged_attention::launchDecodeGeneric(I, p, cuda_stream);
+}
+
+__INFINI_C infiniStatus_t infiniopDestroyPagedDecodeStepDescriptor(infiniopPagedDecodeStepDescriptor_t desc) {
+    B200_RETURN_IF(desc == nullptr, INFINI_STATUS_NULL_POINTER);
+    auto *d = reinterpret_cast<StepDescriptor *>(desc);
+    B200_RETURN_IF(d->base.kind != b200::OpKind::PagedDecodeStep, INFINI_STATUS_BAD_PARAM);
+    delete d;
+    return INFINI_STATUS_SUCCESS;
+}

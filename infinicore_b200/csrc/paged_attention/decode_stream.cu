@@ -564,6 +564,35 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
         if (!a.probe_copy_only) {
         const int tok0 = cur.ti * kTileTokens;
         const int valid = seq_len - tok0; // >= 1 by construction
+        if (p.new_k != nullptr && valid <= kTileTokens) {
+            // Decode step with append: this is the tile that holds the sequence's newest position
+            // (row valid - 1).  Its K and V come from the caller's new rows, not from what the cache
+            // held when the tile was fetched: overwrite the row in shared memory (same swizzle as the
+            // copy engine's) and, once per (sequence, kv-head), store it into the cache for later steps.
+            constexpr int kPieces = HD / 8; // 16-byte pieces per row
+            const int kv_head = cur.j / head_tiles;
+            const int row = valid - 1;
+            const T *nk = static_cast<const T *>(p.new_k) + cur.s * p.new_k_seq_stride + kv_head * HD;
+            const T *nv = static_cast<const T *>(p.new_v) + cur.s * p.new_v_seq_stride + kv_head * HD;
+            const bool writer = (cur.j % head_tiles) == 0;
+            const long long block = writer ? tableEntry(cur) : 0;
+            const int row_in_block = (seq_len - 1) % p.block_size;
+            T *kc = static_cast<T *>(const_cast<void *>(p.k_cache)) + block * p.k_block_stride + kv_head * p.k_head_stride + row_in_block * p.k_row_stride;
+            T *vc = static_cast<T *>(const_cast<void *>(p.v_cache)) + block * p.v_block_stride + kv_head * p.v_head_stride + row_in_block * p.v_row_stride;
+            for (int idx = lane; idx < 2 * kPieces; idx += 32) {
+                const int is_v = idx / kPieces;
+                const int piece = idx % kPieces;
+                const uint4 val = *reinterpret_cast<const uint4 *>((is_v ? nv : nk) + piece * 8);
+                const uint32_t addr = (is_v ? v_tile : k_tile) + (piece >> 3) * kBoxBytes + row * 128 + (((piece & 7) ^ (row & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w) : "memory");
+                if (writer) {
+                    *reinterpret_cast<uint4 *>((is_v ? vc : kc) + piece * 8) = val;
+                }
+            }
+            // these generic-proxy writes precede the next TMA write into the same slot
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+        }
         if (valid < kTileTokens) {
             // Rows past the end of the sequence may hold anything (including NaN bit patterns):
             // K rows are neutralised by the -inf mask below, V rows must be zeroed because
@@ -1082,12 +1111,17 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
     return plan;
 }
 
+bool streamTakesPointers(const DecodeParams &p, const void *workspace) {
+    const auto addr = [](const void *ptr) { return reinterpret_cast<uintptr_t>(ptr); };
+    // TMA needs 16-byte aligned pool bases; the fragment loads need 4-byte aligned q/out.
+    return ((addr(p.k_cache) | addr(p.v_cache)) & 15u) == 0 && ((addr(p.q) | addr(p.out)) & 3u) == 0 && (addr(workspace) & 255u) == 0;
+}
+
 infiniStatus_t launchDecodeStream(const Info &I, const StreamPlan &plan, const DecodeParams &p,
                                   void *workspace, size_t workspace_size, cudaStream_t stream) {
     B200_RETURN_IF(workspace_size < plan.workspace_bytes, INFINI_STATUS_INSUFFICIENT_WORKSPACE);
-    const auto addr = [](const void *ptr) { return reinterpret_cast<uintptr_t>(ptr); };
-    // TMA needs 16-byte aligned pool bases; the fragment loads need 4-byte aligned q/out.
-    if (((addr(p.k_cache) | addr(p.v_cache)) & 15u) != 0 || ((addr(p.q) | addr(p.out)) & 3u) != 0 || (addr(workspace) & 255u) != 0) {
+    if (!streamTakesPointers(p, workspace)) {
+        B200_RETURN_IF(p.new_k != nullptr, INFINI_STATUS_INTERNAL_ERROR); // the append form checks before it gets here
         return launchDecodeGeneric(I, p, stream);
     }
     CUtensorMap mk, mv;

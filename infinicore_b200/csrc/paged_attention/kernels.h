@@ -35,6 +35,13 @@ struct DecodeParams {
     long long bt_seq_stride;
 
     float scale_log2e; // scale * log2(e): scores live in the log2 domain, softmax uses exp2
+
+    // Decode step with append (null otherwise): row [seq, kv_head, :] of new_k / new_v is the K / V of
+    // position seq_len - 1; the streaming kernel uses it instead of what the cache holds there and
+    // stores it into the cache on the way.
+    const void *new_k = nullptr;
+    const void *new_v = nullptr;
+    long long new_k_seq_stride = 0, new_v_seq_stride = 0; // head stride is head_size (dense)
 };
 
 __host__ __device__ inline long long loadIndex(const void *base, long long i, int is64) {
@@ -65,6 +72,14 @@ StreamPlan planStream(const Info &info, const DeviceProps &props);
 
 infiniStatus_t launchDecodeStream(const Info &info, const StreamPlan &plan, const DecodeParams &p,
                                   void *workspace, size_t workspace_size, cudaStream_t stream);
+
+// True when launchDecodeStream will run the streaming kernel for these pointers (and not hand the
+// call to the generic kernel): the caller of the append form needs to know which one takes the rows.
+bool streamTakesPointers(const DecodeParams &p, const void *workspace);
+
+// Stand-alone append for the paths that do not fuse it: position seq_len - 1 of every sequence
+// receives its new_k / new_v row (one warp per row).
+infiniStatus_t launchAppendNewRows(const Info &info, const DecodeParams &p, cudaStream_t stream);
 
 } // namespace b200::paged_attention
 

@@ -21,8 +21,8 @@ struct Descriptor {
     size_t workspace_bytes;
 };
 
-static DecodeParams makeParams(const Info &I, void *out, const void *q, const void *k_cache, const void *v_cache,
-                               const void *block_tables, const void *seq_lens, const void *alibi_slopes) {
+DecodeParams makeDecodeParams(const Info &I, void *out, const void *q, const void *k_cache, const void *v_cache,
+                              const void *block_tables, const void *seq_lens, const void *alibi_slopes) {
     DecodeParams p;
     p.out = out;
     p.q = q;
@@ -137,7 +137,7 @@ __INFINI_C infiniStatus_t infiniopPagedAttention(
     B200_RETURN_IF(workspace_size < d->workspace_bytes, INFINI_STATUS_INSUFFICIENT_WORKSPACE);
     B200_RETURN_IF(d->workspace_bytes > 0 && workspace == nullptr, INFINI_STATUS_NULL_POINTER);
 
-    const auto p = b200::paged_attention::makeParams(I, out, q, k_cache, v_cache, block_tables, seq_lens, alibi_slopes);
+    const auto p = b200::paged_attention::makeDecodeParams(I, out, q, k_cache, v_cache, block_tables, seq_lens, alibi_slopes);
     auto cuda_stream = static_cast<cudaStream_t>(stream);
     if (d->stream.eligible) {
         return b200::paged_attention::launchDecodeStream(I, d->stream, p, workspace, workspace_size, cuda_stream);

@@ -87,6 +87,8 @@ INFINIOP_SYMBOLS = [
     "infiniopPagedAttentionPrefill", "infiniopDestroyPagedAttentionPrefillDescriptor",
     "infiniopCreatePagedCachingDescriptor", "infiniopGetPagedCachingWorkspaceSize",
     "infiniopPagedCaching", "infiniopDestroyPagedCachingDescriptor",
+    "infiniopCreatePagedDecodeStepDescriptor", "infiniopGetPagedDecodeStepWorkspaceSize",
+    "infiniopPagedDecodeStep", "infiniopDestroyPagedDecodeStepDescriptor",
 ]
 INFINIRT_SYMBOLS = [
     "infinirtInit", "infinirtGetAllDeviceCount", "infinirtGetDeviceCount", "infinirtSetDevice",
@@ -190,6 +192,25 @@ def _bind(lib: InfiniLib) -> None:
         ]
         op.infiniopDestroyPagedAttentionPrefillDescriptor.restype = c_int32
         op.infiniopDestroyPagedAttentionPrefillDescriptor.argtypes = [infiniopOperatorDescriptor_t]
+
+    # No reference counterpart: caching of the newest row + decode attention behind one call.
+    if hasattr(op, "infiniopCreatePagedDecodeStepDescriptor"):
+        op.infiniopCreatePagedDecodeStepDescriptor.restype = c_int32
+        op.infiniopCreatePagedDecodeStepDescriptor.argtypes = [
+            infiniopHandle_t, POINTER(infiniopOperatorDescriptor_t),
+            infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t,
+            infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t,
+            c_void_p, c_float,
+        ]
+        op.infiniopGetPagedDecodeStepWorkspaceSize.restype = c_int32
+        op.infiniopGetPagedDecodeStepWorkspaceSize.argtypes = [infiniopOperatorDescriptor_t, POINTER(c_size_t)]
+        op.infiniopPagedDecodeStep.restype = c_int32
+        op.infiniopPagedDecodeStep.argtypes = [
+            infiniopOperatorDescriptor_t, c_void_p, c_size_t,
+            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        ]
+        op.infiniopDestroyPagedDecodeStepDescriptor.restype = c_int32
+        op.infiniopDestroyPagedDecodeStepDescriptor.argtypes = [infiniopOperatorDescriptor_t]
 
     # reference test/infiniop/libinfiniop/op_register.py:2231-2269
     op.infiniopCreatePagedCachingDescriptor.restype = c_int32

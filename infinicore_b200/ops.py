@@ -162,6 +162,43 @@ def paged_attention_prefill(q, k_cache, v_cache, block_tables, history_lens, cu_
     return out
 
 
+def paged_decode_step(q, k_cache, v_cache, new_k, new_v, block_tables, cache_lens, alibi_slopes=None, scale: float = 1.0, *, out=None):
+    """One decode layer's cache update and attention behind one call (no reference counterpart: the
+    reference's callers issue paged_caching and paged_attention).  new_k / new_v [num_seqs, num_kv_heads,
+    head_size] are written to position cache_lens[i] - 1 of sequence i (the slot its block table names),
+    then q attends over the cache_lens[i] positions.  Returns `out`; the caches are updated in place."""
+    dev = _require_cuda(q, k_cache, v_cache, new_k, new_v, block_tables, cache_lens, alibi_slopes, out)
+    if out is None:
+        out = torch.empty((*q.shape[:-1], v_cache.shape[3]), dtype=q.dtype, device=q.device)
+    st = _state(dev)
+    key = ("paged_decode_step", _meta(out), _meta(q), _meta(k_cache), _meta(v_cache), _meta(new_k), _meta(new_v),
+           _meta(block_tables), _meta(cache_lens), _meta(alibi_slopes), float(scale))
+
+    def make():
+        tensors = [_desc(out), _desc(q), _desc(k_cache), _desc(v_cache), _desc(new_k), _desc(new_v), _desc(block_tables), _desc(cache_lens)]
+        alibi = _desc(alibi_slopes) if alibi_slopes is not None else None
+        desc = infiniopOperatorDescriptor_t()
+        check_error(LIBINFINIOP.infiniopCreatePagedDecodeStepDescriptor(
+            st["handle"], ctypes.byref(desc), *[t.descriptor for t in tensors],
+            alibi.descriptor if alibi is not None else None, scale))
+        size = ctypes.c_size_t(0)
+        check_error(LIBINFINIOP.infiniopGetPagedDecodeStepWorkspaceSize(desc, ctypes.byref(size)))
+        for t in tensors + ([alibi] if alibi is not None else []):
+            t.destroy_desc()
+        return {"desc": desc, "workspace": size.value, "destroy": LIBINFINIOP.infiniopDestroyPagedDecodeStepDescriptor}
+
+    entry = _lookup(st, key, make)
+    ws = _workspace(st, entry["workspace"], dev)
+    with torch.cuda.device(dev):
+        check_error(LIBINFINIOP.infiniopPagedDecodeStep(
+            entry["desc"], ws.data_ptr() if ws is not None else None, entry["workspace"],
+            out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), new_k.data_ptr(), new_v.data_ptr(),
+            block_tables.data_ptr(), cache_lens.data_ptr(),
+            alibi_slopes.data_ptr() if alibi_slopes is not None else None,
+            torch.cuda.current_stream(dev).cuda_stream))
+    return out
+
+
 def paged_caching(k_cache, v_cache, k, v, slot_mapping):
     """Scatters k/v rows [num_tokens, num_kv_heads, head_size] into the paged pools at
     slot_mapping (int64; negative = padding).  Returns (k_cache, v_cache)."""

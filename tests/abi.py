@@ -101,6 +101,61 @@ class AttentionOp:
             self.desc = None
 
 
+class DecodeStepOp:
+    """One created paged-decode-step descriptor (append + attention) plus its workspace."""
+
+    def __init__(self, out, q, k_cache, v_cache, new_k, new_v, block_tables, seq_lens, alibi, scale, path=None, index_dtype=None):
+        tensors = [_tt(out), _tt(q), _tt(k_cache), _tt(v_cache), _tt(new_k), _tt(new_v), _tt(block_tables, index_dtype),
+                   _tt(seq_lens, index_dtype)]
+        al = _tt(alibi) if alibi is not None else None
+        self.desc = infiniopOperatorDescriptor_t()
+        with decode_path(path):
+            self.status = LIBINFINIOP.infiniopCreatePagedDecodeStepDescriptor(
+                handle(), ctypes.byref(self.desc), *[t.descriptor for t in tensors],
+                al.descriptor if al is not None else None, scale)
+        for t in tensors + ([al] if al is not None else []):
+            t.destroy_desc()
+        self.workspace_size = 0
+        self.workspace = None
+        if self.status == 0:
+            size = ctypes.c_size_t(0)
+            check_error(LIBINFINIOP.infiniopGetPagedDecodeStepWorkspaceSize(self.desc, ctypes.byref(size)))
+            self.workspace_size = size.value
+            self.workspace = TestWorkspace(size.value, InfiniDeviceEnum.NVIDIA)
+
+    def run(self, out, q, k_cache, v_cache, new_k, new_v, block_tables, seq_lens, alibi=None, stream=None):
+        return LIBINFINIOP.infiniopPagedDecodeStep(
+            self.desc, self.workspace.data(), self.workspace_size,
+            out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), new_k.data_ptr(), new_v.data_ptr(),
+            block_tables.data_ptr(), seq_lens.data_ptr(), alibi.data_ptr() if alibi is not None else None, stream)
+
+    def error_flag(self) -> int:
+        if self.workspace is None or self.workspace.tensor is None:
+            return 0
+        return int(self.workspace.tensor[:4].view(torch.int32).item())
+
+    def destroy(self):
+        if self.status == 0 and self.desc:
+            check_error(LIBINFINIOP.infiniopDestroyPagedDecodeStepDescriptor(self.desc))
+            self.desc = None
+
+
+def paged_decode_step(q, k_cache, v_cache, new_k, new_v, block_tables, seq_lens, scale, alibi=None, path=None, out=None,
+                      index_dtype=None):
+    """Runs one append + decode call through the C ABI; returns `out` (synchronised); caches are updated in place."""
+    if out is None:
+        out = torch.zeros((*q.shape[:-1], v_cache.shape[3]), dtype=q.dtype, device=q.device)
+    op = DecodeStepOp(out, q, k_cache, v_cache, new_k, new_v, block_tables, seq_lens, alibi, scale, path, index_dtype)
+    check_error(op.status)
+    try:
+        check_error(op.run(out, q, k_cache, v_cache, new_k, new_v, block_tables, seq_lens, alibi))
+        torch.cuda.synchronize()
+        assert op.error_flag() == 0 or op.workspace_size == 0, "a worker's bounded wait ran out"
+    finally:
+        op.destroy()
+    return out
+
+
 def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, scale, alibi=None, path=None, out=None,
                     index_dtype=None):
     """Runs one decode call through the C ABI; returns `out` (synchronised)."""

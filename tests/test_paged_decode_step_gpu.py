@@ -1,0 +1,167 @@
+"""GPU parity of infiniopPagedDecodeStep (append the newest K/V row, then attend) through the C ABI.
+
+The operator has no reference counterpart; what it must equal is the reference's pair of calls.  So
+every case is checked three ways: the caches after the call are bit-exact against the oracle's
+paged_caching with the slots the block tables name; the output is within the decode tolerance
+(fp16 2e-3 / 2e-3, bf16 1e-2 / 1e-2) of the oracle's attention over those caches; and the result
+matches infiniopPagedCaching followed by infiniopPagedAttention on a second copy of the inputs.
+Both routes are covered: the streaming kernel that takes the rows itself, and the generic path
+(append kernel + attention kernel)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import ATTN_TOL, assert_close, torch_to_bits
+from infinicore_b200 import workloads
+from infinicore_b200.libinfiniop import InfiniDtype
+
+pytestmark = pytest.mark.gpu
+
+PATHS = [None, "generic", "stream-plan-kernel", "stream-3x4"]
+
+
+@pytest.fixture(scope="module")
+def abi():
+    import abi as _abi
+
+    yield _abi
+
+
+def run_and_check(abi, c, path, alibi=None, index_dtype=None, poison=False):
+    d = c.to("cuda")
+    if poison:
+        # the slots that receive the new rows hold NaN before the call: nothing of them may reach the output
+        nan = torch.tensor(float("nan"), dtype=c.dtype, device="cuda")
+        for i, slot in enumerate(c.slot_mapping.tolist()):
+            if slot >= 0:
+                d.k_cache[slot // c.block_size, :, slot % c.block_size, :] = nan
+                d.v_cache[slot // c.block_size, :, slot % c.block_size, :] = nan
+    k0, v0 = d.k_cache.clone(), d.v_cache.clone()
+    bt, lens = d.block_tables, d.seq_lens
+    if index_dtype is not None:
+        bt, lens = bt.to(index_dtype), lens.to(index_dtype)
+    out = torch.full((c.q.shape[0], c.num_heads, c.v_cache.shape[3]), 7.0, dtype=c.dtype, device="cuda")
+    dt_code = InfiniDtype.I32 if index_dtype == torch.int32 else None
+    got = abi.paged_decode_step(d.q, d.k_cache, d.v_cache, d.new_k, d.new_v, bt, lens, d.scale,
+                                alibi.cuda() if alibi is not None else None, path=path, out=out, index_dtype=dt_code)
+
+    # (1) caches: bit-exact against the oracle's scatter
+    kb, vb = torch_to_bits(k0), torch_to_bits(v0)
+    oracle.paged_caching(kb, vb, torch_to_bits(c.new_k), torch_to_bits(c.new_v), c.slot_mapping.numpy())
+    assert np.array_equal(torch_to_bits(d.k_cache), kb), "k_cache differs from the oracle's scatter"
+    assert np.array_equal(torch_to_bits(d.v_cache), vb), "v_cache differs from the oracle's scatter"
+    # (2) output: the oracle's attention over the updated caches
+    dt = 12 if c.dtype == torch.float16 else 19
+    want = oracle.paged_attention(torch_to_bits(c.q), kb, vb, c.block_tables.numpy(), c.seq_lens.numpy(), c.scale, dt,
+                                  alibi.numpy() if alibi is not None else None)
+    live = (c.seq_lens > 0).numpy()
+    atol, rtol = ATTN_TOL[c.dtype]
+    assert_close(got.float().cpu().numpy()[live], want[live], atol, rtol, c.name)
+    assert bool((got[~torch.from_numpy(live)] == 7.0).all()), "rows of empty sequences must stay untouched"
+    # (3) the reference's pair of calls on the same inputs
+    abi.paged_caching(k0, v0, d.new_k, d.new_v, d.slot_mapping)
+    pair = abi.paged_attention(d.q, k0, v0, bt, lens, d.scale, alibi.cuda() if alibi is not None else None, path=path,
+                               index_dtype=dt_code)
+    assert torch.equal(k0, d.k_cache) and torch.equal(v0, d.v_cache)
+    assert_close(got.float().cpu().numpy()[live], pair.float().cpu().numpy()[live], atol, rtol, c.name + " vs pair of calls")
+    return got
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_config1_flow(abi, path):
+    run_and_check(abi, workloads.config1_small(seed=1), path)
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("dtype,heads,kvh,hd,bs", [(torch.bfloat16, 32, 8, 128, 16), (torch.float16, 8, 2, 64, 16),
+                                                   (torch.bfloat16, 32, 1, 128, 32), (torch.float16, 12, 1, 128, 16),
+                                                   (torch.bfloat16, 16, 2, 256, 16)])
+def test_every_row_of_the_last_page(abi, path, dtype, heads, kvh, hd, bs):
+    """Lengths 1..2*block+1: the newest token lands on every row of a page, on both sides of a page
+    boundary and of a 16-token tile boundary; group sizes 4, 8, 12 and 32 (several head tiles share one
+    kv-head, only one of them stores the row); the destination slots hold NaN beforehand."""
+    lens = list(range(1, 2 * bs + 2)) + [0, 5 * bs, 5 * bs + 1]
+    c = workloads.build_case("lastpage", dtype=dtype, seq_lens=lens, num_heads=heads, num_kv_heads=kvh, head_size=hd,
+                             block_size=bs, seed=41, slack_blocks=3)
+    run_and_check(abi, c, path, poison=True)
+
+
+@pytest.mark.parametrize("path", [None, "generic"])
+def test_ragged_long_batch_with_alibi_and_int32_indices(abi, path):
+    lens = workloads.config3_lengths(seed=7, num_seqs=48, hi=6000)
+    c = workloads.build_case("ragged", dtype=torch.bfloat16, seq_lens=lens, num_heads=16, num_kv_heads=4, head_size=128,
+                             block_size=16, seed=42, std=0.5)
+    alibi = -torch.linspace(0.01, 0.3, 16, dtype=torch.float32)
+    run_and_check(abi, c, path, alibi=alibi, index_dtype=torch.int32, poison=True)
+
+
+def test_shapes_the_streaming_kernel_does_not_take_use_the_append_kernel(abi):
+    """Block size 4 (no streaming plan) and the 576/512 latent-attention shape: append kernel + generic attention."""
+    c = workloads.build_case("bs4", dtype=torch.float16, seq_lens=[1, 4, 5, 23, 0, 64], num_heads=4, num_kv_heads=2, head_size=64,
+                             block_size=4, seed=43)
+    run_and_check(abi, c, None, poison=True)
+    c = workloads.build_case("mla", dtype=torch.bfloat16, seq_lens=[17, 1, 90], num_heads=8, num_kv_heads=1, head_size=576,
+                             block_size=16, seed=44, value_size=512, std=0.3)
+    run_and_check(abi, c, None)
+
+
+def test_unaligned_new_rows_fall_back_to_the_append_kernel(abi):
+    """new_k / new_v views whose rows are not 16-byte aligned: same results through the unfused route."""
+    c = workloads.build_case("unaligned", dtype=torch.bfloat16, seq_lens=[33, 16, 100], num_heads=8, num_kv_heads=2, head_size=128,
+                             block_size=16, seed=45)
+    pad_k = torch.zeros(c.new_k.numel() + 1, dtype=c.dtype)
+    pad_v = torch.zeros(c.new_v.numel() + 1, dtype=c.dtype)
+    pad_k[1:] = c.new_k.flatten()
+    pad_v[1:] = c.new_v.flatten()
+
+    class Shifted:  # the case with new rows living 2 bytes off a 16-byte boundary on the device
+        def __init__(self, base):
+            self.__dict__.update(base.__dict__)
+
+        def to(self, device):
+            d = c.to(device)
+            d.new_k = pad_k.to(device)[1:].view_as(c.new_k)
+            d.new_v = pad_v.to(device)[1:].view_as(c.new_v)
+            return d
+
+    run_and_check(abi, Shifted(c), None)
+
+
+def test_descriptor_refuses_bad_new_rows(abi):
+    from infinicore_b200.libinfiniop import InfiniStatusError
+
+    c = workloads.build_case("bad", dtype=torch.float16, seq_lens=[8, 9], num_heads=4, num_kv_heads=2, head_size=64, block_size=16, seed=46)
+    d = c.to("cuda")
+    out = torch.zeros_like(d.q)
+    for bad_k, code in [(d.new_k[:1], 11), (d.new_k.float(), 10), (torch.zeros((2, 2, 128), dtype=c.dtype, device="cuda")[:, :, ::2], 12),
+                        (torch.zeros((2, 4, 64), dtype=c.dtype, device="cuda")[:, ::2], 12)]:
+        op = abi.DecodeStepOp(out, d.q, d.k_cache, d.v_cache, bad_k, d.new_v, d.block_tables, d.seq_lens, None, d.scale)
+        assert op.status == code, (tuple(bad_k.shape), op.status)
+    with pytest.raises(InfiniStatusError):
+        abi.check_error(abi.LIBINFINIOP.infiniopGetPagedDecodeStepWorkspaceSize(None, None))
+
+
+def test_python_operator_and_two_steps_in_a_row(abi):
+    """infinicore_b200.paged_decode_step: two consecutive decode steps of growing sequences."""
+    import infinicore_b200 as ib
+
+    c = workloads.build_case("steps", dtype=torch.bfloat16, seq_lens=[15, 14, 30, 200], num_heads=32, num_kv_heads=8, head_size=128,
+                             block_size=16, seed=47, slack_blocks=0, max_blocks_per_seq=14)
+    d = c.to("cuda")
+    kb, vb = torch_to_bits(c.k_cache).copy(), torch_to_bits(c.v_cache).copy()
+    lens = c.seq_lens.clone()
+    gen = torch.Generator().manual_seed(5)
+    for step in range(2):
+        nk = torch.randn(c.new_k.shape, generator=gen).to(c.dtype)
+        nv = torch.randn(c.new_v.shape, generator=gen).to(c.dtype)
+        q = torch.randn(c.q.shape, generator=gen).to(c.dtype)
+        slots = torch.tensor([int(c.block_tables[i, (int(lens[i]) - 1) // 16]) * 16 + (int(lens[i]) - 1) % 16 for i in range(4)])
+        got = ib.paged_decode_step(q.cuda(), d.k_cache, d.v_cache, nk.cuda(), nv.cuda(), d.block_tables, lens.cuda(), None, c.scale)
+        torch.cuda.synchronize()
+        oracle.paged_caching(kb, vb, torch_to_bits(nk), torch_to_bits(nv), slots.numpy())
+        want = oracle.paged_attention(torch_to_bits(q), kb, vb, c.block_tables.numpy(), lens.numpy(), c.scale, 19)
+        assert np.array_equal(torch_to_bits(d.k_cache), kb)
+        atol, rtol = ATTN_TOL[c.dtype]
+        assert_close(got.float().cpu().numpy(), want, atol, rtol, f"step {step}")
+        lens = lens + 1  # stays inside each sequence's last allocated page for these lengths
