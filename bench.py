@@ -276,7 +276,13 @@ class AbiStep:
         c = [tt(case.k_cache), tt(case.v_cache), tt(case.new_k), tt(case.new_v), tt(case.slot_mapping)]
         self.cache = infiniopOperatorDescriptor_t()
         check_error(LIBINFINIOP.infiniopCreatePagedCachingDescriptor(self.handle, ctypes.byref(self.cache), *[t.descriptor for t in c]))
-        for t in a + c:
+        # the one-call form of the same step (no reference counterpart): reported beside the two-call step
+        f = [tt(self.out), tt(case.q), tt(case.k_cache), tt(case.v_cache), tt(case.new_k), tt(case.new_v), tt(case.block_tables),
+             tt(case.seq_lens)]
+        self.fused = infiniopOperatorDescriptor_t()
+        check_error(LIBINFINIOP.infiniopCreatePagedDecodeStepDescriptor(self.handle, ctypes.byref(self.fused), *[t.descriptor for t in f],
+                                                                        None, case.scale))
+        for t in a + c + f:
             t.destroy_desc()
         # caching + (streaming path: main + combine, plus a plan launch for batches > 4095 sequences;
         # generic path: one kernel)
@@ -286,6 +292,12 @@ class AbiStep:
         c = self.case
         self.check(self.lib.infiniopPagedCaching(self.cache, None, 0, c.k_cache.data_ptr(), c.v_cache.data_ptr(),
                                                  c.new_k.data_ptr(), c.new_v.data_ptr(), c.slot_mapping.data_ptr(), stream))
+
+    def fused_step(self, stream):
+        c = self.case
+        self.check(self.lib.infiniopPagedDecodeStep(self.fused, self.ws.data_ptr(), self.ws_size, self.out.data_ptr(), c.q.data_ptr(),
+                                                    c.k_cache.data_ptr(), c.v_cache.data_ptr(), c.new_k.data_ptr(), c.new_v.data_ptr(),
+                                                    c.block_tables.data_ptr(), c.seq_lens.data_ptr(), None, stream))
 
     def attention(self, stream):
         c = self.case
@@ -407,6 +419,11 @@ def gpu_arm(args):
     # the dominant kernel on its own: K attention calls back to back (plan/combine launches included)
     attn_ms = timed(lambda: step.attention(sptr), K) / K
     cache_ms = timed(lambda: step.caching(sptr), K) / K
+    fused_ms = None
+    if flush is None and not head_mode:
+        for _ in range(3):
+            step.fused_step(sptr)
+        fused_ms = max_over_ranks(timed(lambda: step.fused_step(sptr), K) / K)
 
     kv_bytes_all = sum_over_ranks(float(case.kv_bytes))
     seqs_all = sum_over_ranks(float(case.num_seqs))
@@ -479,6 +496,10 @@ def gpu_arm(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                     "note": "q, new K/V rows, slots, block tables and lengths copied in from pinned host memory and the output copied "
                             "back every step; the KV cache itself is device state"},
+            "fused_step": (None if fused_ms is None else
+                           {"ms_per_step": fused_ms, "value": kv_bytes_all / (fused_ms * 1e-3) / 1e9, "unit": "GB/s",
+                            "note": "the same step through infiniopPagedDecodeStep (cache append inside the attention kernel, "
+                                    "one launch less); not the reference's call sequence, so not the headline"}),
             "gpu_launches": step.launches_per_step * K,  # inside the timed region that `value` comes from
             "clocks": clocks,
         }
