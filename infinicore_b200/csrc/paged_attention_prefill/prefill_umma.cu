@@ -46,7 +46,6 @@ constexpr int kBN = 64;                  // KV tokens per stage = MMA N of S, K 
 constexpr int kChunks = kHD / 64;        // 128-byte column chunks per row
 constexpr int kQBytes = kChunks * kBM * 128;        // 32 KiB
 constexpr int kTensorBytes = kChunks * kBN * 128;   // one K (or V) tile: 16 KiB
-constexpr int kPBytes = kBM * kBN * 2;              // 16 KiB
 constexpr long long kWaitLimitCycles = 4000000000ll; // an mbarrier wait gives up after ~2 s
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -143,6 +142,32 @@ __device__ __forceinline__ void ummaF16(uint32_t d_tmem, uint64_t a_desc, uint64
         "}\n"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem desc]: A is read from tensor memory (row = lane, two 16-bit
+// elements of the K extent per 32-bit column); one thread issues it
+__device__ __forceinline__ void ummaF16FromTmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 consecutive 32-bit columns of this thread's TMEM lane, raw bits
+__device__ __forceinline__ void tmemStoreBits32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr),
+          "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 // 32 consecutive fp32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tmemLoad32(uint32_t taddr, float (&v)[32]) {
@@ -272,8 +297,10 @@ struct UmmaArgs {
 };
 
 // smem layout (dynamic, 1024-aligned):
-//   [Q: kQ x 32 KiB][K ring: stages x 16 KiB][V ring: stages x 16 KiB][P: kQ x 16 KiB][barriers][tmem base][scratch]
-// TMEM columns of q-tile i (base + i * 256): S buffer 0 [0,64)  S buffer 1 [64,128)  O [128,256)
+//   [Q: kQ x 32 KiB][K ring: stages x 16 KiB][V ring: stages x 16 KiB][barriers][tmem base][scratch]
+// TMEM columns of q-tile i (base + i * 256): S buffer 0 [0,64)  S buffer 1 [64,128)  O [128,256); the
+// probabilities of a tile overwrite the first 32 columns of the S buffer their scores came from (two
+// 16-bit values per column) and feed P.V from there as its A operand - P never touches shared memory.
 //
 // kQ q-heads of one GQA group (same 128 token rows) share every staged KV tile: with kQ = 2 each
 // byte brought in from L2 feeds twice the math and eight softmax warps keep the special-function
@@ -286,7 +313,7 @@ struct UmmaArgs {
 // They talk through mbarriers only:
 //   k_full/v_full[stage]   producers -> MMA (bytes landed; one arrival per producer warp)
 //   k_empty/v_empty[stage] MMA -> producers (tcgen05.commit, one per MMA warp)
-//   s_ready[i][buf]        MMA i -> softmax i (S retired)           s_free[i][buf]  softmax i -> MMA i (S read, 4 arrivals)
+//   s_ready[i][buf]        MMA i -> softmax i (S retired)
 //   p_ready[i]             softmax i -> MMA i (P stored, 4 arrivals) o_done[i]      MMA i -> softmax i (P.V retired)
 // An MMA warp runs one S ahead: S(t+1) is issued before it waits for P(t), so the tensor core works on
 // the next scores while the softmax warps are busy with the current ones.
@@ -306,23 +333,20 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     constexpr int kRingOff = kQ * kQBytes;
-    constexpr int kPOff = kRingOff + kStages * 2 * kTensorBytes;
-    constexpr int kBarOff = kPOff + kQ * kPBytes;
+    constexpr int kBarOff = kRingOff + kStages * 2 * kTensorBytes;
     const uint32_t smem0 = smemAddr(smem_raw);
     const uint32_t q_tiles = smem0;
     const uint32_t ring = smem0 + kRingOff;
-    const uint32_t p_tiles = smem0 + kPOff;
     const uint32_t k_full = smem0 + kBarOff;              // [kStages]
     const uint32_t k_empty = k_full + kStages * 8;        // [kStages]
     const uint32_t v_full = k_empty + kStages * 8;        // [kStages]
     const uint32_t v_empty = v_full + kStages * 8;        // [kStages]
     const uint32_t s_ready = v_empty + kStages * 8;       // [kQ][2]
-    const uint32_t s_free = s_ready + kQ * 16;            // [kQ][2]
-    const uint32_t p_ready = s_free + kQ * 16;            // [kQ]
+    const uint32_t p_ready = s_ready + kQ * 16;           // [kQ]
     const uint32_t o_done = p_ready + kQ * 8;             // [kQ]
     const uint32_t drain_bar = o_done + kQ * 8;           // [kQ]
     const uint32_t q_bar = drain_bar + kQ * 8;
-    constexpr int kNumBars = 4 * kStages + 7 * kQ + 1;
+    constexpr int kNumBars = 4 * kStages + 5 * kQ + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + kBarOff + kNumBars * 8);
     int *scratch = reinterpret_cast<int *>(tmem_slot + 2);
     int &sh_seq = scratch[0];
@@ -351,7 +375,6 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
         for (int i = 0; i < kQ; ++i) {
             for (int b = 0; b < 2; ++b) {
                 mbarInit(s_ready + (i * 2 + b) * 8, 1);
-                mbarInit(s_free + (i * 2 + b) * 8, 4);
             }
             mbarInit(p_ready + i * 8, 4);
             mbarInit(o_done + i * 8, 1);
@@ -529,10 +552,9 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
             // descriptors differ only in their start-address field: build one per operand and add
             const uint64_t q_desc = smemDesc(q_tiles + i * kQBytes, 16, 1024);
             const uint64_t k_desc = smemDesc(ring, 16, 1024);
-            const uint64_t p_desc = smemDesc(p_tiles + i * kPBytes, 16, 1024);
             const uint64_t v_desc = smemDesc(ring + kStages * kTensorBytes, kBN * 128, 1024);
             const uint32_t tmem_q = __shfl_sync(0xffffffffu, tmem_base, 0) + i * 256;
-            const uint32_t my_s_ready = s_ready + i * 16, my_s_free = s_free + i * 16;
+            const uint32_t my_s_ready = s_ready + i * 16;
             auto waitAll = [&](uint32_t bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbarWait(bar, parity)); };
             bool ok = waitAll(q_bar, 0);
 
@@ -542,7 +564,9 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
                 if (!waitAll(k_full + stage * 8, (kt / kStages) & 1)) {
                     return false;
                 }
-                if (kt >= 2 && !waitAll(my_s_free + (kt & 1) * 8, ((kt >> 1) - 1) & 1)) { // S buffer read by tile kt - 2
+                // The S buffer also holds P of tile kt - 2 (written over the scores it came from): P.V of
+                // that tile must have retired before new scores land there.
+                if (kt >= 2 && !waitAll(o_done + i * 8, (kt - 2) & 1)) {
                     return false;
                 }
                 tcgenFenceAfter();
@@ -581,8 +605,9 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
                 if (electOne()) {
 #pragma unroll
                     for (int kk = 0; kk < kBN / 16; ++kk) {
-                        ummaF16(tmem_q + 128, p_desc + ((kk * 32) >> 4), vd + ((kk * 16 * 128) >> 4), kIdescO,
-                                (kt > 0 || kk > 0) ? 1u : 0u);
+                        // P: 16 of the K extent = 8 columns of the score buffer it was written over
+                        ummaF16FromTmem(tmem_q + 128, tmem_q + (kt & 1) * kBN + kk * 8, vd + ((kk * 16 * 128) >> 4), kIdescO,
+                                        (kt > 0 || kk > 0) ? 1u : 0u);
                     }
                     tcgenCommit(o_done + i * 8);
                     tcgenCommit(v_empty + stage * 8); // the V slot is free once every q-tile's P.V has retired
@@ -609,8 +634,7 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
         const uint32_t lane_field = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t tmem_q = tmem_base + qi * 256;
         const uint32_t tmem_o = tmem_q + 128;
-        const uint32_t p_tile = p_tiles + qi * kPBytes;
-        const uint32_t my_s_ready = s_ready + qi * 16, my_s_free = s_free + qi * 16;
+        const uint32_t my_s_ready = s_ready + qi * 16;
         const uint32_t my_p_ready = p_ready + qi * 8, my_o_done = o_done + qi * 8;
         const int gtid = tid & 127;                                    // thread index within this q-tile's four warps
         const float c_log2 = p.scale_log2e;
@@ -636,12 +660,6 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
             tcgenFenceAfter();
             float s[kBN];
             tmemLoad64(tmem_s + lane_field, s);
-            // this warp is done with the S buffer: the MMA warp may overwrite it (tile kt + 2)
-            tcgenFenceBefore();
-            __syncwarp();
-            if (lane == 0) {
-                mbarArrive(my_s_free + (kt & 1) * 8);
-            }
 
             // ---- softmax of this thread's row (log2 domain) -------------------------------------------
             // "plain" tile (the same answer for every row of the CTA): no causal cut, no ragged end, no
@@ -686,17 +704,15 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
             }
             l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
 
-            // The previous tile's P.V must have retired before P (shared memory) is overwritten and
-            // before O (TMEM) is rescaled.
-            if (kt > 0) {
+            if (__any_sync(0xffffffffu, rescale)) {
+                // O is about to be rescaled in place: the previous tile's P.V must have retired first.
+                // (rescale implies kt > 0.)  warp-collective: every lane scales its own row, alpha = 1
+                // where nothing changed.
                 ok = mbarWait(my_o_done, (kt - 1) & 1);
                 if (!ok) {
                     break;
                 }
                 tcgenFenceAfter();
-            }
-            if (__any_sync(0xffffffffu, rescale)) {
-                // warp-collective: every lane scales its own row (alpha = 1 where nothing changed)
 #pragma unroll
                 for (int c = 0; c < kHD / 32; ++c) {
                     float o[32];
@@ -721,16 +737,14 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
                     const uint32_t addr = v_tile + (rest / 8) * (kBN * 128) + vrow * 128 + (rest % 8) * 16;
                     asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
                 }
+                // generic-proxy writes that the tensor core's async-proxy reads must see
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-#pragma unroll
-            for (int c = 0; c < kBN / 8; ++c) {
-                const uint32_t addr = p_tile + row * 128 + ((c ^ (row & 7)) << 4);
-                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pw[c * 4]), "r"(pw[c * 4 + 1]),
-                             "r"(pw[c * 4 + 2]), "r"(pw[c * 4 + 3]) : "memory");
-            }
-            // P and the zeroed V rows (generic-proxy writes) must be visible to the tensor core's
-            // async-proxy reads; the TMEM stores must be ordered before the MMA that accumulates into O
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // P goes where its scores came from: the first 32 columns of this tile's S buffer, two 16-bit
+            // probabilities per column - the A operand of P.V, read by the tensor core straight from
+            // tensor memory.  The other S buffer (P of the previous tile, perhaps still being read) is
+            // not touched.  The store is ordered before the MMA by the fence and the barrier below.
+            tmemStoreBits32(tmem_s + lane_field, pw);
             tcgenFenceBefore();
             __syncwarp();
             if (lane == 0) {
@@ -870,7 +884,7 @@ bool encodeOutMap(CUtensorMap *map, const Info &info, const void *base) {
 }
 
 // tiles + barriers / TMEM slot / scan scratch
-constexpr size_t smemBytes(int stages, int nq) { return static_cast<size_t>(nq) * (kQBytes + kPBytes) + static_cast<size_t>(stages) * 2 * kTensorBytes + 512; }
+constexpr size_t smemBytes(int stages, int nq) { return static_cast<size_t>(nq) * kQBytes + static_cast<size_t>(stages) * 2 * kTensorBytes + 512; }
 
 template <typename T, int STAGES, int NQ>
 infiniStatus_t launchTyped(const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mo,
