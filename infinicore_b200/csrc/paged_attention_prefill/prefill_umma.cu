@@ -260,6 +260,31 @@ __device__ __forceinline__ float rowMax64(const float (&s)[64]) {
     b[7] = a[21];
     return max3(max3(b[0], b[1], b[2]), max3(b[3], b[4], b[5]), fmaxf(b[6], b[7]));
 }
+// Two fp32 lanes per instruction (packed f32x2 arithmetic of sm_100): halves the FMA-pipe
+// instruction count of the per-element work.
+__device__ __forceinline__ void fma2(float &d0, float &d1, float a0, float a1, float b, float c) {
+    asm("{\n"
+        ".reg .b64 ra, rb, rc, rd;\n"
+        "mov.b64 ra, {%2, %3};\n"
+        "mov.b64 rb, {%4, %4};\n"
+        "mov.b64 rc, {%5, %5};\n"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n"
+        "mov.b64 {%0, %1}, rd;\n"
+        "}\n"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add2(float &d0, float &d1, float a0, float a1) {
+    asm("{\n"
+        ".reg .b64 ra, rd;\n"
+        "mov.b64 ra, {%2, %3};\n"
+        "mov.b64 rd, {%0, %1};\n"
+        "add.rn.f32x2 rd, rd, ra;\n"
+        "mov.b64 {%0, %1}, rd;\n"
+        "}\n"
+        : "+f"(d0), "+f"(d1)
+        : "f"(a0), "f"(a1));
+}
 __device__ __forceinline__ float fastExp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -307,28 +332,28 @@ struct UmmaArgs {
 // units busy while the tensor core works.  kQ = 1 is the same kernel for odd group sizes.
 //
 // Warp roles: softmax warps [0, 4 kQ) (warp w serves q-tile w / 4; thread owns query row
-// (w % 4) * 32 + lane = its TMEM lane), then kQ MMA-issuing warps (one per q-tile; the first also owns
-// the TMEM allocation) and 2 kQ TMA producer warps (each stages its share of every K/V tile's pages, so
+// (w % 4) * 32 + lane = its TMEM lane), then 2 kQ MMA-issuing warps (per q-tile one for the scores and
+// one for P.V; the first also owns the TMEM allocation) and 2 kQ TMA producer warps (each stages its share of every K/V tile's pages, so
 // neither the copies' issue cost nor the tensor-core instructions' issue cost sits in one warp).
 // They talk through mbarriers only:
 //   k_full/v_full[stage]   producers -> MMA (bytes landed; one arrival per producer warp)
 //   k_empty/v_empty[stage] MMA -> producers (tcgen05.commit, one per MMA warp)
-//   s_ready[i][buf]        MMA i -> softmax i (S retired)
+//   s_ready[i][buf]        score MMA i -> softmax i (S retired)     s_free[i][buf]  P.V MMA i -> score MMA i (P consumed)
 //   p_ready[i]             softmax i -> MMA i (P stored, 4 arrivals) o_done[i]      MMA i -> softmax i (P.V retired)
-// An MMA warp runs one S ahead: S(t+1) is issued before it waits for P(t), so the tensor core works on
-// the next scores while the softmax warps are busy with the current ones.
+// The score warp runs ahead of the softmax as far as the two S buffers allow, so the tensor core works
+// on the next scores while the softmax warps are busy with the current ones.
 template <typename T, int kStages, int kQ>
-__global__ void __launch_bounds__((7 * kQ) * 32)
+__global__ void __launch_bounds__((8 * kQ) * 32)
     pagedPrefillUmmaKernel(const __grid_constant__ CUtensorMap tmap_q,
                            const __grid_constant__ CUtensorMap tmap_k,
                            const __grid_constant__ CUtensorMap tmap_v,
                            const __grid_constant__ CUtensorMap tmap_o,
                            const UmmaArgs a) {
     constexpr int kSoftmaxWarpsAll = 4 * kQ;
-    constexpr int kMmaWarp0 = kSoftmaxWarpsAll;      // MMA warps [4 kQ, 5 kQ)
+    constexpr int kMmaWarp0 = kSoftmaxWarpsAll;      // MMA warps [4 kQ, 6 kQ): S issuers, then P.V issuers
     constexpr int kProducers = 2 * kQ;
-    constexpr int kProducerWarp0 = 5 * kQ;           // producer warps [5 kQ, 7 kQ)
-    constexpr int kNT = 7 * kQ * 32;
+    constexpr int kProducerWarp0 = 6 * kQ;           // producer warps [6 kQ, 8 kQ)
+    constexpr int kNT = 8 * kQ * 32;
     constexpr int kTmemCols = 256 * kQ;
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -342,11 +367,12 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
     const uint32_t v_full = k_empty + kStages * 8;        // [kStages]
     const uint32_t v_empty = v_full + kStages * 8;        // [kStages]
     const uint32_t s_ready = v_empty + kStages * 8;       // [kQ][2]
-    const uint32_t p_ready = s_ready + kQ * 16;           // [kQ]
+    const uint32_t s_free = s_ready + kQ * 16;            // [kQ][2]
+    const uint32_t p_ready = s_free + kQ * 16;            // [kQ]
     const uint32_t o_done = p_ready + kQ * 8;             // [kQ]
-    const uint32_t drain_bar = o_done + kQ * 8;           // [kQ]
-    const uint32_t q_bar = drain_bar + kQ * 8;
-    constexpr int kNumBars = 4 * kStages + 5 * kQ + 1;
+    const uint32_t drain_bar = o_done + kQ * 8;           // [2 kQ]
+    const uint32_t q_bar = drain_bar + 2 * kQ * 8;
+    constexpr int kNumBars = 4 * kStages + 8 * kQ + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + kBarOff + kNumBars * 8);
     int *scratch = reinterpret_cast<int *>(tmem_slot + 2);
     int &sh_seq = scratch[0];
@@ -375,10 +401,12 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
         for (int i = 0; i < kQ; ++i) {
             for (int b = 0; b < 2; ++b) {
                 mbarInit(s_ready + (i * 2 + b) * 8, 1);
+                mbarInit(s_free + (i * 2 + b) * 8, 1);
             }
             mbarInit(p_ready + i * 8, 4);
             mbarInit(o_done + i * 8, 1);
             mbarInit(drain_bar + i * 8, 1);
+            mbarInit(drain_bar + (kQ + i) * 8, 1);
         }
         mbarInit(q_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -542,10 +570,14 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
         }
     } else if (warp >= kMmaWarp0) {
         // ================================ MMA issuers ==============================================
-        // One warp per q-tile.  The whole warp walks the loop in step and waits on the barriers; one
-        // elected lane issues the tensor-core instructions.
+        // Two warps per q-tile: one issues the score MMAs (S = Q.K^T, up to two tiles ahead of the
+        // softmax - as far as the two S buffers allow), the other the P.V MMAs.  Separate warps keep a
+        // wait for the softmax out of the way of the next scores.  In each, the whole warp walks the loop
+        // in step and waits on the barriers; one elected lane issues the tensor-core instructions.
         {
-            const int i = warp - kMmaWarp0;
+            const int w = warp - kMmaWarp0;
+            const int i = w % kQ;
+            const bool scores = w < kQ;
             constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u; // 0 = f16, 1 = bf16
             constexpr uint32_t kIdescS = instrDesc(kFmt, 0, 0, kBM, kBN);  // Q (K-major) x K (K-major)
             constexpr uint32_t kIdescO = instrDesc(kFmt, 0, 1, kBM, kHD);  // P (K-major) x V (MN-major)
@@ -556,73 +588,67 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
             const uint32_t tmem_q = __shfl_sync(0xffffffffu, tmem_base, 0) + i * 256;
             const uint32_t my_s_ready = s_ready + i * 16;
             auto waitAll = [&](uint32_t bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbarWait(bar, parity)); };
-            bool ok = waitAll(q_bar, 0);
-
-            // S(kt); false if a bounded wait ran out
-            auto issueS = [&](int kt) -> bool {
-                const int stage = kt % kStages;
-                if (!waitAll(k_full + stage * 8, (kt / kStages) & 1)) {
-                    return false;
-                }
-                // The S buffer also holds P of tile kt - 2 (written over the scores it came from): P.V of
-                // that tile must have retired before new scores land there.
-                if (kt >= 2 && !waitAll(o_done + i * 8, (kt - 2) & 1)) {
-                    return false;
-                }
-                tcgenFenceAfter();
-                const uint64_t kd = k_desc + ((stage * kTensorBytes) >> 4);
-                const uint32_t d = tmem_q + (kt & 1) * kBN;
-                if (electOne()) {
-#pragma unroll
-                    for (int ks = 0; ks < kHD / 16; ++ks) {
-                        // 16 elements = 32 bytes inside the 128-byte swizzled row; 4 k-steps per 64-wide chunk
-                        const uint32_t qo = ((ks / 4) * (kBM * 128) + (ks % 4) * 32) >> 4;
-                        const uint32_t ko = ((ks / 4) * (kBN * 128) + (ks % 4) * 32) >> 4;
-                        ummaF16(d, q_desc + qo, kd + ko, kIdescS, ks > 0 ? 1u : 0u);
-                    }
-                    tcgenCommit(my_s_ready + (kt & 1) * 8);
-                    tcgenCommit(k_empty + stage * 8); // the K slot is free once every q-tile's S has retired
-                }
-                __syncwarp();
-                return true;
-            };
-
-            ok = ok && issueS(0);
-            for (int kt = 0; kt < num_kv_tiles && ok; ++kt) {
-                if (kt + 1 < num_kv_tiles) {
-                    ok = issueS(kt + 1);
+            bool ok = true;
+            if (scores) {
+                ok = waitAll(q_bar, 0);
+                for (int kt = 0; kt < num_kv_tiles && ok; ++kt) {
+                    const int stage = kt % kStages;
+                    // The S buffer also holds P of tile kt - 2 (written over the scores it came from): P.V of
+                    // that tile must have retired before new scores land there.  (A barrier per buffer: its
+                    // next arrival needs these very scores, so it is never more than one phase ahead.)
+                    ok = waitAll(k_full + stage * 8, (kt / kStages) & 1)
+                         && (kt < 2 || waitAll(s_free + (i * 2 + (kt & 1)) * 8, ((kt >> 1) - 1) & 1));
                     if (!ok) {
                         break;
                     }
-                }
-                const int stage = kt % kStages;
-                ok = waitAll(v_full + stage * 8, (kt / kStages) & 1) && waitAll(p_ready + i * 8, kt & 1);
-                if (!ok) {
-                    break;
-                }
-                tcgenFenceAfter();
-                const uint64_t vd = v_desc + ((stage * kTensorBytes) >> 4);
-                if (electOne()) {
+                    tcgenFenceAfter();
+                    const uint64_t kd = k_desc + ((stage * kTensorBytes) >> 4);
+                    const uint32_t d = tmem_q + (kt & 1) * kBN;
+                    if (electOne()) {
 #pragma unroll
-                    for (int kk = 0; kk < kBN / 16; ++kk) {
-                        // P: 16 of the K extent = 8 columns of the score buffer it was written over
-                        ummaF16FromTmem(tmem_q + 128, tmem_q + (kt & 1) * kBN + kk * 8, vd + ((kk * 16 * 128) >> 4), kIdescO,
-                                        (kt > 0 || kk > 0) ? 1u : 0u);
+                        for (int ks = 0; ks < kHD / 16; ++ks) {
+                            // 16 elements = 32 bytes inside the 128-byte swizzled row; 4 k-steps per 64-wide chunk
+                            const uint32_t qo = ((ks / 4) * (kBM * 128) + (ks % 4) * 32) >> 4;
+                            const uint32_t ko = ((ks / 4) * (kBN * 128) + (ks % 4) * 32) >> 4;
+                            ummaF16(d, q_desc + qo, kd + ko, kIdescS, ks > 0 ? 1u : 0u);
+                        }
+                        tcgenCommit(my_s_ready + (kt & 1) * 8);
+                        tcgenCommit(k_empty + stage * 8); // the K slot is free once every q-tile's S has retired
                     }
-                    tcgenCommit(o_done + i * 8);
-                    tcgenCommit(v_empty + stage * 8); // the V slot is free once every q-tile's P.V has retired
+                    __syncwarp();
                 }
-                __syncwarp();
+            } else {
+                for (int kt = 0; kt < num_kv_tiles && ok; ++kt) {
+                    const int stage = kt % kStages;
+                    ok = waitAll(v_full + stage * 8, (kt / kStages) & 1) && waitAll(p_ready + i * 8, kt & 1);
+                    if (!ok) {
+                        break;
+                    }
+                    tcgenFenceAfter();
+                    const uint64_t vd = v_desc + ((stage * kTensorBytes) >> 4);
+                    if (electOne()) {
+#pragma unroll
+                        for (int kk = 0; kk < kBN / 16; ++kk) {
+                            // P: 16 of the K extent = 8 columns of the score buffer it was written over
+                            ummaF16FromTmem(tmem_q + 128, tmem_q + (kt & 1) * kBN + kk * 8, vd + ((kk * 16 * 128) >> 4), kIdescO,
+                                            (kt > 0 || kk > 0) ? 1u : 0u);
+                        }
+                        tcgenCommit(o_done + i * 8);
+                        tcgenCommit(s_free + (i * 2 + (kt & 1)) * 8); // this tile's S / P buffer may take new scores
+                        tcgenCommit(v_empty + stage * 8); // the V slot is free once every q-tile's P.V has retired
+                    }
+                    __syncwarp();
+                }
             }
             if (!ok) {
                 sh_failed = 1;
             }
             // whatever this warp issued must retire before TMEM and shared memory are given back
             if (electOne()) {
-                tcgenCommit(drain_bar + i * 8);
+                tcgenCommit(drain_bar + w * 8);
             }
             __syncwarp();
-            (void)waitAll(drain_bar + i * 8, 0);
+            (void)waitAll(drain_bar + w * 8, 0);
         }
     } else {
         // ================================ softmax warps ==========================================
@@ -693,16 +719,19 @@ __global__ void __launch_bounds__((7 * kQ) * 32)
             }
             // p_j = 2^(x_j - m); x_j = s_j * scale (plain) or s_j already transformed
             uint32_t pw[kBN / 2];
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            float sum8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             const float neg_m = -m_used;
+            const float mul = plain ? c_log2 : 1.f; // transformed scores are already scaled
 #pragma unroll
             for (int j = 0; j < kBN; j += 2) {
-                const float p0 = fastExp2(plain ? fmaf(s[j], c_log2, neg_m) : s[j] + neg_m);
-                const float p1 = fastExp2(plain ? fmaf(s[j + 1], c_log2, neg_m) : s[j + 1] + neg_m);
-                sum4[(j >> 1) & 3] += p0 + p1;
+                float x0, x1;
+                fma2(x0, x1, s[j], s[j + 1], mul, neg_m);
+                const float p0 = fastExp2(x0);
+                const float p1 = fastExp2(x1);
+                add2(sum8[j & 6], sum8[(j & 6) + 1], p0, p1);
                 pw[j / 2] = packPair(p0, p1, T());
             }
-            l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            l_run = l_run * alpha + (((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7])));
 
             if (__any_sync(0xffffffffu, rescale)) {
                 // O is about to be rescaled in place: the previous tile's P.V must have retired first.
@@ -905,7 +934,7 @@ infiniStatus_t launchTyped(const UmmaArgs &args, const CUtensorMap &mq, const CU
         }
     }
     const dim3 grid(tiles, args.pp.d.num_heads / NQ);
-    kernel<<<grid, 7 * NQ * 32, smemBytes(STAGES, NQ), stream>>>(mq, mk, mv, mo, args);
+    kernel<<<grid, 8 * NQ * 32, smemBytes(STAGES, NQ), stream>>>(mq, mk, mv, mo, args);
     return checkLaunch("pagedPrefillUmmaKernel");
 }
 
