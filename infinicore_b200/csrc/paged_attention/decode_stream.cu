@@ -92,6 +92,9 @@ __device__ __forceinline__ void mbarExpectTx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 
+__device__ __forceinline__ void mbarArrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ bool mbarTryWait(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
@@ -790,6 +793,393 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
 }
 
 // ---------------------------------------------------------------------------------------
+// Wide-head kernel: key width 576 (value width 576, or 512 for latent attention).
+//
+// Same decomposition, plan, partial records and combine as above, but one worker is a CTA of four
+// warps instead of one warp: a 16-token tile is 36 KiB here and the O accumulator of 8 heads x 576
+// columns does not fit one warp's registers.  The four warps share one ring of staged tiles; every
+// warp computes the full S^T = Q.K^T of the tile (four times the score MMAs, still far below the
+// tensor pipe's rate next to 36 KiB of HBM traffic per tile) and owns a quarter of the value
+// columns for O += P.V.  Warp 0 also issues the copies.  A slot is handed back through an "empty"
+// mbarrier on which each of the four warps arrives once it has read the slot; before it consumes tile
+// i, warp 0 refills the slot tile i - 1 has just left.  All waits are bounded.
+// ---------------------------------------------------------------------------------------
+constexpr int kWideWarps = 4;
+
+template <typename T, int KD, int VD>
+__global__ void __launch_bounds__(kWideWarps * 32)
+    pagedDecodeWideKernel(const __grid_constant__ CUtensorMap tmap_k,
+                          const __grid_constant__ CUtensorMap tmap_v,
+                          const StreamArgs a) {
+    constexpr int kKChunks = KD / 64;
+    constexpr int kVChunks = VD / 64;
+    constexpr int kBoxBytes = kTileTokens * 128;
+    constexpr int kKBytes = kKChunks * kBoxBytes;
+    constexpr int kVBytes = kVChunks * kBoxBytes;
+    constexpr int kStageBytes = kKBytes + kVBytes;
+    constexpr int kKSteps = KD / 16;
+    constexpr int kKChunk = 6;                        // k-steps fetched per batch of ldmatrix (divides 36)
+    constexpr int kCols = VD / kWideWarps;            // value columns per warp: 144 or 128
+    constexpr int kNTiles = kCols / 8;                // 18 or 16 (even)
+    constexpr int kVPieces = kCols / 8;               // 16-byte pieces of a V row per warp
+    static_assert(kKSteps % kKChunk == 0 && kNTiles % 2 == 0 && kKChunks + kVChunks <= 32, "shape");
+
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2;
+    const int t = lane & 3;
+    const int stages = a.stages;
+    const DecodeParams &p = a.p;
+
+    const uint32_t ring = smemAddr(smem_raw);
+    const uint32_t full = ring + stages * kStageBytes;
+    const uint32_t empty = full + stages * 8;
+    __shared__ int failed_s;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < stages; ++i) {
+            mbarInit(full + i * 8, 1);
+            mbarInit(empty + i * 8, kWideWarps);
+        }
+        failed_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    gridDependencyWait();
+    gridLaunchDependents();
+
+    const int worker = blockIdx.x;
+    const long long *prefix = a.prefix;
+    const long long total_tiles = a.header->total_tiles;
+    const long long range_len = a.header->range_len;
+    const int num_ranges = a.header->num_ranges;
+    if (worker >= num_ranges) {
+        return;
+    }
+    const long long x0 = worker * range_len;
+    const long long count = (total_tiles - x0 < range_len) ? (total_tiles - x0) : range_len;
+    const int4 rs = a.range_start[worker];
+    Cursor gen;
+    gen.s = rs.x;
+    gen.j = rs.y;
+    gen.ti = rs.z;
+    gen.nt = static_cast<int>(prefix[rs.x + 1] - prefix[rs.x]);
+    Cursor cur = gen;
+
+    if (threadIdx.x == 0) {
+        int4 task = make_int4(-1, -1, 0, 0);
+        if (rs.z != 0) {
+            const long long unit_start = x0 - rs.z;
+            const long long r_first = unit_start / range_len;
+            if (worker == r_first + 1) {
+                const long long r_last = (unit_start + gen.nt - 1) / range_len;
+                task = make_int4(rs.x, rs.y, static_cast<int>(r_first), static_cast<int>(r_last - r_first + 1));
+            }
+        }
+        a.tasks[worker] = task;
+    }
+
+    const int tpp = a.tiles_per_page;
+    const int head_tiles = a.head_tiles;
+    auto tableEntry = [&](const Cursor &c) -> long long {
+        const int page = (tpp == 1) ? c.ti : c.ti / tpp;
+        return loadIndex(p.block_tables, c.s * p.bt_seq_stride + page, p.index_is_64);
+    };
+    // warp 0 only
+    auto issue = [&](int stage, const Cursor &c, long long block) {
+        const uint32_t bar = full + stage * 8;
+        const uint32_t dst = ring + stage * kStageBytes;
+        if (lane == 0) {
+            mbarExpectTx(bar, kStageBytes);
+        }
+        __syncwarp();
+        if (lane < kKChunks + kVChunks) {
+            const int is_v = lane >= kKChunks;
+            const int chunk = is_v ? lane - kKChunks : lane;
+            const int row0 = (tpp == 1) ? 0 : (c.ti % tpp) * kTileTokens;
+            const int kv_head = (head_tiles == 1) ? c.j : c.j / head_tiles;
+            tmaLoadBox(dst + (is_v ? kKBytes : 0) + chunk * kBoxBytes, is_v ? &tmap_v : &tmap_k, bar,
+                       chunk * 64, row0, kv_head, static_cast<int>(block));
+        }
+    };
+
+    long long issued = 0;
+    long long next_block = 0;
+    if (warp == 0) {
+        for (int i = 0; i < stages && i < count; ++i) {
+            issue(i, gen, tableEntry(gen));
+            ++issued;
+            if (issued < count) {
+                advance(gen, prefix, p.num_seqs, a.units_per_seq);
+            }
+        }
+        next_block = (issued < count) ? tableEntry(gen) : 0;
+    }
+
+    uint32_t qa[kKSteps][2];
+    float o[kNTiles][4];
+    float m_run = -INFINITY, l_run = 0.f, slope_log2 = 0.f;
+    int first_ti = cur.ti, seq_len = 0;
+    bool row_valid = false;
+    auto loadUnit = [&]() {
+        const int kv_head = cur.j / head_tiles;
+        const int head_in_group = (cur.j % head_tiles) * kHeadsPerTile + g;
+        row_valid = head_in_group < p.group_size;
+        const int head = kv_head * p.group_size + (row_valid ? head_in_group : 0);
+        const T *q = static_cast<const T *>(p.q) + cur.s * p.q_seq_stride + head * p.q_head_stride;
+#pragma unroll
+        for (int ks = 0; ks < kKSteps; ++ks) {
+            qa[ks][0] = row_valid ? *reinterpret_cast<const uint32_t *>(q + ks * 16 + 2 * t) : 0u;
+            qa[ks][1] = row_valid ? *reinterpret_cast<const uint32_t *>(q + ks * 16 + 8 + 2 * t) : 0u;
+        }
+        slope_log2 = (p.alibi_slopes != nullptr && row_valid) ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
+        long long len = loadIndex(p.seq_lens, cur.s, p.index_is_64);
+        const long long capacity = static_cast<long long>(p.max_blocks_per_seq) * p.block_size;
+        seq_len = static_cast<int>(len > capacity ? capacity : len);
+#pragma unroll
+        for (int n = 0; n < kNTiles; ++n) {
+            o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+        }
+        m_run = -INFINITY;
+        l_run = 0.f;
+        first_ti = cur.ti;
+    };
+    loadUnit();
+
+    bool failed = false;
+    int stage = 0;
+    uint32_t parity = 0;
+    long long i = 0;
+    for (; i < count; ++i) {
+        const uint32_t k_tile = ring + stage * kStageBytes;
+        const uint32_t v_tile = k_tile + kKBytes;
+        // warp 0 first refills the slot of the previous tile (the four warps have just left it) with
+        // tile i - 1 + stages, so that stages - 1 tiles are in flight behind the one being consumed
+        if (warp == 0 && i >= 1 && issued < count) {
+            const int prev_stage = (stage == 0) ? stages - 1 : stage - 1;
+            const uint32_t prev_parity = (stage == 0) ? (parity ^ 1u) : parity; // phase of the slot's latest use
+            if (!mbarWait(empty + prev_stage * 8, prev_parity)) {
+                failed = true;
+                break;
+            }
+            issue(prev_stage, gen, next_block);
+            ++issued;
+            if (issued < count) {
+                advance(gen, prefix, p.num_seqs, a.units_per_seq);
+                next_block = tableEntry(gen);
+            }
+        }
+        if (!mbarWait(full + stage * 8, parity) || *reinterpret_cast<volatile int *>(&failed_s) != 0) {
+            failed = true;
+            break;
+        }
+        const int tok0 = cur.ti * kTileTokens;
+        const int valid = seq_len - tok0; // >= 1 by construction
+        const int v_piece0 = warp * kVPieces; // this warp's first 16-byte piece of a V row
+
+        if (p.new_k != nullptr && valid <= kTileTokens) {
+            // Decode step with append: every warp swaps the newest row into what it reads itself (all of
+            // K, its own value columns); the stores into the cache are shared out the same way.
+            constexpr int kKPieces = KD / 8;
+            const int kv_head = cur.j / head_tiles;
+            const int row = valid - 1;
+            const T *nk = static_cast<const T *>(p.new_k) + cur.s * p.new_k_seq_stride + kv_head * KD;
+            const T *nv = static_cast<const T *>(p.new_v) + cur.s * p.new_v_seq_stride + kv_head * VD;
+            const bool writer = (cur.j % head_tiles) == 0;
+            const long long block = writer ? tableEntry(cur) : 0;
+            const int row_in_block = (seq_len - 1) % p.block_size;
+            T *kc = static_cast<T *>(const_cast<void *>(p.k_cache)) + block * p.k_block_stride + kv_head * p.k_head_stride + row_in_block * p.k_row_stride;
+            T *vc = static_cast<T *>(const_cast<void *>(p.v_cache)) + block * p.v_block_stride + kv_head * p.v_head_stride + row_in_block * p.v_row_stride;
+            for (int piece = lane; piece < kKPieces; piece += 32) {
+                const uint4 val = *reinterpret_cast<const uint4 *>(nk + piece * 8);
+                const uint32_t addr = k_tile + (piece >> 3) * kBoxBytes + row * 128 + (((piece & 7) ^ (row & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w) : "memory");
+                if (writer && warp == 0) {
+                    *reinterpret_cast<uint4 *>(kc + piece * 8) = val;
+                }
+            }
+            for (int q8 = lane; q8 < kVPieces; q8 += 32) {
+                const int piece = v_piece0 + q8;
+                const uint4 val = *reinterpret_cast<const uint4 *>(nv + piece * 8);
+                const uint32_t addr = v_tile + (piece >> 3) * kBoxBytes + row * 128 + (((piece & 7) ^ (row & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w) : "memory");
+                if (writer) {
+                    *reinterpret_cast<uint4 *>(vc + piece * 8) = val;
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+        }
+        if (valid < kTileTokens) {
+            // V rows past the end may hold anything: zero this warp's columns of them (0 * NaN would
+            // poison the accumulators); K rows are neutralised by the -inf mask below.
+            for (int idx = lane; idx < (kTileTokens - valid) * kVPieces; idx += 32) {
+                const int row = valid + idx / kVPieces;
+                const int piece = v_piece0 + idx % kVPieces;
+                const uint32_t addr = v_tile + (piece >> 3) * kBoxBytes + row * 128 + (((piece & 7) ^ (row & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+        }
+
+        const int k_row = ((lane >> 4) << 3) + (lane & 7);
+        const int k_half = (lane >> 3) & 1;
+        const int v_row = (((lane >> 3) & 1) << 3) + (lane & 7);
+        const int v_sel = lane >> 4;
+        auto kAddr = [&](int ks) {
+            const int col = ks * 2 + k_half;
+            return k_tile + (col >> 3) * kBoxBytes + k_row * 128 + (((col & 7) ^ (k_row & 7)) << 4);
+        };
+        auto vAddr = [&](int np) { // np counts pairs of 8-column n-tiles inside this warp's slice
+            const int col = v_piece0 + np * 2 + v_sel;
+            return v_tile + (col >> 3) * kBoxBytes + v_row * 128 + (((col & 7) ^ (v_row & 7)) << 4);
+        };
+
+        // ---- S^T = Q . K^T over the whole key width (every warp) ------------------------------
+        float sa[2][4], sb[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            sa[n][0] = sa[n][1] = sa[n][2] = sa[n][3] = 0.f;
+            sb[n][0] = sb[n][1] = sb[n][2] = sb[n][3] = 0.f;
+        }
+#pragma unroll
+        for (int c0 = 0; c0 < kKSteps; c0 += kKChunk) {
+            uint32_t kb[kKChunk][4];
+#pragma unroll
+            for (int ks = 0; ks < kKChunk; ++ks) {
+                ldmatrixX4(kAddr(c0 + ks), kb[ks][0], kb[ks][1], kb[ks][2], kb[ks][3]);
+            }
+#pragma unroll
+            for (int ks = 0; ks < kKChunk; ks += 2) {
+                mma16816<T>(sa[0], qa[c0 + ks][0], 0u, qa[c0 + ks][1], 0u, kb[ks][0], kb[ks][1]);
+                mma16816<T>(sa[1], qa[c0 + ks][0], 0u, qa[c0 + ks][1], 0u, kb[ks][2], kb[ks][3]);
+                mma16816<T>(sb[0], qa[c0 + ks + 1][0], 0u, qa[c0 + ks + 1][1], 0u, kb[ks + 1][0], kb[ks + 1][1]);
+                mma16816<T>(sb[1], qa[c0 + ks + 1][0], 0u, qa[c0 + ks + 1][1], 0u, kb[ks + 1][2], kb[ks + 1][3]);
+            }
+        }
+
+        // ---- online softmax (log2 domain), identical in the four warps ---------------------------
+        float x[4];
+        x[0] = (sa[0][0] + sb[0][0]) * p.scale_log2e;
+        x[1] = (sa[0][1] + sb[0][1]) * p.scale_log2e;
+        x[2] = (sa[1][0] + sb[1][0]) * p.scale_log2e;
+        x[3] = (sa[1][1] + sb[1][1]) * p.scale_log2e;
+        if (slope_log2 != 0.f) {
+            const int rel = tok0 + 2 * t - (seq_len - 1);
+            x[0] += slope_log2 * static_cast<float>(rel);
+            x[1] += slope_log2 * static_cast<float>(rel + 1);
+            x[2] += slope_log2 * static_cast<float>(rel + 8);
+            x[3] += slope_log2 * static_cast<float>(rel + 9);
+        }
+        if (valid < kTileTokens) {
+            const int c = 2 * t;
+            x[0] = (c < valid) ? x[0] : -INFINITY;
+            x[1] = (c + 1 < valid) ? x[1] : -INFINITY;
+            x[2] = (c + 8 < valid) ? x[2] : -INFINITY;
+            x[3] = (c + 9 < valid) ? x[3] : -INFINITY;
+        }
+        float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float alpha = fastExp2(m_run - m_new);
+        const float p0 = fastExp2(x[0] - m_new);
+        const float p1 = fastExp2(x[1] - m_new);
+        const float p2 = fastExp2(x[2] - m_new);
+        const float p3 = fastExp2(x[3] - m_new);
+        l_run = l_run * alpha + ((p0 + p1) + (p2 + p3));
+        m_run = m_new;
+        const uint32_t pa0 = packPair(p0, p1, T());
+        const uint32_t pa2 = packPair(p2, p3, T());
+#pragma unroll
+        for (int n = 0; n < kNTiles; ++n) {
+            o[n][0] *= alpha;
+            o[n][1] *= alpha;
+        }
+
+        // ---- O += P . V over this warp's value columns ------------------------------------------
+#pragma unroll
+        for (int np = 0; np < kNTiles / 2; ++np) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrixX4Trans(vAddr(np), b0, b1, b2, b3);
+            mma16816<T>(o[2 * np], pa0, 0u, pa2, 0u, b0, b1);
+            mma16816<T>(o[2 * np + 1], pa0, 0u, pa2, 0u, b2, b3);
+        }
+
+        // ---- this warp is done with the slot ---------------------------------------------------------
+        __syncwarp();
+        if (lane == 0) {
+            mbarArrive(empty + stage * 8);
+        }
+        if (++stage == stages) {
+            stage = 0;
+            parity ^= 1u;
+        }
+
+        // ---- end of unit or end of range: emit ------------------------------------------------------
+        const bool unit_end = (cur.ti + 1 == cur.nt);
+        if (unit_end || i + 1 == count) {
+            float l_all = l_run;
+            l_all += __shfl_xor_sync(0xffffffffu, l_all, 1);
+            l_all += __shfl_xor_sync(0xffffffffu, l_all, 2);
+            const int kv_head = cur.j / head_tiles;
+            const int head_tile = cur.j % head_tiles;
+            const int col0 = warp * kCols; // this warp's first value column
+            if (first_ti == 0 && unit_end) {
+                if (row_valid) {
+                    const int head = kv_head * p.group_size + head_tile * kHeadsPerTile + g;
+                    T *out = static_cast<T *>(p.out) + cur.s * p.o_seq_stride + head * p.o_head_stride + col0;
+                    const float inv = 1.f / l_all;
+#pragma unroll
+                    for (int n = 0; n < kNTiles; ++n) {
+                        *reinterpret_cast<uint32_t *>(out + n * 8 + 2 * t) = packPair(o[n][0] * inv, o[n][1] * inv, T());
+                    }
+                }
+            } else {
+                const long long unit = static_cast<long long>(cur.s) * a.units_per_seq + cur.j;
+                float *rec = a.partials + (unit + worker) * (kHeadsPerTile * (VD + 2));
+                if (row_valid) {
+#pragma unroll
+                    for (int n = 0; n < kNTiles; ++n) {
+                        *reinterpret_cast<float2 *>(rec + g * VD + col0 + n * 8 + 2 * t) = make_float2(o[n][0], o[n][1]);
+                    }
+                }
+                if (warp == 0 && t == 0 && row_valid) {
+                    *reinterpret_cast<float2 *>(rec + kHeadsPerTile * VD + g * 2) = make_float2(m_run, l_all);
+                }
+            }
+        }
+        if (i + 1 < count) {
+            advance(cur, prefix, p.num_seqs, a.units_per_seq);
+            if (unit_end) {
+                loadUnit();
+            }
+        }
+    }
+
+    if (failed) {
+        // tell the other warps of this CTA (they test the flag at their next wait) and the host
+        *reinterpret_cast<volatile int *>(&failed_s) = 1;
+        if (lane == 0) {
+            atomicExch(&a.header->error, 1);
+        }
+    }
+    // Copies still in flight must land before the CTA's shared memory is released: warp 0 issued
+    // them, every issued tile completes its slot's "full" phase; wait (bounded) for those not yet consumed.
+    __syncthreads();
+    if (failed_s != 0 && warp == 0) {
+        for (int sidx = 0; sidx < stages; ++sidx) {
+            // whichever phase is pending in this slot: a bounded wait on both parities covers it
+            (void)mbarWait(full + sidx * 8, 0);
+            (void)mbarWait(full + sidx * 8, 1);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // Combine kernel.  A unit is split exactly when a range boundary falls inside it, so there are
 // fewer split units than workers.  The worker whose range starts at the FIRST boundary inside a
 // unit leaves a task (sequence, unit, first range, number of records) in tasks[worker]; CTA r of
@@ -797,18 +1187,22 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
 // share with a warp-local running maximum, and the per-warp results are merged through shared
 // memory - the same (m, l, acc) algebra at both levels.
 // ---------------------------------------------------------------------------------------
-template <int HD>
+// A record holds 8 heads x VD accumulator floats, then 8 x (m, l).  One CTA merges the columns
+// [blockIdx.y * HD, +HD) of a unit's records: HD = VD for the widths one CTA can hold, 64 for the
+// wide-head kernel (grid.y = VD / 64).
+template <int HD, int VD>
 struct CombineShape {
     static constexpr int kWarps = (HD <= 128) ? 8 : 4;
-    static constexpr int kFloats = kHeadsPerTile * HD;       // accumulator floats per record
-    static constexpr int kVec = kFloats / 4 / 32;             // float4 per lane per record
-    static constexpr int kRec = kHeadsPerTile * (HD + 2);
+    static constexpr int kFloats = kHeadsPerTile * HD;       // accumulator floats per record slice
+    static constexpr int kVec = kFloats / 4 / 32;             // float4 per lane per record slice
+    static constexpr int kRec = kHeadsPerTile * (VD + 2);
+    static constexpr int kMl = kHeadsPerTile * VD;            // offset of the (m, l) pairs in a record
 };
 
-template <typename T, int HD>
-__global__ void __launch_bounds__(CombineShape<HD>::kWarps * 32)
+template <typename T, int HD, int VD = HD>
+__global__ void __launch_bounds__(CombineShape<HD, VD>::kWarps * 32)
     pagedDecodeCombineKernel(const StreamArgs a) {
-    using S = CombineShape<HD>;
+    using S = CombineShape<HD, VD>;
     __shared__ float4 acc_s[S::kWarps][S::kFloats / 4];
     __shared__ float m_s[S::kWarps][kHeadsPerTile];
     __shared__ float l_s[S::kWarps][kHeadsPerTile];
@@ -833,8 +1227,10 @@ __global__ void __launch_bounds__(CombineShape<HD>::kWarps * 32)
     const int heads_valid = min(kHeadsPerTile, p.group_size - head_tile * kHeadsPerTile);
     const long long unit = static_cast<long long>(s) * a.units_per_seq + j;
     const float *base = a.partials + (unit + task.z) * S::kRec;
+    const int slice0 = static_cast<int>(blockIdx.y) * HD; // first value column this CTA merges
 
-    // vector v of this lane covers floats [4 * (v * 32 + lane), +4) of the record's accumulator block
+    // vector v of this lane covers floats [4 * (v * 32 + lane), +4) of the record slice: head
+    // (v * 32 + lane) / (HD / 4), columns slice0 + 4 * ((v * 32 + lane) % (HD / 4)) ...
     int head_of[S::kVec];
     float m_loc[S::kVec], l_loc[S::kVec];
     float4 acc[S::kVec];
@@ -846,7 +1242,7 @@ __global__ void __launch_bounds__(CombineShape<HD>::kWarps * 32)
         acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     for (int i = warp; i < n; i += S::kWarps) {
-        const float *ml = base + static_cast<long long>(i) * S::kRec + S::kFloats;
+        const float *ml = base + static_cast<long long>(i) * S::kRec + S::kMl;
 #pragma unroll
         for (int v = 0; v < S::kVec; ++v) {
             if (head_of[v] < heads_valid) {
@@ -856,13 +1252,12 @@ __global__ void __launch_bounds__(CombineShape<HD>::kWarps * 32)
     }
     for (int i = warp; i < n; i += S::kWarps) {
         const float *rec = base + static_cast<long long>(i) * S::kRec;
-        const float4 *rec4 = reinterpret_cast<const float4 *>(rec);
 #pragma unroll
         for (int v = 0; v < S::kVec; ++v) {
             if (head_of[v] < heads_valid) {
-                const float2 ml = *reinterpret_cast<const float2 *>(rec + S::kFloats + head_of[v] * 2);
+                const float2 ml = *reinterpret_cast<const float2 *>(rec + S::kMl + head_of[v] * 2);
                 const float w = exp2f(ml.x - m_loc[v]);
-                const float4 x = rec4[v * 32 + lane];
+                const float4 x = *reinterpret_cast<const float4 *>(rec + head_of[v] * VD + slice0 + ((v * 32 + lane) % (HD / 4)) * 4);
                 acc[v].x = fmaf(w, x.x, acc[v].x);
                 acc[v].y = fmaf(w, x.y, acc[v].y);
                 acc[v].z = fmaf(w, x.z, acc[v].z);
@@ -908,7 +1303,7 @@ __global__ void __launch_bounds__(CombineShape<HD>::kWarps * 32)
         }
         const float inv = 1.f / l_all;
         const int q_head = kv_head * p.group_size + head_tile * kHeadsPerTile + head;
-        T *out = static_cast<T *>(p.out) + s * p.o_seq_stride + q_head * p.o_head_stride + (f % (HD / 4)) * 4;
+        T *out = static_cast<T *>(p.out) + s * p.o_seq_stride + q_head * p.o_head_stride + slice0 + (f % (HD / 4)) * 4;
         *reinterpret_cast<uint32_t *>(out) = packPair(o4.x * inv, o4.y * inv, T());
         *reinterpret_cast<uint32_t *>(out + 2) = packPair(o4.z * inv, o4.w * inv, T());
     }
@@ -982,7 +1377,7 @@ WorkspaceLayout workspaceLayout(const Info &I, const StreamPlan &plan) {
     L.task_off = roundUp(L.range_off + static_cast<size_t>(plan.num_workers) * sizeof(int4), 256);
     L.partial_off = roundUp(L.task_off + static_cast<size_t>(plan.num_workers) * sizeof(int4), 256);
     const size_t units = I.num_seqs * I.num_kv_heads * static_cast<size_t>(plan.head_tiles_per_group);
-    const size_t rec = kHeadsPerTile * (I.head_size + 2) * sizeof(float);
+    const size_t rec = kHeadsPerTile * (I.value_size + 2) * sizeof(float);
     L.total = roundUp(L.partial_off + (units + plan.num_workers) * rec, 256);
     return L;
 }
@@ -1033,7 +1428,7 @@ infiniStatus_t launchTyped(const StreamPlan &plan, const StreamArgs &args, const
         return checkLaunch("pagedDecodeStreamKernel");
     }
     cfg.gridDim = dim3(plan.num_workers);
-    cfg.blockDim = dim3(CombineShape<HD>::kWarps * 32);
+    cfg.blockDim = dim3(CombineShape<HD, HD>::kWarps * 32);
     cfg.dynamicSmemBytes = 0;
     if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, HD>, args) != cudaSuccess) {
         return checkLaunch("pagedDecodeCombineKernel");
@@ -1041,12 +1436,60 @@ infiniStatus_t launchTyped(const StreamPlan &plan, const StreamArgs &args, const
     return checkLaunch("pagedDecodeStream");
 }
 
+template <typename T, int KD, int VD>
+infiniStatus_t launchWide(const StreamPlan &plan, const StreamArgs &args, const CUtensorMap &mk, const CUtensorMap &mv,
+                          int device_id, cudaStream_t stream) {
+    static std::mutex attr_mutex;
+    static size_t attr_bytes[64] = {};
+    auto kernel = pagedDecodeWideKernel<T, KD, VD>;
+    {
+        std::lock_guard<std::mutex> lock(attr_mutex);
+        const bool tracked = device_id >= 0 && device_id < 64;
+        if (!tracked || attr_bytes[device_id] < plan.smem_bytes) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan.smem_bytes)) != cudaSuccess) {
+                return checkLaunch("cudaFuncSetAttribute(pagedDecodeWideKernel)");
+            }
+            if (tracked) {
+                attr_bytes[device_id] = plan.smem_bytes;
+            }
+        }
+    }
+    cudaLaunchAttribute pdl;
+    pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl.val.programmaticStreamSerializationAllowed = plan.use_pdl ? 1 : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = stream;
+    cfg.attrs = &pdl;
+    cfg.numAttrs = 1;
+    // the plan always comes from the one-CTA plan kernel here
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(kPlanThreads);
+    cfg.dynamicSmemBytes = 0;
+    if (cudaLaunchKernelEx(&cfg, pagedDecodePlanKernel, args) != cudaSuccess) {
+        return checkLaunch("pagedDecodePlanKernel");
+    }
+    cfg.gridDim = dim3(plan.grid);
+    cfg.blockDim = dim3(kWideWarps * 32);
+    cfg.dynamicSmemBytes = plan.smem_bytes;
+    if (cudaLaunchKernelEx(&cfg, kernel, mk, mv, args) != cudaSuccess) {
+        return checkLaunch("pagedDecodeWideKernel");
+    }
+    cfg.gridDim = dim3(plan.num_workers, VD / 64);
+    cfg.blockDim = dim3(CombineShape<64, VD>::kWarps * 32);
+    cfg.dynamicSmemBytes = 0;
+    if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, 64, VD>, args) != cudaSuccess) {
+        return checkLaunch("pagedDecodeCombineKernel");
+    }
+    return checkLaunch("pagedDecodeWide");
+}
+
 } // namespace
 
 StreamPlan planStream(const Info &I, const DeviceProps &props) {
     StreamPlan plan;
     const size_t hd = I.head_size;
-    if (I.value_size != hd || (hd != 64 && hd != 128 && hd != 192 && hd != 256)) {
+    const bool wide = (hd == 576 && (I.value_size == 576 || I.value_size == 512));
+    if (!wide && (I.value_size != hd || (hd != 64 && hd != 128 && hd != 192 && hd != 256))) {
         return plan;
     }
     if (I.block_size % kTileTokens != 0 || I.num_seqs == 0 || I.num_heads == 0) {
@@ -1073,7 +1516,36 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
     CUtensorMap probe;
     void *fake = reinterpret_cast<void *>(static_cast<uintptr_t>(1) << 30);
     if (!encodeCacheMap(&probe, I, fake, I.k_row_stride, I.k_head_stride, I.k_block_stride, hd)
-        || !encodeCacheMap(&probe, I, fake, I.v_row_stride, I.v_head_stride, I.v_block_stride, hd)) {
+        || !encodeCacheMap(&probe, I, fake, I.v_row_stride, I.v_head_stride, I.v_block_stride, I.value_size)) {
+        return plan;
+    }
+    if (wide) {
+        // one worker = one CTA of four warps sharing a ring of 36 KiB (34 KiB) tiles
+        const int group = static_cast<int>(I.num_heads / I.num_kv_heads);
+        plan.wide = true;
+        plan.head_tiles_per_group = (group + kHeadsPerTile - 1) / kHeadsPerTile;
+        plan.warps_per_cta = kWideWarps;
+        plan.stages = envInt("INFINIOP_PAGED_DECODE_STAGES", 3, 2, 4);
+        plan.embedded_plan = false;
+        plan.use_pdl = envInt("INFINIOP_PAGED_DECODE_PDL", 1, 0, 1) != 0;
+        const size_t stage_bytes = (hd / 64 + I.value_size / 64) * kTileTokens * 128;
+        auto smemFor = [&](int stages) { return static_cast<size_t>(stages) * (stage_bytes + 16) + 1024; };
+        while (plan.stages > 2 && smemFor(plan.stages) > props.smem_per_block_optin) {
+            --plan.stages;
+        }
+        if (smemFor(plan.stages) > props.smem_per_block_optin) {
+            plan.wide = false;
+            return plan;
+        }
+        plan.smem_bytes = smemFor(plan.stages);
+        int ctas_per_sm = envInt("INFINIOP_PAGED_DECODE_CTAS_PER_SM", 2, 1, 4);
+        while (ctas_per_sm > 1 && ctas_per_sm * (plan.smem_bytes + 1024) > props.smem_per_sm) {
+            --ctas_per_sm;
+        }
+        plan.grid = props.sm_count * ctas_per_sm;
+        plan.num_workers = plan.grid;
+        plan.workspace_bytes = workspaceLayout(I, plan).total;
+        plan.eligible = true;
         return plan;
     }
 
@@ -1148,6 +1620,14 @@ infiniStatus_t launchDecodeStream(const Info &I, const StreamPlan &plan, const D
     int device_id = -1;
     (void)cudaGetDevice(&device_id);
     const bool f16 = (I.dtype == INFINI_DTYPE_F16);
+    if (plan.wide) {
+        if (I.value_size == 512) {
+            return f16 ? launchWide<__half, 576, 512>(plan, a, mk, mv, device_id, stream)
+                       : launchWide<__nv_bfloat16, 576, 512>(plan, a, mk, mv, device_id, stream);
+        }
+        return f16 ? launchWide<__half, 576, 576>(plan, a, mk, mv, device_id, stream)
+                   : launchWide<__nv_bfloat16, 576, 576>(plan, a, mk, mv, device_id, stream);
+    }
     switch (I.head_size) {
     case 64:
         return f16 ? launchTyped<__half, 64>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 64>(plan, a, mk, mv, device_id, stream);

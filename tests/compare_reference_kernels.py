@@ -2,7 +2,7 @@
 by oracle/build_ref.py) on the benchmark configurations, each in a child process.  Prints one
 JSON line per (configuration, library, environment).
 
-    python tests/compare_reference_kernels.py [c2 c3 c4]
+    python tests/compare_reference_kernels.py [c2 c3 c4 h64 h192 h256 h576 mla p1 p2]
 """
 import json
 import os
@@ -20,6 +20,18 @@ SPECS = {
     "c2": {"builder": "config2_llama8b", "kwargs": {"device": "cuda"}},
     "c3": {"builder": "config3_ragged72b", "kwargs": {"device": "cuda"}},
     "c4": {"builder": "config4_longctx", "kwargs": {"device": "cuda"}},
+    # the other head sizes the descriptor accepts: 64 sequences x 4096 tokens each
+    "h64": {"builder": "build_case", "kwargs": {"name": "h64", "dtype": "float16", "seq_lens": [4096] * 64, "num_heads": 32, "num_kv_heads": 8,
+                                                "head_size": 64, "block_size": 16, "seed": 64, "device": "cuda"}},
+    "h192": {"builder": "build_case", "kwargs": {"name": "h192", "dtype": "bfloat16", "seq_lens": [4096] * 64, "num_heads": 32, "num_kv_heads": 8,
+                                                 "head_size": 192, "block_size": 16, "seed": 192, "device": "cuda"}},
+    "h256": {"builder": "build_case", "kwargs": {"name": "h256", "dtype": "bfloat16", "seq_lens": [4096] * 64, "num_heads": 16, "num_kv_heads": 8,
+                                                 "head_size": 256, "block_size": 16, "seed": 256, "device": "cuda"}},
+    "h576": {"builder": "build_case", "kwargs": {"name": "h576", "dtype": "bfloat16", "seq_lens": [4096] * 64, "num_heads": 16, "num_kv_heads": 1,
+                                                 "head_size": 576, "block_size": 16, "seed": 576, "std": 0.3, "device": "cuda"}},
+    # latent attention: keys 576 wide, values 512 wide, one shared kv-head, 128 query heads
+    "mla": {"builder": "build_case", "kwargs": {"name": "mla", "dtype": "bfloat16", "seq_lens": [4096] * 64, "num_heads": 128, "num_kv_heads": 1,
+                                                "head_size": 576, "value_size": 512, "block_size": 16, "seed": 577, "std": 0.3, "device": "cuda"}},
     # prefill, Llama-3-8B head shape: 8 prompts x 2048 new tokens; and 4 x 1024 new over 3072 cached
     "p1": {"builder": "prefill_llama8b", "kwargs": {"device": "cuda", "num_seqs": 8, "new_len": 2048, "cached_len": 0}},
     "p2": {"builder": "prefill_llama8b", "kwargs": {"device": "cuda", "num_seqs": 4, "new_len": 1024, "cached_len": 3072}},
