@@ -800,9 +800,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
 // columns does not fit one warp's registers.  The four warps share one ring of staged tiles; every
 // warp computes the full S^T = Q.K^T of the tile (four times the score MMAs, still far below the
 // tensor pipe's rate next to 36 KiB of HBM traffic per tile) and owns a quarter of the value
-// columns for O += P.V.  Warp 0 also issues the copies.  A slot is handed back through an "empty"
-// mbarrier on which each of the four warps arrives once it has read the slot; before it consumes tile
-// i, warp 0 refills the slot tile i - 1 has just left.  All waits are bounded.
+// columns for O += P.V.  Each warp issues a quarter of a tile's copies.  A slot is handed back through
+// an "empty" mbarrier on which each of the four warps arrives once it has read the slot; before they
+// consume tile i, the warps refill the slot tile i - 1 has just left.  All waits are bounded.
 // ---------------------------------------------------------------------------------------
 constexpr int kWideWarps = 4;
 
@@ -839,7 +839,7 @@ __global__ void __launch_bounds__(kWideWarps * 32)
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < stages; ++i) {
-            mbarInit(full + i * 8, 1);
+            mbarInit(full + i * 8, kWideWarps);
             mbarInit(empty + i * 8, kWideWarps);
         }
         failed_s = 0;
@@ -887,17 +887,24 @@ __global__ void __launch_bounds__(kWideWarps * 32)
         const int page = (tpp == 1) ? c.ti : c.ti / tpp;
         return loadIndex(p.block_tables, c.s * p.bt_seq_stride + page, p.index_is_64);
     };
-    // warp 0 only
+    // The copies of a tile are shared out over the four warps (a copy costs its issuing lane on the
+    // order of a hundred cycles, and the lanes of one warp issue one after another): warp w takes
+    // boxes w, w + 4, ... of the K chunks followed by the V chunks, one box per lane, and announces
+    // its own bytes with its own arrival on the slot's barrier.
+    constexpr int kBoxes = kKChunks + kVChunks;
+    const int my_box = warp + kWideWarps * lane;
+    const bool has_box = my_box < kBoxes;
+    const uint32_t my_bytes = static_cast<uint32_t>((kBoxes - warp + kWideWarps - 1) / kWideWarps) * kBoxBytes;
     auto issue = [&](int stage, const Cursor &c, long long block) {
         const uint32_t bar = full + stage * 8;
         const uint32_t dst = ring + stage * kStageBytes;
         if (lane == 0) {
-            mbarExpectTx(bar, kStageBytes);
+            mbarExpectTx(bar, my_bytes);
         }
         __syncwarp();
-        if (lane < kKChunks + kVChunks) {
-            const int is_v = lane >= kKChunks;
-            const int chunk = is_v ? lane - kKChunks : lane;
+        if (has_box) {
+            const int is_v = my_box >= kKChunks;
+            const int chunk = is_v ? my_box - kKChunks : my_box;
             const int row0 = (tpp == 1) ? 0 : (c.ti % tpp) * kTileTokens;
             const int kv_head = (head_tiles == 1) ? c.j : c.j / head_tiles;
             tmaLoadBox(dst + (is_v ? kKBytes : 0) + chunk * kBoxBytes, is_v ? &tmap_v : &tmap_k, bar,
@@ -906,17 +913,14 @@ __global__ void __launch_bounds__(kWideWarps * 32)
     };
 
     long long issued = 0;
-    long long next_block = 0;
-    if (warp == 0) {
-        for (int i = 0; i < stages && i < count; ++i) {
-            issue(i, gen, tableEntry(gen));
-            ++issued;
-            if (issued < count) {
-                advance(gen, prefix, p.num_seqs, a.units_per_seq);
-            }
+    for (int i = 0; i < stages && i < count; ++i) {
+        issue(i, gen, tableEntry(gen));
+        ++issued;
+        if (issued < count) {
+            advance(gen, prefix, p.num_seqs, a.units_per_seq);
         }
-        next_block = (issued < count) ? tableEntry(gen) : 0;
     }
+    long long next_block = (issued < count) ? tableEntry(gen) : 0;
 
     uint32_t qa[kKSteps][2];
     float o[kNTiles][4];
@@ -955,9 +959,9 @@ __global__ void __launch_bounds__(kWideWarps * 32)
     for (; i < count; ++i) {
         const uint32_t k_tile = ring + stage * kStageBytes;
         const uint32_t v_tile = k_tile + kKBytes;
-        // warp 0 first refills the slot of the previous tile (the four warps have just left it) with
-        // tile i - 1 + stages, so that stages - 1 tiles are in flight behind the one being consumed
-        if (warp == 0 && i >= 1 && issued < count) {
+        // first refill the slot of the previous tile (the four warps have just left it) with tile
+        // i - 1 + stages, so that stages - 1 tiles are in flight behind the one being consumed
+        if (i >= 1 && issued < count) {
             const int prev_stage = (stage == 0) ? stages - 1 : stage - 1;
             const uint32_t prev_parity = (stage == 0) ? (parity ^ 1u) : parity; // phase of the slot's latest use
             if (!mbarWait(empty + prev_stage * 8, prev_parity)) {
@@ -1167,8 +1171,8 @@ __global__ void __launch_bounds__(kWideWarps * 32)
             atomicExch(&a.header->error, 1);
         }
     }
-    // Copies still in flight must land before the CTA's shared memory is released: warp 0 issued
-    // them, every issued tile completes its slot's "full" phase; wait (bounded) for those not yet consumed.
+    // Copies still in flight must land before the CTA's shared memory is released: every issued tile
+    // completes its slot's "full" phase; wait (bounded) for those not yet consumed.
     __syncthreads();
     if (failed_s != 0 && warp == 0) {
         for (int sidx = 0; sidx < stages; ++sidx) {
