@@ -40,12 +40,12 @@ namespace {
 using paged_attention::DecodeParams;
 using paged_attention::loadIndex;
 
-constexpr int kHD = 128;
 constexpr int kBM = 128;                 // query rows per CTA = MMA M
 constexpr int kBN = 64;                  // KV tokens per stage = MMA N of S, K extent of P.V
-constexpr int kChunks = kHD / 64;        // 128-byte column chunks per row
-constexpr int kQBytes = kChunks * kBM * 128;        // 32 KiB
-constexpr int kTensorBytes = kChunks * kBN * 128;   // one K (or V) tile: 16 KiB
+// per head size HD (64 or 128): HD / 64 column chunks of 128 bytes per row; a Q tile is
+// (HD / 64) * 128 rows * 128 B (32 KiB at head 128), a K or V tile (HD / 64) * 64 rows * 128 B (16 KiB)
+constexpr int qTileBytes(int hd) { return (hd / 64) * kBM * 128; }
+constexpr int kvTileBytes(int hd) { return (hd / 64) * kBN * 128; }
 constexpr long long kWaitLimitCycles = 4000000000ll; // an mbarrier wait gives up after ~2 s
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -342,7 +342,7 @@ struct UmmaArgs {
 //   p_ready[i]             softmax i -> MMA i (P stored, 4 arrivals) o_done[i]      MMA i -> softmax i (P.V retired)
 // The score warp runs ahead of the softmax as far as the two S buffers allow, so the tensor core works
 // on the next scores while the softmax warps are busy with the current ones.
-template <typename T, int kStages, int kQ>
+template <typename T, int kStages, int kQ, int kHD>
 __global__ void __launch_bounds__((8 * kQ) * 32)
     pagedPrefillUmmaKernel(const __grid_constant__ CUtensorMap tmap_q,
                            const __grid_constant__ CUtensorMap tmap_k,
@@ -357,6 +357,9 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
     constexpr int kTmemCols = 256 * kQ;
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
+    constexpr int kChunks = kHD / 64;
+    constexpr int kQBytes = qTileBytes(kHD);
+    constexpr int kTensorBytes = kvTileBytes(kHD);
     constexpr int kRingOff = kQ * kQBytes;
     constexpr int kBarOff = kRingOff + kStages * 2 * kTensorBytes;
     const uint32_t smem0 = smemAddr(smem_raw);
@@ -913,19 +916,21 @@ bool encodeOutMap(CUtensorMap *map, const Info &info, const void *base) {
 }
 
 // tiles + barriers / TMEM slot / scan scratch
-constexpr size_t smemBytes(int stages, int nq) { return static_cast<size_t>(nq) * kQBytes + static_cast<size_t>(stages) * 2 * kTensorBytes + 512; }
+constexpr size_t smemBytes(int stages, int nq, int hd) {
+    return static_cast<size_t>(nq) * qTileBytes(hd) + static_cast<size_t>(stages) * 2 * kvTileBytes(hd) + 512;
+}
 
-template <typename T, int STAGES, int NQ>
+template <typename T, int STAGES, int NQ, int HD>
 infiniStatus_t launchTyped(const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mo,
                            unsigned tiles, int device_id, cudaStream_t stream) {
     static std::mutex attr_mutex;
     static bool attr_done[64] = {};
-    auto kernel = pagedPrefillUmmaKernel<T, STAGES, NQ>;
+    auto kernel = pagedPrefillUmmaKernel<T, STAGES, NQ, HD>;
     {
         std::lock_guard<std::mutex> lock(attr_mutex);
         const bool tracked = device_id >= 0 && device_id < 64;
         if (!tracked || !attr_done[device_id]) {
-            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes(STAGES, NQ))) != cudaSuccess) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes(STAGES, NQ, HD))) != cudaSuccess) {
                 return checkLaunch("cudaFuncSetAttribute(pagedPrefillUmmaKernel)");
             }
             if (tracked) {
@@ -934,30 +939,30 @@ infiniStatus_t launchTyped(const UmmaArgs &args, const CUtensorMap &mq, const CU
         }
     }
     const dim3 grid(tiles, args.pp.d.num_heads / NQ);
-    kernel<<<grid, 8 * NQ * 32, smemBytes(STAGES, NQ), stream>>>(mq, mk, mv, mo, args);
+    kernel<<<grid, 8 * NQ * 32, smemBytes(STAGES, NQ, HD), stream>>>(mq, mk, mv, mo, args);
     return checkLaunch("pagedPrefillUmmaKernel");
 }
 
-template <typename T>
+template <typename T, int HD>
 infiniStatus_t launchShape(int stages, int nq, const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mo,
                            unsigned tiles, int device_id, cudaStream_t stream) {
     if (nq == 2) {
         switch (stages) {
         case 2:
-            return launchTyped<T, 2, 2>(args, mq, mk, mv, mo, tiles, device_id, stream);
+            return launchTyped<T, 2, 2, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
         case 3:
-            return launchTyped<T, 3, 2>(args, mq, mk, mv, mo, tiles, device_id, stream);
+            return launchTyped<T, 3, 2, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
         default:
-            return launchTyped<T, 4, 2>(args, mq, mk, mv, mo, tiles, device_id, stream);
+            return launchTyped<T, 4, 2, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
         }
     }
     switch (stages) {
     case 2:
-        return launchTyped<T, 2, 1>(args, mq, mk, mv, mo, tiles, device_id, stream);
+        return launchTyped<T, 2, 1, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
     case 3:
-        return launchTyped<T, 3, 1>(args, mq, mk, mv, mo, tiles, device_id, stream);
+        return launchTyped<T, 3, 1, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
     default:
-        return launchTyped<T, 4, 1>(args, mq, mk, mv, mo, tiles, device_id, stream);
+        return launchTyped<T, 4, 1, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
     }
 }
 
@@ -966,7 +971,7 @@ infiniStatus_t launchShape(int stages, int nq, const UmmaArgs &args, const CUten
 UmmaPlan planPrefillUmma(const Info &info, const DeviceProps &props) {
     UmmaPlan plan;
     const auto &A = info.attn;
-    if (A.head_size != kHD || A.value_size != kHD) {
+    if ((A.head_size != 128 && A.head_size != 64) || A.value_size != A.head_size) {
         return plan;
     }
     if (A.block_size % 8 != 0 || A.num_seqs == 0 || A.num_seqs > 65536 || info.total_q_tokens == 0 || A.num_blocks == 0) {
@@ -1008,10 +1013,10 @@ UmmaPlan planPrefillUmma(const Info &info, const DeviceProps &props) {
             plan.stages = v;
         }
     }
-    while (plan.stages > 2 && smemBytes(plan.stages, plan.q_tiles) > props.smem_per_block_optin) {
+    while (plan.stages > 2 && smemBytes(plan.stages, plan.q_tiles, static_cast<int>(A.head_size)) > props.smem_per_block_optin) {
         --plan.stages;
     }
-    if (smemBytes(plan.stages, plan.q_tiles) > props.smem_per_block_optin) {
+    if (smemBytes(plan.stages, plan.q_tiles, static_cast<int>(A.head_size)) > props.smem_per_block_optin) {
         return plan;
     }
     plan.eligible = true;
@@ -1040,8 +1045,12 @@ infiniStatus_t launchPrefillUmma(const Info &info, const UmmaPlan &plan, const P
     const unsigned tiles = static_cast<unsigned>((info.total_q_tokens + kBM - 1) / kBM + A.num_seqs);
     int device_id = -1;
     (void)cudaGetDevice(&device_id);
-    return A.dtype == INFINI_DTYPE_F16 ? launchShape<__half>(plan.stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream)
-                                       : launchShape<__nv_bfloat16>(plan.stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream);
+    if (A.head_size == 64) {
+        return A.dtype == INFINI_DTYPE_F16 ? launchShape<__half, 64>(plan.stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream)
+                                           : launchShape<__nv_bfloat16, 64>(plan.stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream);
+    }
+    return A.dtype == INFINI_DTYPE_F16 ? launchShape<__half, 128>(plan.stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream)
+                                       : launchShape<__nv_bfloat16, 128>(plan.stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream);
 }
 
 } // namespace b200::paged_attention_prefill

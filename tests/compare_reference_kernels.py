@@ -2,7 +2,7 @@
 by oracle/build_ref.py) on the benchmark configurations, each in a child process.  Prints one
 JSON line per (configuration, library, environment).
 
-    python tests/compare_reference_kernels.py [c2 c3 c4 h64 h192 h256 h576 mla p1 p2]
+    python tests/compare_reference_kernels.py [c1 c2 c3 c4 h64 h192 h256 h576 mla p1 p2]
 """
 import json
 import os
@@ -17,6 +17,7 @@ ROOT = Path(__file__).resolve().parent.parent
 REF_ROOT = ROOT / "oracle" / "_ref"
 
 SPECS = {
+    "c1": {"builder": "config1_small", "kwargs": {}},
     "c2": {"builder": "config2_llama8b", "kwargs": {"device": "cuda"}},
     "c3": {"builder": "config3_ragged72b", "kwargs": {"device": "cuda"}},
     "c4": {"builder": "config4_longctx", "kwargs": {"device": "cuda"}},

@@ -15,7 +15,7 @@ from infinicore_b200 import workloads
 pytestmark = pytest.mark.gpu
 
 PATHS = [None, "generic", "tiles"]
-PATHS_HD128 = [None, "generic", "tiles", "umma", "umma-q1", "umma-q2-s3"]  # the tcgen05 kernel takes head size 128 (and is the default there)
+PATHS_HD128 = [None, "generic", "tiles", "umma", "umma-q1", "umma-q2-s3"]  # the tcgen05 kernel takes head sizes 64 and 128 (and is the default there)
 
 
 @pytest.fixture(scope="module")
@@ -47,8 +47,8 @@ def check(c, got, want):
 @pytest.mark.parametrize("path", PATHS_HD128)
 @pytest.mark.parametrize("name", golden_names("prefill_"))
 def test_golden(abi, name, path):
-    if path is not None and path.startswith("umma") and "hd128" not in name:
-        pytest.skip("tcgen05 kernel: head size 128 only")
+    if path is not None and path.startswith("umma") and "hd128" not in name and "hd64" not in name:
+        pytest.skip("tcgen05 kernel: head sizes 64 and 128 only")
     if path == "tiles" and "576" in name:
         pytest.skip("tile kernel: head sizes 64 and 128")
     g = load_golden(name)
@@ -94,8 +94,8 @@ def test_reference_case_list_multi_round(abi, case, dtype, index_dtype):
 @pytest.mark.parametrize("dtype,heads,kvh,hd,bs", [(torch.bfloat16, 8, 2, 128, 16), (torch.float16, 4, 1, 64, 16),
                                                    (torch.bfloat16, 4, 4, 128, 8), (torch.float16, 8, 2, 128, 32)])
 def test_gqa_ragged_chunks_and_tile_boundaries(abi, path, dtype, heads, kvh, hd, bs):
-    if path is not None and path.startswith("umma") and hd != 128:
-        pytest.skip("tcgen05 kernel: head size 128 only")
+    if path is not None and path.startswith("umma") and hd not in (64, 128):
+        pytest.skip("tcgen05 kernel: head sizes 64 and 128 only")
     """Chunk lengths around the 64-row tile and the page size, cached prefixes of every alignment,
     one sequence with no new tokens."""
     new = [1, 63, 64, 65, 127, 128, 129, 0, 200, 17]
