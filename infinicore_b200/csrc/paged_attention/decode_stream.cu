@@ -1431,11 +1431,22 @@ infiniStatus_t launchTyped(const StreamPlan &plan, const StreamArgs &args, const
     if (cudaLaunchKernelEx(&cfg, kernel, mk, mv, args) != cudaSuccess) {
         return checkLaunch("pagedDecodeStreamKernel");
     }
-    cfg.gridDim = dim3(plan.num_workers);
-    cfg.blockDim = dim3(CombineShape<HD, HD>::kWarps * 32);
+    // Few units split over many workers each (a handful of very long sequences): a unit's records
+    // are merged by several CTAs, 32 value columns each, instead of one.
+    const long long units = static_cast<long long>(args.p.num_seqs) * args.units_per_seq;
     cfg.dynamicSmemBytes = 0;
-    if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, HD>, args) != cudaSuccess) {
-        return checkLaunch("pagedDecodeCombineKernel");
+    if (units * 4 <= plan.num_workers) {
+        cfg.gridDim = dim3(plan.num_workers, HD / 32);
+        cfg.blockDim = dim3(CombineShape<32, HD>::kWarps * 32);
+        if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, 32, HD>, args) != cudaSuccess) {
+            return checkLaunch("pagedDecodeCombineKernel");
+        }
+    } else {
+        cfg.gridDim = dim3(plan.num_workers);
+        cfg.blockDim = dim3(CombineShape<HD, HD>::kWarps * 32);
+        if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, HD>, args) != cudaSuccess) {
+            return checkLaunch("pagedDecodeCombineKernel");
+        }
     }
     return checkLaunch("pagedDecodeStream");
 }
