@@ -507,3 +507,56 @@ def test_decode_step_graph_replay_matches_direct_calls(abi):
         want = oracle.paged_attention(torch_to_bits(q), kb, vb, base.block_tables.numpy(), base.seq_lens.numpy(), base.scale, 19)
         check(base, got, want)
         assert np.array_equal(torch_to_bits(d.k_cache), kb), f"round {round_}: pools differ"
+
+
+# ---- key width 576: the four-warp wide-head kernel (and the generic kernel beside it) -------------------
+
+WIDE_PATHS = [None, "generic", "stream-3x4"]
+
+
+@pytest.mark.parametrize("path", WIDE_PATHS)
+@pytest.mark.parametrize("dtype,heads,kvh,value,bs", [(torch.bfloat16, 16, 1, 512, 16), (torch.float16, 8, 2, 576, 16),
+                                                      (torch.bfloat16, 24, 2, 576, 32), (torch.float16, 128, 1, 512, 64),
+                                                      (torch.bfloat16, 3, 1, 576, 16)])
+def test_wide_heads_every_length_across_pages(abi, path, dtype, heads, kvh, value, bs):
+    """Lengths 1..2*block+2 plus a few long ones and an empty one: every ragged last tile, page and tile
+    boundaries; latent attention (values 512 wide) and plain 576; 1, 2, 3 and 16 eight-head tiles per
+    kv-head, one of them partly filled; many more ranges than units, so units are split and combined."""
+    lens = list(range(1, 2 * bs + 3)) + [0, 700, 1025, 333]
+    c = workloads.build_case("wide", dtype=dtype, seq_lens=lens, num_heads=heads, num_kv_heads=kvh, head_size=576, value_size=value,
+                             block_size=bs, seed=61, std=0.3, slack_blocks=5)
+    check(c, run_case(abi, c, path), oracle_out(c))
+
+
+@pytest.mark.parametrize("path", WIDE_PATHS)
+def test_wide_heads_alibi_int32_and_poisoned_slots(abi, path):
+    from infinicore_b200.libinfiniop import InfiniDtype
+
+    c = workloads.build_case("wide_alibi", dtype=torch.bfloat16, seq_lens=[130, 48, 1, 2000, 17], num_heads=16, num_kv_heads=2,
+                             head_size=576, value_size=512, block_size=16, seed=62, std=0.3, slack_blocks=4)
+    slopes = -torch.linspace(0.0, 0.2, 16, dtype=torch.float32)
+    want = oracle_out(c, alibi=slopes)
+    poison = torch.tensor(float("nan"), dtype=torch.bfloat16)
+    used = torch.zeros(c.k_cache.shape[0], dtype=torch.bool)
+    for i, ln in enumerate(c.seq_lens.tolist()):
+        nblk = (ln + 15) // 16
+        used[c.block_tables[i, :nblk]] = True
+        if ln % 16:
+            last = int(c.block_tables[i, nblk - 1])
+            c.k_cache[last, :, ln % 16:, :] = poison
+            c.v_cache[last, :, ln % 16:, :] = float("inf")
+    c.k_cache[~used] = poison
+    c.v_cache[~used] = poison
+    got = run_case(abi, c, path, alibi=slopes, index_dtype=InfiniDtype.I32)
+    assert bool(torch.isfinite(got.float()).all())
+    check(c, got, want)
+
+
+def test_wide_heads_long_batch_matches_generic_kernel(abi):
+    """64 x 1500 tokens of latent attention with 32 heads: streaming result against the row-wise kernel's."""
+    c = workloads.build_case("wide_long", dtype=torch.bfloat16, seq_lens=[1500 + 7 * i for i in range(64)], num_heads=32, num_kv_heads=1,
+                             head_size=576, value_size=512, block_size=16, seed=63, std=0.3)
+    a = run_case(abi, c, None)
+    b = run_case(abi, c, "generic")
+    atol, rtol = ATTN_TOL[c.dtype]
+    assert_close(a.float().cpu().numpy(), b.float().cpu().numpy(), atol, rtol, "wide vs generic")

@@ -106,6 +106,16 @@ def test_shapes_the_streaming_kernel_does_not_take_use_the_append_kernel(abi):
     run_and_check(abi, c, None)
 
 
+@pytest.mark.parametrize("value", [576, 512])
+def test_wide_heads_take_the_rows_inside_the_kernel(abi, value):
+    """Key width 576 on the four-warp kernel: every warp swaps the new row into what it reads, the
+    stores into the cache are shared out; lengths on every row of a page; 3 head tiles per kv-head."""
+    lens = list(range(1, 35)) + [0, 400, 1000]
+    c = workloads.build_case("wide_step", dtype=torch.bfloat16, seq_lens=lens, num_heads=20, num_kv_heads=1, head_size=576,
+                             value_size=value, block_size=16, seed=48, std=0.3, slack_blocks=3)
+    run_and_check(abi, c, None, poison=True)
+
+
 def test_unaligned_new_rows_fall_back_to_the_append_kernel(abi):
     """new_k / new_v views whose rows are not 16-byte aligned: same results through the unfused route."""
     c = workloads.build_case("unaligned", dtype=torch.bfloat16, seq_lens=[33, 16, 100], num_heads=8, num_kv_heads=2, head_size=128,
