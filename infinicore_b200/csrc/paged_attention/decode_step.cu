@@ -196,7 +196,7 @@ __INFINI_C infiniStatus_t infiniopPagedDecodeStep(
     p.new_v_seq_stride = d->new_v_seq_stride;
     auto cuda_stream = static_cast<cudaStream_t>(stream);
     const auto addr = [](const void *ptr) { return reinterpret_cast<uintptr_t>(ptr); };
-    const bool fused = d->stream.eligible && b200::paged_attention::streamTakesPointers(p, workspace) && d->rows_vectorisable
+    const bool fused = d->stream.eligible && b200::paged_attention::streamTakesPointers(d->stream, p, workspace) && d->rows_vectorisable
                        && ((addr(new_k) | addr(new_v)) & 15u) == 0;
     if (fused) {
         return b200::paged_attention::launchDecodeStream(I, d->stream, p, workspace, workspace_size, cuda_stream);

@@ -795,16 +795,23 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
 // ---------------------------------------------------------------------------------------
 // Wide-head kernel: key width 576 (value width 576, or 512 for latent attention).
 //
-// Same decomposition, plan, partial records and combine as above, but one worker is a CTA of four
-// warps instead of one warp: a 16-token tile is 36 KiB here and the O accumulator of 8 heads x 576
-// columns does not fit one warp's registers.  The four warps share one ring of staged tiles; every
-// warp computes the full S^T = Q.K^T of the tile (four times the score MMAs, still far below the
-// tensor pipe's rate next to 36 KiB of HBM traffic per tile) and owns a quarter of the value
-// columns for O += P.V.  Each warp issues a quarter of a tile's copies.  A slot is handed back through
-// an "empty" mbarrier on which each of the four warps arrives once it has read the slot; before they
-// consume tile i, the warps refill the slot tile i - 1 has just left.  All waits are bounded.
+// Same decomposition, plan, partial records and combine as above, with two differences.
+//  * One worker is a CTA of four warps instead of one warp: a 16-token tile is 36 KiB here and the O
+//    accumulator of a head tile does not fit one warp's registers.  The four warps share one ring of
+//    staged tiles; every warp computes the full S^T = Q.K^T of the tile (four times the score MMAs,
+//    still far below the tensor pipe's rate next to 36 KiB of HBM traffic per tile) and owns a quarter
+//    of the value columns for O += P.V.  Each warp issues a quarter of a tile's copies and arrives for
+//    its own bytes.  A slot is handed back through an "empty" mbarrier on which each of the four warps
+//    arrives once it has read the slot; before they consume tile i, the warps refill the slot tile
+//    i - 1 has just left.
+//  * A head tile is 16 q-heads, all 16 rows of the MMA's M dimension: shapes with many q-heads per
+//    kv-head (latent attention: 128) re-read K/V once per 16 heads instead of once per 8.  The unit's Q
+//    rows live in shared memory (16 x 576 values, padded rows) and reach the MMA through ldmatrix.
+// All waits are bounded.  A wait that runs out does not leave the loop: the warp keeps walking it
+// with its work switched off, so the four warps reach every CTA-wide barrier together.
 // ---------------------------------------------------------------------------------------
 constexpr int kWideWarps = 4;
+constexpr int kWideHeads = 16;
 
 template <typename T, int KD, int VD>
 __global__ void __launch_bounds__(kWideWarps * 32)
@@ -822,6 +829,8 @@ __global__ void __launch_bounds__(kWideWarps * 32)
     constexpr int kCols = VD / kWideWarps;            // value columns per warp: 144 or 128
     constexpr int kNTiles = kCols / 8;                // 18 or 16 (even)
     constexpr int kVPieces = kCols / 8;               // 16-byte pieces of a V row per warp
+    constexpr int kQStride = KD * 2 + 16;             // bytes per Q row in shared memory: odd multiple of 16 -> conflict-free ldmatrix
+    constexpr int kQBytes = kWideHeads * kQStride;
     static_assert(kKSteps % kKChunk == 0 && kNTiles % 2 == 0 && kKChunks + kVChunks <= 32, "shape");
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -833,16 +842,16 @@ __global__ void __launch_bounds__(kWideWarps * 32)
     const DecodeParams &p = a.p;
 
     const uint32_t ring = smemAddr(smem_raw);
-    const uint32_t full = ring + stages * kStageBytes;
+    const uint32_t q_smem = ring + stages * kStageBytes;
+    const uint32_t full = q_smem + kQBytes;
     const uint32_t empty = full + stages * 8;
-    __shared__ int failed_s;
+    unsigned char *q_ptr = smem_raw + stages * kStageBytes;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < stages; ++i) {
             mbarInit(full + i * 8, kWideWarps);
             mbarInit(empty + i * 8, kWideWarps);
         }
-        failed_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -922,23 +931,38 @@ __global__ void __launch_bounds__(kWideWarps * 32)
     }
     long long next_block = (issued < count) ? tableEntry(gen) : 0;
 
-    uint32_t qa[kKSteps][2];
+    // ---- per-unit state: two q-heads per thread (MMA rows g and g + 8) ------------------------
     float o[kNTiles][4];
-    float m_run = -INFINITY, l_run = 0.f, slope_log2 = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY};
+    float l_run[2] = {0.f, 0.f};
+    float slope_log2[2] = {0.f, 0.f};
+    bool row_valid[2] = {false, false};
     int first_ti = cur.ti, seq_len = 0;
-    bool row_valid = false;
+    // CTA-wide: the four warps copy the unit's 16 Q rows (zero rows past the group) into shared memory
     auto loadUnit = [&]() {
         const int kv_head = cur.j / head_tiles;
-        const int head_in_group = (cur.j % head_tiles) * kHeadsPerTile + g;
-        row_valid = head_in_group < p.group_size;
-        const int head = kv_head * p.group_size + (row_valid ? head_in_group : 0);
-        const T *q = static_cast<const T *>(p.q) + cur.s * p.q_seq_stride + head * p.q_head_stride;
-#pragma unroll
-        for (int ks = 0; ks < kKSteps; ++ks) {
-            qa[ks][0] = row_valid ? *reinterpret_cast<const uint32_t *>(q + ks * 16 + 2 * t) : 0u;
-            qa[ks][1] = row_valid ? *reinterpret_cast<const uint32_t *>(q + ks * 16 + 8 + 2 * t) : 0u;
+        const int head_tile = cur.j % head_tiles;
+        constexpr int kPiecesPerRow = KD / 8;
+        for (int idx = threadIdx.x; idx < kWideHeads * kPiecesPerRow; idx += kWideWarps * 32) {
+            const int r = idx / kPiecesPerRow;
+            const int piece = idx % kPiecesPerRow;
+            const int head_in_group = head_tile * kWideHeads + r;
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (head_in_group < p.group_size) {
+                const T *q = static_cast<const T *>(p.q) + cur.s * p.q_seq_stride + (kv_head * p.group_size + head_in_group) * p.q_head_stride;
+                val = *reinterpret_cast<const uint4 *>(q + piece * 8);
+            }
+            *reinterpret_cast<uint4 *>(q_ptr + r * kQStride + piece * 16) = val;
         }
-        slope_log2 = (p.alibi_slopes != nullptr && row_valid) ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int head_in_group = head_tile * kWideHeads + g + 8 * h;
+            row_valid[h] = head_in_group < p.group_size;
+            const int head = kv_head * p.group_size + (row_valid[h] ? head_in_group : 0);
+            slope_log2[h] = (p.alibi_slopes != nullptr && row_valid[h]) ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
+            m_run[h] = -INFINITY;
+            l_run[h] = 0.f;
+        }
         long long len = loadIndex(p.seq_lens, cur.s, p.index_is_64);
         const long long capacity = static_cast<long long>(p.max_blocks_per_seq) * p.block_size;
         seq_len = static_cast<int>(len > capacity ? capacity : len);
@@ -946,43 +970,41 @@ __global__ void __launch_bounds__(kWideWarps * 32)
         for (int n = 0; n < kNTiles; ++n) {
             o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
         }
-        m_run = -INFINITY;
-        l_run = 0.f;
         first_ti = cur.ti;
     };
     loadUnit();
+    __syncthreads();
 
     bool failed = false;
     int stage = 0;
     uint32_t parity = 0;
-    long long i = 0;
-    for (; i < count; ++i) {
+    for (long long i = 0; i < count; ++i) {
         const uint32_t k_tile = ring + stage * kStageBytes;
         const uint32_t v_tile = k_tile + kKBytes;
         // first refill the slot of the previous tile (the four warps have just left it) with tile
         // i - 1 + stages, so that stages - 1 tiles are in flight behind the one being consumed
-        if (i >= 1 && issued < count) {
+        if (!failed && i >= 1 && issued < count) {
             const int prev_stage = (stage == 0) ? stages - 1 : stage - 1;
             const uint32_t prev_parity = (stage == 0) ? (parity ^ 1u) : parity; // phase of the slot's latest use
             if (!mbarWait(empty + prev_stage * 8, prev_parity)) {
                 failed = true;
-                break;
-            }
-            issue(prev_stage, gen, next_block);
-            ++issued;
-            if (issued < count) {
-                advance(gen, prefix, p.num_seqs, a.units_per_seq);
-                next_block = tableEntry(gen);
+            } else {
+                issue(prev_stage, gen, next_block);
+                ++issued;
+                if (issued < count) {
+                    advance(gen, prefix, p.num_seqs, a.units_per_seq);
+                    next_block = tableEntry(gen);
+                }
             }
         }
-        if (!mbarWait(full + stage * 8, parity) || *reinterpret_cast<volatile int *>(&failed_s) != 0) {
+        if (!failed && !mbarWait(full + stage * 8, parity)) {
             failed = true;
-            break;
         }
         const int tok0 = cur.ti * kTileTokens;
         const int valid = seq_len - tok0; // >= 1 by construction
         const int v_piece0 = warp * kVPieces; // this warp's first 16-byte piece of a V row
 
+        if (!failed) {
         if (p.new_k != nullptr && valid <= kTileTokens) {
             // Decode step with append: every warp swaps the newest row into what it reads itself (all of
             // K, its own value columns); the stores into the cache are shared out the same way.
@@ -1041,8 +1063,10 @@ __global__ void __launch_bounds__(kWideWarps * 32)
             const int col = v_piece0 + np * 2 + v_sel;
             return v_tile + (col >> 3) * kBoxBytes + v_row * 128 + (((col & 7) ^ (v_row & 7)) << 4);
         };
+        // A fragment of k-step ks: matrices (rows 0-7 | 8-15) x (columns 16 ks .. +8 | +8 .. +16)
+        const uint32_t q_lane = q_smem + ((lane & 7) + ((lane >> 3) & 1) * 8) * kQStride + (lane >> 4) * 16;
 
-        // ---- S^T = Q . K^T over the whole key width (every warp) ------------------------------
+        // ---- S^T = Q . K^T over the whole key width (every warp), 16 heads x 16 tokens --------------
         float sa[2][4], sb[2][4];
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
@@ -1051,57 +1075,65 @@ __global__ void __launch_bounds__(kWideWarps * 32)
         }
 #pragma unroll
         for (int c0 = 0; c0 < kKSteps; c0 += kKChunk) {
-            uint32_t kb[kKChunk][4];
+            uint32_t kb[kKChunk][4], qf[kKChunk][4];
 #pragma unroll
             for (int ks = 0; ks < kKChunk; ++ks) {
                 ldmatrixX4(kAddr(c0 + ks), kb[ks][0], kb[ks][1], kb[ks][2], kb[ks][3]);
+                ldmatrixX4(q_lane + (c0 + ks) * 32, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
             }
 #pragma unroll
             for (int ks = 0; ks < kKChunk; ks += 2) {
-                mma16816<T>(sa[0], qa[c0 + ks][0], 0u, qa[c0 + ks][1], 0u, kb[ks][0], kb[ks][1]);
-                mma16816<T>(sa[1], qa[c0 + ks][0], 0u, qa[c0 + ks][1], 0u, kb[ks][2], kb[ks][3]);
-                mma16816<T>(sb[0], qa[c0 + ks + 1][0], 0u, qa[c0 + ks + 1][1], 0u, kb[ks + 1][0], kb[ks + 1][1]);
-                mma16816<T>(sb[1], qa[c0 + ks + 1][0], 0u, qa[c0 + ks + 1][1], 0u, kb[ks + 1][2], kb[ks + 1][3]);
+                mma16816<T>(sa[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], kb[ks][0], kb[ks][1]);
+                mma16816<T>(sa[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], kb[ks][2], kb[ks][3]);
+                mma16816<T>(sb[0], qf[ks + 1][0], qf[ks + 1][1], qf[ks + 1][2], qf[ks + 1][3], kb[ks + 1][0], kb[ks + 1][1]);
+                mma16816<T>(sb[1], qf[ks + 1][0], qf[ks + 1][1], qf[ks + 1][2], qf[ks + 1][3], kb[ks + 1][2], kb[ks + 1][3]);
             }
         }
 
-        // ---- online softmax (log2 domain), identical in the four warps ---------------------------
-        float x[4];
-        x[0] = (sa[0][0] + sb[0][0]) * p.scale_log2e;
-        x[1] = (sa[0][1] + sb[0][1]) * p.scale_log2e;
-        x[2] = (sa[1][0] + sb[1][0]) * p.scale_log2e;
-        x[3] = (sa[1][1] + sb[1][1]) * p.scale_log2e;
-        if (slope_log2 != 0.f) {
-            const int rel = tok0 + 2 * t - (seq_len - 1);
-            x[0] += slope_log2 * static_cast<float>(rel);
-            x[1] += slope_log2 * static_cast<float>(rel + 1);
-            x[2] += slope_log2 * static_cast<float>(rel + 8);
-            x[3] += slope_log2 * static_cast<float>(rel + 9);
+        // ---- online softmax (log2 domain) of rows g and g + 8, identical in the four warps ----------
+        uint32_t pa[4]; // A fragment of P: (row g | g + 8) x (tokens 2t, 2t+1 | 2t+8, 2t+9)
+        float alpha[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float x[4];
+            x[0] = (sa[0][2 * h] + sb[0][2 * h]) * p.scale_log2e;
+            x[1] = (sa[0][2 * h + 1] + sb[0][2 * h + 1]) * p.scale_log2e;
+            x[2] = (sa[1][2 * h] + sb[1][2 * h]) * p.scale_log2e;
+            x[3] = (sa[1][2 * h + 1] + sb[1][2 * h + 1]) * p.scale_log2e;
+            if (slope_log2[h] != 0.f) {
+                const int rel = tok0 + 2 * t - (seq_len - 1);
+                x[0] += slope_log2[h] * static_cast<float>(rel);
+                x[1] += slope_log2[h] * static_cast<float>(rel + 1);
+                x[2] += slope_log2[h] * static_cast<float>(rel + 8);
+                x[3] += slope_log2[h] * static_cast<float>(rel + 9);
+            }
+            if (valid < kTileTokens) {
+                const int c = 2 * t;
+                x[0] = (c < valid) ? x[0] : -INFINITY;
+                x[1] = (c + 1 < valid) ? x[1] : -INFINITY;
+                x[2] = (c + 8 < valid) ? x[2] : -INFINITY;
+                x[3] = (c + 9 < valid) ? x[3] : -INFINITY;
+            }
+            float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[h], mx);
+            alpha[h] = fastExp2(m_run[h] - m_new);
+            const float p0 = fastExp2(x[0] - m_new);
+            const float p1 = fastExp2(x[1] - m_new);
+            const float p2 = fastExp2(x[2] - m_new);
+            const float p3 = fastExp2(x[3] - m_new);
+            l_run[h] = l_run[h] * alpha[h] + ((p0 + p1) + (p2 + p3));
+            m_run[h] = m_new;
+            pa[h] = packPair(p0, p1, T());
+            pa[2 + h] = packPair(p2, p3, T());
         }
-        if (valid < kTileTokens) {
-            const int c = 2 * t;
-            x[0] = (c < valid) ? x[0] : -INFINITY;
-            x[1] = (c + 1 < valid) ? x[1] : -INFINITY;
-            x[2] = (c + 8 < valid) ? x[2] : -INFINITY;
-            x[3] = (c + 9 < valid) ? x[3] : -INFINITY;
-        }
-        float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run, mx);
-        const float alpha = fastExp2(m_run - m_new);
-        const float p0 = fastExp2(x[0] - m_new);
-        const float p1 = fastExp2(x[1] - m_new);
-        const float p2 = fastExp2(x[2] - m_new);
-        const float p3 = fastExp2(x[3] - m_new);
-        l_run = l_run * alpha + ((p0 + p1) + (p2 + p3));
-        m_run = m_new;
-        const uint32_t pa0 = packPair(p0, p1, T());
-        const uint32_t pa2 = packPair(p2, p3, T());
 #pragma unroll
         for (int n = 0; n < kNTiles; ++n) {
-            o[n][0] *= alpha;
-            o[n][1] *= alpha;
+            o[n][0] *= alpha[0];
+            o[n][1] *= alpha[0];
+            o[n][2] *= alpha[1];
+            o[n][3] *= alpha[1];
         }
 
         // ---- O += P . V over this warp's value columns ------------------------------------------
@@ -1109,8 +1141,8 @@ __global__ void __launch_bounds__(kWideWarps * 32)
         for (int np = 0; np < kNTiles / 2; ++np) {
             uint32_t b0, b1, b2, b3;
             ldmatrixX4Trans(vAddr(np), b0, b1, b2, b3);
-            mma16816<T>(o[2 * np], pa0, 0u, pa2, 0u, b0, b1);
-            mma16816<T>(o[2 * np + 1], pa0, 0u, pa2, 0u, b2, b3);
+            mma16816<T>(o[2 * np], pa[0], pa[1], pa[2], pa[3], b0, b1);
+            mma16816<T>(o[2 * np + 1], pa[0], pa[1], pa[2], pa[3], b2, b3);
         }
 
         // ---- this warp is done with the slot ---------------------------------------------------------
@@ -1118,6 +1150,8 @@ __global__ void __launch_bounds__(kWideWarps * 32)
         if (lane == 0) {
             mbarArrive(empty + stage * 8);
         }
+        } // !failed
+
         if (++stage == stages) {
             stage = 0;
             parity ^= 1u;
@@ -1125,62 +1159,62 @@ __global__ void __launch_bounds__(kWideWarps * 32)
 
         // ---- end of unit or end of range: emit ------------------------------------------------------
         const bool unit_end = (cur.ti + 1 == cur.nt);
-        if (unit_end || i + 1 == count) {
-            float l_all = l_run;
-            l_all += __shfl_xor_sync(0xffffffffu, l_all, 1);
-            l_all += __shfl_xor_sync(0xffffffffu, l_all, 2);
+        if ((unit_end || i + 1 == count) && !failed) {
             const int kv_head = cur.j / head_tiles;
             const int head_tile = cur.j % head_tiles;
             const int col0 = warp * kCols; // this warp's first value column
-            if (first_ti == 0 && unit_end) {
-                if (row_valid) {
-                    const int head = kv_head * p.group_size + head_tile * kHeadsPerTile + g;
-                    T *out = static_cast<T *>(p.out) + cur.s * p.o_seq_stride + head * p.o_head_stride + col0;
-                    const float inv = 1.f / l_all;
+            const long long unit = static_cast<long long>(cur.s) * a.units_per_seq + cur.j;
+            float *rec = a.partials + (unit + worker) * (kWideHeads * (VD + 2));
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float l_all = l_run[h];
+                l_all += __shfl_xor_sync(0xffffffffu, l_all, 1);
+                l_all += __shfl_xor_sync(0xffffffffu, l_all, 2);
+                const int r = g + 8 * h;
+                if (first_ti == 0 && unit_end) {
+                    if (row_valid[h]) {
+                        const int head = kv_head * p.group_size + head_tile * kWideHeads + r;
+                        T *out = static_cast<T *>(p.out) + cur.s * p.o_seq_stride + head * p.o_head_stride + col0;
+                        const float inv = 1.f / l_all;
+#pragma unroll
+                        for (int n = 0; n < kNTiles; ++n) {
+                            *reinterpret_cast<uint32_t *>(out + n * 8 + 2 * t) = packPair(o[n][2 * h] * inv, o[n][2 * h + 1] * inv, T());
+                        }
+                    }
+                } else if (row_valid[h]) {
 #pragma unroll
                     for (int n = 0; n < kNTiles; ++n) {
-                        *reinterpret_cast<uint32_t *>(out + n * 8 + 2 * t) = packPair(o[n][0] * inv, o[n][1] * inv, T());
+                        *reinterpret_cast<float2 *>(rec + r * VD + col0 + n * 8 + 2 * t) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
                     }
-                }
-            } else {
-                const long long unit = static_cast<long long>(cur.s) * a.units_per_seq + cur.j;
-                float *rec = a.partials + (unit + worker) * (kHeadsPerTile * (VD + 2));
-                if (row_valid) {
-#pragma unroll
-                    for (int n = 0; n < kNTiles; ++n) {
-                        *reinterpret_cast<float2 *>(rec + g * VD + col0 + n * 8 + 2 * t) = make_float2(o[n][0], o[n][1]);
+                    if (warp == 0 && t == 0) {
+                        *reinterpret_cast<float2 *>(rec + kWideHeads * VD + r * 2) = make_float2(m_run[h], l_all);
                     }
-                }
-                if (warp == 0 && t == 0 && row_valid) {
-                    *reinterpret_cast<float2 *>(rec + kHeadsPerTile * VD + g * 2) = make_float2(m_run, l_all);
                 }
             }
         }
         if (i + 1 < count) {
             advance(cur, prefix, p.num_seqs, a.units_per_seq);
             if (unit_end) {
+                __syncthreads(); // every warp has read the old unit's Q rows for the last time
                 loadUnit();
+                __syncthreads();
             }
         }
     }
 
-    if (failed) {
-        // tell the other warps of this CTA (they test the flag at their next wait) and the host
-        *reinterpret_cast<volatile int *>(&failed_s) = 1;
-        if (lane == 0) {
-            atomicExch(&a.header->error, 1);
-        }
+    if (failed && lane == 0) {
+        atomicExch(&a.header->error, 1);
     }
-    // Copies still in flight must land before the CTA's shared memory is released: every issued tile
-    // completes its slot's "full" phase; wait (bounded) for those not yet consumed.
-    __syncthreads();
-    if (failed_s != 0 && warp == 0) {
+    // Copies still in flight must land before the CTA's shared memory is released.  A warp whose
+    // wait ran out drains its own slots: whichever phase is pending, a bounded wait on both
+    // parities covers it.
+    if (failed) {
         for (int sidx = 0; sidx < stages; ++sidx) {
-            // whichever phase is pending in this slot: a bounded wait on both parities covers it
             (void)mbarWait(full + sidx * 8, 0);
             (void)mbarWait(full + sidx * 8, 1);
         }
     }
+    __syncthreads();
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1194,22 +1228,23 @@ __global__ void __launch_bounds__(kWideWarps * 32)
 // A record holds 8 heads x VD accumulator floats, then 8 x (m, l).  One CTA merges the columns
 // [blockIdx.y * HD, +HD) of a unit's records: HD = VD for the widths one CTA can hold, 64 for the
 // wide-head kernel (grid.y = VD / 64).
-template <int HD, int VD>
+template <int HD, int VD, int HPT>
 struct CombineShape {
     static constexpr int kWarps = (HD <= 128) ? 8 : 4;
-    static constexpr int kFloats = kHeadsPerTile * HD;       // accumulator floats per record slice
+    static constexpr int kFloats = HPT * HD;                  // accumulator floats per record slice
     static constexpr int kVec = kFloats / 4 / 32;             // float4 per lane per record slice
-    static constexpr int kRec = kHeadsPerTile * (VD + 2);
-    static constexpr int kMl = kHeadsPerTile * VD;            // offset of the (m, l) pairs in a record
+    static constexpr int kRec = HPT * (VD + 2);
+    static constexpr int kMl = HPT * VD;                      // offset of the (m, l) pairs in a record
 };
 
-template <typename T, int HD, int VD = HD>
-__global__ void __launch_bounds__(CombineShape<HD, VD>::kWarps * 32)
+// HPT: q-heads per head tile (8 for the one-warp kernel, 16 for the wide-head kernel)
+template <typename T, int HD, int VD = HD, int HPT = kHeadsPerTile>
+__global__ void __launch_bounds__(CombineShape<HD, VD, HPT>::kWarps * 32)
     pagedDecodeCombineKernel(const StreamArgs a) {
-    using S = CombineShape<HD, VD>;
+    using S = CombineShape<HD, VD, HPT>;
     __shared__ float4 acc_s[S::kWarps][S::kFloats / 4];
-    __shared__ float m_s[S::kWarps][kHeadsPerTile];
-    __shared__ float l_s[S::kWarps][kHeadsPerTile];
+    __shared__ float m_s[S::kWarps][HPT];
+    __shared__ float l_s[S::kWarps][HPT];
 
     const DecodeParams &p = a.p;
     const int warp = threadIdx.x >> 5;
@@ -1228,7 +1263,7 @@ __global__ void __launch_bounds__(CombineShape<HD, VD>::kWarps * 32)
     const int s = task.x, j = task.y;
     const int kv_head = j / a.head_tiles;
     const int head_tile = j % a.head_tiles;
-    const int heads_valid = min(kHeadsPerTile, p.group_size - head_tile * kHeadsPerTile);
+    const int heads_valid = min(HPT, p.group_size - head_tile * HPT);
     const long long unit = static_cast<long long>(s) * a.units_per_seq + j;
     const float *base = a.partials + (unit + task.z) * S::kRec;
     const int slice0 = static_cast<int>(blockIdx.y) * HD; // first value column this CTA merges
@@ -1306,7 +1341,7 @@ __global__ void __launch_bounds__(CombineShape<HD, VD>::kWarps * 32)
             }
         }
         const float inv = 1.f / l_all;
-        const int q_head = kv_head * p.group_size + head_tile * kHeadsPerTile + head;
+        const int q_head = kv_head * p.group_size + head_tile * HPT + head;
         T *out = static_cast<T *>(p.out) + s * p.o_seq_stride + q_head * p.o_head_stride + slice0 + (f % (HD / 4)) * 4;
         *reinterpret_cast<uint32_t *>(out) = packPair(o4.x * inv, o4.y * inv, T());
         *reinterpret_cast<uint32_t *>(out + 2) = packPair(o4.z * inv, o4.w * inv, T());
@@ -1381,7 +1416,7 @@ WorkspaceLayout workspaceLayout(const Info &I, const StreamPlan &plan) {
     L.task_off = roundUp(L.range_off + static_cast<size_t>(plan.num_workers) * sizeof(int4), 256);
     L.partial_off = roundUp(L.task_off + static_cast<size_t>(plan.num_workers) * sizeof(int4), 256);
     const size_t units = I.num_seqs * I.num_kv_heads * static_cast<size_t>(plan.head_tiles_per_group);
-    const size_t rec = kHeadsPerTile * (I.value_size + 2) * sizeof(float);
+    const size_t rec = (plan.wide ? kWideHeads : kHeadsPerTile) * (I.value_size + 2) * sizeof(float);
     L.total = roundUp(L.partial_off + (units + plan.num_workers) * rec, 256);
     return L;
 }
@@ -1437,13 +1472,13 @@ infiniStatus_t launchTyped(const StreamPlan &plan, const StreamArgs &args, const
     cfg.dynamicSmemBytes = 0;
     if (units * 4 <= plan.num_workers) {
         cfg.gridDim = dim3(plan.num_workers, HD / 32);
-        cfg.blockDim = dim3(CombineShape<32, HD>::kWarps * 32);
+        cfg.blockDim = dim3(CombineShape<32, HD, kHeadsPerTile>::kWarps * 32);
         if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, 32, HD>, args) != cudaSuccess) {
             return checkLaunch("pagedDecodeCombineKernel");
         }
     } else {
         cfg.gridDim = dim3(plan.num_workers);
-        cfg.blockDim = dim3(CombineShape<HD, HD>::kWarps * 32);
+        cfg.blockDim = dim3(CombineShape<HD, HD, kHeadsPerTile>::kWarps * 32);
         if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, HD>, args) != cudaSuccess) {
             return checkLaunch("pagedDecodeCombineKernel");
         }
@@ -1490,9 +1525,9 @@ infiniStatus_t launchWide(const StreamPlan &plan, const StreamArgs &args, const 
         return checkLaunch("pagedDecodeWideKernel");
     }
     cfg.gridDim = dim3(plan.num_workers, VD / 64);
-    cfg.blockDim = dim3(CombineShape<64, VD>::kWarps * 32);
+    cfg.blockDim = dim3(CombineShape<64, VD, kWideHeads>::kWarps * 32);
     cfg.dynamicSmemBytes = 0;
-    if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, 64, VD>, args) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, 64, VD, kWideHeads>, args) != cudaSuccess) {
         return checkLaunch("pagedDecodeCombineKernel");
     }
     return checkLaunch("pagedDecodeWide");
@@ -1534,17 +1569,21 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
         || !encodeCacheMap(&probe, I, fake, I.v_row_stride, I.v_head_stride, I.v_block_stride, I.value_size)) {
         return plan;
     }
+    if (wide && (!mult8(I.q_seq_stride) || !mult8(I.q_head_stride))) {
+        return plan; // q rows are copied 16 bytes at a time
+    }
     if (wide) {
         // one worker = one CTA of four warps sharing a ring of 36 KiB (34 KiB) tiles
         const int group = static_cast<int>(I.num_heads / I.num_kv_heads);
         plan.wide = true;
-        plan.head_tiles_per_group = (group + kHeadsPerTile - 1) / kHeadsPerTile;
+        plan.head_tiles_per_group = (group + kWideHeads - 1) / kWideHeads;
         plan.warps_per_cta = kWideWarps;
         plan.stages = envInt("INFINIOP_PAGED_DECODE_STAGES", 3, 2, 4);
         plan.embedded_plan = false;
         plan.use_pdl = envInt("INFINIOP_PAGED_DECODE_PDL", 1, 0, 1) != 0;
         const size_t stage_bytes = (hd / 64 + I.value_size / 64) * kTileTokens * 128;
-        auto smemFor = [&](int stages) { return static_cast<size_t>(stages) * (stage_bytes + 16) + 1024; };
+        const size_t q_bytes = kWideHeads * (hd * 2 + 16); // the unit's Q rows, padded
+        auto smemFor = [&](int stages) { return static_cast<size_t>(stages) * (stage_bytes + 16) + q_bytes + 1024; };
         while (plan.stages > 2 && smemFor(plan.stages) > props.smem_per_block_optin) {
             --plan.stages;
         }
@@ -1600,16 +1639,19 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
     return plan;
 }
 
-bool streamTakesPointers(const DecodeParams &p, const void *workspace) {
+bool streamTakesPointers(const StreamPlan &plan, const DecodeParams &p, const void *workspace) {
     const auto addr = [](const void *ptr) { return reinterpret_cast<uintptr_t>(ptr); };
-    // TMA needs 16-byte aligned pool bases; the fragment loads need 4-byte aligned q/out.
-    return ((addr(p.k_cache) | addr(p.v_cache)) & 15u) == 0 && ((addr(p.q) | addr(p.out)) & 3u) == 0 && (addr(workspace) & 255u) == 0;
+    // TMA needs 16-byte aligned pool bases; the fragment loads need 4-byte aligned q/out (the wide-head
+    // kernel copies q rows 16 bytes at a time).
+    const uintptr_t q_mask = plan.wide ? 15u : 3u;
+    return ((addr(p.k_cache) | addr(p.v_cache)) & 15u) == 0 && (addr(p.q) & q_mask) == 0 && (addr(p.out) & 3u) == 0
+           && (addr(workspace) & 255u) == 0;
 }
 
 infiniStatus_t launchDecodeStream(const Info &I, const StreamPlan &plan, const DecodeParams &p,
                                   void *workspace, size_t workspace_size, cudaStream_t stream) {
     B200_RETURN_IF(workspace_size < plan.workspace_bytes, INFINI_STATUS_INSUFFICIENT_WORKSPACE);
-    if (!streamTakesPointers(p, workspace)) {
+    if (!streamTakesPointers(plan, p, workspace)) {
         B200_RETURN_IF(p.new_k != nullptr, INFINI_STATUS_INTERNAL_ERROR); // the append form checks before it gets here
         return launchDecodeGeneric(I, p, stream);
     }

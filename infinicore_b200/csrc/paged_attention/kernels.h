@@ -76,7 +76,7 @@ infiniStatus_t launchDecodeStream(const Info &info, const StreamPlan &plan, cons
 
 // True when launchDecodeStream will run the streaming kernel for these pointers (and not hand the
 // call to the generic kernel): the caller of the append form needs to know which one takes the rows.
-bool streamTakesPointers(const DecodeParams &p, const void *workspace);
+bool streamTakesPointers(const StreamPlan &plan, const DecodeParams &p, const void *workspace);
 
 // Stand-alone append for the paths that do not fuse it: position seq_len - 1 of every sequence
 // receives its new_k / new_v row (one warp per row).
