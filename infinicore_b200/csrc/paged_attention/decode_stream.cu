@@ -325,7 +325,9 @@ __global__ void __launch_bounds__(kPlanThreads)
 // ---------------------------------------------------------------------------------------
 // Main kernel
 // ---------------------------------------------------------------------------------------
-template <typename T, int HD>
+// HPT: q-heads per head tile.  8 uses rows 0-7 of the MMA's M dimension (rows 8-15 are padding); 16 uses
+// all rows, for groups of more than 8 q-heads per kv-head: K/V are then re-read once per 16 heads.
+template <typename T, int HD, int HPT>
 __global__ void __launch_bounds__(kMaxWarps * 32)
     pagedDecodeStreamKernel(const __grid_constant__ CUtensorMap tmap_k,
                             const __grid_constant__ CUtensorMap tmap_v,
@@ -336,6 +338,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     constexpr int kStageBytes = 2 * kTensorBytes;  // K tile + V tile
     constexpr int kKSteps = HD / 16;
     constexpr int kNTiles = HD / 8;
+    constexpr int kRows = HPT / 8; // q-heads per thread: MMA rows g (and g + 8)
+    static_assert(HPT == 8 || HPT == 16, "8 or 16 q-heads per head tile");
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
 
@@ -515,28 +519,31 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     long long next_block = (issued < count) ? tableEntry(gen) : 0;
 
     // ---- per-unit state ---------------------------------------------------------------
-    uint32_t qa[kKSteps][2];
+    uint32_t qa[kKSteps][2 * kRows]; // [.][2h], [.][2h + 1]: low / high 8 of the k-step, q-head g + 8h
     float o[kNTiles][4];
-    float m_run = -INFINITY;
-    float l_run = 0.f;
-    float slope_log2 = 0.f;
+    float m_run[kRows], l_run[kRows], slope_log2[kRows];
+    bool row_valid[kRows];
     int first_ti = cur.ti;
     int seq_len = 0;
-    bool row_valid = false;
 
     auto loadUnit = [&]() {
         const int kv_head = cur.j / head_tiles;
         const int head_tile = cur.j % head_tiles;
-        const int head_in_group = head_tile * kHeadsPerTile + g;
-        row_valid = head_in_group < p.group_size;
-        const int head = kv_head * p.group_size + (row_valid ? head_in_group : 0);
-        const T *q = static_cast<const T *>(p.q) + cur.s * p.q_seq_stride + head * p.q_head_stride;
 #pragma unroll
-        for (int ks = 0; ks < kKSteps; ++ks) {
-            qa[ks][0] = row_valid ? *reinterpret_cast<const uint32_t *>(q + ks * 16 + 2 * t) : 0u;
-            qa[ks][1] = row_valid ? *reinterpret_cast<const uint32_t *>(q + ks * 16 + 8 + 2 * t) : 0u;
+        for (int h = 0; h < kRows; ++h) {
+            const int head_in_group = head_tile * HPT + g + 8 * h;
+            row_valid[h] = head_in_group < p.group_size;
+            const int head = kv_head * p.group_size + (row_valid[h] ? head_in_group : 0);
+            const T *q = static_cast<const T *>(p.q) + cur.s * p.q_seq_stride + head * p.q_head_stride;
+#pragma unroll
+            for (int ks = 0; ks < kKSteps; ++ks) {
+                qa[ks][2 * h] = row_valid[h] ? *reinterpret_cast<const uint32_t *>(q + ks * 16 + 2 * t) : 0u;
+                qa[ks][2 * h + 1] = row_valid[h] ? *reinterpret_cast<const uint32_t *>(q + ks * 16 + 8 + 2 * t) : 0u;
+            }
+            slope_log2[h] = (p.alibi_slopes != nullptr && row_valid[h]) ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
+            m_run[h] = -INFINITY;
+            l_run[h] = 0.f;
         }
-        slope_log2 = (p.alibi_slopes != nullptr && row_valid) ? p.alibi_slopes[head] * 1.4426950408889634f : 0.f;
         long long len = loadIndex(p.seq_lens, cur.s, p.index_is_64);
         const long long capacity = static_cast<long long>(p.max_blocks_per_seq) * p.block_size;
         seq_len = static_cast<int>(len > capacity ? capacity : len);
@@ -544,8 +551,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
         for (int n = 0; n < kNTiles; ++n) {
             o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
         }
-        m_run = -INFINITY;
-        l_run = 0.f;
         first_ti = cur.ti;
     };
     loadUnit();
@@ -655,50 +660,64 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
             }
 #pragma unroll
             for (int ks = 0; ks < kKChunk; ks += 2) {
-                mma16816<T>(sa[0], qa[c0 + ks][0], 0u, qa[c0 + ks][1], 0u, kb[ks][0], kb[ks][1]);
-                mma16816<T>(sa[1], qa[c0 + ks][0], 0u, qa[c0 + ks][1], 0u, kb[ks][2], kb[ks][3]);
-                mma16816<T>(sb[0], qa[c0 + ks + 1][0], 0u, qa[c0 + ks + 1][1], 0u, kb[ks + 1][0], kb[ks + 1][1]);
-                mma16816<T>(sb[1], qa[c0 + ks + 1][0], 0u, qa[c0 + ks + 1][1], 0u, kb[ks + 1][2], kb[ks + 1][3]);
+                // A fragment: (row g, k low), (row g + 8, k low), (row g, k high), (row g + 8, k high)
+                const uint32_t a1 = (kRows == 2) ? qa[c0 + ks][2 * (kRows - 1)] : 0u;
+                const uint32_t a3 = (kRows == 2) ? qa[c0 + ks][2 * (kRows - 1) + 1] : 0u;
+                const uint32_t b1 = (kRows == 2) ? qa[c0 + ks + 1][2 * (kRows - 1)] : 0u;
+                const uint32_t b3 = (kRows == 2) ? qa[c0 + ks + 1][2 * (kRows - 1) + 1] : 0u;
+                mma16816<T>(sa[0], qa[c0 + ks][0], a1, qa[c0 + ks][1], a3, kb[ks][0], kb[ks][1]);
+                mma16816<T>(sa[1], qa[c0 + ks][0], a1, qa[c0 + ks][1], a3, kb[ks][2], kb[ks][3]);
+                mma16816<T>(sb[0], qa[c0 + ks + 1][0], b1, qa[c0 + ks + 1][1], b3, kb[ks + 1][0], kb[ks + 1][1]);
+                mma16816<T>(sb[1], qa[c0 + ks + 1][0], b1, qa[c0 + ks + 1][1], b3, kb[ks + 1][2], kb[ks + 1][3]);
             }
         }
 
-        // ---- online softmax (log2 domain) for q-head g over this tile's 16 tokens -----------
-        float x[4];
-        x[0] = (sa[0][0] + sb[0][0]) * p.scale_log2e;
-        x[1] = (sa[0][1] + sb[0][1]) * p.scale_log2e;
-        x[2] = (sa[1][0] + sb[1][0]) * p.scale_log2e;
-        x[3] = (sa[1][1] + sb[1][1]) * p.scale_log2e;
-        if (slope_log2 != 0.f) {
-            const int rel = tok0 + 2 * t - (seq_len - 1);
-            x[0] += slope_log2 * static_cast<float>(rel);
-            x[1] += slope_log2 * static_cast<float>(rel + 1);
-            x[2] += slope_log2 * static_cast<float>(rel + 8);
-            x[3] += slope_log2 * static_cast<float>(rel + 9);
+        // ---- online softmax (log2 domain) for q-head g (and g + 8) over this tile's 16 tokens -----
+        uint32_t pa[4] = {0u, 0u, 0u, 0u}; // A fragment of P: (row g | g + 8) x (tokens 2t, 2t+1 | 2t+8, 2t+9)
+        float alpha[kRows];
+#pragma unroll
+        for (int h = 0; h < kRows; ++h) {
+            float x[4];
+            x[0] = (sa[0][2 * h] + sb[0][2 * h]) * p.scale_log2e;
+            x[1] = (sa[0][2 * h + 1] + sb[0][2 * h + 1]) * p.scale_log2e;
+            x[2] = (sa[1][2 * h] + sb[1][2 * h]) * p.scale_log2e;
+            x[3] = (sa[1][2 * h + 1] + sb[1][2 * h + 1]) * p.scale_log2e;
+            if (slope_log2[h] != 0.f) {
+                const int rel = tok0 + 2 * t - (seq_len - 1);
+                x[0] += slope_log2[h] * static_cast<float>(rel);
+                x[1] += slope_log2[h] * static_cast<float>(rel + 1);
+                x[2] += slope_log2[h] * static_cast<float>(rel + 8);
+                x[3] += slope_log2[h] * static_cast<float>(rel + 9);
+            }
+            if (valid < kTileTokens) {
+                const int c = 2 * t;
+                x[0] = (c < valid) ? x[0] : -INFINITY;
+                x[1] = (c + 1 < valid) ? x[1] : -INFINITY;
+                x[2] = (c + 8 < valid) ? x[2] : -INFINITY;
+                x[3] = (c + 9 < valid) ? x[3] : -INFINITY;
+            }
+            float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[h], mx);
+            alpha[h] = fastExp2(m_run[h] - m_new);
+            const float p0 = fastExp2(x[0] - m_new);
+            const float p1 = fastExp2(x[1] - m_new);
+            const float p2 = fastExp2(x[2] - m_new);
+            const float p3 = fastExp2(x[3] - m_new);
+            l_run[h] = l_run[h] * alpha[h] + ((p0 + p1) + (p2 + p3));
+            m_run[h] = m_new;
+            pa[h] = packPair(p0, p1, T());
+            pa[2 + h] = packPair(p2, p3, T());
         }
-        if (valid < kTileTokens) {
-            const int c = 2 * t;
-            x[0] = (c < valid) ? x[0] : -INFINITY;
-            x[1] = (c + 1 < valid) ? x[1] : -INFINITY;
-            x[2] = (c + 8 < valid) ? x[2] : -INFINITY;
-            x[3] = (c + 9 < valid) ? x[3] : -INFINITY;
-        }
-        float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run, mx);
-        const float alpha = fastExp2(m_run - m_new);
-        const float p0 = fastExp2(x[0] - m_new);
-        const float p1 = fastExp2(x[1] - m_new);
-        const float p2 = fastExp2(x[2] - m_new);
-        const float p3 = fastExp2(x[3] - m_new);
-        l_run = l_run * alpha + ((p0 + p1) + (p2 + p3));
-        m_run = m_new;
-        const uint32_t pa0 = packPair(p0, p1, T());
-        const uint32_t pa2 = packPair(p2, p3, T());
 #pragma unroll
         for (int n = 0; n < kNTiles; ++n) {
-            o[n][0] *= alpha;
-            o[n][1] *= alpha;
+            o[n][0] *= alpha[0];
+            o[n][1] *= alpha[0];
+            if (kRows == 2) {
+                o[n][2] *= alpha[kRows - 1];
+                o[n][3] *= alpha[kRows - 1];
+            }
         }
 
         // ---- O += P . V -----------------------------------------------------------------
@@ -713,8 +732,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
             } else {
                 ldmatrixX4Trans(vAddr(np), b0, b1, b2, b3);
             }
-            mma16816<T>(o[2 * np], pa0, 0u, pa2, 0u, b0, b1);
-            mma16816<T>(o[2 * np + 1], pa0, 0u, pa2, 0u, b2, b3);
+            mma16816<T>(o[2 * np], pa[0], pa[1], pa[2], pa[3], b0, b1);
+            mma16816<T>(o[2 * np + 1], pa[0], pa[1], pa[2], pa[3], b2, b3);
         }
 
         } // !probe_copy_only
@@ -737,32 +756,36 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
         // ---- end of unit or end of range: emit --------------------------------------------
         const bool unit_end = (cur.ti + 1 == cur.nt);
         if (unit_end || i + 1 == count) {
-            float l_all = l_run;
-            l_all += __shfl_xor_sync(0xffffffffu, l_all, 1);
-            l_all += __shfl_xor_sync(0xffffffffu, l_all, 2);
             const int kv_head = cur.j / head_tiles;
             const int head_tile = cur.j % head_tiles;
-            if (first_ti == 0 && unit_end) {
-                if (row_valid) {
-                    const int head = kv_head * p.group_size + head_tile * kHeadsPerTile + g;
-                    T *out = static_cast<T *>(p.out) + cur.s * p.o_seq_stride + head * p.o_head_stride;
-                    const float inv = 1.f / l_all;
+            const long long unit = static_cast<long long>(cur.s) * a.units_per_seq + cur.j;
+            float *rec = a.partials + (unit + worker) * (HPT * (HD + 2));
 #pragma unroll
-                    for (int n = 0; n < kNTiles; ++n) {
-                        *reinterpret_cast<uint32_t *>(out + n * 8 + 2 * t) = packPair(o[n][0] * inv, o[n][1] * inv, T());
-                    }
-                }
-            } else {
-                const long long unit = static_cast<long long>(cur.s) * a.units_per_seq + cur.j;
-                float *rec = a.partials + (unit + worker) * (kHeadsPerTile * (HD + 2));
-                if (row_valid) {
+            for (int h = 0; h < kRows; ++h) {
+                float l_all = l_run[h];
+                l_all += __shfl_xor_sync(0xffffffffu, l_all, 1);
+                l_all += __shfl_xor_sync(0xffffffffu, l_all, 2);
+                const int r = g + 8 * h;
+                if (first_ti == 0 && unit_end) {
+                    if (row_valid[h]) {
+                        const int head = kv_head * p.group_size + head_tile * HPT + r;
+                        T *out = static_cast<T *>(p.out) + cur.s * p.o_seq_stride + head * p.o_head_stride;
+                        const float inv = 1.f / l_all;
 #pragma unroll
-                    for (int n = 0; n < kNTiles; ++n) {
-                        *reinterpret_cast<float2 *>(rec + g * HD + n * 8 + 2 * t) = make_float2(o[n][0], o[n][1]);
+                        for (int n = 0; n < kNTiles; ++n) {
+                            *reinterpret_cast<uint32_t *>(out + n * 8 + 2 * t) = packPair(o[n][2 * h] * inv, o[n][2 * h + 1] * inv, T());
+                        }
                     }
-                }
-                if (t == 0 && row_valid) {
-                    *reinterpret_cast<float2 *>(rec + kHeadsPerTile * HD + g * 2) = make_float2(m_run, l_all);
+                } else {
+                    if (row_valid[h]) {
+#pragma unroll
+                        for (int n = 0; n < kNTiles; ++n) {
+                            *reinterpret_cast<float2 *>(rec + r * HD + n * 8 + 2 * t) = make_float2(o[n][2 * h], o[n][2 * h + 1]);
+                        }
+                    }
+                    if (t == 0 && row_valid[h]) {
+                        *reinterpret_cast<float2 *>(rec + HPT * HD + r * 2) = make_float2(m_run[h], l_all);
+                    }
                 }
             }
         }
@@ -812,6 +835,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
 // ---------------------------------------------------------------------------------------
 constexpr int kWideWarps = 4;
 constexpr int kWideHeads = 16;
+#ifndef B200_WIDE_DEFAULT_STAGES
+#define B200_WIDE_DEFAULT_STAGES 3
+#endif
+constexpr int kWideDefaultStages = B200_WIDE_DEFAULT_STAGES; // ring slots per CTA unless the environment says otherwise
 
 template <typename T, int KD, int VD>
 __global__ void __launch_bounds__(kWideWarps * 32)
@@ -1416,19 +1443,19 @@ WorkspaceLayout workspaceLayout(const Info &I, const StreamPlan &plan) {
     L.task_off = roundUp(L.range_off + static_cast<size_t>(plan.num_workers) * sizeof(int4), 256);
     L.partial_off = roundUp(L.task_off + static_cast<size_t>(plan.num_workers) * sizeof(int4), 256);
     const size_t units = I.num_seqs * I.num_kv_heads * static_cast<size_t>(plan.head_tiles_per_group);
-    const size_t rec = (plan.wide ? kWideHeads : kHeadsPerTile) * (I.value_size + 2) * sizeof(float);
+    const size_t rec = static_cast<size_t>(plan.heads_per_tile) * (I.value_size + 2) * sizeof(float);
     L.total = roundUp(L.partial_off + (units + plan.num_workers) * rec, 256);
     return L;
 }
 
-template <typename T, int HD>
+template <typename T, int HD, int HPT>
 infiniStatus_t launchTyped(const StreamPlan &plan, const StreamArgs &args, const CUtensorMap &mk, const CUtensorMap &mv,
                            int device_id, cudaStream_t stream) {
     // The opt-in shared memory limit is a per-device, per-kernel attribute; raise it whenever a plan
     // needs more than any earlier plan on that device did.
     static std::mutex attr_mutex;
     static size_t attr_bytes[64] = {};
-    auto kernel = pagedDecodeStreamKernel<T, HD>;
+    auto kernel = pagedDecodeStreamKernel<T, HD, HPT>;
     {
         std::lock_guard<std::mutex> lock(attr_mutex);
         const bool tracked = device_id >= 0 && device_id < 64;
@@ -1467,19 +1494,27 @@ infiniStatus_t launchTyped(const StreamPlan &plan, const StreamArgs &args, const
         return checkLaunch("pagedDecodeStreamKernel");
     }
     // Few units split over many workers each (a handful of very long sequences): a unit's records
-    // are merged by several CTAs, 32 value columns each, instead of one.
+    // are merged by several CTAs, 32 value columns each, instead of one.  Records of 16 heads are
+    // always merged in slices (a whole record does not fit one CTA's shared memory).
     const long long units = static_cast<long long>(args.p.num_seqs) * args.units_per_seq;
     cfg.dynamicSmemBytes = 0;
+    constexpr int kWideSlice = (HD >= 64) ? 64 : HD;
     if (units * 4 <= plan.num_workers) {
         cfg.gridDim = dim3(plan.num_workers, HD / 32);
-        cfg.blockDim = dim3(CombineShape<32, HD, kHeadsPerTile>::kWarps * 32);
-        if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, 32, HD>, args) != cudaSuccess) {
+        cfg.blockDim = dim3(CombineShape<32, HD, HPT>::kWarps * 32);
+        if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, 32, HD, HPT>, args) != cudaSuccess) {
+            return checkLaunch("pagedDecodeCombineKernel");
+        }
+    } else if (HPT == 16) {
+        cfg.gridDim = dim3(plan.num_workers, HD / kWideSlice);
+        cfg.blockDim = dim3(CombineShape<kWideSlice, HD, HPT>::kWarps * 32);
+        if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, kWideSlice, HD, HPT>, args) != cudaSuccess) {
             return checkLaunch("pagedDecodeCombineKernel");
         }
     } else {
         cfg.gridDim = dim3(plan.num_workers);
-        cfg.blockDim = dim3(CombineShape<HD, HD, kHeadsPerTile>::kWarps * 32);
-        if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, HD>, args) != cudaSuccess) {
+        cfg.blockDim = dim3(CombineShape<HD, HD, 8>::kWarps * 32);
+        if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, HD, HD, 8>, args) != cudaSuccess) {
             return checkLaunch("pagedDecodeCombineKernel");
         }
     }
@@ -1576,9 +1611,10 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
         // one worker = one CTA of four warps sharing a ring of 36 KiB (34 KiB) tiles
         const int group = static_cast<int>(I.num_heads / I.num_kv_heads);
         plan.wide = true;
+        plan.heads_per_tile = kWideHeads;
         plan.head_tiles_per_group = (group + kWideHeads - 1) / kWideHeads;
         plan.warps_per_cta = kWideWarps;
-        plan.stages = envInt("INFINIOP_PAGED_DECODE_STAGES", 3, 2, 4);
+        plan.stages = envInt("INFINIOP_PAGED_DECODE_STAGES", kWideDefaultStages, 2, 4);
         plan.embedded_plan = false;
         plan.use_pdl = envInt("INFINIOP_PAGED_DECODE_PDL", 1, 0, 1) != 0;
         const size_t stage_bytes = (hd / 64 + I.value_size / 64) * kTileTokens * 128;
@@ -1591,8 +1627,12 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
             plan.wide = false;
             return plan;
         }
-        plan.smem_bytes = smemFor(plan.stages);
+        // the wanted number of resident CTAs comes first: the ring gives up slots (down to 2) to fit them
         int ctas_per_sm = envInt("INFINIOP_PAGED_DECODE_CTAS_PER_SM", 2, 1, 4);
+        while (plan.stages > 2 && ctas_per_sm * (smemFor(plan.stages) + 1024) > props.smem_per_sm) {
+            --plan.stages;
+        }
+        plan.smem_bytes = smemFor(plan.stages);
         while (ctas_per_sm > 1 && ctas_per_sm * (plan.smem_bytes + 1024) > props.smem_per_sm) {
             --ctas_per_sm;
         }
@@ -1604,7 +1644,10 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
     }
 
     const int group = static_cast<int>(I.num_heads / I.num_kv_heads);
-    plan.head_tiles_per_group = (group + kHeadsPerTile - 1) / kHeadsPerTile;
+    // Groups of more than 8 q-heads per kv-head use all 16 rows of the MMA (head sizes up to 128, where
+    // the second row's Q fragments still fit the registers): K/V are re-read once per 16 heads, not per 8.
+    plan.heads_per_tile = (group > kHeadsPerTile && hd <= 128 && envInt("INFINIOP_PAGED_DECODE_HEADS_PER_TILE", 16, 8, 16) == 16) ? 16 : kHeadsPerTile;
+    plan.head_tiles_per_group = (group + plan.heads_per_tile - 1) / plan.heads_per_tile;
 
     const size_t stage_bytes = 2 * (hd / 64) * kTileTokens * 128;
     const int default_stages = 2;
@@ -1687,15 +1730,22 @@ infiniStatus_t launchDecodeStream(const Info &I, const StreamPlan &plan, const D
         return f16 ? launchWide<__half, 576, 576>(plan, a, mk, mv, device_id, stream)
                    : launchWide<__nv_bfloat16, 576, 576>(plan, a, mk, mv, device_id, stream);
     }
+    const bool h16 = plan.heads_per_tile == 16;
     switch (I.head_size) {
     case 64:
-        return f16 ? launchTyped<__half, 64>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 64>(plan, a, mk, mv, device_id, stream);
+        if (h16) {
+            return f16 ? launchTyped<__half, 64, 16>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 64, 16>(plan, a, mk, mv, device_id, stream);
+        }
+        return f16 ? launchTyped<__half, 64, 8>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 64, 8>(plan, a, mk, mv, device_id, stream);
     case 128:
-        return f16 ? launchTyped<__half, 128>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 128>(plan, a, mk, mv, device_id, stream);
+        if (h16) {
+            return f16 ? launchTyped<__half, 128, 16>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 128, 16>(plan, a, mk, mv, device_id, stream);
+        }
+        return f16 ? launchTyped<__half, 128, 8>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 128, 8>(plan, a, mk, mv, device_id, stream);
     case 192:
-        return f16 ? launchTyped<__half, 192>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 192>(plan, a, mk, mv, device_id, stream);
+        return f16 ? launchTyped<__half, 192, 8>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 192, 8>(plan, a, mk, mv, device_id, stream);
     case 256:
-        return f16 ? launchTyped<__half, 256>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 256>(plan, a, mk, mv, device_id, stream);
+        return f16 ? launchTyped<__half, 256, 8>(plan, a, mk, mv, device_id, stream) : launchTyped<__nv_bfloat16, 256, 8>(plan, a, mk, mv, device_id, stream);
     default:
         return INFINI_STATUS_BAD_TENSOR_SHAPE;
     }

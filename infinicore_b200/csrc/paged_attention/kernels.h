@@ -55,7 +55,8 @@ infiniStatus_t launchDecodeGeneric(const Info &info, const DecodeParams &p, cuda
 // ---- streaming path: TMA page staging + mma.sync, work split evenly over persistent warps
 struct StreamPlan {
     bool eligible = false;
-    int head_tiles_per_group = 1; // q-heads of a GQA group are processed 8 at a time
+    int heads_per_tile = 8;       // q-heads processed together against one staged tile: 8, or 16 for groups of more than 8
+    int head_tiles_per_group = 1; // ceil(group size / heads_per_tile)
     int warps_per_cta = 0;
     int stages = 0;
     int grid = 0;        // persistent CTAs

@@ -2,7 +2,7 @@
 by oracle/build_ref.py) on the benchmark configurations, each in a child process.  Prints one
 JSON line per (configuration, library, environment).
 
-    python tests/compare_reference_kernels.py [c1 c2 c3 c4 b1 b8 b1long h64 h192 h256 h576 mla p1 p2]
+    python tests/compare_reference_kernels.py [c1 c2 c3 c4 b1 b8 b1long g16 h64 h192 h256 h576 mla p1 p2]
 """
 import json
 import os
@@ -28,6 +28,9 @@ SPECS = {
                                                "head_size": 128, "block_size": 16, "seed": 12, "device": "cuda"}},
     "b1long": {"builder": "build_case", "kwargs": {"name": "b1long", "dtype": "bfloat16", "seq_lens": [65536], "num_heads": 32, "num_kv_heads": 8,
                                                    "head_size": 128, "block_size": 16, "seed": 13, "device": "cuda"}},
+    # 16 q-heads per kv-head (Llama-3.1-405B grouping): 128 / 8 heads, 64 sequences x 4096 tokens
+    "g16": {"builder": "build_case", "kwargs": {"name": "g16", "dtype": "bfloat16", "seq_lens": [4096] * 64, "num_heads": 128, "num_kv_heads": 8,
+                                                "head_size": 128, "block_size": 16, "seed": 16, "device": "cuda"}},
     # the other head sizes the descriptor accepts: 64 sequences x 4096 tokens each
     "h64": {"builder": "build_case", "kwargs": {"name": "h64", "dtype": "float16", "seq_lens": [4096] * 64, "num_heads": 32, "num_kv_heads": 8,
                                                 "head_size": 64, "block_size": 16, "seed": 64, "device": "cuda"}},
