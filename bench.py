@@ -48,8 +48,10 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5", "prefill"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--collective", default="infiniccl", choices=["infiniccl", "torch"],
-                    help="head mode only: the all-gather goes through libinfiniccl.so (default) or torch.distributed")
+    ap.add_argument("--collective", default="infiniccl", choices=["infiniccl", "torch", "peer"],
+                    help="head mode only: the all-gather goes through libinfiniccl.so (default) or torch.distributed; "
+                         "peer: no all-gather - the attention kernels store each rank's head slice into every rank's full "
+                         "output in symmetric memory, and a barrier follows")
     ap.add_argument("--mode", default="seq", choices=["seq", "head"],
                     help="seq: shard by sequence, no collective (default); head: optional KV-head-sharded mode, "
                          "every rank holds all sequences for its kv-heads and outputs are all-gathered over NCCL")
@@ -69,7 +71,7 @@ def measured_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
-def workload_config(name, case, n_gpus, mode="seq"):
+def workload_config(name, case, n_gpus, mode="seq", collective="infiniccl"):
     return {
         "workload": {
             "c2": "configs[1]: Llama-3-8B-shape decode, bf16, batch 64 per GPU, 32/8 heads, head 128, block 16, every seq_len 4096, "
@@ -81,7 +83,7 @@ def workload_config(name, case, n_gpus, mode="seq"):
         "num_seqs_per_gpu": case.num_seqs,
         "tokens_per_gpu": case.total_tokens,
         "kv_bytes_per_gpu": case.kv_bytes,
-        "parallelism": (f"kv-head-sharded x{n_gpus}, one NCCL all-gather of the outputs per step" if mode == "head" and n_gpus > 1
+        "parallelism": (f"kv-head-sharded x{n_gpus}, outputs combined per step by {collective}" if mode == "head" and n_gpus > 1
                         else f"sequence-sharded x{n_gpus}, no collective"),
         "l2": "inputs larger than L2 (KV working set per step >> 126 MB)" if case.kv_bytes > (256 << 20) else "L2 flushed between steps",
     }
@@ -249,7 +251,7 @@ class ClockSampler:
 class AbiStep:
     """Descriptors + workspace for one rank's decode step, called through the C ABI on torch's current stream."""
 
-    def __init__(self, case):
+    def __init__(self, case, out=None):
         import torch
 
         from infinicore_b200.libinfiniop import (LIBINFINIOP, InfiniDeviceEnum, TestTensor, check_error, create_handle,
@@ -261,7 +263,10 @@ class AbiStep:
         dev = case.q.device.index
         check_error(LIBINFINIOP.infinirtSetDevice(InfiniDeviceEnum.NVIDIA, dev))
         self.handle = create_handle()
-        self.out = torch.zeros((case.num_seqs, case.num_heads, case.v_cache.shape[3]), dtype=case.dtype, device=case.q.device)
+        # `out` given: a (possibly strided) view the descriptor is made for, e.g. this rank's head slice
+        # inside its full output in symmetric memory
+        self.out = out if out is not None else torch.zeros((case.num_seqs, case.num_heads, case.v_cache.shape[3]), dtype=case.dtype,
+                                                            device=case.q.device)
 
         def tt(t):
             return TestTensor.from_torch(t, to_infini_dtype(t.dtype), InfiniDeviceEnum.NVIDIA)
@@ -298,6 +303,15 @@ class AbiStep:
         self.check(self.lib.infiniopPagedDecodeStep(self.fused, self.ws.data_ptr(), self.ws_size, self.out.data_ptr(), c.q.data_ptr(),
                                                     c.k_cache.data_ptr(), c.v_cache.data_ptr(), c.new_k.data_ptr(), c.new_v.data_ptr(),
                                                     c.block_tables.data_ptr(), c.seq_lens.data_ptr(), None, stream))
+
+    def attention_multi_out(self, stream, destinations):
+        """Attention with the output rows stored to every destination (tensor or raw address); the first is self.out."""
+        c = self.case
+        ptrs = [d.data_ptr() if hasattr(d, "data_ptr") else int(d) for d in destinations]
+        arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+        self.check(self.lib.infiniopPagedAttentionMultiOut(self.attn, self.ws.data_ptr(), self.ws_size, arr, len(ptrs), c.q.data_ptr(),
+                                                          c.k_cache.data_ptr(), c.v_cache.data_ptr(), c.block_tables.data_ptr(),
+                                                          c.seq_lens.data_ptr(), None, stream))
 
     def attention(self, stream):
         c = self.case
@@ -346,7 +360,12 @@ def gpu_arm(args):
 
     head_mode = args.mode == "head" and world > 1
     case = make_case(args.workload, rank, world, device, args.mode)
-    step = AbiStep(case)
+    peers = None
+    if head_mode and args.collective == "peer":
+        from infinicore_b200 import sharding
+
+        peers = sharding.PeerOutputs(case.num_seqs, case.num_heads * world, case.v_cache.shape[3], case.dtype, device)
+    step = AbiStep(case, out=peers.local_slice() if peers is not None else None)
     stream = torch.cuda.current_stream(device)
     sptr = stream.cuda_stream
     small_ws = case.kv_bytes <= (256 << 20)
@@ -363,11 +382,17 @@ def gpu_arm(args):
 
             ccl_comm = ccl.init_from_process_group()
 
+    peer_dests = peers.destinations() if peers is not None else None
+
     def one_step():
         step.caching(sptr)
-        step.attention(sptr)
-        if head_mode:
-            sharding.gather_head_sharded(step.out, world, staging=gather_staging, comm=ccl_comm)
+        if peers is not None:
+            step.attention_multi_out(sptr, peer_dests)
+            peers.barrier()
+        else:
+            step.attention(sptr)
+            if head_mode:
+                sharding.gather_head_sharded(step.out, world, staging=gather_staging, comm=ccl_comm)
 
     # ---- device-resident timing -------------------------------------------------------------
     for _ in range(max(args.warmup, 3)):
@@ -451,9 +476,15 @@ def gpu_arm(args):
         def e2e_step():  # noqa: F811
             estep._dev_arena.copy_(estep._host_arena, non_blocking=True)
             ib.paged_caching(case.k_cache, case.v_cache, estep.dev["new_k"], estep.dev["new_v"], estep.dev["slot_mapping"])
-            o = ib.paged_attention(estep.dev["q"], case.k_cache, case.v_cache, estep.dev["block_tables"], estep.dev["seq_lens"],
-                                   None, case.scale, out=estep.out)
-            full = sharding.gather_head_sharded(o, world, staging=gather_staging, comm=ccl_comm)
+            if peers is not None:
+                ib.paged_attention_multi_out(peer_dests, estep.dev["q"], case.k_cache, case.v_cache, estep.dev["block_tables"],
+                                             estep.dev["seq_lens"], None, case.scale)
+                peers.barrier()
+                full = peers.full
+            else:
+                o = ib.paged_attention(estep.dev["q"], case.k_cache, case.v_cache, estep.dev["block_tables"], estep.dev["seq_lens"],
+                                       None, case.scale, out=estep.out)
+                full = sharding.gather_head_sharded(o, world, staging=gather_staging, comm=ccl_comm)
             host_full.copy_(full, non_blocking=True)
             stream.synchronize()
 
@@ -484,7 +515,9 @@ def gpu_arm(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if (args.workload == "c5" or head_mode) else "weak",
             "vs_baseline": None, "dtype": "f16" if case.dtype == torch.float16 else "bf16", "data": "synthetic",
-            "config": workload_config(args.workload, case, world, args.mode),
+            "config": workload_config(args.workload, case, world, args.mode,
+                                      {"infiniccl": "one infinicclAllGather (NCCL)", "torch": "one torch.distributed all-gather (NCCL)",
+                                       "peer": "peer stores from the attention kernels into every rank's full output + a barrier"}[args.collective]),
             "seqs_per_s": seqs_all / (ms_per_step * 1e-3),
             "frac_of_hbm_peak": value / (peak * world),
             "roofline": {

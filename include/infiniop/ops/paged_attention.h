@@ -85,4 +85,25 @@ __INFINI_C __export infiniStatus_t infiniopPagedAttentionStaticWorkspace(
 __INFINI_C __export infiniStatus_t infiniopDestroyPagedAttentionDescriptor(
     infiniopPagedAttentionDescriptor_t desc);
 
+/* No reference counterpart.  infiniopPagedAttention with every output row stored to `num_outs`
+ * buffers (1..8) that all have the shape and strides of the descriptor's `out`; outs[0] is the
+ * ordinary output.  The buffers may live on other GPUs whose memory this GPU can address (peer
+ * access, symmetric memory): the KV-head-sharded mode hands in the address of its head slice
+ * inside every rank's full output, and the all-gather that would follow the kernel is not needed -
+ * only a barrier across the ranks before anyone reads its full output.  Sequences with
+ * seq_len <= 0 leave their rows untouched in every buffer. */
+__INFINI_C __export infiniStatus_t infiniopPagedAttentionMultiOut(
+    infiniopPagedAttentionDescriptor_t desc,
+    void *workspace,
+    size_t workspace_size,
+    void *const *outs,
+    size_t num_outs,
+    const void *q,
+    const void *k_cache,
+    const void *v_cache,
+    const void *block_tables,
+    const void *seq_lens,
+    const void *alibi_slopes,
+    void *stream);
+
 #endif

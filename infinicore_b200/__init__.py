@@ -13,6 +13,7 @@ _LAZY = {
     "InfiniDtype": "libinfiniop",
     "library_paths": "libinfiniop",
     "paged_attention": "ops",
+    "paged_attention_multi_out": "ops",
     "paged_caching": "ops",
     "paged_attention_prefill": "ops",
     "paged_decode_step": "ops",

@@ -40,10 +40,17 @@ infiniStatus_t launchDecodeGeneric(const Info &info, const DecodeParams &p, cuda
     const dim3 grid(p.num_seqs, p.num_heads);
     const dim3 block(row::kWarps * 32);
     const size_t smem = row::sharedBytes(p.head_size, p.value_size);
-    if (info.dtype == INFINI_DTYPE_F16) {
-        pagedDecodeGenericKernel<__half><<<grid, block, smem, stream>>>(p);
-    } else {
-        pagedDecodeGenericKernel<__nv_bfloat16><<<grid, block, smem, stream>>>(p);
+    // further destinations: the same launch again with its output redirected (this path is the
+    // uncommon one; the streaming kernels store every destination themselves)
+    for (int d = 0; d <= p.num_extra_out; ++d) {
+        DecodeParams pd = p;
+        pd.out = (d == 0) ? p.out : p.extra_out[d - 1];
+        pd.num_extra_out = 0;
+        if (info.dtype == INFINI_DTYPE_F16) {
+            pagedDecodeGenericKernel<__half><<<grid, block, smem, stream>>>(pd);
+        } else {
+            pagedDecodeGenericKernel<__nv_bfloat16><<<grid, block, smem, stream>>>(pd);
+        }
     }
     return checkLaunch("pagedDecodeGenericKernel");
 }

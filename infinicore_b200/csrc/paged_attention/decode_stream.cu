@@ -769,11 +769,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
                 if (first_ti == 0 && unit_end) {
                     if (row_valid[h]) {
                         const int head = kv_head * p.group_size + head_tile * HPT + r;
-                        T *out = static_cast<T *>(p.out) + cur.s * p.o_seq_stride + head * p.o_head_stride;
+                        const long long off = cur.s * p.o_seq_stride + head * p.o_head_stride;
                         const float inv = 1.f / l_all;
+                        for (int d = 0; d <= p.num_extra_out; ++d) { // the output and every further destination
+                            T *out = static_cast<T *>(d == 0 ? p.out : p.extra_out[d - 1]) + off;
 #pragma unroll
-                        for (int n = 0; n < kNTiles; ++n) {
-                            *reinterpret_cast<uint32_t *>(out + n * 8 + 2 * t) = packPair(o[n][2 * h] * inv, o[n][2 * h + 1] * inv, T());
+                            for (int n = 0; n < kNTiles; ++n) {
+                                *reinterpret_cast<uint32_t *>(out + n * 8 + 2 * t) = packPair(o[n][2 * h] * inv, o[n][2 * h + 1] * inv, T());
+                            }
                         }
                     }
                 } else {
@@ -1201,11 +1204,14 @@ __global__ void __launch_bounds__(kWideWarps * 32)
                 if (first_ti == 0 && unit_end) {
                     if (row_valid[h]) {
                         const int head = kv_head * p.group_size + head_tile * kWideHeads + r;
-                        T *out = static_cast<T *>(p.out) + cur.s * p.o_seq_stride + head * p.o_head_stride + col0;
+                        const long long off = cur.s * p.o_seq_stride + head * p.o_head_stride + col0;
                         const float inv = 1.f / l_all;
+                        for (int d = 0; d <= p.num_extra_out; ++d) { // the output and every further destination
+                            T *out = static_cast<T *>(d == 0 ? p.out : p.extra_out[d - 1]) + off;
 #pragma unroll
-                        for (int n = 0; n < kNTiles; ++n) {
-                            *reinterpret_cast<uint32_t *>(out + n * 8 + 2 * t) = packPair(o[n][2 * h] * inv, o[n][2 * h + 1] * inv, T());
+                            for (int n = 0; n < kNTiles; ++n) {
+                                *reinterpret_cast<uint32_t *>(out + n * 8 + 2 * t) = packPair(o[n][2 * h] * inv, o[n][2 * h + 1] * inv, T());
+                            }
                         }
                     }
                 } else if (row_valid[h]) {
@@ -1369,9 +1375,14 @@ __global__ void __launch_bounds__(CombineShape<HD, VD, HPT>::kWarps * 32)
         }
         const float inv = 1.f / l_all;
         const int q_head = kv_head * p.group_size + head_tile * HPT + head;
-        T *out = static_cast<T *>(p.out) + s * p.o_seq_stride + q_head * p.o_head_stride + slice0 + (f % (HD / 4)) * 4;
-        *reinterpret_cast<uint32_t *>(out) = packPair(o4.x * inv, o4.y * inv, T());
-        *reinterpret_cast<uint32_t *>(out + 2) = packPair(o4.z * inv, o4.w * inv, T());
+        const long long off = s * p.o_seq_stride + q_head * p.o_head_stride + slice0 + (f % (HD / 4)) * 4;
+        const uint32_t lo = packPair(o4.x * inv, o4.y * inv, T());
+        const uint32_t hi = packPair(o4.z * inv, o4.w * inv, T());
+        for (int d = 0; d <= p.num_extra_out; ++d) { // the output and every further destination
+            T *out = static_cast<T *>(d == 0 ? p.out : p.extra_out[d - 1]) + off;
+            *reinterpret_cast<uint32_t *>(out) = lo;
+            *reinterpret_cast<uint32_t *>(out + 2) = hi;
+        }
     }
 }
 
@@ -1687,7 +1698,11 @@ bool streamTakesPointers(const StreamPlan &plan, const DecodeParams &p, const vo
     // TMA needs 16-byte aligned pool bases; the fragment loads need 4-byte aligned q/out (the wide-head
     // kernel copies q rows 16 bytes at a time).
     const uintptr_t q_mask = plan.wide ? 15u : 3u;
-    return ((addr(p.k_cache) | addr(p.v_cache)) & 15u) == 0 && (addr(p.q) & q_mask) == 0 && (addr(p.out) & 3u) == 0
+    uintptr_t outs = addr(p.out);
+    for (int d = 0; d < p.num_extra_out; ++d) {
+        outs |= addr(p.extra_out[d]);
+    }
+    return ((addr(p.k_cache) | addr(p.v_cache)) & 15u) == 0 && (addr(p.q) & q_mask) == 0 && (outs & 3u) == 0
            && (addr(workspace) & 255u) == 0;
 }
 

@@ -42,6 +42,13 @@ struct DecodeParams {
     const void *new_k = nullptr;
     const void *new_v = nullptr;
     long long new_k_seq_stride = 0, new_v_seq_stride = 0; // head stride is head_size (dense)
+
+    // Further destinations of every output row (same shape and strides as `out`; null otherwise).  The
+    // KV-head-sharded mode stores a rank's head slice straight into every peer's full output this way,
+    // so no all-gather follows the kernel.
+    static constexpr int kMaxExtraOut = 7;
+    void *extra_out[kMaxExtraOut] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int num_extra_out = 0;
 };
 
 __host__ __device__ inline long long loadIndex(const void *base, long long i, int is64) {

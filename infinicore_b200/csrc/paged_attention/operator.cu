@@ -145,6 +145,51 @@ __INFINI_C infiniStatus_t infiniopPagedAttention(
     return b200::paged_attention::launchDecodeGeneric(I, p, cuda_stream);
 }
 
+// No reference counterpart: the same call with every output row stored to several buffers of the
+// descriptor's `out` shape and strides (outs[0] is the ordinary output).
+__INFINI_C infiniStatus_t infiniopPagedAttentionMultiOut(
+    infiniopPagedAttentionDescriptor_t desc,
+    void *workspace,
+    size_t workspace_size,
+    void *const *outs,
+    size_t num_outs,
+    const void *q,
+    const void *k_cache,
+    const void *v_cache,
+    const void *block_tables,
+    const void *seq_lens,
+    const void *alibi_slopes,
+    void *stream) {
+    B200_RETURN_IF(desc == nullptr, INFINI_STATUS_NULL_POINTER);
+    auto *d = reinterpret_cast<Descriptor *>(desc);
+    B200_RETURN_IF(d->base.kind != b200::OpKind::PagedAttention, INFINI_STATUS_BAD_PARAM);
+    B200_RETURN_IF(outs == nullptr, INFINI_STATUS_NULL_POINTER);
+    B200_RETURN_IF(num_outs < 1 || num_outs > 1 + b200::paged_attention::DecodeParams::kMaxExtraOut, INFINI_STATUS_BAD_PARAM);
+    const auto &I = d->info;
+    if (I.num_seqs == 0 || I.num_heads == 0) {
+        return INFINI_STATUS_SUCCESS;
+    }
+    for (size_t i = 0; i < num_outs; ++i) {
+        B200_RETURN_IF(outs[i] == nullptr, INFINI_STATUS_NULL_POINTER);
+    }
+    B200_RETURN_IF(q == nullptr || k_cache == nullptr || v_cache == nullptr || block_tables == nullptr || seq_lens == nullptr,
+                   INFINI_STATUS_NULL_POINTER);
+    B200_RETURN_IF(I.has_alibi && alibi_slopes == nullptr, INFINI_STATUS_NULL_POINTER);
+    B200_RETURN_IF(workspace_size < d->workspace_bytes, INFINI_STATUS_INSUFFICIENT_WORKSPACE);
+    B200_RETURN_IF(d->workspace_bytes > 0 && workspace == nullptr, INFINI_STATUS_NULL_POINTER);
+
+    auto p = b200::paged_attention::makeDecodeParams(I, outs[0], q, k_cache, v_cache, block_tables, seq_lens, alibi_slopes);
+    p.num_extra_out = static_cast<int>(num_outs) - 1;
+    for (int i = 0; i < p.num_extra_out; ++i) {
+        p.extra_out[i] = outs[i + 1];
+    }
+    auto cuda_stream = static_cast<cudaStream_t>(stream);
+    if (d->stream.eligible) {
+        return b200::paged_attention::launchDecodeStream(I, d->stream, p, workspace, workspace_size, cuda_stream);
+    }
+    return b200::paged_attention::launchDecodeGeneric(I, p, cuda_stream);
+}
+
 __INFINI_C infiniStatus_t infiniopDestroyPagedAttentionDescriptor(
     infiniopPagedAttentionDescriptor_t desc) {
     B200_RETURN_IF(desc == nullptr, INFINI_STATUS_NULL_POINTER);

@@ -82,7 +82,8 @@ INFINIOP_SYMBOLS = [
     "infiniopCreateTensorDescriptor", "infiniopDestroyTensorDescriptor",
     "infiniopGetDescriptorDeviceType", "infiniopGetDescriptorDeviceId",
     "infiniopCreatePagedAttentionDescriptor", "infiniopGetPagedAttentionWorkspaceSize",
-    "infiniopPagedAttention", "infiniopPagedAttentionStaticWorkspace", "infiniopDestroyPagedAttentionDescriptor",
+    "infiniopPagedAttention", "infiniopPagedAttentionStaticWorkspace", "infiniopPagedAttentionMultiOut",
+    "infiniopDestroyPagedAttentionDescriptor",
     "infiniopCreatePagedAttentionPrefillDescriptor", "infiniopGetPagedAttentionPrefillWorkspaceSize",
     "infiniopPagedAttentionPrefill", "infiniopDestroyPagedAttentionPrefillDescriptor",
     "infiniopCreatePagedCachingDescriptor", "infiniopGetPagedCachingWorkspaceSize",
@@ -171,6 +172,13 @@ def _bind(lib: InfiniLib) -> None:
         op.infiniopPagedAttentionStaticWorkspace.argtypes = [
             infiniopOperatorDescriptor_t,
             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        ]
+    # No reference counterpart: every output row stored to several buffers (outs[0] the ordinary one).
+    if hasattr(op, "infiniopPagedAttentionMultiOut"):
+        op.infiniopPagedAttentionMultiOut.restype = c_int32
+        op.infiniopPagedAttentionMultiOut.argtypes = [
+            infiniopOperatorDescriptor_t, c_void_p, c_size_t, POINTER(c_void_p), c_size_t,
+            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
         ]
     op.infiniopDestroyPagedAttentionDescriptor.restype = c_int32
     op.infiniopDestroyPagedAttentionDescriptor.argtypes = [infiniopOperatorDescriptor_t]

@@ -124,6 +124,52 @@ def paged_attention(q, k_cache, v_cache, block_tables, cache_lens, alibi_slopes=
     return out
 
 
+def paged_attention_multi_out(outs, q, k_cache, v_cache, block_tables, cache_lens, alibi_slopes=None, scale: float = 1.0):
+    """paged_attention with every output row stored to several buffers (no reference counterpart).
+
+    `outs[0]` is a tensor [num_seqs, num_heads, head_size] (it may be a strided view, e.g. a head slice
+    of a wider tensor); the further entries are tensors of the same shape and strides or raw device
+    addresses (ints) of such buffers - for instance the same head slice inside other ranks' outputs in
+    symmetric memory.  Returns outs[0]."""
+    out = outs[0]
+    dev = _require_cuda(q, k_cache, v_cache, block_tables, cache_lens, alibi_slopes, out)
+    st = _state(dev)
+    key = ("paged_attention", _meta(out), _meta(q), _meta(k_cache), _meta(v_cache), _meta(block_tables),
+           _meta(cache_lens), _meta(alibi_slopes), float(scale))
+
+    def make():
+        tensors = [_desc(out), _desc(q), _desc(k_cache), _desc(v_cache), _desc(block_tables), _desc(cache_lens)]
+        alibi = _desc(alibi_slopes) if alibi_slopes is not None else None
+        desc = infiniopOperatorDescriptor_t()
+        check_error(LIBINFINIOP.infiniopCreatePagedAttentionDescriptor(
+            st["handle"], ctypes.byref(desc), *[t.descriptor for t in tensors],
+            alibi.descriptor if alibi is not None else None, scale))
+        size = ctypes.c_size_t(0)
+        check_error(LIBINFINIOP.infiniopGetPagedAttentionWorkspaceSize(desc, ctypes.byref(size)))
+        for t in tensors + ([alibi] if alibi is not None else []):
+            t.destroy_desc()
+        return {"desc": desc, "workspace": size.value, "destroy": LIBINFINIOP.infiniopDestroyPagedAttentionDescriptor}
+
+    entry = _lookup(st, key, make)
+    ws = _workspace(st, entry["workspace"], dev)
+    ptrs = []
+    for o in outs:
+        if isinstance(o, torch.Tensor):
+            if tuple(o.shape) != tuple(out.shape) or o.stride() != out.stride() or o.dtype != out.dtype:
+                raise ValueError("every destination must have the shape, strides and dtype of outs[0]")
+            ptrs.append(o.data_ptr())
+        else:
+            ptrs.append(int(o))
+    arr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+    with torch.cuda.device(dev):
+        check_error(LIBINFINIOP.infiniopPagedAttentionMultiOut(
+            entry["desc"], ws.data_ptr() if ws is not None else None, entry["workspace"], arr, len(ptrs),
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr(), cache_lens.data_ptr(),
+            alibi_slopes.data_ptr() if alibi_slopes is not None else None,
+            torch.cuda.current_stream(dev).cuda_stream))
+    return out
+
+
 def paged_attention_prefill(q, k_cache, v_cache, block_tables, history_lens, cu_seqlens_q, alibi_slopes=None,
                             scale: float = 1.0, *, out=None):
     """Causal attention of packed new tokens q [total_q, num_heads, head_size] over each sequence's paged

@@ -87,3 +87,42 @@ def gather_head_sharded(out_local, world: int, group=None, staging=None, comm=No
 
         dist.all_gather_into_tensor(staging.view(-1), out_local.contiguous().view(-1), group=group)
     return staging.permute(1, 0, 2, 3).reshape(num_seqs, world * hpr, d)
+
+
+class PeerOutputs:
+    """Full outputs [num_seqs, heads, d] of every rank, allocated in symmetric memory so that each
+    rank can address all of them.  In the KV-head-sharded mode a rank then stores its head slice
+    straight into every rank's full output from inside the attention kernels
+    (infiniopPagedAttentionMultiOut) and the all-gather that would follow is replaced by one barrier.
+
+    The exchange itself is plain stores over NVLink to peer addresses; nothing here waits on a peer
+    except `barrier()`, which is torch's symmetric-memory barrier (it carries its own timeout)."""
+
+    def __init__(self, num_seqs: int, heads_total: int, d: int, dtype, device, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if heads_total % self.world != 0:
+            raise ValueError("heads must divide over the ranks")
+        self.heads_per_rank = heads_total // self.world
+        self.full = symm_mem.empty((num_seqs, heads_total, d), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.full, group)
+        self._slice_bytes = self.heads_per_rank * d * self.full.element_size()
+
+    def local_slice(self):
+        """This rank's heads inside its own full output: the `out` the attention descriptor is made for."""
+        h0 = self.rank * self.heads_per_rank
+        return self.full[:, h0:h0 + self.heads_per_rank]
+
+    def destinations(self):
+        """outs for paged_attention_multi_out: the local slice first, then the address of the same
+        slice inside every other rank's full output."""
+        base = list(self.handle.buffer_ptrs)
+        off = self.rank * self._slice_bytes
+        return [self.local_slice()] + [base[r] + off for r in range(self.world) if r != self.rank]
+
+    def barrier(self):
+        """Every rank's stores have landed everywhere once all ranks have passed this point in stream order."""
+        self.handle.barrier()

@@ -560,3 +560,74 @@ def test_wide_heads_long_batch_matches_generic_kernel(abi):
     b = run_case(abi, c, "generic")
     atol, rtol = ATTN_TOL[c.dtype]
     assert_close(a.float().cpu().numpy(), b.float().cpu().numpy(), atol, rtol, "wide vs generic")
+
+
+# ---- several destinations for the output rows (what the KV-head-sharded mode stores into its peers) -------
+
+@pytest.mark.parametrize("path", [None, "generic", "stream-3x4"])
+@pytest.mark.parametrize("dtype,heads,kvh,hd,value", [(torch.bfloat16, 8, 2, 128, 128), (torch.float16, 12, 1, 64, 64),
+                                                      (torch.bfloat16, 16, 1, 576, 512)])
+def test_multi_out_stores_every_destination(abi, path, dtype, heads, kvh, hd, value):
+    """Three destinations, each the same head slice of a wider buffer (as a rank's slice inside every
+    rank's full output): all equal the single-output result, nothing outside the slices is touched,
+    rows of empty sequences stay untouched everywhere.  Long and short sequences, so that both the
+    direct stores of the main kernels and the combine kernel's stores are exercised."""
+    import infinicore_b200 as ib
+
+    lens = [3000, 17, 0, 260, 1, 1500]
+    c = workloads.build_case("multi", dtype=dtype, seq_lens=lens, num_heads=heads, num_kv_heads=kvh, head_size=hd, value_size=value,
+                             block_size=16, seed=71, std=0.4).to("cuda")
+    single = run_case(abi, c, path)
+    wide = [torch.full((len(lens), 3 * heads, value), 9.0, dtype=dtype, device="cuda") for _ in range(3)]
+    outs = [w[:, heads:2 * heads] for w in wide]
+    if path is None:
+        # through the Python operator (tensors and a raw address mixed)
+        ib.paged_attention_multi_out([outs[0], outs[1], outs[2].data_ptr()], c.q, c.k_cache, c.v_cache, c.block_tables, c.seq_lens,
+                                     None, c.scale)
+    else:
+        # through the C ABI with a descriptor created under this path's environment
+        import ctypes
+
+        from infinicore_b200.libinfiniop import LIBINFINIOP, check_error
+
+        op = abi.AttentionOp(outs[0], c.q, c.k_cache, c.v_cache, c.block_tables, c.seq_lens, None, c.scale, path)
+        check_error(op.status)
+        try:
+            arr = (ctypes.c_void_p * 3)(*[o.data_ptr() for o in outs])
+            check_error(LIBINFINIOP.infiniopPagedAttentionMultiOut(
+                op.desc, op.workspace.data(), op.workspace_size, arr, 3, c.q.data_ptr(), c.k_cache.data_ptr(), c.v_cache.data_ptr(),
+                c.block_tables.data_ptr(), c.seq_lens.data_ptr(), None, None))
+            torch.cuda.synchronize()
+        finally:
+            op.destroy()
+    torch.cuda.synchronize()
+    live = [i for i, n in enumerate(lens) if n > 0]
+    for w, o in zip(wide, outs):
+        assert torch.equal(o[live], single[live])
+        assert bool((o[2] == 9.0).all())                                       # the empty sequence's row
+        assert bool((w[:, :heads] == 9.0).all()) and bool((w[:, 2 * heads:] == 9.0).all())  # outside the slice
+    check(c, outs[0][live].contiguous(), oracle_out(c.to("cpu"))[live])
+
+
+def test_multi_out_argument_checks(abi):
+    import ctypes
+
+    from infinicore_b200.libinfiniop import LIBINFINIOP
+
+    c = workloads.build_case("multi_bad", dtype=torch.float16, seq_lens=[5, 6], num_heads=4, num_kv_heads=2, head_size=64, block_size=16,
+                             seed=72).to("cuda")
+    out = torch.zeros_like(c.q)
+    op = abi.AttentionOp(out, c.q, c.k_cache, c.v_cache, c.block_tables, c.seq_lens, None, c.scale)
+    try:
+        args = (c.q.data_ptr(), c.k_cache.data_ptr(), c.v_cache.data_ptr(), c.block_tables.data_ptr(), c.seq_lens.data_ptr(), None, None)
+        one = (ctypes.c_void_p * 1)(out.data_ptr())
+        nine = (ctypes.c_void_p * 9)(*([out.data_ptr()] * 9))
+        hole = (ctypes.c_void_p * 2)(out.data_ptr(), None)
+        assert LIBINFINIOP.infiniopPagedAttentionMultiOut(op.desc, op.workspace.data(), op.workspace_size, None, 1, *args) == 4
+        assert LIBINFINIOP.infiniopPagedAttentionMultiOut(op.desc, op.workspace.data(), op.workspace_size, one, 0, *args) == 3
+        assert LIBINFINIOP.infiniopPagedAttentionMultiOut(op.desc, op.workspace.data(), op.workspace_size, nine, 9, *args) == 3
+        assert LIBINFINIOP.infiniopPagedAttentionMultiOut(op.desc, op.workspace.data(), op.workspace_size, hole, 2, *args) == 4
+        assert LIBINFINIOP.infiniopPagedAttentionMultiOut(op.desc, op.workspace.data(), op.workspace_size, one, 1, *args) == 0
+        torch.cuda.synchronize()
+    finally:
+        op.destroy()
