@@ -304,6 +304,60 @@ class AbiStep:
                                                     c.k_cache.data_ptr(), c.v_cache.data_ptr(), c.new_k.data_ptr(), c.new_v.data_ptr(),
                                                     c.block_tables.data_ptr(), c.seq_lens.data_ptr(), None, stream))
 
+    def make_rope(self):
+        """Descriptors for a decode layer WITH its rotary embedding: the four calls a caller of the reference
+        issues (rope on q, rope on the new K, caching, attention) and the one call that does all of it."""
+        import torch
+
+        from infinicore_b200.libinfiniop import InfiniDeviceEnum, TestTensor, infiniopOperatorDescriptor_t, to_infini_dtype
+
+        c = self.case
+        dev = c.q.device
+        self.pos = (c.seq_lens.to(torch.int64) - 1).clamp(min=0)
+        table_len, dhead = int(self.pos.max().item()) + 1, c.q.shape[-1]
+        freqs = 1.0 / (1e4 ** (torch.arange(0, dhead, 2, device=dev).float() / dhead))
+        angles = torch.outer(torch.arange(table_len, device=dev).float(), freqs)
+        self.sin, self.cos = torch.sin(angles).to(c.dtype), torch.cos(angles).to(c.dtype)
+        self.q_rot, self.k_rot = torch.empty_like(c.q), torch.empty_like(c.new_k)
+
+        def tt(t):
+            return TestTensor.from_torch(t, to_infini_dtype(t.dtype), InfiniDeviceEnum.NVIDIA)
+
+        made = []
+        self.rope_q, self.rope_k, self.fused_rope = (infiniopOperatorDescriptor_t() for _ in range(3))
+        for desc, y, x in ((self.rope_q, self.q_rot, c.q), (self.rope_k, self.k_rot, c.new_k)):
+            t = [tt(y), tt(x), tt(self.pos), tt(self.sin), tt(self.cos)]
+            self.check(self.lib.infiniopCreateRoPEDescriptor(self.handle, ctypes.byref(desc), *[d.descriptor for d in t], 1))
+            made += t
+        f = [tt(self.out), tt(c.q), tt(c.k_cache), tt(c.v_cache), tt(c.new_k), tt(c.new_v), tt(c.block_tables), tt(c.seq_lens)]
+        r = [tt(self.pos), tt(self.sin), tt(self.cos)]
+        self.check(self.lib.infiniopCreatePagedDecodeStepRoPEDescriptor(
+            self.handle, ctypes.byref(self.fused_rope), *[d.descriptor for d in f], None, *[d.descriptor for d in r], 1, c.scale))
+        size = ctypes.c_size_t(0)
+        self.check(self.lib.infiniopGetPagedDecodeStepWorkspaceSize(self.fused_rope, ctypes.byref(size)))
+        self.rope_ws_size = size.value
+        self.rope_ws = torch.empty(max(size.value, 1), dtype=torch.uint8, device=dev)
+        for d in made + f + r:
+            d.destroy_desc()
+
+    def rope_four_calls(self, stream):
+        c = self.case
+        for desc, y, x in ((self.rope_q, self.q_rot, c.q), (self.rope_k, self.k_rot, c.new_k)):
+            self.check(self.lib.infiniopRoPE(desc, None, 0, y.data_ptr(), x.data_ptr(), self.pos.data_ptr(), self.sin.data_ptr(),
+                                             self.cos.data_ptr(), stream))
+        self.check(self.lib.infiniopPagedCaching(self.cache, None, 0, c.k_cache.data_ptr(), c.v_cache.data_ptr(),
+                                                 self.k_rot.data_ptr(), c.new_v.data_ptr(), c.slot_mapping.data_ptr(), stream))
+        self.check(self.lib.infiniopPagedAttention(self.attn, self.ws.data_ptr(), self.ws_size, self.out.data_ptr(), self.q_rot.data_ptr(),
+                                                   c.k_cache.data_ptr(), c.v_cache.data_ptr(), c.block_tables.data_ptr(),
+                                                   c.seq_lens.data_ptr(), None, stream))
+
+    def rope_one_call(self, stream):
+        c = self.case
+        self.check(self.lib.infiniopPagedDecodeStepRoPE(
+            self.fused_rope, self.rope_ws.data_ptr(), self.rope_ws_size, self.out.data_ptr(), c.q.data_ptr(), c.k_cache.data_ptr(),
+            c.v_cache.data_ptr(), c.new_k.data_ptr(), c.new_v.data_ptr(), c.block_tables.data_ptr(), c.seq_lens.data_ptr(), None,
+            self.pos.data_ptr(), self.sin.data_ptr(), self.cos.data_ptr(), stream))
+
     def attention_multi_out(self, stream, destinations):
         """Attention with the output rows stored to every destination (tensor or raw address); the first is self.out."""
         c = self.case
@@ -449,6 +503,15 @@ def gpu_arm(args):
         for _ in range(3):
             step.fused_step(sptr)
         fused_ms = max_over_ranks(timed(lambda: step.fused_step(sptr), K) / K)
+    # the same layer with its rotary embedding (q and the new K row rotated first): four calls against one
+    rope_ms = None
+    if flush is None and not head_mode and case.q.shape[-1] == case.k_cache.shape[-1] and case.q.shape[-1] % 2 == 0:
+        step.make_rope()
+        for fn in (step.rope_four_calls, step.rope_one_call):
+            for _ in range(3):
+                fn(sptr)
+        rope_ms = (max_over_ranks(timed(lambda: step.rope_four_calls(sptr), K) / K),
+                   max_over_ranks(timed(lambda: step.rope_one_call(sptr), K) / K))
 
     kv_bytes_all = sum_over_ranks(float(case.kv_bytes))
     seqs_all = sum_over_ranks(float(case.num_seqs))
@@ -533,6 +596,10 @@ def gpu_arm(args):
                            {"ms_per_step": fused_ms, "value": kv_bytes_all / (fused_ms * 1e-3) / 1e9, "unit": "GB/s",
                             "note": "the same step through infiniopPagedDecodeStep (cache append inside the attention kernel, "
                                     "one launch less); not the reference's call sequence, so not the headline"}),
+            "rope_step": (None if rope_ms is None else
+                          {"four_calls_ms": rope_ms[0], "one_call_ms": rope_ms[1],
+                           "note": "the decode layer with its rotary embedding: infiniopRoPE(q), infiniopRoPE(new K), infiniopPagedCaching, "
+                                   "infiniopPagedAttention against infiniopPagedDecodeStepRoPE"}),
             "gpu_launches": step.launches_per_step * K,  # inside the timed region that `value` comes from
             "clocks": clocks,
         }

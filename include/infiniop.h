@@ -1,5 +1,5 @@
 /* Umbrella header for the operator library (the subset this library implements:
- * handle, tensor/operator descriptors, paged_attention, paged_attention_prefill, paged_caching, paged_decode_step). */
+ * handle, tensor/operator descriptors, paged_attention, paged_attention_prefill, paged_caching, paged_decode_step, rope). */
 #ifndef __INFINIOP_API_H__
 #define __INFINIOP_API_H__
 
@@ -9,6 +9,7 @@
 #include "infiniop/ops/paged_attention_prefill.h"
 #include "infiniop/ops/paged_caching.h"
 #include "infiniop/ops/paged_decode_step.h"
+#include "infiniop/ops/rope.h"
 #include "infiniop/tensor_descriptor.h"
 
 #endif

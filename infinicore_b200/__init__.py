@@ -17,6 +17,8 @@ _LAZY = {
     "paged_caching": "ops",
     "paged_attention_prefill": "ops",
     "paged_decode_step": "ops",
+    "rope": "ops",
+    "RopeAlgo": "ops",
     "DecodeStep": "decode_step",
 }
 

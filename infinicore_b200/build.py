@@ -46,6 +46,7 @@ OP_SOURCES = [
     "paged_attention/decode_stream.cu",
     "paged_attention/static_workspace.cu",
     "paged_attention/decode_step.cu",
+    "rope/rope.cu",
     "paged_attention_prefill/operator.cu",
     "paged_attention_prefill/prefill_generic.cu",
     "paged_attention_prefill/prefill_tiles.cu",

@@ -90,6 +90,7 @@ enum class OpKind : int {
     PagedCaching = 2,
     PagedAttentionPrefill = 3,
     PagedDecodeStep = 4,
+    RoPE = 5,
 };
 
 struct OpDescriptorBase {

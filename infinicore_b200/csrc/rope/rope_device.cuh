@@ -1,0 +1,145 @@
+// Device-side pieces of the rotary embedding, shared by infiniopRoPE and by the decode step that
+// rotates q and the new K row on its way into the paged cache.
+//
+// Arithmetic follows reference src/infiniop/ops/rope/cpu/rope_cpu.cc:78-101: 16-bit operands are
+// widened to fp32, y0 = x0 cos - x1 sin and y1 = x0 sin + x1 cos with every product and sum rounded
+// on its own (the _rn intrinsics keep the compiler from fusing them), one rounding to nearest even
+// back to the storage type.
+#ifndef INFINIOP_B200_ROPE_DEVICE_CUH
+#define INFINIOP_B200_ROPE_DEVICE_CUH
+
+#include "infiniop.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstdint>
+
+namespace b200::rope {
+
+// A position id of any integer type as an unsigned 64-bit value: negative ids become huge and fail
+// the `< table_len` test like any other id outside the tables.
+__device__ __forceinline__ unsigned long long loadPosition(const void *base, long long i, int dtype) {
+    switch (dtype) {
+    case INFINI_DTYPE_I8:
+        return static_cast<unsigned long long>(static_cast<long long>(static_cast<const signed char *>(base)[i]));
+    case INFINI_DTYPE_U8:
+        return static_cast<const unsigned char *>(base)[i];
+    case INFINI_DTYPE_I16:
+        return static_cast<unsigned long long>(static_cast<long long>(static_cast<const short *>(base)[i]));
+    case INFINI_DTYPE_U16:
+        return static_cast<const unsigned short *>(base)[i];
+    case INFINI_DTYPE_I32:
+        return static_cast<unsigned long long>(static_cast<long long>(static_cast<const int *>(base)[i]));
+    case INFINI_DTYPE_U32:
+        return static_cast<const unsigned int *>(base)[i];
+    case INFINI_DTYPE_I64:
+        return static_cast<unsigned long long>(static_cast<const long long *>(base)[i]);
+    default: // INFINI_DTYPE_U64
+        return static_cast<const unsigned long long *>(base)[i];
+    }
+}
+
+__host__ __device__ inline bool isIntegerDtype(int dtype) {
+    return dtype == INFINI_DTYPE_I8 || dtype == INFINI_DTYPE_U8 || dtype == INFINI_DTYPE_I16 || dtype == INFINI_DTYPE_U16
+        || dtype == INFINI_DTYPE_I32 || dtype == INFINI_DTYPE_U32 || dtype == INFINI_DTYPE_I64 || dtype == INFINI_DTYPE_U64;
+}
+
+__device__ __forceinline__ float widen(__half v) { return __half2float(v); }
+__device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float widen(float v) { return v; }
+__device__ __forceinline__ double widen(double v) { return v; }
+
+__device__ __forceinline__ void narrow(__half &dst, float v) { dst = __float2half_rn(v); }
+__device__ __forceinline__ void narrow(__nv_bfloat16 &dst, float v) { dst = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void narrow(float &dst, float v) { dst = v; }
+__device__ __forceinline__ void narrow(double &dst, double v) { dst = v; }
+
+__device__ __forceinline__ void rotatePair(float a, float b, float s, float c, float &ya, float &yb) {
+    ya = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+    yb = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
+}
+__device__ __forceinline__ void rotatePair(double a, double b, double s, double c, double &ya, double &yb) {
+    ya = __dsub_rn(__dmul_rn(a, c), __dmul_rn(b, s));
+    yb = __dadd_rn(__dmul_rn(a, s), __dmul_rn(b, c));
+}
+
+// Eight 16-bit values moved as one 128-bit word.
+template <typename T>
+union Pack8 {
+    uint4 bits;
+    T v[8];
+};
+template <typename T>
+union Pack4 {
+    uint2 bits;
+    T v[4];
+};
+
+// One warp rotates one row of `2 * table_dim` elements: y and x point at the row, sin_row / cos_row at
+// the table rows of its position (null: the position is outside the tables, the row is copied).
+// `vec` says every address involved is a multiple of 16 bytes and table_dim a multiple of 8 (16-bit
+// types only).  A lane reads both elements of each of its pairs before it writes either, and no pair
+// is shared between lanes, so y == x (in place) is fine.
+template <typename T, bool kGptJ>
+__device__ __forceinline__ void rotateRow(T *y, const T *x, const T *sin_row, const T *cos_row, int table_dim, int lane, bool vec) {
+    if (sin_row == nullptr) {
+        if (y != x) {
+            for (int i = lane; i < 2 * table_dim; i += 32) {
+                y[i] = x[i];
+            }
+        }
+        return;
+    }
+    if constexpr (sizeof(T) == 2) {
+        if (vec) {
+            if constexpr (kGptJ) {
+                for (int i = lane * 4; i < table_dim; i += 128) {
+                    Pack8<T> in, out;
+                    Pack4<T> s, c;
+                    in.bits = *reinterpret_cast<const uint4 *>(x + 2 * i);
+                    s.bits = *reinterpret_cast<const uint2 *>(sin_row + i);
+                    c.bits = *reinterpret_cast<const uint2 *>(cos_row + i);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float ya, yb;
+                        rotatePair(widen(in.v[2 * j]), widen(in.v[2 * j + 1]), widen(s.v[j]), widen(c.v[j]), ya, yb);
+                        narrow(out.v[2 * j], ya);
+                        narrow(out.v[2 * j + 1], yb);
+                    }
+                    *reinterpret_cast<uint4 *>(y + 2 * i) = out.bits;
+                }
+            } else {
+                for (int i = lane * 8; i < table_dim; i += 256) {
+                    Pack8<T> lo, hi, s, c, out_lo, out_hi;
+                    lo.bits = *reinterpret_cast<const uint4 *>(x + i);
+                    hi.bits = *reinterpret_cast<const uint4 *>(x + table_dim + i);
+                    s.bits = *reinterpret_cast<const uint4 *>(sin_row + i);
+                    c.bits = *reinterpret_cast<const uint4 *>(cos_row + i);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float ya, yb;
+                        rotatePair(widen(lo.v[j]), widen(hi.v[j]), widen(s.v[j]), widen(c.v[j]), ya, yb);
+                        narrow(out_lo.v[j], ya);
+                        narrow(out_hi.v[j], yb);
+                    }
+                    *reinterpret_cast<uint4 *>(y + i) = out_lo.bits;
+                    *reinterpret_cast<uint4 *>(y + table_dim + i) = out_hi.bits;
+                }
+            }
+            return;
+        }
+    }
+    for (int i = lane; i < table_dim; i += 32) {
+        const int a = kGptJ ? 2 * i : i;
+        const int b = kGptJ ? 2 * i + 1 : i + table_dim;
+        decltype(widen(x[0])) ya, yb;
+        rotatePair(widen(x[a]), widen(x[b]), widen(sin_row[i]), widen(cos_row[i]), ya, yb);
+        narrow(y[a], ya);
+        narrow(y[b], yb);
+    }
+}
+
+} // namespace b200::rope
+
+#endif

@@ -90,6 +90,8 @@ INFINIOP_SYMBOLS = [
     "infiniopPagedCaching", "infiniopDestroyPagedCachingDescriptor",
     "infiniopCreatePagedDecodeStepDescriptor", "infiniopGetPagedDecodeStepWorkspaceSize",
     "infiniopPagedDecodeStep", "infiniopDestroyPagedDecodeStepDescriptor",
+    "infiniopCreatePagedDecodeStepRoPEDescriptor", "infiniopPagedDecodeStepRoPE",
+    "infiniopCreateRoPEDescriptor", "infiniopGetRoPEWorkspaceSize", "infiniopRoPE", "infiniopDestroyRoPEDescriptor",
 ]
 INFINIRT_SYMBOLS = [
     "infinirtInit", "infinirtGetAllDeviceCount", "infinirtGetDeviceCount", "infinirtSetDevice",
@@ -219,6 +221,39 @@ def _bind(lib: InfiniLib) -> None:
         ]
         op.infiniopDestroyPagedDecodeStepDescriptor.restype = c_int32
         op.infiniopDestroyPagedDecodeStepDescriptor.argtypes = [infiniopOperatorDescriptor_t]
+
+    # The same with the rotary embedding of q and of the new K row in front.
+    if hasattr(op, "infiniopCreatePagedDecodeStepRoPEDescriptor"):
+        op.infiniopCreatePagedDecodeStepRoPEDescriptor.restype = c_int32
+        op.infiniopCreatePagedDecodeStepRoPEDescriptor.argtypes = [
+            infiniopHandle_t, POINTER(infiniopOperatorDescriptor_t),
+            infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t,
+            infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t,
+            c_void_p, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, c_int32, c_float,
+        ]
+        op.infiniopPagedDecodeStepRoPE.restype = c_int32
+        op.infiniopPagedDecodeStepRoPE.argtypes = [
+            infiniopOperatorDescriptor_t, c_void_p, c_size_t,
+            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+            c_void_p, c_void_p, c_void_p, c_void_p,
+        ]
+
+    # the signatures of reference include/infiniop/ops/rope.h:16-39
+    if hasattr(op, "infiniopCreateRoPEDescriptor"):
+        op.infiniopCreateRoPEDescriptor.restype = c_int32
+        op.infiniopCreateRoPEDescriptor.argtypes = [
+            infiniopHandle_t, POINTER(infiniopOperatorDescriptor_t),
+            infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t,
+            infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, c_int32,
+        ]
+        op.infiniopGetRoPEWorkspaceSize.restype = c_int32
+        op.infiniopGetRoPEWorkspaceSize.argtypes = [infiniopOperatorDescriptor_t, POINTER(c_size_t)]
+        op.infiniopRoPE.restype = c_int32
+        op.infiniopRoPE.argtypes = [
+            infiniopOperatorDescriptor_t, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        ]
+        op.infiniopDestroyRoPEDescriptor.restype = c_int32
+        op.infiniopDestroyRoPEDescriptor.argtypes = [infiniopOperatorDescriptor_t]
 
     # reference test/infiniop/libinfiniop/op_register.py:2231-2269
     op.infiniopCreatePagedCachingDescriptor.restype = c_int32

@@ -208,11 +208,53 @@ def paged_attention_prefill(q, k_cache, v_cache, block_tables, history_lens, cu_
     return out
 
 
-def paged_decode_step(q, k_cache, v_cache, new_k, new_v, block_tables, cache_lens, alibi_slopes=None, scale: float = 1.0, *, out=None):
+class RopeAlgo:
+    """Pairing of the rotary embedding (reference python/infinicore/nn/functional/rope.py:5-9)."""
+
+    GPT_J = 0
+    GPT_NEOX = 1
+
+
+def rope(x, pos_ids, sin_table, cos_table, algo: int = RopeAlgo.GPT_NEOX, *, out=None):
+    """Rotary position embedding (same signature as the reference's python/infinicore/nn/functional/rope.py:12-45):
+    x [seqlen, nhead, dhead] or [batch, seqlen, nhead, dhead], pos_ids [seqlen] or [batch, seqlen] (any integer
+    type), tables [table_len, dhead / 2] in x's dtype.  Returns `out` (a new tensor when not given; may be x)."""
+    dev = _require_cuda(x, pos_ids, sin_table, cos_table, out)
+    if out is None:
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    st = _state(dev)
+    key = ("rope", _meta(out), _meta(x), _meta(pos_ids), _meta(sin_table), _meta(cos_table), int(algo))
+
+    def make():
+        tensors = [_desc(out), _desc(x), _desc(pos_ids), _desc(sin_table), _desc(cos_table)]
+        desc = infiniopOperatorDescriptor_t()
+        check_error(LIBINFINIOP.infiniopCreateRoPEDescriptor(
+            st["handle"], ctypes.byref(desc), *[t.descriptor for t in tensors], int(algo)))
+        for t in tensors:
+            t.destroy_desc()
+        return {"desc": desc, "workspace": 0, "destroy": LIBINFINIOP.infiniopDestroyRoPEDescriptor}
+
+    entry = _lookup(st, key, make)
+    with torch.cuda.device(dev):
+        check_error(LIBINFINIOP.infiniopRoPE(
+            entry["desc"], None, 0, out.data_ptr(), x.data_ptr(), pos_ids.data_ptr(), sin_table.data_ptr(),
+            cos_table.data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
+    return out
+
+
+def paged_decode_step(q, k_cache, v_cache, new_k, new_v, block_tables, cache_lens, alibi_slopes=None, scale: float = 1.0, *, out=None,
+                      pos_ids=None, sin_table=None, cos_table=None, rope_algo: int = RopeAlgo.GPT_NEOX):
     """One decode layer's cache update and attention behind one call (no reference counterpart: the
     reference's callers issue paged_caching and paged_attention).  new_k / new_v [num_seqs, num_kv_heads,
     head_size] are written to position cache_lens[i] - 1 of sequence i (the slot its block table names),
-    then q attends over the cache_lens[i] positions.  Returns `out`; the caches are updated in place."""
+    then q attends over the cache_lens[i] positions.  Returns `out`; the caches are updated in place.
+
+    With pos_ids [num_seqs], sin_table and cos_table [table_len, head_size / 2] the call also does the work
+    of rope(q) and rope(new_k) first: the cache receives the rotated K row and the attention uses the rotated
+    q (q and new_k themselves are left as they are)."""
+    if pos_ids is not None:
+        return _paged_decode_step_rope(q, k_cache, v_cache, new_k, new_v, block_tables, cache_lens, alibi_slopes, scale, out,
+                                       pos_ids, sin_table, cos_table, rope_algo)
     dev = _require_cuda(q, k_cache, v_cache, new_k, new_v, block_tables, cache_lens, alibi_slopes, out)
     if out is None:
         out = torch.empty((*q.shape[:-1], v_cache.shape[3]), dtype=q.dtype, device=q.device)
@@ -241,6 +283,43 @@ def paged_decode_step(q, k_cache, v_cache, new_k, new_v, block_tables, cache_len
             out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), new_k.data_ptr(), new_v.data_ptr(),
             block_tables.data_ptr(), cache_lens.data_ptr(),
             alibi_slopes.data_ptr() if alibi_slopes is not None else None,
+            torch.cuda.current_stream(dev).cuda_stream))
+    return out
+
+
+def _paged_decode_step_rope(q, k_cache, v_cache, new_k, new_v, block_tables, cache_lens, alibi_slopes, scale, out,
+                            pos_ids, sin_table, cos_table, rope_algo):
+    dev = _require_cuda(q, k_cache, v_cache, new_k, new_v, block_tables, cache_lens, alibi_slopes, out, pos_ids, sin_table, cos_table)
+    if out is None:
+        out = torch.empty((*q.shape[:-1], v_cache.shape[3]), dtype=q.dtype, device=q.device)
+    st = _state(dev)
+    key = ("paged_decode_step_rope", _meta(out), _meta(q), _meta(k_cache), _meta(v_cache), _meta(new_k), _meta(new_v),
+           _meta(block_tables), _meta(cache_lens), _meta(alibi_slopes), _meta(pos_ids), _meta(sin_table), _meta(cos_table),
+           int(rope_algo), float(scale))
+
+    def make():
+        tensors = [_desc(out), _desc(q), _desc(k_cache), _desc(v_cache), _desc(new_k), _desc(new_v), _desc(block_tables), _desc(cache_lens)]
+        rope_tensors = [_desc(pos_ids), _desc(sin_table), _desc(cos_table)]
+        alibi = _desc(alibi_slopes) if alibi_slopes is not None else None
+        desc = infiniopOperatorDescriptor_t()
+        check_error(LIBINFINIOP.infiniopCreatePagedDecodeStepRoPEDescriptor(
+            st["handle"], ctypes.byref(desc), *[t.descriptor for t in tensors],
+            alibi.descriptor if alibi is not None else None, *[t.descriptor for t in rope_tensors], int(rope_algo), scale))
+        size = ctypes.c_size_t(0)
+        check_error(LIBINFINIOP.infiniopGetPagedDecodeStepWorkspaceSize(desc, ctypes.byref(size)))
+        for t in tensors + rope_tensors + ([alibi] if alibi is not None else []):
+            t.destroy_desc()
+        return {"desc": desc, "workspace": size.value, "destroy": LIBINFINIOP.infiniopDestroyPagedDecodeStepDescriptor}
+
+    entry = _lookup(st, key, make)
+    ws = _workspace(st, entry["workspace"], dev)
+    with torch.cuda.device(dev):
+        check_error(LIBINFINIOP.infiniopPagedDecodeStepRoPE(
+            entry["desc"], ws.data_ptr() if ws is not None else None, entry["workspace"],
+            out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), new_k.data_ptr(), new_v.data_ptr(),
+            block_tables.data_ptr(), cache_lens.data_ptr(),
+            alibi_slopes.data_ptr() if alibi_slopes is not None else None,
+            pos_ids.data_ptr(), sin_table.data_ptr(), cos_table.data_ptr(),
             torch.cuda.current_stream(dev).cuda_stream))
     return out
 

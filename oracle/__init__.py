@@ -2,7 +2,8 @@
 
 Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline leg may import this package.
 It wraps oracle/paged_oracle.c (a restatement of the reference's torch checkers, see the
-header of that file) for numpy arrays holding raw 16-bit patterns.
+header of that file) and oracle/rope_oracle.c (the reference's CPU rotary embedding) for numpy
+arrays holding raw 16-bit patterns.
 """
 from __future__ import annotations
 
@@ -13,7 +14,7 @@ import numpy as np
 
 from .build import build as _build
 
-F16, F32, BF16 = 12, 13, 19
+F16, F32, F64, BF16 = 12, 13, 14, 19
 
 _lib = None
 
@@ -65,6 +66,15 @@ def lib() -> ctypes.CDLL:
         _lib.oracle_bf16_to_float.restype = c_float
         _lib.oracle_bf16_to_float.argtypes = [c_uint16]
         _lib.oracle_num_threads.restype = c_int
+        _lib.oracle_rope.restype = c_int
+        _lib.oracle_rope.argtypes = [
+            c_int, c_int,
+            c_void_p, c_ssize_t, c_ssize_t, c_ssize_t,
+            c_void_p, c_ssize_t, c_ssize_t, c_ssize_t,
+            c_void_p, c_ssize_t,
+            c_void_p, c_void_p,
+            c_int64, c_int64, c_int64, c_int64, c_int64,
+        ]
     return _lib
 
 
@@ -168,3 +178,37 @@ def paged_caching(k_cache, v_cache, k, v, slot_mapping) -> None:
     )
     if rc != 0:
         raise ValueError(f"oracle_paged_caching rejected its input (code {rc})")
+
+
+def rope(x, pos_ids, sin_table, cos_table, dtype, gpt_j, out=None) -> np.ndarray:
+    """x: [seqlen, nhead, dhead] or [batch, seqlen, nhead, dhead]; uint16 bit patterns for F16 / BF16,
+    float32 / float64 otherwise (any strides, last dim dense).  pos_ids: [seqlen] or [batch, seqlen].
+    Tables: [table_len, dhead / 2] in the same representation.  Returns `out` (a new dense array when
+    not given; `out` may be `x` itself)."""
+    want = {F16: np.uint16, BF16: np.uint16, F32: np.float32, F64: np.float64}[int(dtype)]
+    assert x.dtype == want and sin_table.dtype == want and cos_table.dtype == want
+    sin_table = np.ascontiguousarray(sin_table)
+    cos_table = np.ascontiguousarray(cos_table)
+    if out is None:
+        out = np.empty(x.shape, dtype=want)
+    assert out.shape == x.shape and out.dtype == want
+    x4 = x if x.ndim == 4 else x[None]
+    y4 = out if out.ndim == 4 else out[None]
+    batch, seqlen, nhead, dhead = x4.shape
+    table_len, table_dim = sin_table.shape
+    assert dhead == 2 * table_dim and cos_table.shape == sin_table.shape
+    pos = np.ascontiguousarray(pos_ids, dtype=np.int64)
+    assert pos.shape in ((seqlen,), (batch, seqlen))
+    xs, ys = _elem_strides(x4), _elem_strides(y4)
+    assert xs[3] == 1 and ys[3] == 1
+    rc = lib().oracle_rope(
+        int(dtype), 1 if gpt_j else 0,
+        y4.ctypes.data, ys[0], ys[1], ys[2],
+        x4.ctypes.data, xs[0], xs[1], xs[2],
+        pos.ctypes.data, seqlen if pos.ndim == 2 else 0,
+        sin_table.ctypes.data, cos_table.ctypes.data,
+        batch, seqlen, nhead, table_dim, table_len,
+    )
+    if rc != 0:
+        raise ValueError(f"oracle_rope rejected its input (code {rc})")
+    return out

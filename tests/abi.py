@@ -156,6 +156,76 @@ def paged_decode_step(q, k_cache, v_cache, new_k, new_v, block_tables, seq_lens,
     return out
 
 
+def rope_create(y, x, pos_ids, sin_table, cos_table, algo, pos_dtype=None):
+    """Creates a RoPE descriptor as reference test/infiniop/rope.py:170-186 does; returns (status, descriptor)."""
+    tensors = [_tt(y), _tt(x), _tt(pos_ids, pos_dtype), _tt(sin_table), _tt(cos_table)]
+    desc = infiniopOperatorDescriptor_t()
+    status = LIBINFINIOP.infiniopCreateRoPEDescriptor(handle(), ctypes.byref(desc), *[t.descriptor for t in tensors], int(algo))
+    for t in tensors:
+        t.destroy_desc()
+    return status, desc
+
+
+def rope(x, pos_ids, sin_table, cos_table, algo, y=None, pos_dtype=None):
+    """One infiniopRoPE call through the C ABI on the NULL stream; returns y (x itself for the in-place form)."""
+    if y is None:
+        y = torch.zeros_like(x)
+    status, desc = rope_create(y, x, pos_ids, sin_table, cos_table, algo, pos_dtype)
+    check_error(status)
+    try:
+        size = ctypes.c_size_t(1)
+        check_error(LIBINFINIOP.infiniopGetRoPEWorkspaceSize(desc, ctypes.byref(size)))
+        assert size.value == 0
+        check_error(LIBINFINIOP.infiniopRoPE(desc, None, 0, y.data_ptr(), x.data_ptr(), pos_ids.data_ptr(),
+                                             sin_table.data_ptr(), cos_table.data_ptr(), None))
+        torch.cuda.synchronize()
+    finally:
+        check_error(LIBINFINIOP.infiniopDestroyRoPEDescriptor(desc))
+    return y
+
+
+def paged_decode_step_rope(q, k_cache, v_cache, new_k, new_v, block_tables, seq_lens, scale, pos_ids, sin_table, cos_table, algo,
+                           alibi=None, path=None, out=None, index_dtype=None, pos_dtype=None):
+    """One rotate + append + decode call through the C ABI; returns `out` (synchronised); caches are updated in place."""
+    if out is None:
+        out = torch.zeros((*q.shape[:-1], v_cache.shape[3]), dtype=q.dtype, device=q.device)
+    tensors = [_tt(out), _tt(q), _tt(k_cache), _tt(v_cache), _tt(new_k), _tt(new_v), _tt(block_tables, index_dtype),
+               _tt(seq_lens, index_dtype)]
+    rope_tensors = [_tt(pos_ids, pos_dtype), _tt(sin_table), _tt(cos_table)]
+    al = _tt(alibi) if alibi is not None else None
+    desc = infiniopOperatorDescriptor_t()
+    with decode_path(path):
+        status = LIBINFINIOP.infiniopCreatePagedDecodeStepRoPEDescriptor(
+            handle(), ctypes.byref(desc), *[t.descriptor for t in tensors], al.descriptor if al is not None else None,
+            *[t.descriptor for t in rope_tensors], int(algo), scale)
+    for t in tensors + rope_tensors + ([al] if al is not None else []):
+        t.destroy_desc()
+    check_error(status)
+    try:
+        size = ctypes.c_size_t(0)
+        check_error(LIBINFINIOP.infiniopGetPagedDecodeStepWorkspaceSize(desc, ctypes.byref(size)))
+        workspace = TestWorkspace(size.value, InfiniDeviceEnum.NVIDIA)
+        # the plain entry point refuses a descriptor of the RoPE form
+        assert LIBINFINIOP.infiniopPagedDecodeStep(
+            desc, workspace.data(), size.value, out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            new_k.data_ptr(), new_v.data_ptr(), block_tables.data_ptr(), seq_lens.data_ptr(), None, None) == 3
+        check_error(LIBINFINIOP.infiniopPagedDecodeStepRoPE(
+            desc, workspace.data(), size.value, out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            new_k.data_ptr(), new_v.data_ptr(), block_tables.data_ptr(), seq_lens.data_ptr(),
+            alibi.data_ptr() if alibi is not None else None, pos_ids.data_ptr(), sin_table.data_ptr(), cos_table.data_ptr(), None))
+        torch.cuda.synchronize()
+        # the workspace ends with the rotated q and K rows; what precedes them (if anything) is the
+        # streaming kernel's, whose first int is its error flag
+        r256 = lambda n: (n + 255) // 256 * 256
+        rotated = r256(q.shape[0] * q.shape[1] * q.shape[2] * q.element_size()) + r256(new_k.numel() * new_k.element_size())
+        assert size.value >= rotated
+        if size.value > rotated:
+            assert int(workspace.tensor[:4].view(torch.int32).item()) == 0, "a worker's bounded wait ran out"
+    finally:
+        check_error(LIBINFINIOP.infiniopDestroyPagedDecodeStepDescriptor(desc))
+    return out
+
+
 def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, scale, alibi=None, path=None, out=None,
                     index_dtype=None):
     """Runs one decode call through the C ABI; returns `out` (synchronised)."""

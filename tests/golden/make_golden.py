@@ -2,12 +2,13 @@
 
 Run in a container that has the reference checkout (it is not needed to run the tests):
 
-    python tests/golden/make_golden.py /path/to/InfiniCore
+    python tests/golden/make_golden.py /path/to/InfiniCore [--only=attention|caching|prefill|rope]
 
 The two functions executed are imported unmodified from the reference tree:
   ref_single_query_cached_kv_attention   test/infiniop/paged_attention.py:47-88
   ref_paged_caching                      test/infiniop/paged_caching.py:25-55
   ref_paged_attention_multi_turn         test/infiniop/paged_attention_prefill.py:96-140
+  rotary_embedding, sin_cos_table        test/infiniop/rope.py:87-133 (run with its CPU device value, i.e. fp32 arithmetic)
 Those files import the reference's ctypes harness at module level (which would try to load the
 reference's compiled library); a stand-in `libinfiniop` module with empty attributes is put
 in sys.modules first so that only the pure-torch functions are used.
@@ -40,12 +41,12 @@ def load_reference(ref_root: Path):
 
     sys.modules["libinfiniop"] = _Anything("libinfiniop")
     mods = {}
-    for name in ("paged_attention", "paged_caching", "paged_attention_prefill"):
+    for name in ("paged_attention", "paged_caching", "paged_attention_prefill", "rope"):
         spec = importlib.util.spec_from_file_location(f"_ref_{name}", ref_root / "test" / "infiniop" / f"{name}.py")
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
         mods[name] = mod
-    return mods["paged_attention"], mods["paged_caching"], mods["paged_attention_prefill"]
+    return mods["paged_attention"], mods["paged_caching"], mods["paged_attention_prefill"], mods["rope"]
 
 
 def bits(t: torch.Tensor) -> np.ndarray:
@@ -167,13 +168,73 @@ def make_prefill(ref_prefill):
         print("wrote", name, tuple(out.shape))
 
 
+def rope_cases():
+    # (name, dtype, shape, x strides or None, algorithm 0 GPT-J / 1 GPT-NeoX, table_len, 2-D position ids)
+    # shapes and strides after the reference's own cases (test/infiniop/rope.py:27-38)
+    yield "rope_fp16_neox_3d", torch.float16, (10, 32, 64), None, 1, 64, False
+    yield "rope_bf16_gptj_3d", torch.bfloat16, (11, 33, 128), None, 0, 48, False
+    yield "rope_fp16_gptj_strided", torch.float16, (3, 32, 128), (8000, 200, 1), 0, 32, False
+    yield "rope_bf16_neox_4d", torch.bfloat16, (8, 10, 32, 64), None, 1, 40, True
+    yield "rope_bf16_neox_4d_permuted", torch.bfloat16, (8, 20, 4, 64), (20 * 4 * 64 * 2, 64, 20 * 64 * 2, 1), 1, 40, False
+    yield "rope_f32_neox_3d", torch.float32, (7, 5, 32), None, 1, 16, False
+    yield "rope_f32_gptj_3d", torch.float32, (4, 1, 32), (64, 64, 1), 0, 16, False
+
+
+def strided(shape, strides, dtype, g):
+    if strides is None:
+        return torch.randn(shape, generator=g).to(dtype)
+    extent = 1 + sum((n - 1) * s for n, s in zip(shape, strides))
+    return torch.randn(extent, generator=g).to(dtype).as_strided(shape, strides)
+
+
+def make_rope(ref_rope):
+    class _Algo:  # the checker compares against the module's own enum members
+        pass
+
+    for idx, (name, dtype, shape, strides, algo, table_len, pos_2d) in enumerate(rope_cases()):
+        g = torch.Generator()
+        g.manual_seed(300 + idx)
+        x = strided(shape, strides, dtype, g)
+        seqlen, dhead = shape[-3], shape[-1]
+        pos_shape = (shape[0], seqlen) if pos_2d else (seqlen,)
+        pos = torch.randint(0, table_len, pos_shape, generator=g, dtype=torch.int64)
+        # tables as the reference test builds them (theta 1e5 there; values are rounded to the tensor type)
+        freqs = 1.0 / (1e5 ** (torch.arange(0, dhead, 2)[: dhead // 2].float() / dhead))
+        angles = torch.outer(torch.arange(table_len).float(), freqs)
+        sin_table, cos_table = torch.sin(angles).to(dtype), torch.cos(angles).to(dtype)
+        ans = torch.zeros(shape, dtype=dtype)
+        # rows of the tables per token, shaped to broadcast over heads as the reference test passes them
+        sin_rows, cos_rows = sin_table[pos], cos_table[pos]
+        algo_member = ref_rope.Algorithm.GPT_J if algo == 0 else ref_rope.Algorithm.GPT_NEOX
+        if x.ndim == 3:
+            ref_rope.rotary_embedding(ans, x, sin_rows, cos_rows, 0, algo_member)
+        else:
+            for b in range(shape[0]):
+                rows = (sin_rows[b], cos_rows[b]) if pos_2d else (sin_rows, cos_rows)
+                ref_rope.rotary_embedding(ans[b], x[b], rows[0], rows[1], 0, algo_member)
+        np.savez_compressed(
+            HERE / f"{name}.npz",
+            dtype=np.int64(DTYPE_CODE[dtype]), algo=np.int64(algo),
+            x=bits(x.contiguous()), x_strides=np.array(strides if strides is not None else [], dtype=np.int64),
+            pos_ids=pos.numpy(), sin_table=bits(sin_table), cos_table=bits(cos_table), y=bits(ans),
+        )
+        print("wrote", name, shape)
+
+
 def main():
-    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
-    ref_attn, ref_cache, ref_prefill = load_reference(ref_root)
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    only = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--only=")]
+    ref_root = Path(args[0]) if args else Path("/root/reference")
+    ref_attn, ref_cache, ref_prefill, ref_rope = load_reference(ref_root)
     torch.set_num_threads(4)
-    make_attention(ref_attn)
-    make_caching(ref_cache)
-    make_prefill(ref_prefill)
+    if not only or "attention" in only:
+        make_attention(ref_attn)
+    if not only or "caching" in only:
+        make_caching(ref_cache)
+    if not only or "prefill" in only:
+        make_prefill(ref_prefill)
+    if not only or "rope" in only:
+        make_rope(ref_rope)
 
 
 if __name__ == "__main__":

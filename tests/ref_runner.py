@@ -1,5 +1,5 @@
-"""Runs one decode step (paged_caching, then paged_attention) through the C ABI of whichever
-libinfiniop the loader finds, in a process of its own.
+"""Runs one decode step (paged_caching, then paged_attention), one prefill call or one rotary
+embedding through the C ABI of whichever libinfiniop the loader finds, in a process of its own.
 
 Used with INFINI_ROOT=oracle/_ref (the reference's own CUDA sources compiled for sm_100a by
 oracle/build_ref.py) to obtain the REFERENCE KERNELS' results and timings on identical seeded
@@ -63,9 +63,55 @@ def run_prefill(spec, case, d, out_path):
     torch.save(result, out_path)
 
 
+def run_rope(spec, out_path):
+    """spec = {"op": "rope", "shape": [...], "dtype": "...", "algo": 0 | 1, "seed": n, "table_len": n, "iters": N}"""
+    import ctypes
+
+    import abi
+    from infinicore_b200.libinfiniop import LIBINFINIOP, check_error, library_paths
+
+    dtype = getattr(torch, spec["dtype"])
+    gen = torch.Generator().manual_seed(int(spec.get("seed", 0)))
+    shape = list(spec["shape"])
+    x = torch.randn(shape, generator=gen).to(dtype).cuda()
+    table_len, dhead = int(spec["table_len"]), shape[-1]
+    pos = torch.randint(0, table_len, (shape[-3],), generator=gen).cuda()
+    freqs = 1.0 / (1e4 ** (torch.arange(0, dhead, 2).float() / dhead))
+    angles = torch.outer(torch.arange(table_len).float(), freqs)
+    sin, cos = torch.sin(angles).to(dtype).cuda(), torch.cos(angles).to(dtype).cuda()
+    y = torch.zeros_like(x)
+    status, desc = abi.rope_create(y, x, pos, sin, cos, int(spec["algo"]))
+    check_error(status)
+
+    def call(stream=None):
+        check_error(LIBINFINIOP.infiniopRoPE(desc, None, 0, y.data_ptr(), x.data_ptr(), pos.data_ptr(), sin.data_ptr(), cos.data_ptr(), stream))
+
+    call()
+    torch.cuda.synchronize()
+    result = {"y": y.cpu(), "library": str(library_paths()[1])}
+    iters = int(spec.get("iters", 0))
+    if iters:
+        stream = torch.cuda.current_stream().cuda_stream
+        for _ in range(3):
+            call(stream)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            call(stream)
+        b.record()
+        torch.cuda.synchronize()
+        result["ms"] = a.elapsed_time(b) / iters
+        result["bytes"] = 2 * x.numel() * x.element_size()
+    check_error(LIBINFINIOP.infiniopDestroyRoPEDescriptor(desc))
+    torch.save(result, out_path)
+
+
 def main():
     spec = json.loads(sys.argv[1])
     out_path = sys.argv[2]
+    if spec.get("op") == "rope":
+        return run_rope(spec, out_path)
     from infinicore_b200 import workloads
     from infinicore_b200.libinfiniop import LIBINFINIOP, check_error, library_paths
 

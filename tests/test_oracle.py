@@ -136,3 +136,42 @@ def test_prefill_row_equals_decode_with_the_causal_length():
             dec = oracle.paged_attention(g["q"][row:row + 1], g["k_cache"], g["v_cache"], g["block_tables"][s:s + 1],
                                          np.array([lens[s] - n + t + 1]), float(g["scale"]), dt)
             assert np.array_equal(dec[0], full[row])
+
+
+# ---- rotary embedding -----------------------------------------------------------------------------------
+
+
+def _rope_inputs(g):
+    x = g["x"]
+    if g["x_strides"].size:  # rebuild the strided layout the fixture was generated with
+        strides = [int(s) for s in g["x_strides"]]
+        extent = 1 + sum((n - 1) * s for n, s in zip(x.shape, strides))
+        base = np.zeros(extent, dtype=x.dtype)
+        view = np.lib.stride_tricks.as_strided(base, x.shape, [s * x.itemsize for s in strides])
+        view[...] = x
+        x = view
+    return x
+
+
+@pytest.mark.parametrize("name", golden_names("rope_"))
+def test_rope_bit_exact_against_reference_checker(name):
+    g = load_golden(name)
+    x = _rope_inputs(g)
+    got = oracle.rope(x, g["pos_ids"], g["sin_table"], g["cos_table"], int(g["dtype"]), int(g["algo"]) == 0)
+    assert np.array_equal(got, g["y"])
+    # in place, as half of the reference's test cases run it
+    oracle.rope(x, g["pos_ids"], g["sin_table"], g["cos_table"], int(g["dtype"]), int(g["algo"]) == 0, out=x)
+    assert np.array_equal(np.ascontiguousarray(x), g["y"])
+
+
+def test_rope_is_a_rotation_and_positions_outside_the_tables_copy():
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((6, 3, 32))
+    ang = rng.uniform(0, 6.28, (10, 16))
+    pos = np.array([0, 9, 3, -1, 10, 5])
+    for gpt_j in (True, False):
+        y = oracle.rope(x, pos, np.sin(ang), np.cos(ang), oracle.F64, gpt_j)
+        assert np.allclose((y ** 2).sum(-1), (x ** 2).sum(-1), rtol=1e-12)      # pairs keep their norm
+        assert np.array_equal(y[3], x[3]) and np.array_equal(y[4], x[4])        # -1 and 10 are outside a table of 10 rows
+        back = oracle.rope(y, pos, -np.sin(ang), np.cos(ang), oracle.F64, gpt_j)  # the inverse rotation
+        assert np.allclose(back, x, atol=1e-12)

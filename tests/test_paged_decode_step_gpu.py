@@ -175,3 +175,137 @@ def test_python_operator_and_two_steps_in_a_row(abi):
         atol, rtol = ATTN_TOL[c.dtype]
         assert_close(got.float().cpu().numpy(), want, atol, rtol, f"step {step}")
         lens = lens + 1  # stays inside each sequence's last allocated page for these lengths
+
+
+# ---- the RoPE form: rotate q and the new K row, append, attend ---------------------------------------
+
+
+def rope_tables(table_len, dhead, dtype, theta=1e4):
+    freqs = 1.0 / (theta ** (torch.arange(0, dhead, 2)[: dhead // 2].float() / dhead))
+    angles = torch.outer(torch.arange(table_len).float(), freqs)
+    return torch.sin(angles).to(dtype), torch.cos(angles).to(dtype)
+
+
+def run_and_check_rope(abi, c, path, algo, alibi=None, pos_ids=None, table_len=None, q_view=None):
+    """Checks infiniopPagedDecodeStepRoPE against the oracle's rope -> caching -> attention (caches bit-exact,
+    output within the decode tolerance) and against the four separate calls of this library."""
+    d = c.to("cuda")
+    nan = torch.tensor(float("nan"), dtype=c.dtype, device="cuda")
+    for slot in c.slot_mapping.tolist():
+        if slot >= 0:
+            d.k_cache[slot // c.block_size, :, slot % c.block_size, :] = nan
+            d.v_cache[slot // c.block_size, :, slot % c.block_size, :] = nan
+    k0, v0 = d.k_cache.clone(), d.v_cache.clone()
+    # the position of the new token is its index in the sequence
+    pos = (c.seq_lens - 1).clamp(min=0) if pos_ids is None else pos_ids
+    table_len = int(pos.max()) + 1 if table_len is None else table_len
+    sin, cos = rope_tables(table_len, c.head_size, c.dtype)
+    q_dev = d.q if q_view is None else q_view(d.q)
+    q_before, nk_before = q_dev.clone(), d.new_k.clone()
+    out = torch.full((c.q.shape[0], c.num_heads, c.v_cache.shape[3]), 7.0, dtype=c.dtype, device="cuda")
+    got = abi.paged_decode_step_rope(q_dev, d.k_cache, d.v_cache, d.new_k, d.new_v, d.block_tables, d.seq_lens, d.scale,
+                                     pos.cuda(), sin.cuda(), cos.cuda(), algo,
+                                     alibi.cuda() if alibi is not None else None, path=path, out=out)
+    assert torch.equal(q_dev, q_before) and torch.equal(d.new_k, nk_before), "q / new_k must stay as they were"
+
+    dt = 12 if c.dtype == torch.float16 else 19
+    q_rot = oracle.rope(torch_to_bits(c.q), pos.numpy(), torch_to_bits(sin), torch_to_bits(cos), dt, algo == 0)
+    k_rot = oracle.rope(torch_to_bits(c.new_k), pos.numpy(), torch_to_bits(sin), torch_to_bits(cos), dt, algo == 0)
+    kb, vb = torch_to_bits(k0), torch_to_bits(v0)
+    oracle.paged_caching(kb, vb, k_rot, torch_to_bits(c.new_v), c.slot_mapping.numpy())
+    assert np.array_equal(torch_to_bits(d.k_cache), kb), "k_cache differs from the oracle's rotated scatter"
+    assert np.array_equal(torch_to_bits(d.v_cache), vb), "v_cache differs from the oracle's scatter"
+    want = oracle.paged_attention(q_rot, kb, vb, c.block_tables.numpy(), c.seq_lens.numpy(), c.scale, dt,
+                                  alibi.numpy() if alibi is not None else None)
+    live = (c.seq_lens > 0).numpy()
+    atol, rtol = ATTN_TOL[c.dtype]
+    assert_close(got.float().cpu().numpy()[live], want[live], atol, rtol, c.name)
+    assert bool((got[~torch.from_numpy(live)] == 7.0).all()), "rows of empty sequences must stay untouched"
+
+    # the four calls a decode layer of the reference issues
+    q2 = abi.rope(q_dev, pos.cuda(), sin.cuda(), cos.cuda(), algo)
+    nk2 = abi.rope(d.new_k, pos.cuda(), sin.cuda(), cos.cuda(), algo)
+    assert np.array_equal(torch_to_bits(q2), q_rot) and np.array_equal(torch_to_bits(nk2), k_rot)
+    abi.paged_caching(k0, v0, nk2, d.new_v, d.slot_mapping)
+    four = abi.paged_attention(q2, k0, v0, d.block_tables, d.seq_lens, d.scale, alibi.cuda() if alibi is not None else None, path=path)
+    assert torch.equal(k0, d.k_cache) and torch.equal(v0, d.v_cache)
+    assert_close(got.float().cpu().numpy()[live], four.float().cpu().numpy()[live], atol, rtol, c.name + " vs four calls")
+
+
+@pytest.mark.parametrize("algo", [0, 1])
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("dtype,heads,kvh,hd,bs", [(torch.bfloat16, 32, 8, 128, 16), (torch.float16, 8, 2, 64, 16),
+                                                   (torch.float16, 12, 1, 128, 32), (torch.bfloat16, 16, 2, 256, 16)])
+def test_rope_form_on_every_row_of_the_last_page(abi, path, algo, dtype, heads, kvh, hd, bs):
+    lens = list(range(1, 2 * bs + 2)) + [0, 5 * bs, 5 * bs + 1]
+    c = workloads.build_case("rope_lastpage", dtype=dtype, seq_lens=lens, num_heads=heads, num_kv_heads=kvh, head_size=hd,
+                             block_size=bs, seed=51, slack_blocks=3)
+    run_and_check_rope(abi, c, path, algo)
+
+
+@pytest.mark.parametrize("path", [None, "generic"])
+def test_rope_form_ragged_long_batch_with_alibi(abi, path):
+    lens = workloads.config3_lengths(seed=9, num_seqs=40, hi=5000)
+    c = workloads.build_case("rope_ragged", dtype=torch.bfloat16, seq_lens=lens, num_heads=16, num_kv_heads=4, head_size=128,
+                             block_size=16, seed=52, std=0.5)
+    alibi = -torch.linspace(0.01, 0.3, 16, dtype=torch.float32)
+    run_and_check_rope(abi, c, path, 1, alibi=alibi)
+
+
+def test_rope_form_positions_outside_the_tables_and_strided_q(abi):
+    """Position ids beyond the tables leave their rows unrotated; q as a view with padded rows (the rotated
+    copy the attention reads is dense whatever q's strides are)."""
+    c = workloads.build_case("rope_edge", dtype=torch.float16, seq_lens=[40, 3, 17, 64], num_heads=8, num_kv_heads=2, head_size=64,
+                             block_size=16, seed=53)
+    pos = torch.tensor([39, 100, -2, 5], dtype=torch.int64)
+
+    def padded(q):
+        base = torch.zeros((q.shape[0], q.shape[1], q.shape[2] + 8), dtype=q.dtype, device=q.device)
+        base[:, :, : q.shape[2]] = q
+        return base[:, :, : q.shape[2]]
+
+    run_and_check_rope(abi, c, None, 1, pos_ids=pos, table_len=64, q_view=padded)
+    run_and_check_rope(abi, c, "generic", 0, pos_ids=pos, table_len=64, q_view=padded)
+
+
+def test_rope_form_without_a_streaming_plan(abi):
+    """Block size 4: rotation kernel, append kernel, generic attention; the workspace holds only the rotated rows."""
+    c = workloads.build_case("rope_bs4", dtype=torch.bfloat16, seq_lens=[1, 4, 5, 23, 0, 64], num_heads=4, num_kv_heads=2, head_size=64,
+                             block_size=4, seed=54)
+    run_and_check_rope(abi, c, None, 1)
+
+
+def test_rope_form_python_operator(abi):
+    import infinicore_b200 as ib
+
+    c = workloads.build_case("rope_py", dtype=torch.bfloat16, seq_lens=[15, 14, 30, 200], num_heads=32, num_kv_heads=8, head_size=128,
+                             block_size=16, seed=55)
+    d = c.to("cuda")
+    pos = c.seq_lens - 1
+    sin, cos = rope_tables(256, 128, c.dtype)
+    k0, v0 = d.k_cache.clone(), d.v_cache.clone()
+    got = ib.paged_decode_step(d.q, d.k_cache, d.v_cache, d.new_k, d.new_v, d.block_tables, d.seq_lens, None, c.scale,
+                               pos_ids=pos.cuda(), sin_table=sin.cuda(), cos_table=cos.cuda(), rope_algo=ib.RopeAlgo.GPT_NEOX)
+    q2 = ib.rope(d.q, pos.cuda(), sin.cuda(), cos.cuda(), ib.RopeAlgo.GPT_NEOX)
+    nk2 = ib.rope(d.new_k, pos.cuda(), sin.cuda(), cos.cuda())
+    ib.paged_caching(k0, v0, nk2, d.new_v, d.slot_mapping)
+    want = ib.paged_attention(q2, k0, v0, d.block_tables, d.seq_lens, None, c.scale)
+    torch.cuda.synchronize()
+    assert torch.equal(k0, d.k_cache) and torch.equal(v0, d.v_cache)
+    atol, rtol = ATTN_TOL[c.dtype]
+    assert_close(got.float().cpu().numpy(), want.float().cpu().numpy(), atol, rtol, "python rope step")
+
+
+def test_rope_form_refuses_bad_tables(abi):
+    c = workloads.build_case("rope_bad", dtype=torch.float16, seq_lens=[8, 9], num_heads=4, num_kv_heads=2, head_size=64, block_size=16, seed=56)
+    d = c.to("cuda")
+    sin, cos = (t.cuda() for t in rope_tables(16, 64, c.dtype))
+    pos = torch.tensor([7, 8], device="cuda")
+    from infinicore_b200.libinfiniop import InfiniStatusError
+
+    for bad_pos, bad_sin, code in [(pos.float(), sin, 10), (pos[:1], sin, 11), (pos, sin[:, :16], 11), (pos, sin.to(torch.bfloat16), 10),
+                                   (pos, sin.t().contiguous().t(), 12)]:
+        with pytest.raises(InfiniStatusError) as err:
+            abi.paged_decode_step_rope(d.q, d.k_cache, d.v_cache, d.new_k, d.new_v, d.block_tables, d.seq_lens, d.scale,
+                                       bad_pos, bad_sin, bad_sin if bad_sin.shape != sin.shape or bad_sin.dtype != sin.dtype else cos, 1)
+        assert err.value.status == code

@@ -8,6 +8,7 @@ import subprocess
 import sys
 from pathlib import Path
 
+import numpy as np
 import pytest
 import torch
 
@@ -75,3 +76,36 @@ def test_prefill_same_results_as_the_reference_kernels(spec, tmp_path):
     assert "oracle/_ref" in ref["library"] and "oracle/_ref" not in mine["library"]
     atol, rtol = ATTN_TOL[ref["out"].dtype]
     assert_close(mine["out"].float().numpy(), ref["out"].float().numpy(), atol, rtol, "prefill vs reference kernels")
+
+
+# the reference test's tolerances for this operator (test/infiniop/rope.py:46-50); its CUDA kernel computes
+# in the tensor's own 16-bit type, this library in fp32 with one rounding
+ROPE_TOL = {torch.float16: (1e-3, 1e-2), torch.bfloat16: (5e-3, 5e-2), torch.float32: (1e-4, 1e-3)}
+ROPE_SPECS = [
+    {"op": "rope", "shape": [10, 32, 64], "dtype": "float16", "algo": 0, "seed": 61, "table_len": 64},
+    {"op": "rope", "shape": [11, 33, 128], "dtype": "bfloat16", "algo": 1, "seed": 62, "table_len": 64},
+    {"op": "rope", "shape": [8, 10, 32, 64], "dtype": "float32", "algo": 1, "seed": 63, "table_len": 32},
+    {"op": "rope", "shape": [4096, 32, 128], "dtype": "bfloat16", "algo": 1, "seed": 64, "table_len": 4096, "iters": 20},
+]
+
+
+@pytest.mark.skipif(not (REF_ROOT / "lib" / "libinfiniop.so").is_file(), reason="oracle/_ref not built")
+@pytest.mark.parametrize("spec", ROPE_SPECS, ids=lambda s: "x".join(map(str, s["shape"])) + s["dtype"])
+def test_rope_same_results_as_the_reference_kernel(spec, tmp_path):
+    ref = run(spec, tmp_path, reference=True)
+    mine = run(spec, tmp_path, reference=False)
+    assert "oracle/_ref" in ref["library"] and "oracle/_ref" not in mine["library"]
+    atol, rtol = ROPE_TOL[ref["y"].dtype]
+    a, b = mine["y"].float().numpy(), ref["y"].float().numpy()
+    if a.size < 1 << 20:
+        assert_close(a, b, atol, rtol, "rope vs reference kernel")
+    else:
+        # Among millions of pairs a few have products that cancel (x0 cos ~ x1 sin): the reference kernel rounds
+        # each product to the 16-bit type first, so its difference carries up to 2^-8 of the products (|x| up to ~5)
+        # there, while this library's fp32 arithmetic (bit-exact against the oracle in test_rope_gpu.py) does not.
+        err = np.abs(a - b)
+        outside = err > atol + rtol * np.abs(b)
+        assert outside.mean() < 1e-5 and err.max() < 0.05, (int(outside.sum()), float(err.max()))
+    if "ms" in ref:
+        print(f"rope {spec['shape']}: reference {ref['ms'] * 1e3:.1f} us, this library {mine['ms'] * 1e3:.1f} us "
+              f"({mine['bytes'] / mine['ms'] / 1e6:.0f} GB/s)")
