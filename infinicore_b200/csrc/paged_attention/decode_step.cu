@@ -58,21 +58,28 @@ struct RopeRowsArgs {
     int vec;
 };
 
-// One warp per (sequence, q-head | kv-head) row: rotate it by the sequence's position id.
+// One thread per item of a (sequence, q-head | kv-head) row (see rotateItem): rotate it by the sequence's position id.
 template <typename T, bool kGptJ>
 __global__ void __launch_bounds__(128) pagedRopeRowsKernel(const RopeRowsArgs a) {
-    // The attention kernel that follows is launched with the programmatic-serialization attribute: let its
-    // CTAs become resident and run their shared-memory prologue now.  It reads nothing from global memory
-    // before its griddepcontrol.wait, which returns only when this whole grid has finished and its rows are visible.
+    // Programmatic dependent launch on both sides.  This kernel may itself have started under the tail of
+    // its predecessor in the stream: it touches no global memory before the wait returns (predecessor complete,
+    // its writes visible).  The attention kernel that follows is launched the same way: let its CTAs become
+    // resident and run their shared-memory prologue now; it reads nothing from global memory before its own
+    // wait, which returns only when this whole grid has finished and its rows are visible.  Every CTA waits
+    // before it exits, so the ordering is transitive.  Both instructions are no-ops for a plain launch.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
+    const int table_dim = a.head_size / 2;
+    const int per_row = b200::rope::itemsPerRow<kGptJ>(table_dim, a.vec != 0);
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     const int rows_per_seq = a.num_heads + a.num_kv_heads;
-    if (warp >= a.num_seqs * rows_per_seq) {
+    const long long row = idx / per_row;
+    if (row >= static_cast<long long>(a.num_seqs) * rows_per_seq) {
         return;
     }
-    const int seq = warp / rows_per_seq;
-    const int h = warp % rows_per_seq;
+    const int item = static_cast<int>(idx - row * per_row);
+    const int seq = static_cast<int>(row / rows_per_seq);
+    const int h = static_cast<int>(row % rows_per_seq);
     const T *src;
     T *dst;
     if (h < a.num_heads) {
@@ -83,23 +90,34 @@ __global__ void __launch_bounds__(128) pagedRopeRowsKernel(const RopeRowsArgs a)
         src = static_cast<const T *>(a.new_k) + seq * a.new_k_seq_stride + static_cast<long long>(kv) * a.head_size;
         dst = static_cast<T *>(a.k_rot) + (static_cast<long long>(seq) * a.num_kv_heads + kv) * a.head_size;
     }
-    const int table_dim = a.head_size / 2;
     const unsigned long long pos = b200::rope::loadPosition(a.pos_ids, seq, a.pos_dtype);
     const bool in_table = pos < a.table_len;
     const T *sin_row = in_table ? static_cast<const T *>(a.sin_table) + pos * table_dim : nullptr;
     const T *cos_row = in_table ? static_cast<const T *>(a.cos_table) + pos * table_dim : nullptr;
-    b200::rope::rotateRow<T, kGptJ>(dst, src, sin_row, cos_row, table_dim, lane, a.vec != 0);
+    b200::rope::rotateItem<T, kGptJ>(dst, src, sin_row, cos_row, table_dim, item, a.vec != 0);
 }
 
 template <typename T>
-infiniStatus_t launchRopeRows(const RopeRowsArgs &a, bool gpt_j, cudaStream_t stream) {
+infiniStatus_t launchRopeRows(const RopeRowsArgs &a, bool gpt_j, bool use_pdl, cudaStream_t stream) {
     const long long rows = static_cast<long long>(a.num_seqs) * (a.num_heads + a.num_kv_heads);
-    const unsigned blocks = static_cast<unsigned>((rows * 32 + 127) / 128);
-    if (gpt_j) {
-        pagedRopeRowsKernel<T, true><<<blocks, 128, 0, stream>>>(a);
-    } else {
-        pagedRopeRowsKernel<T, false><<<blocks, 128, 0, stream>>>(a);
+    const int table_dim = a.head_size / 2;
+    const long long per_row = gpt_j ? b200::rope::itemsPerRow<true>(table_dim, a.vec != 0) : b200::rope::itemsPerRow<false>(table_dim, a.vec != 0);
+    const unsigned blocks = static_cast<unsigned>((rows * per_row + 127) / 128);
+    if (blocks == 0) {
+        return INFINI_STATUS_SUCCESS;
     }
+    cudaLaunchAttribute pdl;
+    pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl.val.programmaticStreamSerializationAllowed = use_pdl ? 1 : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(128);
+    cfg.stream = stream;
+    cfg.attrs = &pdl;
+    cfg.numAttrs = 1;
+    const cudaError_t err = gpt_j ? cudaLaunchKernelEx(&cfg, pagedRopeRowsKernel<T, true>, a)
+                                  : cudaLaunchKernelEx(&cfg, pagedRopeRowsKernel<T, false>, a);
+    (void)err; // reported through cudaGetLastError below
     return checkLaunch("pagedRopeRowsKernel");
 }
 
@@ -329,9 +347,11 @@ infiniStatus_t runStep(
         r.pos_dtype = static_cast<int>(d->pos_dtype);
         r.vec = (I.head_size % 16) == 0 && (d->q_seq_stride % 8) == 0 && (d->q_head_stride % 8) == 0 && (d->new_k_seq_stride % 8) == 0
              && ((addr(q) | addr(new_k) | addr(sin_table) | addr(cos_table)) & 15u) == 0;
+        // only in front of the streaming kernels, which wait for their predecessor themselves
+        const bool use_pdl = d->stream.eligible && d->stream.use_pdl;
         const infiniStatus_t st = I.dtype == INFINI_DTYPE_F16
-                                    ? b200::paged_attention::launchRopeRows<__half>(r, d->gpt_j, cuda_stream)
-                                    : b200::paged_attention::launchRopeRows<__nv_bfloat16>(r, d->gpt_j, cuda_stream);
+                                    ? b200::paged_attention::launchRopeRows<__half>(r, d->gpt_j, use_pdl, cuda_stream)
+                                    : b200::paged_attention::launchRopeRows<__nv_bfloat16>(r, d->gpt_j, use_pdl, cuda_stream);
         B200_RETURN_IF(st != INFINI_STATUS_SUCCESS, st);
         q = r.q_rot;
         new_k = r.k_rot;

@@ -4,9 +4,10 @@
 // 1-D or 2-D position ids, contiguous tables of dhead / 2 columns, last stride 1, which strides are
 // captured); the arithmetic follows src/infiniop/ops/rope/cpu/rope_cpu.cc:34-105 (see rope_device.cuh).
 //
-// Kernel shape: the op moves every element once in and once out (HBM-bound); one warp owns one
-// (batch, token, head) row and moves it with 128-bit accesses when all row starts are 16-byte
-// aligned; the table rows of a token are shared by its heads and stay in L1/L2.
+// Kernel shape: the op moves every element once in and once out (HBM-bound); a row is cut into
+// 128-bit items (when all row starts are 16-byte aligned; single pairs otherwise), one per thread,
+// consecutive threads on consecutive items; the table rows of a token are shared by its heads and
+// stay in L1/L2.
 #include "../common.h"
 #include "rope_device.cuh"
 
@@ -108,37 +109,58 @@ struct KernelArgs {
     int pos_dtype;
     int pos_has_batch;
     int vec;
+    int small; // rows * items per row (rounded up to whole blocks) fits 32 bits
 };
 
-constexpr int kWarpsPerBlock = 8;
+constexpr int kThreads = 256;
 
+// One thread per item (see rotateItem); consecutive threads take consecutive items of a row, then the next row.
 template <typename T, bool kGptJ>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32) ropeRowsKernel(const KernelArgs a) {
-    const long long row = static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+__global__ void __launch_bounds__(kThreads) ropeRowsKernel(const KernelArgs a) {
+    const int per_row = itemsPerRow<kGptJ>(a.table_dim, a.vec != 0);
+    long long row, head, tok, b;
+    int item;
+    if (a.small) {
+        // fewer than 2^32 items: 32-bit divisions (a 64-bit one costs several times as much)
+        const unsigned idx = blockIdx.x * static_cast<unsigned>(kThreads) + threadIdx.x;
+        const unsigned r = idx / static_cast<unsigned>(per_row);
+        const unsigned th = r / static_cast<unsigned>(a.nhead);
+        item = static_cast<int>(idx - r * per_row);
+        row = r;
+        head = r - th * a.nhead;
+        b = th / static_cast<unsigned>(a.seqlen);
+        tok = th - static_cast<unsigned>(b) * a.seqlen;
+    } else {
+        const long long idx = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+        row = idx / per_row;
+        item = static_cast<int>(idx - row * per_row);
+        head = row % a.nhead;
+        tok = (row / a.nhead) % a.seqlen;
+        b = row / (static_cast<long long>(a.nhead) * a.seqlen);
+    }
     if (row >= a.rows) {
         return;
     }
-    const int lane = threadIdx.x & 31;
-    const long long head = row % a.nhead;
-    const long long tok = (row / a.nhead) % a.seqlen;
-    const long long b = row / (static_cast<long long>(a.nhead) * a.seqlen);
     const unsigned long long pos = loadPosition(a.pos_ids, (a.pos_has_batch ? b * a.seqlen : 0) + tok, a.pos_dtype);
     const T *x = static_cast<const T *>(a.x) + b * a.x_stride_batch + tok * a.x_stride_seqlen + head * a.x_stride_nhead;
     T *y = static_cast<T *>(a.y) + b * a.y_stride_batch + tok * a.y_stride_seqlen + head * a.y_stride_nhead;
     const bool in_table = pos < a.table_len;
     const T *sin_row = in_table ? static_cast<const T *>(a.sin_table) + pos * a.table_dim : nullptr;
     const T *cos_row = in_table ? static_cast<const T *>(a.cos_table) + pos * a.table_dim : nullptr;
-    rotateRow<T, kGptJ>(y, x, sin_row, cos_row, a.table_dim, lane, a.vec != 0);
+    rotateItem<T, kGptJ>(y, x, sin_row, cos_row, a.table_dim, item, a.vec != 0);
 }
 
 template <typename T>
 static infiniStatus_t launch(const Info &I, const KernelArgs &a, cudaStream_t stream) {
-    const long long blocks = (a.rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    const long long per_row = I.gpt_j ? itemsPerRow<true>(a.table_dim, a.vec != 0) : itemsPerRow<false>(a.table_dim, a.vec != 0);
+    const long long blocks = (a.rows * per_row + kThreads - 1) / kThreads;
     B200_RETURN_IF(blocks > 0x7fffffffLL, INFINI_STATUS_BAD_TENSOR_SHAPE);
+    KernelArgs args = a;
+    args.small = blocks * kThreads <= 0xffffffffLL ? 1 : 0;
     if (I.gpt_j) {
-        ropeRowsKernel<T, true><<<static_cast<unsigned>(blocks), kWarpsPerBlock * 32, 0, stream>>>(a);
+        ropeRowsKernel<T, true><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(args);
     } else {
-        ropeRowsKernel<T, false><<<static_cast<unsigned>(blocks), kWarpsPerBlock * 32, 0, stream>>>(a);
+        ropeRowsKernel<T, false><<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(args);
     }
     return checkLaunch("ropeRowsKernel");
 }

@@ -76,28 +76,30 @@ union Pack4 {
     T v[4];
 };
 
-// One warp rotates one row of `2 * table_dim` elements: y and x point at the row, sin_row / cos_row at
-// the table rows of its position (null: the position is outside the tables, the row is copied).
-// `vec` says every address involved is a multiple of 16 bytes and table_dim a multiple of 8 (16-bit
-// types only).  A lane reads both elements of each of its pairs before it writes either, and no pair
-// is shared between lanes, so y == x (in place) is fine.
+// Work of one row is cut into items, one per thread: with `vec` (16-bit types, every address involved a
+// multiple of 16 bytes, table_dim a multiple of 8) an item is 8 pairs for GPT-NeoX (one 128-bit word from
+// each half of the row) or 4 pairs for GPT-J (one 128-bit word); otherwise an item is one pair.
+template <bool kGptJ>
+__host__ __device__ inline int itemsPerRow(int table_dim, bool vec) {
+    return vec ? (kGptJ ? table_dim / 4 : table_dim / 8) : table_dim;
+}
+
+// Rotates item `item` of one row of `2 * table_dim` elements: y and x point at the row, sin_row / cos_row
+// at the table rows of its position (null: the position is outside the tables, the item is copied).
+// A thread reads both elements of each of its pairs before it writes either, and no pair is shared
+// between threads, so y == x (in place) is fine.
 template <typename T, bool kGptJ>
-__device__ __forceinline__ void rotateRow(T *y, const T *x, const T *sin_row, const T *cos_row, int table_dim, int lane, bool vec) {
-    if (sin_row == nullptr) {
-        if (y != x) {
-            for (int i = lane; i < 2 * table_dim; i += 32) {
-                y[i] = x[i];
-            }
-        }
-        return;
-    }
+__device__ __forceinline__ void rotateItem(T *y, const T *x, const T *sin_row, const T *cos_row, int table_dim, int item, bool vec) {
     if constexpr (sizeof(T) == 2) {
         if (vec) {
             if constexpr (kGptJ) {
-                for (int i = lane * 4; i < table_dim; i += 128) {
-                    Pack8<T> in, out;
+                const int i = item * 4;
+                Pack8<T> in, out;
+                in.bits = *reinterpret_cast<const uint4 *>(x + 2 * i);
+                if (sin_row == nullptr) {
+                    out.bits = in.bits;
+                } else {
                     Pack4<T> s, c;
-                    in.bits = *reinterpret_cast<const uint4 *>(x + 2 * i);
                     s.bits = *reinterpret_cast<const uint2 *>(sin_row + i);
                     c.bits = *reinterpret_cast<const uint2 *>(cos_row + i);
 #pragma unroll
@@ -107,13 +109,18 @@ __device__ __forceinline__ void rotateRow(T *y, const T *x, const T *sin_row, co
                         narrow(out.v[2 * j], ya);
                         narrow(out.v[2 * j + 1], yb);
                     }
-                    *reinterpret_cast<uint4 *>(y + 2 * i) = out.bits;
                 }
+                *reinterpret_cast<uint4 *>(y + 2 * i) = out.bits;
             } else {
-                for (int i = lane * 8; i < table_dim; i += 256) {
-                    Pack8<T> lo, hi, s, c, out_lo, out_hi;
-                    lo.bits = *reinterpret_cast<const uint4 *>(x + i);
-                    hi.bits = *reinterpret_cast<const uint4 *>(x + table_dim + i);
+                const int i = item * 8;
+                Pack8<T> lo, hi, out_lo, out_hi;
+                lo.bits = *reinterpret_cast<const uint4 *>(x + i);
+                hi.bits = *reinterpret_cast<const uint4 *>(x + table_dim + i);
+                if (sin_row == nullptr) {
+                    out_lo.bits = lo.bits;
+                    out_hi.bits = hi.bits;
+                } else {
+                    Pack8<T> s, c;
                     s.bits = *reinterpret_cast<const uint4 *>(sin_row + i);
                     c.bits = *reinterpret_cast<const uint4 *>(cos_row + i);
 #pragma unroll
@@ -123,21 +130,25 @@ __device__ __forceinline__ void rotateRow(T *y, const T *x, const T *sin_row, co
                         narrow(out_lo.v[j], ya);
                         narrow(out_hi.v[j], yb);
                     }
-                    *reinterpret_cast<uint4 *>(y + i) = out_lo.bits;
-                    *reinterpret_cast<uint4 *>(y + table_dim + i) = out_hi.bits;
                 }
+                *reinterpret_cast<uint4 *>(y + i) = out_lo.bits;
+                *reinterpret_cast<uint4 *>(y + table_dim + i) = out_hi.bits;
             }
             return;
         }
     }
-    for (int i = lane; i < table_dim; i += 32) {
-        const int a = kGptJ ? 2 * i : i;
-        const int b = kGptJ ? 2 * i + 1 : i + table_dim;
-        decltype(widen(x[0])) ya, yb;
-        rotatePair(widen(x[a]), widen(x[b]), widen(sin_row[i]), widen(cos_row[i]), ya, yb);
-        narrow(y[a], ya);
-        narrow(y[b], yb);
+    const int a = kGptJ ? 2 * item : item;
+    const int b = kGptJ ? 2 * item + 1 : item + table_dim;
+    if (sin_row == nullptr) {
+        const T xa = x[a], xb = x[b];
+        y[a] = xa;
+        y[b] = xb;
+        return;
     }
+    decltype(widen(x[0])) ya, yb;
+    rotatePair(widen(x[a]), widen(x[b]), widen(sin_row[item]), widen(cos_row[item]), ya, yb);
+    narrow(y[a], ya);
+    narrow(y[b], yb);
 }
 
 } // namespace b200::rope

@@ -85,7 +85,7 @@ ROPE_SPECS = [
     {"op": "rope", "shape": [10, 32, 64], "dtype": "float16", "algo": 0, "seed": 61, "table_len": 64},
     {"op": "rope", "shape": [11, 33, 128], "dtype": "bfloat16", "algo": 1, "seed": 62, "table_len": 64},
     {"op": "rope", "shape": [8, 10, 32, 64], "dtype": "float32", "algo": 1, "seed": 63, "table_len": 32},
-    {"op": "rope", "shape": [4096, 32, 128], "dtype": "bfloat16", "algo": 1, "seed": 64, "table_len": 4096, "iters": 20},
+    {"op": "rope", "shape": [8192, 32, 128], "dtype": "bfloat16", "algo": 1, "seed": 64, "table_len": 8192, "iters": 20},
 ]
 
 
