@@ -18,6 +18,7 @@ _LAZY = {
     "paged_attention_prefill": "ops",
     "paged_decode_step": "ops",
     "rope": "ops",
+    "kv_caching": "ops",
     "RopeAlgo": "ops",
     "DecodeStep": "decode_step",
 }

@@ -47,6 +47,7 @@ OP_SOURCES = [
     "paged_attention/static_workspace.cu",
     "paged_attention/decode_step.cu",
     "rope/rope.cu",
+    "kv_caching/kv_caching.cu",
     "paged_attention_prefill/operator.cu",
     "paged_attention_prefill/prefill_generic.cu",
     "paged_attention_prefill/prefill_tiles.cu",

@@ -91,6 +91,7 @@ enum class OpKind : int {
     PagedAttentionPrefill = 3,
     PagedDecodeStep = 4,
     RoPE = 5,
+    KVCaching = 6,
 };
 
 struct OpDescriptorBase {

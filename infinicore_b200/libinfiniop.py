@@ -92,6 +92,8 @@ INFINIOP_SYMBOLS = [
     "infiniopPagedDecodeStep", "infiniopDestroyPagedDecodeStepDescriptor",
     "infiniopCreatePagedDecodeStepRoPEDescriptor", "infiniopPagedDecodeStepRoPE",
     "infiniopCreateRoPEDescriptor", "infiniopGetRoPEWorkspaceSize", "infiniopRoPE", "infiniopDestroyRoPEDescriptor",
+    "infiniopCreateKVCachingDescriptor", "infiniopGetKVCachingWorkspaceSize", "infiniopKVCaching",
+    "infiniopDestroyKVCachingDescriptor",
 ]
 INFINIRT_SYMBOLS = [
     "infinirtInit", "infinirtGetAllDeviceCount", "infinirtGetDeviceCount", "infinirtSetDevice",
@@ -254,6 +256,23 @@ def _bind(lib: InfiniLib) -> None:
         ]
         op.infiniopDestroyRoPEDescriptor.restype = c_int32
         op.infiniopDestroyRoPEDescriptor.argtypes = [infiniopOperatorDescriptor_t]
+
+    # the signatures of reference include/infiniop/ops/kv_caching.h:8-29
+    if hasattr(op, "infiniopCreateKVCachingDescriptor"):
+        op.infiniopCreateKVCachingDescriptor.restype = c_int32
+        op.infiniopCreateKVCachingDescriptor.argtypes = [
+            infiniopHandle_t, POINTER(infiniopOperatorDescriptor_t),
+            infiniopTensorDescriptor_t, infiniopTensorDescriptor_t, infiniopTensorDescriptor_t,
+            infiniopTensorDescriptor_t, infiniopTensorDescriptor_t,
+        ]
+        op.infiniopGetKVCachingWorkspaceSize.restype = c_int32
+        op.infiniopGetKVCachingWorkspaceSize.argtypes = [infiniopOperatorDescriptor_t, POINTER(c_size_t)]
+        op.infiniopKVCaching.restype = c_int32
+        op.infiniopKVCaching.argtypes = [
+            infiniopOperatorDescriptor_t, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        ]
+        op.infiniopDestroyKVCachingDescriptor.restype = c_int32
+        op.infiniopDestroyKVCachingDescriptor.argtypes = [infiniopOperatorDescriptor_t]
 
     # reference test/infiniop/libinfiniop/op_register.py:2231-2269
     op.infiniopCreatePagedCachingDescriptor.restype = c_int32

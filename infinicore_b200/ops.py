@@ -324,6 +324,30 @@ def _paged_decode_step_rope(q, k_cache, v_cache, new_k, new_v, block_tables, cac
     return out
 
 
+def kv_caching(k_cache, v_cache, k, v, past_kv_lengths):
+    """Appends k / v [batch, kv_heads, seq_len, hidden] to the contiguous caches [batch, kv_heads, max_seq_len, hidden]
+    behind the past_kv_lengths[b] rows each sequence holds (the reference's infiniopKVCaching).  Returns (k_cache, v_cache)."""
+    dev = _require_cuda(k_cache, v_cache, k, v, past_kv_lengths)
+    st = _state(dev)
+    key = ("kv_caching", _meta(k_cache), _meta(v_cache), _meta(k), _meta(v), _meta(past_kv_lengths))
+
+    def make():
+        tensors = [_desc(k_cache), _desc(v_cache), _desc(k), _desc(v), _desc(past_kv_lengths)]
+        desc = infiniopOperatorDescriptor_t()
+        check_error(LIBINFINIOP.infiniopCreateKVCachingDescriptor(
+            st["handle"], ctypes.byref(desc), *[t.descriptor for t in tensors]))
+        for t in tensors:
+            t.destroy_desc()
+        return {"desc": desc, "workspace": 0, "destroy": LIBINFINIOP.infiniopDestroyKVCachingDescriptor}
+
+    entry = _lookup(st, key, make)
+    with torch.cuda.device(dev):
+        check_error(LIBINFINIOP.infiniopKVCaching(
+            entry["desc"], None, 0, k_cache.data_ptr(), v_cache.data_ptr(), k.data_ptr(), v.data_ptr(),
+            past_kv_lengths.data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
+    return (k_cache, v_cache)
+
+
 def paged_caching(k_cache, v_cache, k, v, slot_mapping):
     """Scatters k/v rows [num_tokens, num_kv_heads, head_size] into the paged pools at
     slot_mapping (int64; negative = padding).  Returns (k_cache, v_cache)."""

@@ -212,3 +212,19 @@ def rope(x, pos_ids, sin_table, cos_table, dtype, gpt_j, out=None) -> np.ndarray
     if rc != 0:
         raise ValueError(f"oracle_rope rejected its input (code {rc})")
     return out
+
+
+def kv_caching(k_cache, v_cache, k, v, past_kv_lengths) -> None:
+    """In-place restatement of the reference checker torch_kv_caching (test/infiniop/kv_caching.py:25-41) and of
+    its kernel's indexing (src/infiniop/ops/kv_caching/cuda/kernel.cuh:32-60) for numpy arrays of any dtype and
+    strides: cache[b, h, past[b] + s, :] = new[b, h, s, :].  Rows whose destination lies outside the cache are
+    skipped (the checker's slice assignment would raise, the reference kernel writes out of bounds)."""
+    batch, heads, max_len, _ = k_cache.shape
+    seq_len = k.shape[2]
+    past = np.asarray(past_kv_lengths).astype(np.int64)
+    for b in range(batch):
+        for s in range(seq_len):
+            dst = int(past[b]) + s
+            if 0 <= dst < max_len:
+                k_cache[b, :, dst, :] = k[b, :, s, :]
+                v_cache[b, :, dst, :] = v[b, :, s, :]

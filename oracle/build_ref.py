@@ -41,6 +41,8 @@ OP_SOURCES = [
     "src/infiniop/ops/paged_attention_prefill/nvidia/paged_attention_prefill_nvidia.cu",
     "src/infiniop/ops/paged_caching/operator.cc",
     "src/infiniop/ops/paged_caching/nvidia/paged_caching_nvidia.cu",
+    "src/infiniop/ops/kv_caching/operator.cc",
+    "src/infiniop/ops/kv_caching/nvidia/kv_caching_nvidia.cu",
     "src/infiniop/ops/rope/operator.cc",
     "src/infiniop/ops/rope/nvidia/rope_nvidia.cu",
     "src/utils/custom_types.cc",

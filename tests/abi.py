@@ -156,6 +156,31 @@ def paged_decode_step(q, k_cache, v_cache, new_k, new_v, block_tables, seq_lens,
     return out
 
 
+def kv_caching_create(k_cache, v_cache, k, v, past_kv_lengths, len_dtype=None):
+    """Creates a KVCaching descriptor as reference test/infiniop/kv_caching.py:115-127 does; returns (status, descriptor)."""
+    tensors = [_tt(k_cache), _tt(v_cache), _tt(k), _tt(v), _tt(past_kv_lengths, len_dtype)]
+    desc = infiniopOperatorDescriptor_t()
+    status = LIBINFINIOP.infiniopCreateKVCachingDescriptor(handle(), ctypes.byref(desc), *[t.descriptor for t in tensors])
+    for t in tensors:
+        t.destroy_desc()
+    return status, desc
+
+
+def kv_caching(k_cache, v_cache, k, v, past_kv_lengths, stream=None):
+    """One infiniopKVCaching call through the C ABI; the caches are updated in place (synchronised)."""
+    status, desc = kv_caching_create(k_cache, v_cache, k, v, past_kv_lengths)
+    check_error(status)
+    try:
+        size = ctypes.c_size_t(1)
+        check_error(LIBINFINIOP.infiniopGetKVCachingWorkspaceSize(desc, ctypes.byref(size)))
+        assert size.value == 0
+        check_error(LIBINFINIOP.infiniopKVCaching(desc, None, 0, k_cache.data_ptr(), v_cache.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                  past_kv_lengths.data_ptr(), stream))
+        torch.cuda.synchronize()
+    finally:
+        check_error(LIBINFINIOP.infiniopDestroyKVCachingDescriptor(desc))
+
+
 def rope_create(y, x, pos_ids, sin_table, cos_table, algo, pos_dtype=None):
     """Creates a RoPE descriptor as reference test/infiniop/rope.py:170-186 does; returns (status, descriptor)."""
     tensors = [_tt(y), _tt(x), _tt(pos_ids, pos_dtype), _tt(sin_table), _tt(cos_table)]

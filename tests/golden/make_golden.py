@@ -2,13 +2,14 @@
 
 Run in a container that has the reference checkout (it is not needed to run the tests):
 
-    python tests/golden/make_golden.py /path/to/InfiniCore [--only=attention|caching|prefill|rope]
+    python tests/golden/make_golden.py /path/to/InfiniCore [--only=attention|caching|prefill|rope|kv_caching]
 
 The two functions executed are imported unmodified from the reference tree:
   ref_single_query_cached_kv_attention   test/infiniop/paged_attention.py:47-88
   ref_paged_caching                      test/infiniop/paged_caching.py:25-55
   ref_paged_attention_multi_turn         test/infiniop/paged_attention_prefill.py:96-140
   rotary_embedding, sin_cos_table        test/infiniop/rope.py:87-133 (run with its CPU device value, i.e. fp32 arithmetic)
+  torch_kv_caching                       test/infiniop/kv_caching.py:25-41
 Those files import the reference's ctypes harness at module level (which would try to load the
 reference's compiled library); a stand-in `libinfiniop` module with empty attributes is put
 in sys.modules first so that only the pure-torch functions are used.
@@ -41,12 +42,12 @@ def load_reference(ref_root: Path):
 
     sys.modules["libinfiniop"] = _Anything("libinfiniop")
     mods = {}
-    for name in ("paged_attention", "paged_caching", "paged_attention_prefill", "rope"):
+    for name in ("paged_attention", "paged_caching", "paged_attention_prefill", "rope", "kv_caching"):
         spec = importlib.util.spec_from_file_location(f"_ref_{name}", ref_root / "test" / "infiniop" / f"{name}.py")
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
         mods[name] = mod
-    return mods["paged_attention"], mods["paged_caching"], mods["paged_attention_prefill"], mods["rope"]
+    return mods["paged_attention"], mods["paged_caching"], mods["paged_attention_prefill"], mods["rope"], mods["kv_caching"]
 
 
 def bits(t: torch.Tensor) -> np.ndarray:
@@ -221,11 +222,39 @@ def make_rope(ref_rope):
         print("wrote", name, shape)
 
 
+def kv_caching_cases():
+    # (name, dtype, cache shape, cache strides or None, seq_len): shapes and strides of the reference's own cases
+    # (test/infiniop/kv_caching.py:48-56)
+    yield "kvc_bf16_8x8x64x32", torch.bfloat16, (8, 8, 64, 32), None, 5
+    yield "kvc_fp16_strided_1x32x8x64", torch.float16, (1, 32, 8, 64), (32768, 1024, 64, 1), 3
+    yield "kvc_f32_strided_4x8x32x16", torch.float32, (4, 8, 32, 16), (65536, 8192, 256, 16), 7
+    yield "kvc_fp16_1x1x8x1", torch.float16, (1, 1, 8, 1), None, 2
+
+
+def make_kv_caching(ref_kvc):
+    for idx, (name, dtype, shape, strides, seq_len) in enumerate(kv_caching_cases()):
+        g = torch.Generator()
+        g.manual_seed(400 + idx)
+        k_cache, v_cache = strided(shape, strides, dtype, g), strided(shape, strides, dtype, g)
+        new_shape = (shape[0], shape[1], seq_len, shape[3])
+        k, v = torch.randn(new_shape, generator=g).to(dtype), torch.randn(new_shape, generator=g).to(dtype)
+        past = torch.randint(0, shape[2] - seq_len + 1, (shape[0],), generator=g, dtype=torch.int64)
+        before_k, before_v = bits(k_cache.contiguous()), bits(v_cache.contiguous())
+        k_after, v_after = ref_kvc.torch_kv_caching(k_cache, v_cache, k, v, past)
+        np.savez_compressed(
+            HERE / f"{name}.npz",
+            dtype=np.int64(DTYPE_CODE[dtype]), cache_strides=np.array(strides if strides is not None else [], dtype=np.int64),
+            k_cache=before_k, v_cache=before_v, k=bits(k), v=bits(v), past_kv_lengths=past.numpy(),
+            k_cache_after=bits(k_after.contiguous()), v_cache_after=bits(v_after.contiguous()),
+        )
+        print("wrote", name, shape)
+
+
 def main():
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
     only = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--only=")]
     ref_root = Path(args[0]) if args else Path("/root/reference")
-    ref_attn, ref_cache, ref_prefill, ref_rope = load_reference(ref_root)
+    ref_attn, ref_cache, ref_prefill, ref_rope, ref_kvc = load_reference(ref_root)
     torch.set_num_threads(4)
     if not only or "attention" in only:
         make_attention(ref_attn)
@@ -235,6 +264,8 @@ def main():
         make_prefill(ref_prefill)
     if not only or "rope" in only:
         make_rope(ref_rope)
+    if not only or "kv_caching" in only:
+        make_kv_caching(ref_kvc)
 
 
 if __name__ == "__main__":

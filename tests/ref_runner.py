@@ -107,11 +107,53 @@ def run_rope(spec, out_path):
     torch.save(result, out_path)
 
 
+def run_kv_caching(spec, out_path):
+    """spec = {"op": "kv_caching", "shape": [batch, heads, max_len, hidden], "seq_len": n, "dtype": "...", "seed": n, "iters": N}"""
+    import abi
+    from infinicore_b200.libinfiniop import LIBINFINIOP, check_error, library_paths
+
+    dtype = getattr(torch, spec["dtype"])
+    gen = torch.Generator().manual_seed(int(spec.get("seed", 0)))
+    shape, seq_len = list(spec["shape"]), int(spec["seq_len"])
+    k_cache, v_cache = torch.randn(shape, generator=gen).to(dtype).cuda(), torch.randn(shape, generator=gen).to(dtype).cuda()
+    new_shape = [shape[0], shape[1], seq_len, shape[3]]
+    k, v = torch.randn(new_shape, generator=gen).to(dtype).cuda(), torch.randn(new_shape, generator=gen).to(dtype).cuda()
+    past = torch.randint(0, shape[2] - seq_len + 1, (shape[0],), generator=gen).cuda()
+    status, desc = abi.kv_caching_create(k_cache, v_cache, k, v, past)
+    check_error(status)
+
+    def call(stream=None):
+        check_error(LIBINFINIOP.infiniopKVCaching(desc, None, 0, k_cache.data_ptr(), v_cache.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                  past.data_ptr(), stream))
+
+    call()
+    torch.cuda.synchronize()
+    result = {"k_cache": k_cache.cpu(), "v_cache": v_cache.cpu(), "library": str(library_paths()[1])}
+    iters = int(spec.get("iters", 0))
+    if iters:
+        stream = torch.cuda.current_stream().cuda_stream
+        for _ in range(3):
+            call(stream)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            call(stream)
+        b.record()
+        torch.cuda.synchronize()
+        result["ms"] = a.elapsed_time(b) / iters
+        result["bytes"] = 2 * 2 * k.numel() * k.element_size()  # K and V rows, read once and written once
+    check_error(LIBINFINIOP.infiniopDestroyKVCachingDescriptor(desc))
+    torch.save(result, out_path)
+
+
 def main():
     spec = json.loads(sys.argv[1])
     out_path = sys.argv[2]
     if spec.get("op") == "rope":
         return run_rope(spec, out_path)
+    if spec.get("op") == "kv_caching":
+        return run_kv_caching(spec, out_path)
     from infinicore_b200 import workloads
     from infinicore_b200.libinfiniop import LIBINFINIOP, check_error, library_paths
 

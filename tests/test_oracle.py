@@ -175,3 +175,35 @@ def test_rope_is_a_rotation_and_positions_outside_the_tables_copy():
         assert np.array_equal(y[3], x[3]) and np.array_equal(y[4], x[4])        # -1 and 10 are outside a table of 10 rows
         back = oracle.rope(y, pos, -np.sin(ang), np.cos(ang), oracle.F64, gpt_j)  # the inverse rotation
         assert np.allclose(back, x, atol=1e-12)
+
+
+# ---- contiguous KV cache append -------------------------------------------------------------------------
+
+
+def _strided_np(dense, strides):
+    if not len(strides):
+        return dense.copy()
+    strides = [int(s) for s in strides]
+    extent = 1 + sum((n - 1) * s for n, s in zip(dense.shape, strides))
+    base = np.zeros(extent, dtype=dense.dtype)
+    view = np.lib.stride_tricks.as_strided(base, dense.shape, [s * dense.itemsize for s in strides])
+    view[...] = dense
+    return view
+
+
+@pytest.mark.parametrize("name", golden_names("kvc_"))
+def test_kv_caching_bit_exact_against_reference_checker(name):
+    g = load_golden(name)
+    kc, vc = _strided_np(g["k_cache"], g["cache_strides"]), _strided_np(g["v_cache"], g["cache_strides"])
+    oracle.kv_caching(kc, vc, g["k"], g["v"], g["past_kv_lengths"])
+    assert np.array_equal(np.ascontiguousarray(kc), g["k_cache_after"])
+    assert np.array_equal(np.ascontiguousarray(vc), g["v_cache_after"])
+
+
+def test_kv_caching_skips_rows_outside_the_cache():
+    kc, vc = np.zeros((2, 1, 4, 2), np.float32), np.zeros((2, 1, 4, 2), np.float32)
+    k = np.arange(12, dtype=np.float32).reshape(2, 1, 3, 2) + 1
+    oracle.kv_caching(kc, vc, k, -k, np.array([2, -1]))
+    assert np.array_equal(kc[0, 0], [[0, 0], [0, 0], [1, 2], [3, 4]])          # third row would land at 4: skipped
+    assert np.array_equal(kc[1, 0], [[9, 10], [11, 12], [0, 0], [0, 0]])       # first row would land at -1: skipped
+    assert np.array_equal(vc, -kc)

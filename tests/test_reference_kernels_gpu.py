@@ -109,3 +109,26 @@ def test_rope_same_results_as_the_reference_kernel(spec, tmp_path):
     if "ms" in ref:
         print(f"rope {spec['shape']}: reference {ref['ms'] * 1e3:.1f} us, this library {mine['ms'] * 1e3:.1f} us "
               f"({mine['bytes'] / mine['ms'] / 1e6:.0f} GB/s)")
+
+
+KV_CACHING_SPECS = [
+    {"op": "kv_caching", "shape": [8, 8, 64, 32], "seq_len": 5, "dtype": "bfloat16", "seed": 71},
+    {"op": "kv_caching", "shape": [2, 4, 32, 16], "seq_len": 31, "dtype": "float32", "seed": 72},
+    # a prefill-sized append: 16 sequences x 8 heads x 2048 new rows of 128 (134 MB of rows in and out)
+    {"op": "kv_caching", "shape": [16, 8, 2048, 128], "seq_len": 2048, "dtype": "bfloat16", "seed": 73, "iters": 20},
+]
+
+
+@pytest.mark.skipif(not (REF_ROOT / "lib" / "libinfiniop.so").is_file(), reason="oracle/_ref not built")
+@pytest.mark.parametrize("spec", KV_CACHING_SPECS, ids=lambda s: "x".join(map(str, s["shape"])) + s["dtype"])
+def test_kv_caching_same_results_as_the_reference_kernel(spec, tmp_path):
+    ref = run(spec, tmp_path, reference=True)
+    mine = run(spec, tmp_path, reference=False)
+    assert "oracle/_ref" in ref["library"] and "oracle/_ref" not in mine["library"]
+    for name in ("k_cache", "v_cache"):
+        a, b = mine[name], ref[name]
+        view = torch.int16 if a.element_size() == 2 else torch.int32
+        assert torch.equal(a.view(view), b.view(view)), f"{name} differs from the reference kernel's"
+    if "ms" in ref:
+        print(f"kv_caching {spec['shape']}: reference {ref['ms'] * 1e3:.1f} us, this library {mine['ms'] * 1e3:.1f} us "
+              f"({mine['bytes'] / mine['ms'] / 1e6:.0f} GB/s)")
