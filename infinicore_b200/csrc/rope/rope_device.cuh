@@ -64,10 +64,21 @@ __device__ __forceinline__ void rotatePair(double a, double b, double s, double 
     yb = __dadd_rn(__dmul_rn(a, s), __dmul_rn(b, c));
 }
 
+// Two fp32 values rounded (to nearest even) and packed by one paired conversion.
+__device__ __forceinline__ uint32_t packPair(float lo, float hi, __half) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+__device__ __forceinline__ uint32_t packPair(float lo, float hi, __nv_bfloat16) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+
 // Eight 16-bit values moved as one 128-bit word.
 template <typename T>
 union Pack8 {
     uint4 bits;
+    uint32_t words[4];
     T v[8];
 };
 template <typename T>
@@ -106,8 +117,7 @@ __device__ __forceinline__ void rotateItem(T *y, const T *x, const T *sin_row, c
                     for (int j = 0; j < 4; ++j) {
                         float ya, yb;
                         rotatePair(widen(in.v[2 * j]), widen(in.v[2 * j + 1]), widen(s.v[j]), widen(c.v[j]), ya, yb);
-                        narrow(out.v[2 * j], ya);
-                        narrow(out.v[2 * j + 1], yb);
+                        out.words[j] = packPair(ya, yb, T());
                     }
                 }
                 *reinterpret_cast<uint4 *>(y + 2 * i) = out.bits;
@@ -124,11 +134,12 @@ __device__ __forceinline__ void rotateItem(T *y, const T *x, const T *sin_row, c
                     s.bits = *reinterpret_cast<const uint4 *>(sin_row + i);
                     c.bits = *reinterpret_cast<const uint4 *>(cos_row + i);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        float ya, yb;
-                        rotatePair(widen(lo.v[j]), widen(hi.v[j]), widen(s.v[j]), widen(c.v[j]), ya, yb);
-                        narrow(out_lo.v[j], ya);
-                        narrow(out_hi.v[j], yb);
+                    for (int j = 0; j < 8; j += 2) {
+                        float ya0, yb0, ya1, yb1;
+                        rotatePair(widen(lo.v[j]), widen(hi.v[j]), widen(s.v[j]), widen(c.v[j]), ya0, yb0);
+                        rotatePair(widen(lo.v[j + 1]), widen(hi.v[j + 1]), widen(s.v[j + 1]), widen(c.v[j + 1]), ya1, yb1);
+                        out_lo.words[j / 2] = packPair(ya0, ya1, T());
+                        out_hi.words[j / 2] = packPair(yb0, yb1, T());
                     }
                 }
                 *reinterpret_cast<uint4 *>(y + i) = out_lo.bits;
