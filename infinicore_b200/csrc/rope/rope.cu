@@ -150,8 +150,81 @@ __global__ void __launch_bounds__(kThreads) ropeRowsKernel(const KernelArgs a) {
     rotateItem<T, kGptJ>(y, x, sin_row, cos_row, a.table_dim, item, a.vec != 0);
 }
 
+// Vector path, two rows per thread (row r and row r + ceil(rows / 2), the same item of each): the position
+// ids of both are loaded first, then the x words of both, then the table words of both, so that twice the
+// bytes are in flight while a thread waits.  16-bit types and 32-bit item counts only.
+template <typename T, bool kGptJ>
+__global__ void __launch_bounds__(kThreads) ropeRowPairsKernel(const KernelArgs a) {
+    const unsigned per_row = static_cast<unsigned>(itemsPerRow<kGptJ>(a.table_dim, true));
+    const unsigned half_rows = static_cast<unsigned>((a.rows + 1) / 2);
+    const unsigned idx = blockIdx.x * static_cast<unsigned>(kThreads) + threadIdx.x;
+    const unsigned r0 = idx / per_row;
+    if (r0 >= half_rows) {
+        return;
+    }
+    const int item = static_cast<int>(idx - r0 * per_row);
+    const T *x[2];
+    T *y[2];
+    const T *sin_row[2], *cos_row[2];
+    bool live[2];
+    unsigned long long pos[2];
+    long long pos_index[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const unsigned r = r0 + u * half_rows;
+        live[u] = r < a.rows;
+        const unsigned th = r / static_cast<unsigned>(a.nhead);
+        const unsigned head = r - th * a.nhead;
+        const unsigned b = th / static_cast<unsigned>(a.seqlen);
+        const unsigned tok = th - b * a.seqlen;
+        pos_index[u] = (a.pos_has_batch ? static_cast<long long>(b) * a.seqlen : 0) + tok;
+        x[u] = static_cast<const T *>(a.x) + b * a.x_stride_batch + tok * a.x_stride_seqlen + head * a.x_stride_nhead;
+        y[u] = static_cast<T *>(a.y) + b * a.y_stride_batch + tok * a.y_stride_seqlen + head * a.y_stride_nhead;
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        pos[u] = live[u] ? loadPosition(a.pos_ids, pos_index[u], a.pos_dtype) : ~0ull;
+    }
+    VecItem<T> in[2];
+    VecTables<T> t[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        if (live[u]) {
+            loadItemVec<T, kGptJ>(in[u], x[u], a.table_dim, item);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const bool in_table = pos[u] < a.table_len;
+        sin_row[u] = in_table ? static_cast<const T *>(a.sin_table) + pos[u] * a.table_dim : nullptr;
+        cos_row[u] = in_table ? static_cast<const T *>(a.cos_table) + pos[u] * a.table_dim : nullptr;
+        if (live[u]) {
+            loadTablesVec<T, kGptJ>(t[u], sin_row[u], cos_row[u], item);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        if (live[u]) {
+            rotateStoreVec<T, kGptJ>(y[u], in[u], t[u], sin_row[u] != nullptr, a.table_dim, item);
+        }
+    }
+}
+
 template <typename T>
 static infiniStatus_t launch(const Info &I, const KernelArgs &a, cudaStream_t stream) {
+    if constexpr (sizeof(T) == 2) {
+        const long long per_row_vec = I.gpt_j ? itemsPerRow<true>(a.table_dim, true) : itemsPerRow<false>(a.table_dim, true);
+        const long long pair_blocks = ((a.rows + 1) / 2 * per_row_vec + kThreads - 1) / kThreads;
+        // rows of the two halves must not overlap in y (they cannot for a tensor that does not alias itself)
+        if (a.vec != 0 && a.rows >= 2 && a.rows <= 0x7fffffffLL && pair_blocks * kThreads <= 0x7fffffffLL) {
+            if (I.gpt_j) {
+                ropeRowPairsKernel<T, true><<<static_cast<unsigned>(pair_blocks), kThreads, 0, stream>>>(a);
+            } else {
+                ropeRowPairsKernel<T, false><<<static_cast<unsigned>(pair_blocks), kThreads, 0, stream>>>(a);
+            }
+            return checkLaunch("ropeRowPairsKernel");
+        }
+    }
     const long long per_row = I.gpt_j ? itemsPerRow<true>(a.table_dim, a.vec != 0) : itemsPerRow<false>(a.table_dim, a.vec != 0);
     const long long blocks = (a.rows * per_row + kThreads - 1) / kThreads;
     B200_RETURN_IF(blocks > 0x7fffffffLL, INFINI_STATUS_BAD_TENSOR_SHAPE);

@@ -81,11 +81,6 @@ union Pack8 {
     uint32_t words[4];
     T v[8];
 };
-template <typename T>
-union Pack4 {
-    uint2 bits;
-    T v[4];
-};
 
 // Work of one row is cut into items, one per thread: with `vec` (16-bit types, every address involved a
 // multiple of 16 bytes, table_dim a multiple of 8) an item is 8 pairs for GPT-NeoX (one 128-bit word from
@@ -93,6 +88,78 @@ union Pack4 {
 template <bool kGptJ>
 __host__ __device__ inline int itemsPerRow(int table_dim, bool vec) {
     return vec ? (kGptJ ? table_dim / 4 : table_dim / 8) : table_dim;
+}
+
+// The vector path in three phases, so that a caller can put the loads of several items in flight before the
+// first of them is needed: (1) the item's words of x, (2) its words of the two table rows, (3) rotate and store.
+template <typename T>
+struct VecItem {
+    Pack8<T> a, b; // GPT-NeoX: word of the first half, word of the second half; GPT-J: `a` only
+};
+template <typename T>
+struct VecTables {
+    Pack8<T> s, c; // GPT-J uses the first four values of each
+};
+
+template <typename T, bool kGptJ>
+__device__ __forceinline__ void loadItemVec(VecItem<T> &in, const T *x, int table_dim, int item) {
+    if constexpr (kGptJ) {
+        in.a.bits = *reinterpret_cast<const uint4 *>(x + 8 * item);
+    } else {
+        in.a.bits = *reinterpret_cast<const uint4 *>(x + 8 * item);
+        in.b.bits = *reinterpret_cast<const uint4 *>(x + table_dim + 8 * item);
+    }
+}
+
+template <typename T, bool kGptJ>
+__device__ __forceinline__ void loadTablesVec(VecTables<T> &t, const T *sin_row, const T *cos_row, int item) {
+    if (sin_row == nullptr) {
+        return;
+    }
+    if constexpr (kGptJ) {
+        const uint2 s = *reinterpret_cast<const uint2 *>(sin_row + 4 * item);
+        const uint2 c = *reinterpret_cast<const uint2 *>(cos_row + 4 * item);
+        t.s.words[0] = s.x, t.s.words[1] = s.y;
+        t.c.words[0] = c.x, t.c.words[1] = c.y;
+    } else {
+        t.s.bits = *reinterpret_cast<const uint4 *>(sin_row + 8 * item);
+        t.c.bits = *reinterpret_cast<const uint4 *>(cos_row + 8 * item);
+    }
+}
+
+template <typename T, bool kGptJ>
+__device__ __forceinline__ void rotateStoreVec(T *y, const VecItem<T> &in, const VecTables<T> &t, bool in_table, int table_dim, int item) {
+    if constexpr (kGptJ) {
+        Pack8<T> out;
+        if (!in_table) {
+            out.bits = in.a.bits;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float ya, yb;
+                rotatePair(widen(in.a.v[2 * j]), widen(in.a.v[2 * j + 1]), widen(t.s.v[j]), widen(t.c.v[j]), ya, yb);
+                out.words[j] = packPair(ya, yb, T());
+            }
+        }
+        *reinterpret_cast<uint4 *>(y + 8 * item) = out.bits;
+    } else {
+        Pack8<T> out_lo, out_hi;
+        if (!in_table) {
+            out_lo.bits = in.a.bits;
+            out_hi.bits = in.b.bits;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                float ya0, yb0, ya1, yb1;
+                rotatePair(widen(in.a.v[j]), widen(in.b.v[j]), widen(t.s.v[j]), widen(t.c.v[j]), ya0, yb0);
+                rotatePair(widen(in.a.v[j + 1]), widen(in.b.v[j + 1]), widen(t.s.v[j + 1]), widen(t.c.v[j + 1]), ya1, yb1);
+                out_lo.words[j / 2] = packPair(ya0, ya1, T());
+                out_hi.words[j / 2] = packPair(yb0, yb1, T());
+            }
+        }
+        *reinterpret_cast<uint4 *>(y + 8 * item) = out_lo.bits;
+        *reinterpret_cast<uint4 *>(y + table_dim + 8 * item) = out_hi.bits;
+    }
 }
 
 // Rotates item `item` of one row of `2 * table_dim` elements: y and x point at the row, sin_row / cos_row
@@ -103,48 +170,11 @@ template <typename T, bool kGptJ>
 __device__ __forceinline__ void rotateItem(T *y, const T *x, const T *sin_row, const T *cos_row, int table_dim, int item, bool vec) {
     if constexpr (sizeof(T) == 2) {
         if (vec) {
-            if constexpr (kGptJ) {
-                const int i = item * 4;
-                Pack8<T> in, out;
-                in.bits = *reinterpret_cast<const uint4 *>(x + 2 * i);
-                if (sin_row == nullptr) {
-                    out.bits = in.bits;
-                } else {
-                    Pack4<T> s, c;
-                    s.bits = *reinterpret_cast<const uint2 *>(sin_row + i);
-                    c.bits = *reinterpret_cast<const uint2 *>(cos_row + i);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float ya, yb;
-                        rotatePair(widen(in.v[2 * j]), widen(in.v[2 * j + 1]), widen(s.v[j]), widen(c.v[j]), ya, yb);
-                        out.words[j] = packPair(ya, yb, T());
-                    }
-                }
-                *reinterpret_cast<uint4 *>(y + 2 * i) = out.bits;
-            } else {
-                const int i = item * 8;
-                Pack8<T> lo, hi, out_lo, out_hi;
-                lo.bits = *reinterpret_cast<const uint4 *>(x + i);
-                hi.bits = *reinterpret_cast<const uint4 *>(x + table_dim + i);
-                if (sin_row == nullptr) {
-                    out_lo.bits = lo.bits;
-                    out_hi.bits = hi.bits;
-                } else {
-                    Pack8<T> s, c;
-                    s.bits = *reinterpret_cast<const uint4 *>(sin_row + i);
-                    c.bits = *reinterpret_cast<const uint4 *>(cos_row + i);
-#pragma unroll
-                    for (int j = 0; j < 8; j += 2) {
-                        float ya0, yb0, ya1, yb1;
-                        rotatePair(widen(lo.v[j]), widen(hi.v[j]), widen(s.v[j]), widen(c.v[j]), ya0, yb0);
-                        rotatePair(widen(lo.v[j + 1]), widen(hi.v[j + 1]), widen(s.v[j + 1]), widen(c.v[j + 1]), ya1, yb1);
-                        out_lo.words[j / 2] = packPair(ya0, ya1, T());
-                        out_hi.words[j / 2] = packPair(yb0, yb1, T());
-                    }
-                }
-                *reinterpret_cast<uint4 *>(y + i) = out_lo.bits;
-                *reinterpret_cast<uint4 *>(y + table_dim + i) = out_hi.bits;
-            }
+            VecItem<T> in;
+            VecTables<T> t;
+            loadItemVec<T, kGptJ>(in, x, table_dim, item);
+            loadTablesVec<T, kGptJ>(t, sin_row, cos_row, item);
+            rotateStoreVec<T, kGptJ>(y, in, t, sin_row != nullptr, table_dim, item);
             return;
         }
     }
