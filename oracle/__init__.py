@@ -66,6 +66,8 @@ def lib() -> ctypes.CDLL:
         _lib.oracle_bf16_to_float.restype = c_float
         _lib.oracle_bf16_to_float.argtypes = [c_uint16]
         _lib.oracle_num_threads.restype = c_int
+        _lib.oracle_set_num_threads.restype = c_int
+        _lib.oracle_set_num_threads.argtypes = [c_int]
         _lib.oracle_rope.restype = c_int
         _lib.oracle_rope.argtypes = [
             c_int, c_int,
@@ -80,6 +82,15 @@ def lib() -> ctypes.CDLL:
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+def use_all_cores() -> int:
+    """Lets the oracle's OpenMP loops use every core this process may run on, whatever OMP_NUM_THREADS a
+    launcher exported (torch.distributed.run sets it to 1 for its workers).  Returns the thread count."""
+    import os
+
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    return int(lib().oracle_set_num_threads(cores))
 
 
 def _elem_strides(a: np.ndarray):

@@ -155,6 +155,20 @@ int oracle_num_threads(void) {
 #endif
 }
 
+/* Sets the number of OpenMP threads of later calls (a launcher may have exported OMP_NUM_THREADS=1 for its
+ * worker processes; the timed CPU baseline wants every core the process may run on).  Returns the new count. */
+int oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) {
+        omp_set_num_threads(n);
+    }
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 /* One query row (one q-head) against the first `len` tokens of one paged sequence.  `o` receives
  * value_size doubles.  Returns 0 or -5 (out of memory). */
 static int attend_row(
