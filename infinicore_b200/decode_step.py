@@ -10,6 +10,8 @@ operators themselves allocate nothing and never synchronise, which is what makes
     step = DecodeStep(k_cache, v_cache, num_seqs=64, num_heads=32, max_blocks_per_seq=256, scale=s)
     step.host["q"][...] = ...            # fill the pinned inputs: q, new_k, new_v, slot_mapping,
     out = step.run()                     #   block_tables, seq_lens; run() returns the pinned output
+
+With direct_output=True the output needs no copy at all: the kernels write it into the pinned buffer.
 """
 from __future__ import annotations
 
@@ -23,7 +25,7 @@ _INPUTS = ("q", "new_k", "new_v", "slot_mapping", "block_tables", "seq_lens")
 class DecodeStep:
     def __init__(self, k_cache: torch.Tensor, v_cache: torch.Tensor, *, num_seqs: int, num_heads: int,
                  max_blocks_per_seq: int, scale: float, index_dtype: torch.dtype = torch.int64,
-                 alibi_slopes: torch.Tensor | None = None):
+                 alibi_slopes: torch.Tensor | None = None, direct_output: bool = False):
         if not (k_cache.is_cuda and v_cache.is_cuda):
             raise RuntimeError("DecodeStep needs the cache pools on a GPU; there is no CPU fallback")
         self.k_cache, self.v_cache = k_cache, v_cache
@@ -61,6 +63,9 @@ class DecodeStep:
         self.out = torch.empty((num_seqs, num_heads, vd), dtype=dt, device=self.device)
         self.host_out = torch.empty((num_seqs, num_heads, vd), dtype=dt).pin_memory()
         self.d2h_bytes = self.host_out.numel() * self.host_out.element_size()
+        # direct_output: the attention kernels store their rows straight into the pinned host buffer (mapped
+        # into the device's address space) while they run, instead of a device buffer that is copied afterwards
+        self.direct_output = bool(direct_output)
         self._graph = None
         self._stream = torch.cuda.Stream(device=self.device)
 
@@ -68,8 +73,9 @@ class DecodeStep:
         self._dev_arena.copy_(self._host_arena, non_blocking=True)
         ops.paged_caching(self.k_cache, self.v_cache, self.dev["new_k"], self.dev["new_v"], self.dev["slot_mapping"])
         ops.paged_attention(self.dev["q"], self.k_cache, self.v_cache, self.dev["block_tables"], self.dev["seq_lens"],
-                            self.alibi, self.scale, out=self.out)
-        self.host_out.copy_(self.out, non_blocking=True)
+                            self.alibi, self.scale, out=self.host_out if self.direct_output else self.out)
+        if not self.direct_output:
+            self.host_out.copy_(self.out, non_blocking=True)
 
     def capture(self):
         """Warm up (creates descriptors and the workspace outside the capture), then record the step."""

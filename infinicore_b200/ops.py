@@ -91,8 +91,11 @@ def paged_attention(q, k_cache, v_cache, block_tables, cache_lens, alibi_slopes=
 
     q [num_seqs, num_heads, head_size]; k_cache/v_cache [num_blocks, num_kv_heads, block_size,
     head_size]; block_tables [num_seqs, max_blocks] and cache_lens [num_seqs] int64 or int32.
-    Returns `out` (allocated when not given)."""
-    dev = _require_cuda(q, k_cache, v_cache, block_tables, cache_lens, alibi_slopes, out)
+    Returns `out` (allocated when not given).  `out` may also be a PINNED HOST tensor: page-locked memory is
+    mapped into the device's address space, so the kernels store the output rows over PCIe themselves and no
+    device-to-host copy is needed afterwards (valid once the stream has been synchronised)."""
+    host_out = out is not None and not out.is_cuda and out.is_pinned()
+    dev = _require_cuda(q, k_cache, v_cache, block_tables, cache_lens, alibi_slopes, None if host_out else out)
     if out is None:
         out = torch.empty((*q.shape[:-1], v_cache.shape[3]), dtype=q.dtype, device=q.device)
     st = _state(dev)

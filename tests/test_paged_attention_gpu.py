@@ -480,16 +480,18 @@ def test_python_operators_match_the_abi_path(abi):
     assert torch.equal(got, again)
 
 
-def test_decode_step_graph_replay_matches_direct_calls(abi):
+@pytest.mark.parametrize("direct_output", [False, True])
+def test_decode_step_graph_replay_matches_direct_calls(abi, direct_output):
     """infinicore_b200.DecodeStep: host inputs -> H2D -> caching -> attention -> D2H captured once and
-    replayed; two replays with different inputs, each checked against the oracle."""
+    replayed; two replays with different inputs, each checked against the oracle.  With direct_output the
+    kernels store the rows into the pinned host buffer themselves (no copy node)."""
     import infinicore_b200 as ib
 
     base = workloads.build_case("step", dtype=torch.bfloat16, seq_lens=[100, 37, 64, 5, 900, 16], num_heads=32, num_kv_heads=8,
                                 head_size=128, block_size=16, seed=61)
     d = base.to("cuda")
     step = ib.DecodeStep(d.k_cache, d.v_cache, num_seqs=6, num_heads=32, max_blocks_per_seq=base.block_tables.shape[1],
-                         scale=base.scale)
+                         scale=base.scale, direct_output=direct_output)
     kb, vb = torch_to_bits(base.k_cache).copy(), torch_to_bits(base.v_cache).copy()
     g = torch.Generator().manual_seed(62)
     for round_ in range(2):
