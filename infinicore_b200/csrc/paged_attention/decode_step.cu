@@ -33,6 +33,7 @@ struct StepDescriptor {
     size_t workspace_bytes;
     ptrdiff_t new_k_seq_stride, new_v_seq_stride;
     bool rows_vectorisable; // row starts stay 16-byte aligned given aligned bases
+    int fuse_mode = -1; // INFINIOP_PAGED_DECODE_STEP_FUSE: 1 always hand the rows to the attention kernel, 0 never, unset: by batch size
     // RoPE form only
     bool has_rope = false;
     bool gpt_j = false;
@@ -282,6 +283,9 @@ infiniStatus_t createStep(
         return INFINI_STATUS_BAD_PARAM;
     }
     d->workspace_bytes = d->stream.eligible ? d->stream.workspace_bytes : 0;
+    if (const char *fuse = std::getenv("INFINIOP_PAGED_DECODE_STEP_FUSE")) {
+        d->fuse_mode = std::strcmp(fuse, "1") == 0 ? 1 : (std::strcmp(fuse, "0") == 0 ? 0 : -1);
+    }
     if (rope) {
         const size_t elem = b200::dtypeSize(info.dtype);
         d->attention_workspace_bytes = roundUp256(d->workspace_bytes);
@@ -364,8 +368,14 @@ infiniStatus_t runStep(
     p.new_k_seq_stride = new_k_seq_stride;
     p.new_v_seq_stride = d->new_v_seq_stride;
     const bool rows_vectorisable = (new_k_seq_stride % 8) == 0 && (d->new_v_seq_stride % 8) == 0;
-    const bool fused = d->stream.eligible && b200::paged_attention::streamTakesPointers(d->stream, p, workspace) && rows_vectorisable
-                       && ((addr(new_k) | addr(new_v)) & 15u) == 0;
+    // The row hand-over costs a worker one dependent round trip to global memory at the end of every unit
+    // (sequence, kv-head, head tile).  With at most one unit per worker on average that is cheaper than a
+    // launch; with several it piles up (256 ragged sequences: 0.786 ms against 0.735 ms for append kernel +
+    // attention), so larger batches take the append kernel.  INFINIOP_PAGED_DECODE_STEP_FUSE = 1 | 0 overrides.
+    const size_t units = I.num_seqs * I.num_kv_heads * static_cast<size_t>(d->stream.head_tiles_per_group);
+    const bool wanted = d->fuse_mode == 1 || (d->fuse_mode < 0 && units <= static_cast<size_t>(d->stream.num_workers));
+    const bool fused = wanted && d->stream.eligible && b200::paged_attention::streamTakesPointers(d->stream, p, workspace)
+                       && rows_vectorisable && ((addr(new_k) | addr(new_v)) & 15u) == 0;
     if (fused) {
         return b200::paged_attention::launchDecodeStream(I, d->stream, p, workspace, workspace_size, cuda_stream);
     }

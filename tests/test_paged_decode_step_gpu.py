@@ -309,3 +309,20 @@ def test_rope_form_refuses_bad_tables(abi):
             abi.paged_decode_step_rope(d.q, d.k_cache, d.v_cache, d.new_k, d.new_v, d.block_tables, d.seq_lens, d.scale,
                                        bad_pos, bad_sin, bad_sin if bad_sin.shape != sin.shape or bad_sin.dtype != sin.dtype else cos, 1)
         assert err.value.status == code
+
+
+@pytest.mark.parametrize("fuse", [None, "1", "0"])
+def test_large_batches_take_the_append_kernel_unless_told_otherwise(abi, fuse, monkeypatch):
+    """More units (sequence x kv-head x head tile) than workers: by default the rows go through the append
+    kernel; INFINIOP_PAGED_DECODE_STEP_FUSE = 1 hands them to the attention kernel all the same, 0 never does.
+    Every route gives the same caches and outputs."""
+    if fuse is None:
+        monkeypatch.delenv("INFINIOP_PAGED_DECODE_STEP_FUSE", raising=False)
+    else:
+        monkeypatch.setenv("INFINIOP_PAGED_DECODE_STEP_FUSE", fuse)
+    gen = torch.Generator().manual_seed(57)
+    lens = torch.randint(1, 200, (320,), generator=gen).tolist()
+    c = workloads.build_case("many", dtype=torch.bfloat16, seq_lens=lens, num_heads=32, num_kv_heads=8, head_size=128,
+                             block_size=16, seed=58)
+    run_and_check(abi, c, None, poison=True)
+    run_and_check_rope(abi, c, None, 1)
