@@ -15,6 +15,7 @@
 #include <map>
 #include <sstream>
 #include <string>
+#include <thread>
 #include <vector>
 
 namespace ib = infinicore_b200;
@@ -236,6 +237,50 @@ int main(int argc, char **argv) {
             report << "evictions " << after.evictions - before.evictions << "\n";
             report << "cached " << ib::cached_descriptors() << "\n";
             report << "capacity " << ib::kDescriptorCacheCapacity << "\n";
+        }
+        // J. two more host threads at once, each with its own handle, descriptor cache, stream and workspace
+        //    (the layer's state is per thread; libinfinirt's current device is too, so each thread selects it)
+        {
+            struct Job {
+                ib::Tensor kc, vc, out;
+                std::string error;
+            };
+            Job jobs[2];
+            for (int t = 0; t < 2; ++t) {
+                const std::string tag = "_j" + std::to_string(t);
+                jobs[t].kc = copyOf("k_cache", "k_cache" + tag);
+                jobs[t].vc = copyOf("v_cache", "v_cache" + tag);
+                jobs[t].out = zeros("out" + tag, dt, out_shape);
+            }
+            auto work = [&](Job *job) {
+                try {
+                    ib::check(infinirtSetDevice(INFINI_DEVICE_NVIDIA, 0), "infinirtSetDevice");
+                    infinirtStream_t stream = nullptr;
+                    ib::check(infinirtStreamCreate(&stream), "infinirtStreamCreate");
+                    for (int i = 0; i < 20; ++i) {
+                        ib::op::paged_caching_(job->kc, job->vc, new_k, new_v, slots, stream);
+                        ib::op::paged_attention_(job->out, q, job->kc, job->vc, tables, lens, std::nullopt, scale, stream);
+                    }
+                    ib::check(infinirtStreamSynchronize(stream), "infinirtStreamSynchronize");
+                    if (ib::cache_stats().misses != 2) {
+                        job->error = "a thread's cache should have missed exactly twice";
+                    }
+                    ib::clear_cache();
+                    ib::check(infinirtStreamDestroy(stream), "infinirtStreamDestroy");
+                } catch (const std::exception &e) {
+                    job->error = e.what();
+                }
+            };
+            std::thread a(work, &jobs[0]), b(work, &jobs[1]);
+            a.join();
+            b.join();
+            for (int t = 0; t < 2; ++t) {
+                if (!jobs[t].error.empty()) {
+                    throw std::runtime_error("thread " + std::to_string(t) + ": " + jobs[t].error);
+                }
+                save("out_j" + std::to_string(t));
+            }
+            report << "threads 2\n";
         }
         // I. a rejected call surfaces as an exception carrying the status
         try {

@@ -5,7 +5,8 @@ CPU: the header and its test program compile with g++ -Wall -Wextra and link aga
 GPU: tests/cpp/infinicore_ops_test.cpp runs every wrapper on seeded inputs written here; its outputs are
 checked against the CPU oracle (caches bit-exact, attention within fp16 2e-3 / 2e-3, bf16 1e-2 / 1e-2), its
 report against the expected cache behaviour (second calls are hits, capture creates nothing, eviction keeps
-the cache bounded, a rejected call throws with its status)."""
+the cache bounded, a rejected call throws with its status, two more host threads with their own state agree
+bit for bit with the main thread)."""
 import subprocess
 from pathlib import Path
 
@@ -28,7 +29,7 @@ def build_program(out_dir: Path) -> Path:
 
     build()
     exe = out_dir / "infinicore_ops_test"
-    cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-Wextra", "-Werror", f"-I{ROOT / 'include'}", str(SOURCE), "-o", str(exe),
+    cmd = ["g++", "-std=c++17", "-O1", "-pthread", "-Wall", "-Wextra", "-Werror", f"-I{ROOT / 'include'}", str(SOURCE), "-o", str(exe),
            f"-L{LIBDIR}", "-linfiniop", "-linfinirt", f"-Wl,-rpath,{LIBDIR}"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     assert res.returncode == 0, res.stdout + res.stderr
@@ -97,7 +98,7 @@ def test_every_wrapper_against_the_oracle(tmp_path):
     for tag in ("a", "b"):
         assert np.array_equal(torch_to_bits(read_output(tmp_path, f"k_cache_{tag}", c.k_cache)), kb), tag
         assert np.array_equal(torch_to_bits(read_output(tmp_path, f"v_cache_{tag}", c.v_cache)), vb), tag
-    for tag in ("a", "b", "g"):
+    for tag in ("a", "b", "g", "j0", "j1"):
         assert_close(read_output(tmp_path, f"out_{tag}", out_like).float().numpy(), want, atol, rtol, f"scenario {tag}")
     # C / D: with the rotary embedding
     q_rot = oracle.rope(torch_to_bits(c.q), pos.numpy(), torch_to_bits(sin), torch_to_bits(cos), 19, False)
@@ -126,3 +127,7 @@ def test_every_wrapper_against_the_oracle(tmp_path):
     assert int(report["evictions"]) >= 10 and int(report["cached"]) <= int(report["capacity"])
     assert report["error_status"] == "10"
     assert report["cached_after_clear"] == "0"
+    assert report["threads"] == "2"
+    # the two extra host threads ran the same kernels on the same inputs as scenario A: identical bits
+    for tag in ("j0", "j1"):
+        assert torch.equal(read_output(tmp_path, f"out_{tag}", out_like).view(torch.int16), read_output(tmp_path, "out_a", out_like).view(torch.int16))
