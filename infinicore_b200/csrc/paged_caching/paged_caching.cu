@@ -6,12 +6,13 @@
 // slot skipped, K and V copied element for element).  The copy is a pure byte move, so the
 // result is bit-exact for every dtype.
 //
-// Kernel shape: one warp moves one (token, kv-head) row of K or of V.  A row is
-// head_size * sizeof(T) contiguous bytes on both sides (last-dim stride is 1), so when the
-// row length, both base pointers and all strides are 16-byte multiples the warp moves it
-// with 128-bit loads/stores; otherwise it falls back to element-sized accesses.  The
-// workload is tiny (config "Llama-3-8B decode": 64 tokens x 8 heads x 256 B x {K,V} =
-// 256 KiB in, 256 KiB out) and launch-latency bound; the grid is sized to the row count.
+// Kernel shape: a row is head_size * sizeof(T) contiguous bytes on both sides (last-dim stride
+// is 1).  When the row lengths, the base pointers and all strides are 16-byte multiples it is
+// cut into 128-bit words, otherwise into elements; one thread moves word i of the K row and of
+// the V row of one (token, kv-head), consecutive threads consecutive words.  In a decode step the
+// workload is tiny (config "Llama-3-8B decode": 64 tokens x 8 heads x 256 B x {K,V} = 256 KiB in,
+// 256 KiB out) and launch-latency bound; after a prefill it is tens of thousands of tokens and
+// HBM-bound.  The grid is sized to the word count.
 #include "../common.h"
 
 #include <cstdlib>
@@ -106,7 +107,9 @@ struct KernelArgs {
     const unsigned char *k;
     const unsigned char *v;
     const int64_t *slot_mapping;
-    long long num_rows; // num_tokens * num_kv_heads * 2 (K rows then V rows interleaved per (token, head))
+    long long num_pairs; // num_tokens * num_kv_heads: a K row and a V row each
+    int items_per_pair;  // words of the longer of the two rows
+    int small;           // num_pairs * items_per_pair (rounded up to whole blocks) fits 32 bits
     int num_kv_heads;
     int block_size;
     int k_row_bytes;
@@ -115,50 +118,70 @@ struct KernelArgs {
     long long k_blk, k_head, k_slot, v_blk, v_head, v_slot;
 };
 
-constexpr int kWarpsPerBlock = 8;
+constexpr int kThreads = 128;
 
+// One thread per item of a (token, kv-head) pair: item i is the i-th Vec-sized word of the K row and of the
+// V row (a thread skips the side whose row is shorter than i words).  Consecutive threads take consecutive
+// words, so a warp covers whole rows with 128-bit accesses and both loads are in flight before the first
+// store.  The same kernel serves a decode step (64 tokens, launch-latency bound) and a prefill-sized scatter
+// (tens of thousands of tokens, HBM-bound).
 template <typename Vec>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
-    pagedCachingScatterKernel(const KernelArgs a) {
+__global__ void __launch_bounds__(kThreads) pagedCachingScatterKernel(const KernelArgs a) {
     // Launched with the programmatic-serialization attribute: wait for the preceding kernel in the
     // stream (which may still be reading the pools or producing k/v), then let the next one start
     // its prologue.  Both are no-ops for a normal launch.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const long long row = static_cast<long long>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
-    if (row >= a.num_rows) {
+    long long pair, token;
+    int item, head;
+    if (a.small) {
+        // fewer than 2^32 items: 32-bit divisions (a 64-bit one costs several times as much)
+        const unsigned idx = blockIdx.x * static_cast<unsigned>(kThreads) + threadIdx.x;
+        const unsigned pr = idx / static_cast<unsigned>(a.items_per_pair);
+        const unsigned tk = pr / static_cast<unsigned>(a.num_kv_heads);
+        item = static_cast<int>(idx - pr * a.items_per_pair);
+        head = static_cast<int>(pr - tk * a.num_kv_heads);
+        pair = pr;
+        token = tk;
+    } else {
+        const long long idx = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+        pair = idx / a.items_per_pair;
+        item = static_cast<int>(idx - pair * a.items_per_pair);
+        head = static_cast<int>(pair % a.num_kv_heads);
+        token = pair / a.num_kv_heads;
+    }
+    if (pair >= a.num_pairs) {
         return;
     }
-    const int lane = threadIdx.x & 31;
-    const int is_v = static_cast<int>(row & 1);
-    const long long th = row >> 1;
-    const int head = static_cast<int>(th % a.num_kv_heads);
-    const long long token = th / a.num_kv_heads;
-
     const int64_t slot = a.slot_mapping[token];
     if (slot < 0) {
         return; // padding token
     }
-    const int64_t block = slot / a.block_size;
-    const int64_t off = slot % a.block_size;
-
-    const unsigned char *src;
-    unsigned char *dst;
-    int bytes;
-    if (is_v) {
-        src = a.v + token * a.v_src_token + head * a.v_src_head;
-        dst = a.v_cache + block * a.v_blk + head * a.v_head + off * a.v_slot;
-        bytes = a.v_row_bytes;
+    long long block, off;
+    if (slot <= 0x7fffffffLL) {
+        const unsigned s32 = static_cast<unsigned>(slot);
+        const unsigned blk = s32 / static_cast<unsigned>(a.block_size);
+        block = blk;
+        off = s32 - blk * static_cast<unsigned>(a.block_size);
     } else {
-        src = a.k + token * a.k_src_token + head * a.k_src_head;
-        dst = a.k_cache + block * a.k_blk + head * a.k_head + off * a.k_slot;
-        bytes = a.k_row_bytes;
+        block = slot / a.block_size;
+        off = slot % a.block_size;
     }
-    const int n = bytes / static_cast<int>(sizeof(Vec));
-    const Vec *s = reinterpret_cast<const Vec *>(src);
-    Vec *d = reinterpret_cast<Vec *>(dst);
-    for (int i = lane; i < n; i += 32) {
-        d[i] = s[i];
+    const long long byte = static_cast<long long>(item) * static_cast<long long>(sizeof(Vec));
+    const bool has_k = byte < a.k_row_bytes;
+    const bool has_v = byte < a.v_row_bytes;
+    Vec k_item{}, v_item{};
+    if (has_k) {
+        k_item = *reinterpret_cast<const Vec *>(a.k + token * a.k_src_token + head * a.k_src_head + byte);
+    }
+    if (has_v) {
+        v_item = *reinterpret_cast<const Vec *>(a.v + token * a.v_src_token + head * a.v_src_head + byte);
+    }
+    if (has_k) {
+        *reinterpret_cast<Vec *>(a.k_cache + block * a.k_blk + head * a.k_head + off * a.k_slot + byte) = k_item;
+    }
+    if (has_v) {
+        *reinterpret_cast<Vec *>(a.v_cache + block * a.v_blk + head * a.v_head + off * a.v_slot + byte) = v_item;
     }
 }
 
@@ -176,7 +199,7 @@ static infiniStatus_t launch(const Descriptor &desc,
     a.k = static_cast<const unsigned char *>(k);
     a.v = static_cast<const unsigned char *>(v);
     a.slot_mapping = static_cast<const int64_t *>(slot_mapping);
-    a.num_rows = static_cast<long long>(I.num_tokens) * static_cast<long long>(I.num_kv_heads) * 2;
+    a.num_pairs = static_cast<long long>(I.num_tokens) * static_cast<long long>(I.num_kv_heads);
     a.num_kv_heads = static_cast<int>(I.num_kv_heads);
     a.block_size = static_cast<int>(I.block_size);
     a.k_row_bytes = static_cast<int>(I.head_size * I.elem_size);
@@ -192,13 +215,20 @@ static infiniStatus_t launch(const Descriptor &desc,
     a.v_head = I.v_cache_head_stride * es;
     a.v_slot = I.v_cache_slot_stride * es;
 
-    const long long blocks = (a.num_rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    B200_RETURN_IF(blocks > 0x7fffffffLL, INFINI_STATUS_BAD_TENSOR_SHAPE);
-    const dim3 grid(static_cast<unsigned>(blocks));
-    const dim3 block(kWarpsPerBlock * 32);
-
     auto aligned16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     const bool vec16 = I.strides_vec16 && aligned16(k_cache) && aligned16(v_cache) && aligned16(k) && aligned16(v);
+    const int word = vec16 ? 16 : static_cast<int>(I.elem_size);
+    const int longer = a.k_row_bytes > a.v_row_bytes ? a.k_row_bytes : a.v_row_bytes;
+    a.items_per_pair = longer / word;
+    if (a.items_per_pair == 0) {
+        return INFINI_STATUS_SUCCESS; // rows of zero width
+    }
+    const long long blocks = (a.num_pairs * a.items_per_pair + kThreads - 1) / kThreads;
+    B200_RETURN_IF(blocks > 0x7fffffffLL, INFINI_STATUS_BAD_TENSOR_SHAPE);
+    a.small = blocks * kThreads <= 0xffffffffLL ? 1 : 0;
+    const dim3 grid(static_cast<unsigned>(blocks));
+    const dim3 block(kThreads);
+
     cudaLaunchAttribute pdl;
     pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     pdl.val.programmaticStreamSerializationAllowed = desc.use_pdl ? 1 : 0;

@@ -147,9 +147,57 @@ def run_kv_caching(spec, out_path):
     torch.save(result, out_path)
 
 
+def run_paged_caching(spec, out_path):
+    """spec = {"op": "paged_caching", "tokens": n, "kv_heads": h, "head": d, "block": b, "dtype": "...", "seed": n, "iters": N}:
+    a prefill-sized scatter (every slot of the pool written once, in shuffled order)."""
+    import ctypes
+
+    import abi
+    from infinicore_b200.libinfiniop import LIBINFINIOP, check_error, library_paths
+
+    dtype = getattr(torch, spec["dtype"])
+    gen = torch.Generator().manual_seed(int(spec.get("seed", 0)))
+    tokens, kvh, hd, bs = int(spec["tokens"]), int(spec["kv_heads"]), int(spec["head"]), int(spec["block"])
+    blocks = (tokens + bs - 1) // bs
+    k_cache = torch.zeros((blocks, kvh, bs, hd), dtype=dtype, device="cuda")
+    v_cache = torch.zeros((blocks, kvh, bs, hd), dtype=dtype, device="cuda")
+    k, v = torch.randn((tokens, kvh, hd), generator=gen).to(dtype).cuda(), torch.randn((tokens, kvh, hd), generator=gen).to(dtype).cuda()
+    # tokens of a prompt land in consecutive slots of shuffled blocks, as a block table would place them
+    order = torch.randperm(blocks, generator=gen)
+    slots = (order.repeat_interleave(bs) * bs + torch.arange(bs).repeat(blocks))[:tokens].to(torch.int64).cuda()
+    status, desc = abi.create_caching(k_cache, v_cache, k, v, slots)
+    check_error(status)
+
+    def call(stream=None):
+        check_error(LIBINFINIOP.infiniopPagedCaching(desc, None, 0, k_cache.data_ptr(), v_cache.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                     slots.data_ptr(), stream))
+
+    call()
+    torch.cuda.synchronize()
+    result = {"k_cache": k_cache.cpu(), "v_cache": v_cache.cpu(), "library": str(library_paths()[1])}
+    iters = int(spec.get("iters", 0))
+    if iters:
+        stream = torch.cuda.current_stream().cuda_stream
+        for _ in range(3):
+            call(stream)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            call(stream)
+        b.record()
+        torch.cuda.synchronize()
+        result["ms"] = a.elapsed_time(b) / iters
+        result["bytes"] = 2 * 2 * k.numel() * k.element_size()
+    check_error(LIBINFINIOP.infiniopDestroyPagedCachingDescriptor(desc))
+    torch.save(result, out_path)
+
+
 def main():
     spec = json.loads(sys.argv[1])
     out_path = sys.argv[2]
+    if spec.get("op") == "paged_caching":
+        return run_paged_caching(spec, out_path)
     if spec.get("op") == "rope":
         return run_rope(spec, out_path)
     if spec.get("op") == "kv_caching":

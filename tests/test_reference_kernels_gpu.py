@@ -132,3 +132,23 @@ def test_kv_caching_same_results_as_the_reference_kernel(spec, tmp_path):
     if "ms" in ref:
         print(f"kv_caching {spec['shape']}: reference {ref['ms'] * 1e3:.1f} us, this library {mine['ms'] * 1e3:.1f} us "
               f"({mine['bytes'] / mine['ms'] / 1e6:.0f} GB/s)")
+
+
+PAGED_CACHING_SPECS = [
+    # a prefill-sized scatter: 8 prompts x 2048 tokens, 8 kv-heads, head 128 (134 MB of rows in, 134 MB out)
+    {"op": "paged_caching", "tokens": 16384, "kv_heads": 8, "head": 128, "block": 16, "dtype": "bfloat16", "seed": 74, "iters": 20},
+    {"op": "paged_caching", "tokens": 1000, "kv_heads": 2, "head": 64, "block": 32, "dtype": "float16", "seed": 75},
+]
+
+
+@pytest.mark.skipif(not (REF_ROOT / "lib" / "libinfiniop.so").is_file(), reason="oracle/_ref not built")
+@pytest.mark.parametrize("spec", PAGED_CACHING_SPECS, ids=lambda s: f"{s['tokens']}x{s['kv_heads']}x{s['head']}")
+def test_prefill_sized_paged_caching_same_as_the_reference_kernel(spec, tmp_path):
+    ref = run(spec, tmp_path, reference=True)
+    mine = run(spec, tmp_path, reference=False)
+    assert "oracle/_ref" in ref["library"] and "oracle/_ref" not in mine["library"]
+    for name in ("k_cache", "v_cache"):
+        assert torch.equal(mine[name].view(torch.int16), ref[name].view(torch.int16)), f"{name} differs from the reference kernel's"
+    if "ms" in ref:
+        print(f"paged_caching {spec['tokens']} tokens: reference {ref['ms'] * 1e3:.1f} us, this library {mine['ms'] * 1e3:.1f} us "
+              f"({mine['bytes'] / mine['ms'] / 1e6:.0f} GB/s)")
