@@ -94,6 +94,21 @@ def test_null_pointers_are_reported():
     assert LIBINFINIOP.infinirtGetDevice(None, None) == 4
     assert LIBINFINIOP.infiniopGetPagedAttentionWorkspaceSize(None, None) == 4
     assert LIBINFINIOP.infiniopDestroyPagedCachingDescriptor(None) == 4
+    # the operators beside the path: a missing handle, descriptor or size pointer is reported, not dereferenced
+    from infinicore_b200.libinfiniop import infiniopOperatorDescriptor_t
+
+    d = infiniopOperatorDescriptor_t()
+    assert LIBINFINIOP.infiniopCreateRoPEDescriptor(None, ctypes.byref(d), None, None, None, None, None, 0) == 4
+    assert LIBINFINIOP.infiniopGetRoPEWorkspaceSize(None, None) == 4
+    assert LIBINFINIOP.infiniopRoPE(None, None, 0, None, None, None, None, None, None) == 4
+    assert LIBINFINIOP.infiniopDestroyRoPEDescriptor(None) == 4
+    assert LIBINFINIOP.infiniopCreateKVCachingDescriptor(None, ctypes.byref(d), None, None, None, None, None) == 4
+    assert LIBINFINIOP.infiniopGetKVCachingWorkspaceSize(None, None) == 4
+    assert LIBINFINIOP.infiniopKVCaching(None, None, 0, None, None, None, None, None, None) == 4
+    assert LIBINFINIOP.infiniopDestroyKVCachingDescriptor(None) == 4
+    assert LIBINFINIOP.infiniopCreatePagedDecodeStepRoPEDescriptor(None, ctypes.byref(d), *([None] * 12), 1, 1.0) == 4
+    assert LIBINFINIOP.infiniopPagedDecodeStepRoPE(None, None, 0, *([None] * 13)) == 4
+    assert LIBINFINIOP.infiniopGetPagedDecodeStepWorkspaceSize(None, None) == 4
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU behaviour")
@@ -115,6 +130,12 @@ def test_operators_refuse_cpu_tensors():
         ib.paged_attention(q, kc, kc, torch.zeros(1, 1, dtype=torch.int64), torch.ones(1, dtype=torch.int64))
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         ib.paged_caching(kc, kc, q, q, torch.zeros(1, dtype=torch.int64))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        ib.rope(q, torch.zeros(1, dtype=torch.int64), torch.zeros(4, 32, dtype=torch.float16), torch.zeros(4, 32, dtype=torch.float16))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        ib.kv_caching(kc, kc, kc[:, :, :1], kc[:, :, :1], torch.zeros(1, dtype=torch.int64))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        ib.paged_decode_step(q, kc, kc, q, q, torch.zeros(1, 1, dtype=torch.int64), torch.ones(1, dtype=torch.int64))
 
 
 def test_missing_library_fails_loudly(tmp_path, monkeypatch):
