@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout (it is not needed to run the tests):
 
-    python tests/golden/make_golden.py /path/to/InfiniCore [--only=attention|caching|prefill|rope|kv_caching]
+    python tests/golden/make_golden.py /path/to/InfiniCore [--only=attention|caching|prefill|rope|kv_caching|layer]
 
 The two functions executed are imported unmodified from the reference tree:
   ref_single_query_cached_kv_attention   test/infiniop/paged_attention.py:47-88
@@ -250,6 +250,41 @@ def make_kv_caching(ref_kvc):
         print("wrote", name, shape)
 
 
+def layer_cases():
+    # (name, case, algorithm): a whole decode layer = the reference's four checkers in the order its callers
+    # issue the operators: rotary embedding of q and of the new K row, cache scatter, attention
+    yield "layer_bf16_gqa4_hd128_neox", workloads.build_case(
+        "x", dtype=torch.bfloat16, seq_lens=[100, 17, 1, 60, 33], num_heads=16, num_kv_heads=4, head_size=128,
+        block_size=16, seed=501), 1
+    yield "layer_fp16_gqa2_hd64_gptj", workloads.build_case(
+        "x", dtype=torch.float16, seq_lens=[64, 5, 100], num_heads=4, num_kv_heads=2, head_size=64,
+        block_size=16, seed=502), 0
+
+
+def make_layers(ref_attn, ref_cache, ref_rope):
+    for name, c, algo in layer_cases():
+        pos = (c.seq_lens - 1).clamp(min=0)
+        table_len = int(pos.max()) + 1
+        freqs = 1.0 / (1e4 ** (torch.arange(0, c.head_size, 2).float() / c.head_size))
+        angles = torch.outer(torch.arange(table_len).float(), freqs)
+        sin_table, cos_table = torch.sin(angles).to(c.dtype), torch.cos(angles).to(c.dtype)
+        member = ref_rope.Algorithm.GPT_J if algo == 0 else ref_rope.Algorithm.GPT_NEOX
+        q_rot, k_rot = torch.zeros_like(c.q), torch.zeros_like(c.new_k)
+        ref_rope.rotary_embedding(q_rot, c.q, sin_table[pos], cos_table[pos], 0, member)
+        ref_rope.rotary_embedding(k_rot, c.new_k, sin_table[pos], cos_table[pos], 0, member)
+        k_after, v_after = ref_cache.ref_paged_caching(c.k_cache.clone(), c.v_cache.clone(), k_rot, c.new_v, c.slot_mapping)
+        out = ref_attn.ref_single_query_cached_kv_attention(q_rot, k_after, v_after, c.block_tables, c.seq_lens, c.scale, None)
+        np.savez_compressed(
+            HERE / f"{name}.npz",
+            dtype=np.int64(DTYPE_CODE[c.dtype]), algo=np.int64(algo), scale=np.float32(c.scale),
+            q=bits(c.q), k_cache=bits(c.k_cache), v_cache=bits(c.v_cache), new_k=bits(c.new_k), new_v=bits(c.new_v),
+            slot_mapping=c.slot_mapping.numpy(), block_tables=c.block_tables.numpy(), seq_lens=c.seq_lens.numpy(),
+            pos_ids=pos.numpy(), sin_table=bits(sin_table), cos_table=bits(cos_table),
+            q_rot=bits(q_rot), k_cache_after=bits(k_after), v_cache_after=bits(v_after), out=bits(out),
+        )
+        print("wrote", name, tuple(out.shape))
+
+
 def main():
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
     only = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--only=")]
@@ -266,6 +301,8 @@ def main():
         make_rope(ref_rope)
     if not only or "kv_caching" in only:
         make_kv_caching(ref_kvc)
+    if not only or "layer" in only:
+        make_layers(ref_attn, ref_cache, ref_rope)
 
 
 if __name__ == "__main__":

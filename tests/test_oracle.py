@@ -207,3 +207,24 @@ def test_kv_caching_skips_rows_outside_the_cache():
     assert np.array_equal(kc[0, 0], [[0, 0], [0, 0], [1, 2], [3, 4]])          # third row would land at 4: skipped
     assert np.array_equal(kc[1, 0], [[9, 10], [11, 12], [0, 0], [0, 0]])       # first row would land at -1: skipped
     assert np.array_equal(vc, -kc)
+
+
+# ---- a whole decode layer: rotary embedding of q and the new K row, scatter, attention --------------------
+
+
+@pytest.mark.parametrize("name", golden_names("layer_"))
+def test_decode_layer_composition_matches_the_reference_checkers(name):
+    """The four oracle functions chained as a decode layer chains the operators, against the same chain of the
+    reference's own checkers: rotated rows and caches bit for bit, attention as in the attention tests."""
+    g = load_golden(name)
+    dt, gpt_j = int(g["dtype"]), int(g["algo"]) == 0
+    q_rot = oracle.rope(g["q"], g["pos_ids"], g["sin_table"], g["cos_table"], dt, gpt_j)
+    k_rot = oracle.rope(g["new_k"], g["pos_ids"], g["sin_table"], g["cos_table"], dt, gpt_j)
+    assert np.array_equal(q_rot, g["q_rot"])
+    kc, vc = g["k_cache"].copy(), g["v_cache"].copy()
+    oracle.paged_caching(kc, vc, k_rot, g["new_v"], g["slot_mapping"])
+    assert np.array_equal(kc, g["k_cache_after"]) and np.array_equal(vc, g["v_cache_after"])
+    got = oracle.paged_attention(q_rot, kc, vc, g["block_tables"], g["seq_lens"], float(g["scale"]), dt, None, mode="reference")
+    want = bits_to_float(g["out"], dt)
+    err = np.abs(got - want)
+    assert np.all(err <= 4 * _ulp(dt, want) + 1e-3 * np.abs(want).max()), f"max err {err.max():.3e}"

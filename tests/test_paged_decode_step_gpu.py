@@ -326,3 +326,22 @@ def test_large_batches_take_the_append_kernel_unless_told_otherwise(abi, fuse, m
                              block_size=16, seed=58)
     run_and_check(abi, c, None, poison=True)
     run_and_check_rope(abi, c, None, 1)
+
+
+@pytest.mark.parametrize("path", [None, "generic"])
+@pytest.mark.parametrize("name", ["layer_bf16_gqa4_hd128_neox", "layer_fp16_gqa2_hd64_gptj"])
+def test_rope_form_against_the_reference_checkers_chained(abi, name, path):
+    """infiniopPagedDecodeStepRoPE against golden files made by chaining the reference's own checkers (rotary
+    embedding of q and new K, cache scatter, attention): caches bit for bit, output within the decode tolerance."""
+    from helpers import bits_to_float, bits_to_torch, load_golden
+
+    g = load_golden(name)
+    dt = int(g["dtype"])
+    t = {k: bits_to_torch(g[k], dt).cuda() for k in ("q", "k_cache", "v_cache", "new_k", "new_v", "sin_table", "cos_table")}
+    idx = {k: torch.from_numpy(g[k]).cuda() for k in ("block_tables", "seq_lens", "pos_ids")}
+    got = abi.paged_decode_step_rope(t["q"], t["k_cache"], t["v_cache"], t["new_k"], t["new_v"], idx["block_tables"], idx["seq_lens"],
+                                     float(g["scale"]), idx["pos_ids"], t["sin_table"], t["cos_table"], int(g["algo"]), path=path)
+    assert np.array_equal(torch_to_bits(t["k_cache"]), g["k_cache_after"])
+    assert np.array_equal(torch_to_bits(t["v_cache"]), g["v_cache_after"])
+    atol, rtol = ATTN_TOL[dt]
+    assert_close(got.float().cpu().numpy(), bits_to_float(g["out"], dt), atol, rtol, name)
