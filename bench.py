@@ -2,15 +2,22 @@
 """Benchmark of the paged decode hot path: one step = infiniopPagedCaching (the newest token's
 K/V rows) followed by infiniopPagedAttention over the paged KV cache.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--blocks R] [--workload c2|c3|c4|c5] [--impl reference]
 
 One JSON line on stdout (rank 0).  `value` is KV-read bandwidth of the whole job in GB/s:
 algorithmic KV bytes of one step (every K and V element of every live token once, independent of
 the GQA group size and of how the work is split) summed over all ranks, divided by the device-timed
-step (max over ranks).  Multi-GPU runs shard by sequence: every rank owns its sequences, its block
-tables and its own cache pool; there is no data-path collective (scaling "weak": each rank runs a
-full copy of the workload with its own seed; workload c5 instead splits one 2048-sequence batch
-round-robin, "strong").
+step (max over ranks).  The timed region is R blocks of K back-to-back steps, each block bracketed by
+a barrier and a synchronize; `ms_per_step` is the median block (min and max beside it).  Multi-GPU
+runs shard by sequence: every rank owns its sequences, its block tables and its own cache pool; there
+is no data-path collective (scaling "weak": each rank runs a full copy of the workload with its own
+seed; workload c5 instead splits one 2048-sequence batch round-robin, "strong").
+
+Side records in the same line (each guarded: a failure costs the record, never the headline): the
+ragged and the long-context configurations on one GPU (`c3`, `c4`), the 2048-sequence batch split
+over the N ranks under two placement policies (`c5_strong`), at N > 1 the KV-head-sharded mode with
+its two ways of combining the outputs (`head_sharded`), and at N = 1 the reference's own CUDA kernels
+on the same inputs (`reference_gpu`, a child process, only where oracle/_ref was built).
 
 `--impl reference` times the CPU restatement of the reference's checker (oracle/, all host
 threads) on the same workload; only rank 0 works.
@@ -36,9 +43,30 @@ METRIC = "paged_attn_decode_kv_read_bandwidth"
 UNIT = "GB/s"
 FALLBACK_HBM_GBS = 6650.0
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one pagedDecodeStreamKernel launch, from the ncu
-# capture summarised under profiles/ (None until a capture exists for that workload).
-NCU_TRAFFIC_BYTES = {"c2": 1074814000 + 5161000}  # profiles/pagedDecodeStreamKernel_c2.md, launch 1
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel, taken from one ncu
+# capture of this workload.  A capture describes the kernel source it was taken from: the entry is only
+# reported while that source file still has the recorded hash, so it cannot silently go stale.
+NCU_TRAFFIC = {
+    "c2": {"bytes": 1074814000 + 5161000, "kernel": "pagedDecodeStreamKernel<bf16,128,8>", "captured": "2026-11-24",
+           "source": "infinicore_b200/csrc/paged_attention/decode_stream.cu", "source_sha256_16": "a778713ffd339d52"},
+}
+
+
+def ncu_traffic(workload):
+    """(bytes per launch or None, provenance string)."""
+    import hashlib
+
+    rec = NCU_TRAFFIC.get(workload)
+    if rec is None:
+        return None, "no ncu capture of this workload"
+    try:
+        now = hashlib.sha256((ROOT / rec["source"]).read_bytes()).hexdigest()[:16]
+    except OSError:
+        now = None
+    if now != rec["source_sha256_16"]:
+        return None, f"ncu capture of {rec['captured']} predates the current {rec['source']}: not reported"
+    return rec["bytes"], (f"dram__bytes_read.sum + dram__bytes_write.sum of one {rec['kernel']} launch, ncu capture of "
+                          f"{rec['captured']} (kernel source sha256 {rec['source_sha256_16']})")
 
 
 def parse_args():
@@ -46,6 +74,8 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--blocks", type=int, default=15, help="timed blocks of --steps steps; the median block is reported")
+    ap.add_argument("--no-side", action="store_true", help="skip the side records (c3, c4, c5_strong, head_sharded, reference_gpu)")
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c4", "c5", "prefill"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--collective", default="infiniccl", choices=["infiniccl", "torch", "peer"],
@@ -71,22 +101,53 @@ def measured_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
-def workload_config(name, case, n_gpus, mode="seq", collective="infiniccl"):
+WORKLOAD_TEXT = {
+    "c2": "configs[1]: Llama-3-8B-shape decode, bf16, batch 64 per GPU, 32/8 heads, head 128, block 16, every seq_len 4096, "
+          "permuted tables over a 16384-block pool, 64 new K/V rows cached before attention",
+    "c3": "configs[2]: ragged 72B-shape decode, bf16, batch 256, 64/8 heads, head 128, block 16, seq_lens log-uniform [16,32768]",
+    "c4": "configs[3]: long-context decode, fp16, batch 2, 32/8 heads, head 128, block 16, seq_lens 131072",
+    "c5": "configs[4]: 2048-sequence batch, bf16, 64/8 heads, head 128, seq_lens U[1024,8192], round-robin over the GPUs",
+}
+
+
+def workload_lengths(name, rank=0, world=1, mode="seq"):
+    """Sequence lengths one rank holds for a workload (the seeded generators of infinicore_b200.workloads)."""
+    import torch
+
+    from infinicore_b200 import workloads
+
+    if name == "c2":
+        return torch.full((64,), 4096, dtype=torch.int64)
+    if name == "c3":
+        return workloads.config3_lengths(seed=3 + (rank if mode == "seq" else 0))
+    if name == "c4":
+        return torch.full((2,), 131072, dtype=torch.int64)
+    lens = workloads.config5_lengths()
+    return lens[rank::world] if mode == "seq" else lens
+
+
+def workload_config(name, n_gpus, mode="seq", collective="infiniccl"):
+    """The `config` object of the JSON line: a function of the arguments only, so the GPU arm and the
+    reference arm print the same one."""
+    lens = workload_lengths(name, 0, n_gpus, mode)
+    head_mode = mode == "head" and n_gpus > 1
+    kvh = 8 // n_gpus if head_mode else 8
+    tokens = int(lens.sum())
+    kv_bytes = tokens * kvh * 256 * 2
     return {
-        "workload": {
-            "c2": "configs[1]: Llama-3-8B-shape decode, bf16, batch 64 per GPU, 32/8 heads, head 128, block 16, every seq_len 4096, "
-                  "permuted tables over a 16384-block pool, 64 new K/V rows cached before attention",
-            "c3": "configs[2]: ragged 72B-shape decode, bf16, batch 256, 64/8 heads, head 128, block 16, seq_lens log-uniform [16,32768]",
-            "c4": "configs[3]: long-context decode, fp16, batch 2, 32/8 heads, head 128, block 16, seq_lens 131072",
-            "c5": "configs[4]: 2048-sequence batch, bf16, 64/8 heads, head 128, seq_lens U[1024,8192], round-robin over the GPUs",
-        }[name],
-        "num_seqs_per_gpu": case.num_seqs,
-        "tokens_per_gpu": case.total_tokens,
-        "kv_bytes_per_gpu": case.kv_bytes,
-        "parallelism": (f"kv-head-sharded x{n_gpus}, outputs combined per step by {collective}" if mode == "head" and n_gpus > 1
+        "workload": WORKLOAD_TEXT[name],
+        "num_seqs_per_gpu": int(lens.numel()),
+        "tokens_per_gpu": tokens,
+        "kv_bytes_per_gpu": kv_bytes,
+        "parallelism": (f"kv-head-sharded x{n_gpus}, outputs combined per step by {collective}" if head_mode
                         else f"sequence-sharded x{n_gpus}, no collective"),
-        "l2": "inputs larger than L2 (KV working set per step >> 126 MB)" if case.kv_bytes > (256 << 20) else "L2 flushed between steps",
+        "l2": ("inputs larger than L2 (KV working set per step >> 126 MB)" if kv_bytes > (256 << 20)
+               else "L2 flushed between steps (a 256 MB buffer is rewritten before every timed step)"),
     }
+
+
+COLLECTIVE_TEXT = {"infiniccl": "one infinicclAllGather (NCCL)", "torch": "one torch.distributed all-gather (NCCL)",
+                   "peer": "peer stores from the attention kernels into every rank's full output + a barrier"}
 
 
 def make_case(name, rank, world, device, mode="seq"):
@@ -169,23 +230,42 @@ def run_cpu(case, steps, warmup):
 
 
 def reference_arm(args):
+    """The reference's CPU path for this workload (the C/OpenMP port of its torch checker: it has no CPU
+    kernel), W warm-up and exactly K timed steps on every host core this process may use.  A step is a
+    bounded sample of the workload - the whole batch while K steps of it fit into about two minutes,
+    its first n sequences otherwise - and the line says which."""
+    import torch
+
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    from infinicore_b200 import workloads  # noqa: F401  (builders used by cpu_sample)
+
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
     case, sample = cpu_sample(args.workload, args.cpu_seqs)
-    steps = max(1, min(args.steps, 20))
-    warmup = max(1, min(args.warmup, 3))
+    if not args.cpu_seqs:
+        # size the sample from one probe step of the whole batch
+        _, probe_ms, _ = run_cpu(case, steps=1, warmup=0)
+        budget_ms = 120e3 / (steps + warmup)
+        if probe_ms > budget_ms and case.num_seqs > 1:
+            n = max(1, int(case.num_seqs * budget_ms / probe_ms))
+            case, sample = cpu_sample(args.workload, n)
     gbs, ms, threads = run_cpu(case, steps, warmup)
+    full = workload_config(args.workload, args.gpus, args.mode, COLLECTIVE_TEXT[args.collective])
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong" if args.workload == "c5" else "weak", "vs_baseline": None,
         "dtype": "bf16" if args.workload != "c4" else "f16", "data": "synthetic",
-        "config": {"workload": workload_config(args.workload, case, 1)["workload"], "sample": sample},
+        "config": full,
+        "sample": sample + " per step",
         "seqs_per_s": case.num_seqs / (ms / 1e3),
-        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample + " per step"},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample + " per step",
+                         "processes": 1},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-        "note": "the reference has no CPU kernel for this path; this is the C/OpenMP port of its torch checker",
+        "note": "the reference has no CPU kernel for this path; this is the C/OpenMP port of its torch checker, ONE process on "
+                "the host cores whatever --gpus says (a ratio against N GPUs is N GPUs over one CPU process)",
     }
     print(json.dumps(line), flush=True)
 
@@ -381,6 +461,7 @@ def gpu_arm(args):
     import torch.distributed as dist
 
     import infinicore_b200 as ib
+    from infinicore_b200 import sharding, workloads
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -400,72 +481,30 @@ def gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(x):
+    def reduce_ranks(values, op):
+        """Element-wise reduction of a list of floats over the ranks."""
         if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+            return list(values)
+        t = torch.tensor(list(values), dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=op)
+        return t.tolist()
+
+    def max_over_ranks(x):
+        return reduce_ranks([x], dist.ReduceOp.MAX)[0] if world > 1 else x
 
     def min_over_ranks(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MIN)
-        return float(t.item())
+        return reduce_ranks([x], dist.ReduceOp.MIN)[0] if world > 1 else x
 
     def sum_over_ranks(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
+        return reduce_ranks([x], dist.ReduceOp.SUM)[0] if world > 1 else x
 
-    head_mode = args.mode == "head" and world > 1
-    case = make_case(args.workload, rank, world, device, args.mode)
-    peers = None
-    if head_mode and args.collective == "peer":
-        from infinicore_b200 import sharding
+    def all_ranks_ok(ok):
+        """True only if every rank reports ok: every rank then takes the same branch (the branches contain
+        rank-wide reductions, and sometimes collectives)."""
+        return min_over_ranks(1.0 if ok else 0.0) > 0.5
 
-        peers = sharding.PeerOutputs(case.num_seqs, case.num_heads * world, case.v_cache.shape[3], case.dtype, device)
-    step = AbiStep(case, out=peers.local_slice() if peers is not None else None)
     stream = torch.cuda.current_stream(device)
     sptr = stream.cuda_stream
-    small_ws = case.kv_bytes <= (256 << 20)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device) if small_ws else None
-
-    gather_staging = None
-    ccl_comm = None  # infinicclAllGather through libinfiniccl.so; None: torch.distributed's all-gather
-    if head_mode:
-        from infinicore_b200 import sharding
-
-        gather_staging = torch.empty((world, *step.out.shape), dtype=step.out.dtype, device=device)
-        if args.collective == "infiniccl":
-            from infinicore_b200 import ccl
-
-            ccl_comm = ccl.init_from_process_group()
-
-    peer_dests = peers.destinations() if peers is not None else None
-
-    def one_step():
-        step.caching(sptr)
-        if peers is not None:
-            step.attention_multi_out(sptr, peer_dests)
-            peers.barrier()
-        else:
-            step.attention(sptr)
-            if head_mode:
-                sharding.gather_head_sharded(step.out, world, staging=gather_staging, comm=ccl_comm)
-
-    # ---- device-resident timing -------------------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
-        one_step()
-    barrier()
-    sampler = ClockSampler(local_rank)
-    sample_clocks = rank == 0 and not args.no_clocks
-    if sample_clocks:
-        sampler.start()
-    K = args.steps
 
     def timed(fn, iters):
         """Device time of `iters` back-to-back calls of fn, bracketed by a barrier and a synchronize on
@@ -479,19 +518,71 @@ def gpu_arm(args):
         barrier()
         return a_ev.elapsed_time(b_ev)
 
+    def timed_blocks(fn, iters, blocks):
+        """`blocks` timed blocks of `iters` calls; per block the slowest rank's ms per call.  Returns
+        (median, min, max, this rank's own median) over the blocks."""
+        mine = [timed(fn, iters) / iters for _ in range(blocks)]
+        worst = reduce_ranks(mine, dist.ReduceOp.MAX) if world > 1 else mine
+        return statistics.median(worst), min(worst), max(worst), statistics.median(mine)
+
+    head_mode = args.mode == "head" and world > 1
+    case = make_case(args.workload, rank, world, device, args.mode)
+    peers = None
+    if head_mode and args.collective == "peer":
+        peers = sharding.PeerOutputs(case.num_seqs, case.num_heads * world, case.v_cache.shape[3], case.dtype, device)
+    step = AbiStep(case, out=peers.local_slice() if peers is not None else None)
+    small_ws = case.kv_bytes <= (256 << 20)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device) if small_ws else None
+
+    gather_staging = None
+    ccl_comm = None  # infinicclAllGather through libinfiniccl.so; None: torch.distributed's all-gather
+    if head_mode:
+        gather_staging = torch.empty((world, *step.out.shape), dtype=step.out.dtype, device=device)
+        if args.collective == "infiniccl":
+            from infinicore_b200 import ccl
+
+            ccl_comm = ccl.init_from_process_group()
+
+    def one_step():
+        step.caching(sptr)
+        if peers is not None:
+            # the head slice goes into every rank's full output (two alternating buffers), then one barrier
+            step.attention_multi_out(sptr, peers.destinations())
+            peers.barrier()
+            peers.advance()
+        else:
+            step.attention(sptr)
+            if head_mode:
+                sharding.gather_head_sharded(step.out, world, staging=gather_staging, comm=ccl_comm)
+
+    # ---- device-resident timing -------------------------------------------------------------
+    W = max(args.warmup, 3)
+    K = max(args.steps, 1)
+    R = max(args.blocks, 1)
+    for _ in range(W):
+        one_step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sample_clocks = rank == 0 and not args.no_clocks
+    if sample_clocks:
+        sampler.start()
+
     if flush is None:
-        total_ms = timed(one_step, K)
-        flush_ms = 0.0
+        ms_per_step, ms_min, ms_max, _ = timed_blocks(one_step, K, R)
     else:
         # small working set: scrub L2 before every step and time each step on its own
-        total_ms = 0.0
-        for i in range(K):
-            flush.fill_(i & 0xff)
-            total_ms += timed(one_step, 1)
-        flush_ms = 0.0
-    ms_per_step = max_over_ranks((total_ms - flush_ms) / K)
+        per_block = []
+        for _ in range(R):
+            total = 0.0
+            for i in range(K):
+                flush.fill_(i & 0xff)
+                total += timed(one_step, 1)
+            per_block.append(total / K)
+        worst = reduce_ranks(per_block, dist.ReduceOp.MAX) if world > 1 else per_block
+        ms_per_step, ms_min, ms_max = statistics.median(worst), min(worst), max(worst)
+    timed_ms = ms_per_step * K * R
     clock_window = "timed region"
-    if not args.no_clocks and ms_per_step * K < 400.0:
+    if not args.no_clocks and timed_ms < 400.0:
         # Too short for nvidia-smi's 100 ms sampling: keep the identical load running (untimed) so the
         # clocks under this load are still observed.  Every rank runs the same number of extra steps
         # (the count derives from the rank-agreed step time), because a step may contain a collective.
@@ -499,19 +590,19 @@ def gpu_arm(args):
         for _ in range(extra):
             one_step()
         torch.cuda.synchronize()
-        clock_window = f"timed region ({ms_per_step * K:.1f} ms) + {extra} identical untimed steps"
+        clock_window = f"timed region ({timed_ms:.1f} ms) + {extra} identical untimed steps"
     clocks = sampler.stop() if sample_clocks else None
     if clocks is not None:
         clocks["window"] = clock_window
 
-    # the dominant kernel on its own: K attention calls back to back (plan/combine launches included)
-    attn_ms = timed(lambda: step.attention(sptr), K) / K
+    # the dominant kernel on its own: attention calls back to back (plan/combine launches included)
+    attn_ms, attn_min, attn_max, _ = timed_blocks(lambda: step.attention(sptr), K, R)
     cache_ms = timed(lambda: step.caching(sptr), K) / K
     fused_ms = None
     if flush is None and not head_mode:
         for _ in range(3):
             step.fused_step(sptr)
-        fused_ms = max_over_ranks(timed(lambda: step.fused_step(sptr), K) / K)
+        fused_ms = timed_blocks(lambda: step.fused_step(sptr), K, min(R, 5))[0]
     # the same layer with its rotary embedding (q and the new K row rotated first): four calls against one
     rope_ms = None
     if flush is None and not head_mode and case.q.shape[-1] == case.k_cache.shape[-1] and case.q.shape[-1] % 2 == 0:
@@ -521,14 +612,13 @@ def gpu_arm(args):
             for fn in (step.rope_four_calls, step.rope_one_call):
                 for _ in range(3):
                     fn(sptr)
-            rope_ok = 1.0
+            rope_ok = True
         except Exception as exc:  # noqa: BLE001
             print(f"[bench] rope_step skipped on rank {rank}: {exc}", file=sys.stderr)
-            rope_ok = 0.0
-        # every rank takes the same branch (the timing below contains rank-wide reductions)
-        if min_over_ranks(rope_ok) > 0.5:
-            rope_ms = (max_over_ranks(timed(lambda: step.rope_four_calls(sptr), K) / K),
-                       max_over_ranks(timed(lambda: step.rope_one_call(sptr), K) / K))
+            rope_ok = False
+        if all_ranks_ok(rope_ok):
+            rope_ms = (timed_blocks(lambda: step.rope_four_calls(sptr), K, min(R, 5))[0],
+                       timed_blocks(lambda: step.rope_one_call(sptr), K, min(R, 5))[0])
 
     kv_bytes_all = sum_over_ranks(float(case.kv_bytes))
     seqs_all = sum_over_ranks(float(case.num_seqs))
@@ -548,22 +638,6 @@ def gpu_arm(args):
     def e2e_step():
         estep.run(sync=True)  # the host reads the step's result before it issues the next step
 
-    # the same step with the output rows stored straight into the pinned host buffer by the kernels
-    dstep = None
-    if not head_mode:
-        # a side measurement as well: skipped (on every rank) if page-locked memory cannot be written from the device here
-        try:
-            dstep = ib.DecodeStep(case.k_cache, case.v_cache, num_seqs=case.num_seqs, num_heads=case.num_heads,
-                                  max_blocks_per_seq=case.block_tables.shape[1], scale=case.scale, direct_output=True)
-            for k in ("q", "new_k", "new_v", "slot_mapping", "block_tables", "seq_lens"):
-                dstep.host[k].copy_(getattr(case, k).cpu())
-            dstep.capture()
-        except Exception as exc:  # noqa: BLE001
-            print(f"[bench] direct-output step skipped on rank {rank}: {exc}", file=sys.stderr)
-            dstep = None
-        if min_over_ranks(1.0 if dstep is not None else 0.0) < 0.5:
-            dstep = None
-
     if head_mode:
         # NCCL inside the step: issue the calls directly instead of replaying a graph
         host_full = torch.empty((case.num_seqs, case.num_heads * world, step.out.shape[2]), dtype=step.out.dtype).pin_memory()
@@ -573,10 +647,11 @@ def gpu_arm(args):
             estep._dev_arena.copy_(estep._host_arena, non_blocking=True)
             ib.paged_caching(case.k_cache, case.v_cache, estep.dev["new_k"], estep.dev["new_v"], estep.dev["slot_mapping"])
             if peers is not None:
-                ib.paged_attention_multi_out(peer_dests, estep.dev["q"], case.k_cache, case.v_cache, estep.dev["block_tables"],
-                                             estep.dev["seq_lens"], None, case.scale)
+                ib.paged_attention_multi_out(peers.destinations(), estep.dev["q"], case.k_cache, case.v_cache,
+                                             estep.dev["block_tables"], estep.dev["seq_lens"], None, case.scale)
                 peers.barrier()
                 full = peers.full
+                peers.advance()
             else:
                 o = ib.paged_attention(estep.dev["q"], case.k_cache, case.v_cache, estep.dev["block_tables"], estep.dev["seq_lens"],
                                        None, case.scale, out=estep.out)
@@ -586,60 +661,177 @@ def gpu_arm(args):
 
     for _ in range(3):
         e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(K):
-        e2e_step()
-    e1.record(stream)
-    barrier()
-    e2e_ms = max_over_ranks(e0.elapsed_time(e1) / K)
+    e2e_ms, e2e_min, e2e_max, _ = timed_blocks(e2e_step, K, R)
     e2e_value = kv_bytes_all / (e2e_ms * 1e-3) / 1e9
-    direct_ms = None
-    if dstep is not None:
-        for _ in range(3):
-            dstep.run(sync=True)
-        barrier()
-        e0.record(stream)
-        for _ in range(K):
-            dstep.run(sync=True)
-        e1.record(stream)
-        barrier()
-        direct_ms = max_over_ranks(e0.elapsed_time(e1) / K)
 
-    # ---- CPU baseline (rank 0, N = 1 only) -------------------------------------------------------
+    # ---- side records -----------------------------------------------------------------------------
+    side = {}
+    if not args.no_side and args.workload == "c2" and not head_mode:
+        K_side, R_side = min(K, 20), min(R, 5)
+
+        def side_case(build, label):
+            """Builds a workload on this rank, times its decode step (caching + attention) like the headline.
+            Returns this rank's record or None; never raises."""
+            try:
+                c = build()
+                st = AbiStep(c)
+
+                def fn():
+                    st.caching(sptr)
+                    st.attention(sptr)
+
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                ok = True
+            except Exception as exc:  # noqa: BLE001
+                print(f"[bench] side record {label} skipped on rank {rank}: {exc}", file=sys.stderr)
+                ok, c, fn = False, None, None
+            if not all_ranks_ok(ok):
+                return None
+            med, lo, hi, own = timed_blocks(fn, K_side, R_side)
+            attn_only = timed_blocks(lambda: st.attention(sptr), K_side, R_side)[0]
+            bytes_all = sum_over_ranks(float(c.kv_bytes))
+            rec = {"ms_per_step": med, "ms_min": lo, "ms_max": hi, "value": bytes_all / (med * 1e-3) / 1e9, "unit": UNIT,
+                   "attn_ms": attn_only, "num_seqs": int(sum_over_ranks(float(c.num_seqs))),
+                   "tokens": int(sum_over_ranks(float(c.total_tokens))), "kv_bytes": int(bytes_all),
+                   "seqs_per_s": sum_over_ranks(float(c.num_seqs)) / (med * 1e-3), "steps": K_side, "blocks": R_side,
+                   "_own_ms": own, "_own_tokens": float(c.total_tokens)}
+            del st, c
+            torch.cuda.empty_cache()
+            return rec
+
+        peak_now = measured_peak()[0]
+        if world == 1:
+            for name, build in (("c3", lambda: workloads.config3_ragged72b(seed=3, device=device)),
+                                ("c4", lambda: workloads.config4_longctx(seed=4, device=device))):
+                rec = side_case(build, name)
+                if rec is not None:
+                    rec.pop("_own_ms"), rec.pop("_own_tokens")
+                    rec["frac"] = rec["kv_bytes"] / (rec["attn_ms"] * 1e-3) / 1e9 / peak_now
+                    rec["frac_whole_step"] = rec["value"] / peak_now
+                    rec["workload"] = WORKLOAD_TEXT[name]
+                side[name] = rec
+
+        # BASELINE configs[4]: ONE batch of 2048 sequences split over the N ranks (strong scaling), each rank
+        # with its own pool; two placement policies
+        all_lens = workloads.config5_lengths()
+        c5 = {"workload": WORKLOAD_TEXT["c5"], "scaling": "strong", "n_gpus": world}
+        for policy in (("round_robin",) if world == 1 else ("round_robin", "balanced")):
+            idx = sharding.shard(all_lens.tolist(), rank, world, policy)
+
+            def build(idx=idx, policy=policy):
+                return workloads.build_case(f"c5_{policy}_{rank}of{world}", dtype=torch.bfloat16, seq_lens=all_lens[idx], num_heads=64,
+                                            num_kv_heads=8, head_size=128, block_size=16, max_blocks_per_seq=8192 // 16,
+                                            seed=5000 + rank, device=device)
+
+            rec = side_case(build, f"c5_strong/{policy}")
+            if rec is not None:
+                own_ms, own_tok = rec.pop("_own_ms"), rec.pop("_own_tokens")
+                rec["rank_ms_min"] = min_over_ranks(own_ms)
+                rec["rank_ms_max"] = max_over_ranks(own_ms)
+                rec["rank_tokens_min"] = int(min_over_ranks(own_tok))
+                rec["rank_tokens_max"] = int(max_over_ranks(own_tok))
+                rec["slowest_rank_token_share"] = rec["rank_tokens_max"] / max(rec["tokens"], 1)
+                rec["frac_of_hbm_peak"] = rec["value"] / (peak_now * world)
+            c5[policy] = rec
+        if world == 1 and c5.get("round_robin") is not None:
+            c5["balanced"] = "same as round_robin on one GPU"
+        side["c5_strong"] = c5
+
+        # KV-head-sharded mode at N > 1 (configs[4]'s optional variant, on the configs[1] shape): every rank holds all
+        # 64 sequences for kv_heads / N of the kv-heads; the outputs are combined (a) by one infinicclAllGather,
+        # (b) by the attention kernels' own stores into every rank's full output plus a barrier
+        if world > 1 and 8 % world == 0:
+            hs = {"workload": "configs[1] shape sharded by kv-head over the ranks (8 / N kv-heads and 32 / N q-heads per rank)"}
+            try:
+                from infinicore_b200 import ccl
+
+                hcase = make_case("c2", rank, world, device, "head")
+                hpeers = sharding.PeerOutputs(hcase.num_seqs, hcase.num_heads * world, hcase.v_cache.shape[3], hcase.dtype, device)
+                hstep_a = AbiStep(hcase)
+                hstep_p = AbiStep(hcase, out=hpeers.local_slice())
+                hstage = torch.empty((world, *hstep_a.out.shape), dtype=hstep_a.out.dtype, device=device)
+                hcomm = ccl.init_from_process_group()
+                ok = True
+            except Exception as exc:  # noqa: BLE001
+                print(f"[bench] head_sharded skipped on rank {rank}: {exc}", file=sys.stderr)
+                ok = False
+            if all_ranks_ok(ok):
+                def step_allgather():
+                    hstep_a.caching(sptr)
+                    hstep_a.attention(sptr)
+                    sharding.gather_head_sharded(hstep_a.out, world, staging=hstage, comm=hcomm)
+
+                def step_peer():
+                    hstep_p.caching(sptr)
+                    hstep_p.attention_multi_out(sptr, hpeers.destinations())
+                    hpeers.barrier()
+                    hpeers.advance()
+
+                hflush = torch.empty(256 << 20, dtype=torch.uint8, device=device) if hcase.kv_bytes <= (256 << 20) else None
+
+                def timed_steps(fn):
+                    for _ in range(3):
+                        fn()
+                    if hflush is None:
+                        return timed_blocks(fn, K_side, R_side)[0]
+                    vals = []
+                    for i in range(K_side):
+                        hflush.fill_(i & 0xff)
+                        vals.append(timed(fn, 1))
+                    return max_over_ranks(statistics.median(vals))
+
+                bytes_all = sum_over_ranks(float(hcase.kv_bytes))
+                for key, fn in (("allgather", step_allgather), ("peer_store", step_peer)):
+                    ms = timed_steps(fn)
+                    hs[key + "_ms"] = ms
+                    hs[key + "_value"] = bytes_all / (ms * 1e-3) / 1e9
+                hs["allgather_via"] = "infinicclAllGather (libinfiniccl.so over NCCL)"
+                hs["peer_store_via"] = "infiniopPagedAttentionMultiOut into double-buffered symmetric memory + one barrier per step"
+                hs["l2"] = "flushed before every timed step" if hflush is not None else "working set larger than L2"
+                torch.cuda.synchronize()
+                hcomm.destroy()
+            else:
+                hs = None
+            side["head_sharded"] = hs
+
+    # ---- CPU baseline and the reference's own GPU kernels (rank 0, N = 1 only) -------------------------
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         sample_case, sample = cpu_sample(args.workload, args.cpu_seqs)
         gbs, ms, threads = run_cpu(sample_case, steps=3, warmup=1)
         cpu = {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample + " per step, 3 timed steps",
-               "ms_per_step": ms}
+               "ms_per_step": ms, "processes": 1}
+    ref_gpu = None
+    if rank == 0 and world == 1 and not args.no_side and args.workload == "c2":
+        ref_gpu = reference_gpu_leg(case, step, sptr, attn_ms, ms_per_step)
 
     if rank == 0:
         peak, peak_kind = measured_peak()
         achieved = case.kv_bytes / (attn_ms * 1e-3) / 1e9
+        traffic, traffic_source = ncu_traffic(args.workload)
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if (args.workload == "c5" or head_mode) else "weak",
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "blocks": R,
+            "ms_per_step": ms_per_step, "ms_per_step_min": ms_min, "ms_per_step_max": ms_max,
+            "timing": f"median of {R} blocks of {K} back-to-back steps (max over ranks per block); min and max block beside it",
+            "higher_is_better": True, "scaling": "strong" if (args.workload == "c5" or head_mode) else "weak",
             "vs_baseline": None, "dtype": "f16" if case.dtype == torch.float16 else "bf16", "data": "synthetic",
-            "config": workload_config(args.workload, case, world, args.mode,
-                                      {"infiniccl": "one infinicclAllGather (NCCL)", "torch": "one torch.distributed all-gather (NCCL)",
-                                       "peer": "peer stores from the attention kernels into every rank's full output + a barrier"}[args.collective]),
+            "config": workload_config(args.workload, world, args.mode, COLLECTIVE_TEXT[args.collective]),
             "seqs_per_s": seqs_all / (ms_per_step * 1e-3),
             "frac_of_hbm_peak": value / (peak * world),
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_kind": f"of {peak_kind}",
-                "kernel": "pagedDecodeStreamKernel (timed with its plan and combine launches: events bracket infiniopPagedAttention)",
-                "algorithmic_bytes_per_launch": case.kv_bytes, "attn_ms_mean": attn_ms, "caching_ms_mean": cache_ms,
+                "traffic": traffic, "traffic_source": traffic_source, "peak_kind": f"of {peak_kind}",
+                "kernel": "pagedDecodeStreamKernel (timed with every launch of the call: events bracket infiniopPagedAttention)",
+                "algorithmic_bytes_per_launch": case.kv_bytes, "attn_ms_mean": attn_ms, "attn_ms_min": attn_min,
+                "attn_ms_max": attn_max, "caching_ms_mean": cache_ms,
             },
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "ms_per_step_min": e2e_min, "ms_per_step_max": e2e_max,
                     "note": "q, new K/V rows, slots, block tables and lengths copied in from pinned host memory and the output copied "
-                            "back every step; the KV cache itself is device state",
-                    "direct_output": (None if direct_ms is None else
-                                      {"ms_per_step": direct_ms, "value": kv_bytes_all / (direct_ms * 1e-3) / 1e9,
-                                       "note": "the same step with the output rows stored by the attention kernels straight into the "
-                                               "pinned host buffer (no device-to-host copy node); the same bytes cross PCIe"})},
+                            "back every step, the host waiting for the result before it issues the next step; the KV cache itself "
+                            "is device state"},
             "fused_step": (None if fused_ms is None else
                            {"ms_per_step": fused_ms, "value": kv_bytes_all / (fused_ms * 1e-3) / 1e9, "unit": "GB/s",
                             "note": "the same step through infiniopPagedDecodeStep (cache append inside the attention kernel, "
@@ -648,9 +840,12 @@ def gpu_arm(args):
                           {"four_calls_ms": rope_ms[0], "one_call_ms": rope_ms[1],
                            "note": "the decode layer with its rotary embedding: infiniopRoPE(q), infiniopRoPE(new K), infiniopPagedCaching, "
                                    "infiniopPagedAttention against infiniopPagedDecodeStepRoPE"}),
-            "gpu_launches": step.launches_per_step * K,  # inside the timed region that `value` comes from
+            "gpu_launches": step.launches_per_step * K * R,  # inside the timed region that `value` comes from
             "clocks": clocks,
         }
+        line.update(side)
+        if ref_gpu is not None:
+            line["reference_gpu"] = ref_gpu
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
@@ -659,6 +854,46 @@ def gpu_arm(args):
         ccl_comm.destroy()
     if world > 1:
         dist.destroy_process_group()
+
+
+def reference_gpu_leg(case, step, sptr, attn_ms, step_ms):
+    """The reference's own CUDA kernels (its sources compiled for sm_100a into oracle/_ref) on the same seeded
+    configs[1] inputs, in a child process - the two libraries export the same symbols and never share one.
+    Returns the record for the JSON line; never raises."""
+    import torch
+
+    ref_root = ROOT / "oracle" / "_ref"
+    if not (ref_root / "lib" / "libinfiniop.so").is_file():
+        return {"unavailable": "oracle/_ref was not built (the reference checkout is needed for that)"}
+    try:
+        with tempfile.TemporaryDirectory() as tmp:
+            out_path = os.path.join(tmp, "ref.pt")
+            spec = {"builder": "config2_llama8b", "kwargs": {"seed": 2, "device": "cuda"}, "iters": 20, "warmup": 3}
+            env = dict(os.environ)
+            env["INFINI_ROOT"] = str(ref_root)
+            for k in [k for k in env if k.startswith("INFINIOP_")]:
+                env.pop(k)  # the reference's default environment
+            res = subprocess.run([sys.executable, str(ROOT / "oracle" / "ref_kernels.py"), json.dumps(spec), out_path],
+                                 env=env, capture_output=True, text=True, timeout=600)
+            if res.returncode != 0:
+                return {"unavailable": "the reference kernels' child process failed: " + (res.stderr or res.stdout)[-300:]}
+            ref = torch.load(out_path)
+        # this library on the same inputs: the bench's own case has the same seed; one more step so `out` is current
+        step.caching(sptr)
+        step.attention(sptr)
+        torch.cuda.synchronize()
+        diff = (step.out.float().cpu() - ref["out"].float()).abs().max().item()
+        return {
+            "ms_per_call": ref["attn_ms"], "ms_per_step": ref["step_ms"],
+            "value": ref["kv_bytes"] / (ref["attn_ms"] * 1e-3) / 1e9, "unit": UNIT,
+            "speedup": ref["attn_ms"] / attn_ms, "speedup_whole_step": ref["step_ms"] / step_ms,
+            "max_abs_diff": diff,
+            "what": "infiniopPagedAttention of the reference's own kernels (default environment: split-KV, 4 splits), compiled "
+                    "for sm_100a from its sources, same seeded inputs, 20 calls after 3 warm-up; speedup = its time per call over "
+                    "this library's",
+        }
+    except Exception as exc:  # noqa: BLE001
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
 
 
 def prefill_arm(args):

@@ -63,11 +63,13 @@ __INFINI_C __export infiniStatus_t infiniopPagedAttention(
  * No counterpart in the reference.  Same operation as infiniopPagedAttention, for callers that
  * cannot provide a workspace because they cannot allocate device memory (all of HBM already given
  * to the KV pool, a frozen allocator, a host framework that owns every buffer): the scratch is a
- * 16 MiB array inside this library (INFINIOP_PAGED_ATTENTION_STATIC_WORKSPACE_BYTES), resident on
- * every GPU that loads the library.  Descriptors that need more are refused with
- * INFINI_STATUS_INSUFFICIENT_WORKSPACE.  The first call on a device resolves the array's address
- * and should be made before any stream capture.  All calls on a device share the array: calls that
- * overlap on the GPU race.  Allocates nothing.
+ * 16 MiB array inside this library (INFINIOP_PAGED_ATTENTION_STATIC_WORKSPACE_BYTES).  Descriptors
+ * that need more are refused with INFINI_STATUS_INSUFFICIENT_WORKSPACE.  The first call on a device
+ * resolves the array's address; under the CUDA runtime's lazy module loading that is also the moment
+ * the device sets the 16 MiB aside, so make that call at start-up, while the memory is still free
+ * (before the KV pool takes the rest) and before any stream capture; from then on the device holds
+ * the array until the process exits and no call takes further memory.  All calls on a device share
+ * the array: calls that overlap on the GPU race.  Calls no allocating routine.
  */
 #define INFINIOP_PAGED_ATTENTION_STATIC_WORKSPACE_BYTES (16u << 20)
 __INFINI_C __export infiniStatus_t infiniopPagedAttentionStaticWorkspace(
@@ -90,8 +92,12 @@ __INFINI_C __export infiniStatus_t infiniopDestroyPagedAttentionDescriptor(
  * ordinary output.  The buffers may live on other GPUs whose memory this GPU can address (peer
  * access, symmetric memory): the KV-head-sharded mode hands in the address of its head slice
  * inside every rank's full output, and the all-gather that would follow the kernel is not needed -
- * only a barrier across the ranks before anyone reads its full output.  Sequences with
- * seq_len <= 0 leave their rows untouched in every buffer. */
+ * only a barrier across the ranks before anyone reads its full output.  That one barrier does not
+ * protect a buffer that is reused by the next step: a rank that passed it may start the next step and
+ * store new rows into a peer's buffer while that peer still reads this step's.  Alternate between two
+ * sets of buffers from step to step (then one barrier per step is enough), or synchronise the ranks a
+ * second time between the reads and the next step's stores.  Sequences with seq_len <= 0 leave their
+ * rows untouched in every buffer. */
 __INFINI_C __export infiniStatus_t infiniopPagedAttentionMultiOut(
     infiniopPagedAttentionDescriptor_t desc,
     void *workspace,

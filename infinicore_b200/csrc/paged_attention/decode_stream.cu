@@ -73,7 +73,6 @@ struct StreamArgs {
     int tiles_per_page; // block_size / 16
     int stages;
     int num_workers;
-    int probe_copy_only; // measurement aid: stream the tiles but skip the arithmetic (output is garbage)
     int embedded_plan;   // 1: every CTA derives the plan itself in shared memory (no plan kernel)
 };
 
@@ -569,7 +568,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
             break;
         }
 
-        if (!a.probe_copy_only) {
+        {
         const int tok0 = cur.ti * kTileTokens;
         const int valid = seq_len - tok0; // >= 1 by construction
         if (p.new_k != nullptr && valid <= kTileTokens) {
@@ -736,7 +735,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
             mma16816<T>(o[2 * np + 1], pa[0], pa[1], pa[2], pa[3], b2, b3);
         }
 
-        } // !probe_copy_only
+        }
 
         // ---- the slot is free: refill it with tile i + stages -----------------------------
         __syncwarp();
@@ -1685,7 +1684,6 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
     while (ctas_per_sm > 1 && ctas_per_sm * (plan.smem_bytes + 1024) > props.smem_per_sm) {
         --ctas_per_sm;
     }
-    plan.probe_copy_only = envInt("INFINIOP_PAGED_DECODE_PROBE_COPY_ONLY", 0, 0, 1) != 0;
     plan.grid = props.sm_count * ctas_per_sm;
     plan.num_workers = plan.grid * plan.warps_per_cta;
     plan.workspace_bytes = workspaceLayout(I, plan).total;
@@ -1731,7 +1729,6 @@ infiniStatus_t launchDecodeStream(const Info &I, const StreamPlan &plan, const D
     a.tiles_per_page = static_cast<int>(I.block_size / kTileTokens);
     a.stages = plan.stages;
     a.num_workers = plan.num_workers;
-    a.probe_copy_only = plan.probe_copy_only ? 1 : 0;
     a.embedded_plan = plan.embedded_plan ? 1 : 0;
 
     int device_id = -1;

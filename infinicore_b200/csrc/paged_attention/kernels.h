@@ -73,7 +73,6 @@ struct StreamPlan {
     bool embedded_plan = false;   // the main kernel derives the plan itself (no plan kernel)
     bool use_pdl = true;          // launches carry the programmatic-serialization attribute
     bool wide = false;            // key width 576: one worker is a CTA of four warps (pagedDecodeWideKernel)
-    bool probe_copy_only = false; // measurement aid (INFINIOP_PAGED_DECODE_PROBE_COPY_ONLY=1): tiles are streamed, math skipped
 };
 
 // Decides at descriptor creation whether the streaming path applies and sizes its workspace.

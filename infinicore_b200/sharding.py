@@ -96,9 +96,26 @@ class PeerOutputs:
     (infiniopPagedAttentionMultiOut) and the all-gather that would follow is replaced by one barrier.
 
     The exchange itself is plain stores over NVLink to peer addresses; nothing here waits on a peer
-    except `barrier()`, which is torch's symmetric-memory barrier (it carries its own timeout)."""
+    except `barrier()`, which is torch's symmetric-memory barrier (it carries its own timeout).
 
-    def __init__(self, num_seqs: int, heads_total: int, d: int, dtype, device, group=None):
+    Reuse across steps.  One barrier per step orders "every rank has stored" before "this rank reads",
+    but not "this rank has finished reading" before "a faster rank stores the next step's rows": with a
+    single buffer a rank that is still reading step n could see rows of step n + 1.  So the outputs are
+    double-buffered: `buffers` (default 2) full outputs per rank, and `advance()` moves to the next one
+    after a step.  A rank can only store into buffer b again after it has passed the barrier of the step
+    in between, which every rank enters only after it has issued its reads of buffer b (stream order):
+    with two buffers and one barrier per step no store can overtake a read.  With `buffers=1` the caller
+    must add a second cross-rank synchronisation between its reads and the next step's stores.
+
+        peers = PeerOutputs(...)
+        for step in ...:
+            paged_attention_multi_out(peers.destinations(), ...)   # stores into buffer `peers.current`
+            peers.barrier()
+            use(peers.full)                                        # this rank's complete output of the step
+            peers.advance()
+    """
+
+    def __init__(self, num_seqs: int, heads_total: int, d: int, dtype, device, group=None, buffers: int = 2):
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
 
@@ -106,21 +123,42 @@ class PeerOutputs:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         if heads_total % self.world != 0:
             raise ValueError("heads must divide over the ranks")
+        if buffers < 1:
+            raise ValueError("at least one buffer")
         self.heads_per_rank = heads_total // self.world
-        self.full = symm_mem.empty((num_seqs, heads_total, d), dtype=dtype, device=device)
-        self.handle = symm_mem.rendezvous(self.full, group)
-        self._slice_bytes = self.heads_per_rank * d * self.full.element_size()
+        self.buffers = int(buffers)
+        self.current = 0
+        self._all = symm_mem.empty((self.buffers, num_seqs, heads_total, d), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self._all, group)
+        self._slice_bytes = self.heads_per_rank * d * self._all.element_size()
+        self._buffer_bytes = num_seqs * heads_total * d * self._all.element_size()
+
+    @property
+    def full(self):
+        """This rank's full output in the current buffer (complete after the step's barrier)."""
+        return self._all[self.current]
+
+    def fill_(self, value):
+        """Initialises every buffer of this rank (call before the first step, then synchronise all ranks)."""
+        self._all.fill_(value)
+        return self
+
+    def advance(self) -> int:
+        """Moves to the next buffer; call once per step, after this rank has issued its reads of `full`."""
+        self.current = (self.current + 1) % self.buffers
+        return self.current
 
     def local_slice(self):
-        """This rank's heads inside its own full output: the `out` the attention descriptor is made for."""
+        """This rank's heads inside its own full output (current buffer).  Every buffer's slice has the same
+        shape and strides, so one attention descriptor made for it serves all of them."""
         h0 = self.rank * self.heads_per_rank
         return self.full[:, h0:h0 + self.heads_per_rank]
 
     def destinations(self):
         """outs for paged_attention_multi_out: the local slice first, then the address of the same
-        slice inside every other rank's full output."""
+        slice inside every other rank's full output (current buffer)."""
         base = list(self.handle.buffer_ptrs)
-        off = self.rank * self._slice_bytes
+        off = self.current * self._buffer_bytes + self.rank * self._slice_bytes
         return [self.local_slice()] + [base[r] + off for r in range(self.world) if r != self.rank]
 
     def barrier(self):

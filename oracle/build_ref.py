@@ -55,7 +55,8 @@ FLAGS = [
 
 
 def reference_root(arg: str | None = None) -> Path | None:
-    for cand in (arg, os.getenv("INFINICORE_REFERENCE"), "/root/reference"):
+    # the argument, the environment, or a checkout named `reference` beside this repository
+    for cand in (arg, os.getenv("INFINICORE_REFERENCE"), str(Path(__file__).resolve().parent.parent.parent / "reference")):
         if cand and (Path(cand) / "src" / "infiniop" / "ops" / "paged_attention").is_dir():
             return Path(cand)
     return None

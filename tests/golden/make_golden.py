@@ -20,6 +20,7 @@ output, so the tests need neither torch-specific pickles nor the reference.
 from __future__ import annotations
 
 import importlib.util
+import os
 import sys
 import types
 from pathlib import Path
@@ -288,7 +289,10 @@ def make_layers(ref_attn, ref_cache, ref_rope):
 def main():
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
     only = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--only=")]
-    ref_root = Path(args[0]) if args else Path("/root/reference")
+    ref_arg = args[0] if args else os.getenv("INFINICORE_REFERENCE")
+    if not ref_arg:
+        raise SystemExit("usage: make_golden.py <reference checkout> [--only=...]  (or set INFINICORE_REFERENCE)")
+    ref_root = Path(ref_arg)
     ref_attn, ref_cache, ref_prefill, ref_rope, ref_kvc = load_reference(ref_root)
     torch.set_num_threads(4)
     if not only or "attention" in only:

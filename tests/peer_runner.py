@@ -30,25 +30,37 @@ def main():
     heads, kvh, hd = 32, 8, 128
     full = workloads.build_case("peer_full", dtype=torch.bfloat16, seq_lens=[700, 33, 0, 2048, 1, 129], num_heads=heads, num_kv_heads=kvh,
                                 head_size=hd, block_size=16, seed=81).to(dev)
-    want = ib.paged_attention(full.q, full.k_cache, full.v_cache, full.block_tables, full.seq_lens, None, full.scale,
-                              out=torch.full((6, heads, hd), 4.0, dtype=torch.bfloat16, device=dev))
     q_sl, kv_sl = sharding.head_slices(heads, kvh, rank, world)
     q = full.q[:, q_sl].contiguous()
     kc = full.k_cache[:, kv_sl].contiguous()
     vc = full.v_cache[:, kv_sl].contiguous()
 
     peers = sharding.PeerOutputs(6, heads, hd, torch.bfloat16, dev)
-    peers.full.fill_(4.0)
+    peers.fill_(4.0)
     torch.cuda.synchronize()
-    dist.barrier()  # every rank's buffer is initialised before anyone stores into it
-    for _ in range(3):  # repeated steps reuse the same buffers
-        ib.paged_attention_multi_out(peers.destinations(), q, kc, vc, full.block_tables, full.seq_lens, None, full.scale)
-        peers.barrier()
-    torch.cuda.synchronize()
-    got = peers.full
+    dist.barrier()  # every rank's buffers are initialised before anyone stores into them
+    # Six steps into the two alternating buffers.  The query changes every step (scaled by a power of two, so
+    # the expected output is computed locally from the whole problem), and after each barrier the ranks read
+    # their full output at different speeds: an odd rank first keeps its stream busy for a while, so an even
+    # rank is already storing the next step's rows while the odd one still reads this step's.
+    ok, err = True, 0.0
     live = [0, 1, 3, 4, 5]
-    err = (got[live].float() - want[live].float()).abs().max().item()
-    ok = err <= 1e-2 and bool((got[2] == 4.0).all())
+    busy = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    for step in range(6):
+        f = float(2 ** (step % 3 - 1))
+        want = ib.paged_attention(full.q * f, full.k_cache, full.v_cache, full.block_tables, full.seq_lens, None, full.scale,
+                                  out=torch.full((6, heads, hd), 4.0, dtype=torch.bfloat16, device=dev))
+        ib.paged_attention_multi_out(peers.destinations(), q * f, kc, vc, full.block_tables, full.seq_lens, None, full.scale)
+        peers.barrier()
+        if rank % 2 == 1:
+            for _ in range(20):
+                busy.fill_(step)
+        got = peers.full.clone()
+        peers.advance()
+        e = (got[live].float() - want[live].float()).abs().max().item()
+        err = max(err, e)
+        ok = ok and e <= 1e-2 and bool((got[2] == 4.0).all())
+    torch.cuda.synchronize()
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
