@@ -63,15 +63,15 @@ __INFINI_C __export infiniStatus_t infiniopPagedAttention(
  * No counterpart in the reference.  Same operation as infiniopPagedAttention, for callers that
  * cannot provide a workspace because they cannot allocate device memory (all of HBM already given
  * to the KV pool, a frozen allocator, a host framework that owns every buffer): the scratch is a
- * 16 MiB array inside this library (INFINIOP_PAGED_ATTENTION_STATIC_WORKSPACE_BYTES).  Descriptors
+ * 32 MiB array inside this library (INFINIOP_PAGED_ATTENTION_STATIC_WORKSPACE_BYTES).  Descriptors
  * that need more are refused with INFINI_STATUS_INSUFFICIENT_WORKSPACE.  The first call on a device
  * resolves the array's address; under the CUDA runtime's lazy module loading that is also the moment
- * the device sets the 16 MiB aside, so make that call at start-up, while the memory is still free
+ * the device sets the 32 MiB aside, so make that call at start-up, while the memory is still free
  * (before the KV pool takes the rest) and before any stream capture; from then on the device holds
  * the array until the process exits and no call takes further memory.  All calls on a device share
  * the array: calls that overlap on the GPU race.  Calls no allocating routine.
  */
-#define INFINIOP_PAGED_ATTENTION_STATIC_WORKSPACE_BYTES (16u << 20)
+#define INFINIOP_PAGED_ATTENTION_STATIC_WORKSPACE_BYTES (32u << 20)
 __INFINI_C __export infiniStatus_t infiniopPagedAttentionStaticWorkspace(
     infiniopPagedAttentionDescriptor_t desc,
     void *out,

@@ -9,31 +9,40 @@
 //  * Work decomposition.  A "tile" is 16 consecutive tokens of one KV page for one kv-head.
 //    A "unit" is (sequence, kv-head, group of <= 8 q-heads that share that kv-head); its length
 //    is ceil(seq_len / 16) tiles.  All units are laid end to end in one linear tile space and
-//    that space is cut into equal contiguous ranges, one per persistent warp ("worker").  Every
-//    worker therefore streams the same number of bytes (+-1 tile) whatever the mix of
-//    sequence lengths, with no host knowledge of seq_lens: a one-CTA plan kernel builds the
-//    per-sequence tile prefix and each range's starting (sequence, kv-head, tile) on the device.
+//    that space is cut into equal contiguous ranges, one per persistent warp ("worker"), with no
+//    host knowledge of seq_lens: the per-sequence tile prefix is built on the device.  A range is
+//    cut once more, into "pieces": a head piece (its first 7/8) that the range's own worker streams,
+//    and a few tail chunks of halving size that go into a pool shared by all workers.  A worker that
+//    has finished takes the next chunk of the pool (one atomicAdd), so workers whose SM gets a
+//    smaller share of the memory system - per-worker rates spread by about 3 % - hand the end of
+//    their range to faster ones and everybody finishes together.  Piece boundaries depend only on
+//    the lengths and the plan, never on timing, and every piece starts from fresh softmax state: the
+//    result is bit-identical from run to run whoever computes a piece.
 //  * Data movement.  Each worker owns a private ring of `stages` shared-memory slots.  Lanes
 //    0..2*HD/64-1 each issue one non-multicast `cp.async.bulk.tensor` (TMA) box of
 //    16 rows x 128 bytes with the 128-byte swizzle; completion is tracked by one mbarrier per
-//    slot.  Block-table entries are fetched one tile ahead of the TMA issue that needs them, so
-//    the table -> page indirection is off the critical path and the ring never drains at page,
-//    kv-head or sequence boundaries.
+//    slot.  Block-table entries are fetched one tile ahead of the TMA issue that needs them, and the
+//    next chunk is claimed one tile before the current piece runs out, so the ring never drains at
+//    page, kv-head, sequence or piece boundaries.
 //  * Arithmetic.  All q-heads of the GQA group consume the same staged tile:
 //    S^T[8 heads x 16 tokens] = Q.K^T and O[8 heads x HD] += P.V run as warp-level
 //    mma.sync.m16n8k16 (bf16/fp16 in, fp32 accumulate) with ldmatrix / ldmatrix.trans operand
 //    loads that are bank-conflict-free under the swizzle.  P is rounded to the cache dtype
 //    before the PV product, as the reference's torch check does
 //    (test/infiniop/paged_attention.py:43).  Rows 8..15 of the M dimension are padding.
-//  * Reduction.  A worker that covers a whole unit writes the normalised output directly.
-//    Otherwise it writes (acc, m, l) to workspace slot (unit + range): along the linear space the
-//    pair (unit, range) only ever moves forward in one or both coordinates, so that sum is
-//    unique.  A combine kernel merges the slots of every split unit.  No kernel waits on another
-//    CTA; the only waits are mbarrier waits on a worker's own TMA copies, and those are bounded.
+//  * Reduction.  A piece that covers a whole unit writes the normalised output directly.
+//    Otherwise the worker writes (acc, m, l) to workspace slot (unit + piece): along the linear space
+//    the pair (unit, piece) only ever moves forward in one or both coordinates, so that sum is
+//    unique.  It then adds its tile count to the unit's counter (release fence, atomicAdd); whoever
+//    brings the counter to the unit's length is the last to arrive and merges the unit's records in
+//    piece order - nobody ever waits for anybody.  When a handful of very long sequences are cut into
+//    hundreds of pieces each, a combine kernel (several CTAs per unit) merges instead.  A small
+//    reset kernel in front clears the counters.  The only waits are mbarrier waits on a worker's own
+//    TMA copies, and those are bounded.
 //
 // HBM traffic per launch: K and V tiles once each (the algorithmic bytes), plus q/out, block
-// tables, and 8*(HD+2)*4 bytes written and read back per (unit, range) boundary - at most
-// units + workers records.
+// tables, and 8*(HD+2)*4 bytes written and read back per (unit, piece) boundary - at most
+// units + pieces records.
 #include "kernels.h"
 
 #include <cuda_bf16.h>
@@ -53,6 +62,8 @@ constexpr int kMaxStages = 8;
 constexpr int kMaxWarps = 8;
 constexpr int kPlanThreads = 1024;
 constexpr long long kWaitLimitCycles = 4000000000ll; // an mbarrier wait gives up after ~2 s
+constexpr int kResetThreads = 1024;
+constexpr int kMinDynamicRange = 32; // ranges shorter than this many tiles are not cut into pieces
 
 struct PlanHeader {
     int error;      // set non-zero by a worker whose bounded wait ran out
@@ -66,14 +77,20 @@ struct StreamArgs {
     PlanHeader *header;
     long long *prefix;  // [num_seqs + 1] tiles before each sequence (one kv-head, one head tile)
     int4 *range_start;  // [workers] (sequence, unit-within-sequence, tile) where a range begins
-    int4 *tasks;        // [workers] combine tasks: (sequence, unit-within-sequence, first range, records)
-    float *partials;    // [(units + workers)] records of 8 * (HD + 2) floats
+    int4 *tasks;        // [workers] combine tasks of the wide-head kernel: (sequence, unit-within-sequence, first range, records)
+    int *counters;      // one-warp kernel: [0] next chunk of the pool, [1 + unit] tiles of the unit done so far; cleared by the reset kernel
+    float *partials;    // [(units + pieces)] records of 8 * (HD + 2) floats
     int units_per_seq;  // num_kv_heads * head_tiles
     int head_tiles;
     int tiles_per_page; // block_size / 16
     int stages;
     int num_workers;
     int embedded_plan;   // 1: every CTA derives the plan itself in shared memory (no plan kernel)
+    int max_chunks;      // tail chunks a range may be cut into (0: ranges are not cut)
+    int min_chunk;       // smallest chunk, in tiles (the last chunk of a range takes what is left)
+    int tail_shift;      // the last range_len >> tail_shift tiles of a range go to the pool
+    int merge_in_kernel; // 1: the last worker to arrive at a unit merges its records; 0: the combine kernel does
+    int l2_evict_first;  // 1: K/V copies carry the evict-first L2 policy
 };
 
 // ---------------------------------------------------------------------------------------
@@ -132,6 +149,23 @@ __device__ __forceinline__ void tmaLoadBox(uint32_t dst, const CUtensorMap *map,
         " [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
+}
+
+// The same copy with an L2 eviction policy.  K and V are read once per launch: marked evict-first they
+// leave the L2 to what IS read again - block tables, q rows and the split-unit records.
+__device__ __forceinline__ void tmaLoadBoxHint(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                               int c0, int c1, int c2, int c3, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
+        : "memory");
+}
+
+__device__ __forceinline__ uint64_t evictFirstPolicy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
 }
 
 __device__ __forceinline__ void ldmatrixX4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
@@ -239,6 +273,94 @@ __device__ __forceinline__ int4 locate(const long long *prefix, int num_seqs, in
 }
 
 // ---------------------------------------------------------------------------------------
+// Pieces of a range
+// ---------------------------------------------------------------------------------------
+// Every range of `range_len` tiles is cut the same way: a head piece [0, range_len - budget) and
+// `chunks` tail chunks that cover the last `budget` tiles; chunk i takes half of what is left (at
+// least min_chunk tiles), the last possible chunk takes all of it.  Pieces are numbered along the
+// tile space: range r owns ids r * (chunks + 1) + {0: head, 1 + i: chunk i}.
+struct PieceGeometry {
+    int budget;
+    int chunks;
+};
+
+__device__ __forceinline__ int chunkLength(int rem, int index, int max_chunks, int min_chunk) {
+    const int half = max((rem + 1) >> 1, min_chunk);
+    return (index == max_chunks - 1) ? rem : min(half, rem);
+}
+
+__device__ __forceinline__ PieceGeometry pieceGeometry(long long range_len, int max_chunks, int min_chunk, int tail_shift) {
+    PieceGeometry g;
+    g.budget = 0;
+    g.chunks = 0;
+    if (max_chunks <= 0 || range_len < kMinDynamicRange || range_len > 0x3fffffffll) {
+        return g;
+    }
+    g.budget = static_cast<int>(range_len >> tail_shift);
+    int rem = g.budget;
+    while (rem > 0 && g.chunks < max_chunks) {
+        rem -= chunkLength(rem, g.chunks, max_chunks, min_chunk);
+        ++g.chunks;
+    }
+    return g;
+}
+
+// Chunk j of a range: its first tile within the range and its length.
+__device__ __forceinline__ void chunkSpan(long long range_len, PieceGeometry g, int max_chunks, int min_chunk, int j,
+                                          int &begin, int &len) {
+    int rem = g.budget;
+    begin = static_cast<int>(range_len) - g.budget;
+    len = 0;
+    for (int i = 0; i <= j; ++i) {
+        begin += len;
+        len = chunkLength(rem, i, max_chunks, min_chunk);
+        rem -= len;
+    }
+}
+
+// Id of the piece that holds linear position x.
+__device__ __forceinline__ long long pieceOf(long long x, long long range_len, PieceGeometry g, int max_chunks, int min_chunk) {
+    const long long r = x / range_len;
+    const long long id = r * (g.chunks + 1);
+    if (g.chunks == 0) {
+        return id;
+    }
+    const int off = static_cast<int>(x - r * range_len);
+    int end = static_cast<int>(range_len) - g.budget; // end of the head piece
+    if (off < end) {
+        return id;
+    }
+    int rem = g.budget;
+    for (int i = 0; i < g.chunks - 1; ++i) {
+        const int len = chunkLength(rem, i, max_chunks, min_chunk);
+        end += len;
+        rem -= len;
+        if (off < end) {
+            return id + 1 + i;
+        }
+    }
+    return id + g.chunks;
+}
+
+// ---------------------------------------------------------------------------------------
+// Reset kernel: clears the chunk counter and the per-unit tile counters (and the error flag) of the
+// one-warp kernel.  It sits in front of every launch because the workspace is the caller's scratch:
+// nothing can be assumed about what the previous user left in it.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kResetThreads)
+    pagedDecodeResetKernel(const StreamArgs a, long long count) {
+    gridDependencyWait(); // the previous launch on this workspace may still be counting
+    gridLaunchDependents();
+    for (long long i = static_cast<long long>(blockIdx.x) * kResetThreads + threadIdx.x; i < count;
+         i += static_cast<long long>(gridDim.x) * kResetThreads) {
+        a.counters[i] = 0;
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        a.header->error = 0;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // Plan kernel: tile prefix per sequence, range length, and where each range starts.
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kPlanThreads)
@@ -322,15 +444,109 @@ __global__ void __launch_bounds__(kPlanThreads)
 }
 
 // ---------------------------------------------------------------------------------------
+// Merge of a unit's records (one warp).  The records sit in consecutive slots, one per piece the
+// unit touches, and are folded in that order - whichever worker arrived last and does it - so the
+// result does not depend on timing.  Lane l handles float4 l, l + 32, ... of the HPT x HD accumulator
+// block of a record; the (m, l) pairs follow the block.  Records are fetched a few at a time (all
+// loads of a batch in flight together) and folded one after the other with the usual rescaling.
+// Runs after the worker's streaming loop, when its registers are free; kept out of line.
+// ---------------------------------------------------------------------------------------
+constexpr int kMergeList = 20; // units a worker can note down for merging once its streaming is done
+constexpr int kMergeStop = 8;  // ... and how many make it stop taking chunks from the pool
+
+template <typename T, int HD, int HPT>
+__device__ __noinline__ void mergeUnit(const StreamArgs &a, const long long *prefix, long long range_len, PieceGeometry geom,
+                                       long long unit, int lane) {
+    constexpr int kRec = HPT * (HD + 2);
+    constexpr int kVecs = HPT * HD / 128;             // float4 per lane per record
+    constexpr int kRowVecs = HD / 4;                  // float4 per accumulator row
+    constexpr int kBatch = (24 / kVecs) > 0 ? (24 / kVecs) : 1; // records fetched together
+    const DecodeParams &p = a.p;
+    const int s = static_cast<int>(unit / a.units_per_seq);
+    const int j = static_cast<int>(unit - static_cast<long long>(s) * a.units_per_seq);
+    const long long nt = prefix[s + 1] - prefix[s];
+    const long long xs = prefix[s] * a.units_per_seq + j * nt; // the unit's first tile in the linear space
+    const long long p_first = pieceOf(xs, range_len, geom, a.max_chunks, a.min_chunk);
+    const int nrec = static_cast<int>(pieceOf(xs + nt - 1, range_len, geom, a.max_chunks, a.min_chunk) - p_first) + 1;
+    const int kv_head = j / a.head_tiles;
+    const int head_tile = j % a.head_tiles;
+    const int heads_valid = min(HPT, p.group_size - head_tile * HPT);
+    const float *base = a.partials + (unit + p_first) * kRec;
+
+    __threadfence(); // the other workers' records were published before they counted their tiles
+    float mx[kVecs], ls[kVecs];
+    float4 acc[kVecs];
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) {
+        mx[v] = -INFINITY;
+        ls[v] = 0.f;
+        acc[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int i0 = 0; i0 < nrec; i0 += kBatch) {
+        float2 ml[kBatch][kVecs];
+        float4 x[kBatch][kVecs];
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            // past the last record: fetch the last one again, it is not folded
+            const float *rr = base + static_cast<long long>(min(i0 + b, nrec - 1)) * kRec;
+#pragma unroll
+            for (int v = 0; v < kVecs; ++v) {
+                const int f = v * 32 + lane;
+                const int row = min(f / kRowVecs, heads_valid - 1);
+                ml[b][v] = __ldcg(reinterpret_cast<const float2 *>(rr + HPT * HD + row * 2));
+                x[b][v] = __ldcg(reinterpret_cast<const float4 *>(rr) + f);
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            if (i0 + b < nrec) {
+#pragma unroll
+                for (int v = 0; v < kVecs; ++v) {
+                    const float m_new = fmaxf(mx[v], ml[b][v].x);
+                    const float keep = exp2f(mx[v] - m_new);
+                    const float w = exp2f(ml[b][v].x - m_new);
+                    acc[v].x = fmaf(w, x[b][v].x, acc[v].x * keep);
+                    acc[v].y = fmaf(w, x[b][v].y, acc[v].y * keep);
+                    acc[v].z = fmaf(w, x[b][v].z, acc[v].z * keep);
+                    acc[v].w = fmaf(w, x[b][v].w, acc[v].w * keep);
+                    ls[v] = fmaf(w, ml[b][v].y, ls[v] * keep);
+                    mx[v] = m_new;
+                }
+            }
+        }
+    }
+    const long long off0 = s * p.o_seq_stride + (kv_head * p.group_size + head_tile * HPT) * p.o_head_stride;
+#pragma unroll
+    for (int v = 0; v < kVecs; ++v) {
+        const int f = v * 32 + lane;
+        const int row = f / kRowVecs;
+        if (row < heads_valid) {
+            const float inv = 1.f / ls[v];
+            const long long off = off0 + row * p.o_head_stride + (f % kRowVecs) * 4;
+            const uint32_t lo = packPair(acc[v].x * inv, acc[v].y * inv, T());
+            const uint32_t hi = packPair(acc[v].z * inv, acc[v].w * inv, T());
+            for (int d = 0; d <= p.num_extra_out; ++d) { // the output and every further destination
+                T *out = static_cast<T *>(d == 0 ? p.out : p.extra_out[d - 1]) + off;
+                *reinterpret_cast<uint32_t *>(out) = lo;
+                *reinterpret_cast<uint32_t *>(out + 2) = hi;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // Main kernel
 // ---------------------------------------------------------------------------------------
 // HPT: q-heads per head tile.  8 uses rows 0-7 of the MMA's M dimension (rows 8-15 are padding); 16 uses
 // all rows, for groups of more than 8 q-heads per kv-head: K/V are then re-read once per 16 heads.
-template <typename T, int HD, int HPT>
-__global__ void __launch_bounds__(kMaxWarps * 32)
+// Head 64 wants three resident CTAs per SM (half the bytes per tile, the same per-tile latencies): its
+// CTAs are bounded to four warps so that the register allocation leaves room for three.
+// POOL: ranges are cut into pieces and their tail chunks claimed from the pool (otherwise that code is not compiled in).
+template <typename T, int HD, int HPT, bool POOL>
+__global__ void __launch_bounds__(HD == 64 ? 128 : kMaxWarps * 32, HD == 64 ? 3 : 1)
     pagedDecodeStreamKernel(const __grid_constant__ CUtensorMap tmap_k,
                             const __grid_constant__ CUtensorMap tmap_v,
-                            const StreamArgs a) {
+                            const __grid_constant__ StreamArgs a) {
     constexpr int kChunks = HD / 64;               // 128-byte column chunks per row
     constexpr int kBoxBytes = kTileTokens * 128;   // one TMA box
     constexpr int kTensorBytes = kChunks * kBoxBytes;
@@ -352,8 +568,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
 
     const uint32_t ring = smemAddr(smem_raw) + warp * stages * kStageBytes;
     const uint32_t bars = smemAddr(smem_raw) + nwarps * stages * kStageBytes + warp * stages * 8;
+    // units this worker merges once its streaming is done
+    long long *merge_list = reinterpret_cast<long long *>(smem_raw + nwarps * stages * (kStageBytes + 8)) + warp * kMergeList;
     // shared-memory copy of the plan (embedded mode): tile prefix per sequence + scan scratch
-    long long *prefix_s = reinterpret_cast<long long *>(smem_raw + nwarps * stages * (kStageBytes + 8));
+    long long *prefix_s = reinterpret_cast<long long *>(smem_raw + nwarps * stages * (kStageBytes + 8)) + nwarps * kMergeList;
     long long *scan_s = prefix_s + (p.num_seqs + 1);
 
     if (lane == 0) {
@@ -425,9 +643,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
                 a.prefix[s] = prefix_s[s];
             }
             if (tid == 0) {
-                // A worker can only raise the flag after a 2 s wait ran out; CTA 0 is resident from
-                // the start of the launch, so this store precedes any such write.
-                a.header->error = 0;
                 a.header->num_ranges = num_ranges;
                 a.header->total_tiles = total_tiles;
                 a.header->range_len = range_len;
@@ -442,8 +657,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     if (worker >= num_ranges) {
         return;
     }
+    // The range's pieces: this worker streams the head piece, then chunks of the pool.
+    const PieceGeometry geom = pieceGeometry(range_len, POOL ? a.max_chunks : 0, a.min_chunk, a.tail_shift);
+    const int pieces_per_range = geom.chunks + 1;
+    const int pool_total = num_ranges * geom.chunks;
     const long long x0 = worker * range_len;
-    const long long count = (total_tiles - x0 < range_len) ? (total_tiles - x0) : range_len;
 
     const int4 rs = a.embedded_plan ? locate(prefix, p.num_seqs, a.units_per_seq, x0) : a.range_start[worker];
     Cursor gen; // next tile to fetch
@@ -453,23 +671,28 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     gen.nt = static_cast<int>(prefix[rs.x + 1] - prefix[rs.x]);
     Cursor cur = gen; // next tile to consume
 
-    if (lane == 0) {
-        // This range starts mid-unit when rs.z != 0; if it is the first range to do so for that
-        // unit, it owns the unit's combine task.
-        int4 task = make_int4(-1, -1, 0, 0);
-        if (rs.z != 0) {
-            const long long unit_start = x0 - rs.z;
-            const long long r_first = unit_start / range_len;
-            if (worker == r_first + 1) {
-                const long long r_last = (unit_start + gen.nt - 1) / range_len;
-                task = make_int4(rs.x, rs.y, static_cast<int>(r_first), static_cast<int>(r_last - r_first + 1));
-            }
-        }
-        a.tasks[worker] = task;
+    // Consumer side: the piece whose tiles are being consumed.  Generator side: the piece whose tiles
+    // are being fetched - the same one (g_same) or, once that is fully issued, the next one (q_*).
+    long long c_left = range_len - geom.budget; // tiles of the piece still to consume
+    if (total_tiles - x0 < c_left) {
+        c_left = total_tiles - x0;
     }
+    long long c_id = static_cast<long long>(worker) * pieces_per_range;
+    long long g_left = c_left; // tiles of the generator's piece still to issue
+    bool g_same = true;
+    Cursor q_start = gen;
+    long long q_id = 0;
+    int q_count = 0;
+    bool pool_empty = (pool_total == 0);
+    bool stop_claiming = false; // this worker has noted enough units to merge: it takes no further chunk
+    bool ahead = false; // lane 0 holds a claimed pool index in k_ahead
+    int k_ahead = 0;
+    int free_slots = stages;
+    int gen_stage = 0;
 
     const int tpp = a.tiles_per_page;
     const int head_tiles = a.head_tiles;
+    const uint64_t stream_policy = evictFirstPolicy();
 
     auto tableEntry = [&](const Cursor &c) -> long long {
         const int page = (tpp == 1) ? c.ti : c.ti / tpp;
@@ -486,36 +709,90 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
             const int chunk = lane % kChunks;
             const int row0 = (tpp == 1) ? 0 : (c.ti % tpp) * kTileTokens;
             const int kv_head = (head_tiles == 1) ? c.j : c.j / head_tiles;
-            tmaLoadBox(dst + is_v * kTensorBytes + chunk * kBoxBytes, is_v ? &tmap_v : &tmap_k, bar,
-                       chunk * 64, row0, kv_head, static_cast<int>(block));
+            if (a.l2_evict_first) {
+                tmaLoadBoxHint(dst + is_v * kTensorBytes + chunk * kBoxBytes, is_v ? &tmap_v : &tmap_k, bar,
+                               chunk * 64, row0, kv_head, static_cast<int>(block), stream_policy);
+            } else {
+                tmaLoadBox(dst + is_v * kTensorBytes + chunk * kBoxBytes, is_v ? &tmap_v : &tmap_k, bar,
+                           chunk * 64, row0, kv_head, static_cast<int>(block));
+            }
+        }
+    };
+    auto claim = [&]() -> int { // the pool index lands in lane 0
+        int k = 0;
+        if (lane == 0) {
+            k = atomicAdd(a.counters, 1);
+        }
+        return k;
+    };
+    long long next_block = tableEntry(gen); // table entry of the generator's tile, fetched ahead of its issue
+
+    // Issues the generator's next tile into the next free slot.  False when there is nothing to issue:
+    // the pool is empty (or this worker claims no more), or the generator has finished the piece after the
+    // consumer's and may not open a third.  (Every claimed chunk is processed: `ahead` is only ever dropped
+    // by using k_ahead.)
+    auto tryIssue = [&]() -> bool {
+        if (g_left == 0) {
+            if (!POOL || !g_same) {
+                return false;
+            }
+            for (;;) {
+                if (!ahead && (pool_empty || stop_claiming)) {
+                    return false;
+                }
+                int k = ahead ? k_ahead : claim();
+                ahead = false;
+                k = __shfl_sync(0xffffffffu, k, 0);
+                if (k >= pool_total) {
+                    pool_empty = true;
+                    return false;
+                }
+                // the pool hands out every range's first (largest) chunk before any second one
+                const int j = k / num_ranges;
+                const int r = k - j * num_ranges;
+                int begin, len;
+                chunkSpan(range_len, geom, a.max_chunks, a.min_chunk, j, begin, len);
+                const long long qx0 = r * range_len + begin;
+                const long long avail = total_tiles - qx0;
+                if (avail <= 0) {
+                    continue; // the last range is shorter than the others
+                }
+                q_count = avail < len ? static_cast<int>(avail) : len;
+                q_id = static_cast<long long>(r) * pieces_per_range + 1 + j;
+                const int4 qs = locate(prefix, p.num_seqs, a.units_per_seq, qx0);
+                gen.s = qs.x;
+                gen.j = qs.y;
+                gen.ti = qs.z;
+                gen.nt = static_cast<int>(prefix[qs.x + 1] - prefix[qs.x]);
+                q_start = gen;
+                g_left = q_count;
+                g_same = false;
+                next_block = tableEntry(gen);
+                break;
+            }
+        }
+        issue(gen_stage, gen, next_block);
+        gen_stage = (gen_stage + 1 == stages) ? 0 : gen_stage + 1;
+        --free_slots;
+        --g_left;
+        if (g_left > 0) {
+            advance(gen, prefix, p.num_seqs, a.units_per_seq);
+            next_block = tableEntry(gen);
+        }
+        if (POOL && g_left == 1 && !ahead && !pool_empty && !stop_claiming) {
+            // one tile before the piece runs out: the atomic's round trip hides behind that tile
+            k_ahead = claim();
+            ahead = true;
+        }
+        return true;
+    };
+    auto refill = [&]() {
+        while (free_slots > 0 && tryIssue()) {
         }
     };
 
     // ---- prologue: fill the ring ------------------------------------------------------
-    long long issued = 0;
-    {
-        Cursor pc[kMaxStages];
-        long long pb[kMaxStages];
-#pragma unroll
-        for (int i = 0; i < kMaxStages; ++i) {
-            if (i < stages && i < count) {
-                pc[i] = gen;
-                pb[i] = tableEntry(gen);
-                if (i + 1 < count) {
-                    advance(gen, prefix, p.num_seqs, a.units_per_seq);
-                }
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < kMaxStages; ++i) {
-            if (i < stages && i < count) {
-                issue(i, pc[i], pb[i]);
-                ++issued;
-            }
-        }
-    }
-    // `gen` now names tile number `issued` of the range (when it exists); fetch its table entry early.
-    long long next_block = (issued < count) ? tableEntry(gen) : 0;
+    refill();
 
     // ---- per-unit state ---------------------------------------------------------------
     uint32_t qa[kKSteps][2 * kRows]; // [.][2h], [.][2h + 1]: low / high 8 of the k-step, q-head g + 8h
@@ -554,12 +831,53 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     };
     loadUnit();
 
+    // ---- split units: who merges ----------------------------------------------------------
+    // A record is published in two lazy steps, so that nothing here waits on the memory system in the
+    // middle of the stream.  When the NEXT record is about to be written (or the stream is over): a fence
+    // - the record's stores were issued a piece ago and have long landed - and an atomicAdd of the
+    // segment's tile count on the unit's counter, whose return value stays in flight.  One step later that
+    // value is looked at: the worker that brought the count to the unit's length is the last to arrive, every
+    // other record of the unit is visible to it, and it notes the unit down; it merges its noted units when
+    // its streaming is done.  Nobody waits for anybody.
+    bool pend_valid = false, infl_valid = false;
+    long long pend_unit = 0, infl_unit = 0;
+    int pend_tiles = 0, pend_nt = 0, infl_tiles = 0, infl_nt = 0, infl_before = 0;
+    int merge_count = 0;
+    auto countSegments = [&]() {
+        if (infl_valid) {
+            const int before = __shfl_sync(0xffffffffu, infl_before, 0);
+            if (before + infl_tiles == infl_nt) {
+                if (lane == 0) {
+                    merge_list[merge_count] = infl_unit;
+                }
+                // With kMergeStop units noted the worker claims no further chunk.  What it still holds - the
+                // piece it consumes, the one after and a chunk claimed ahead, two partial segments each, plus
+                // the two segments in the counting steps - adds at most eight, so the list never overflows.
+                if (++merge_count >= kMergeStop) {
+                    stop_claiming = true;
+                }
+            }
+            infl_valid = false;
+        }
+        if (pend_valid) {
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) {
+                infl_before = atomicAdd(a.counters + 1 + pend_unit, pend_tiles);
+            }
+            infl_unit = pend_unit;
+            infl_tiles = pend_tiles;
+            infl_nt = pend_nt;
+            infl_valid = true;
+            pend_valid = false;
+        }
+    };
+
     bool failed = false;
     int stage = 0;
     uint32_t parity = 0;
 
-    long long i = 0;
-    for (; i < count; ++i) {
+    for (;;) {
         const uint32_t bar = bars + stage * 8;
         const uint32_t k_tile = ring + stage * kStageBytes;
         const uint32_t v_tile = k_tile + kTensorBytes;
@@ -737,35 +1055,34 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
 
         }
 
-        // ---- the slot is free: refill it with tile i + stages -----------------------------
+        // ---- the slot is free: top the ring up (this may open the next piece) --------------------
         __syncwarp();
-        if (issued < count) {
-            issue(stage, gen, next_block);
-            ++issued;
-            if (issued < count) {
-                advance(gen, prefix, p.num_seqs, a.units_per_seq);
-                next_block = tableEntry(gen);
-            }
-        }
+        ++free_slots;
         if (++stage == stages) {
             stage = 0;
             parity ^= 1u;
         }
+        refill();
+        --c_left;
 
-        // ---- end of unit or end of range: emit --------------------------------------------
+        // ---- end of unit or end of piece: emit --------------------------------------------
         const bool unit_end = (cur.ti + 1 == cur.nt);
-        if (unit_end || i + 1 == count) {
+        if (unit_end || c_left == 0) {
             const int kv_head = cur.j / head_tiles;
             const int head_tile = cur.j % head_tiles;
             const long long unit = static_cast<long long>(cur.s) * a.units_per_seq + cur.j;
-            float *rec = a.partials + (unit + worker) * (HPT * (HD + 2));
+            const bool whole_unit = (first_ti == 0 && unit_end);
+            float *rec = a.partials + (unit + c_id) * (HPT * (HD + 2));
+            if (!whole_unit && a.merge_in_kernel) {
+                countSegments(); // before this record's stores: the fence in there is about the previous record
+            }
 #pragma unroll
             for (int h = 0; h < kRows; ++h) {
                 float l_all = l_run[h];
                 l_all += __shfl_xor_sync(0xffffffffu, l_all, 1);
                 l_all += __shfl_xor_sync(0xffffffffu, l_all, 2);
                 const int r = g + 8 * h;
-                if (first_ti == 0 && unit_end) {
+                if (whole_unit) {
                     if (row_valid[h]) {
                         const int head = kv_head * p.group_size + head_tile * HPT + r;
                         const long long off = cur.s * p.o_seq_stride + head * p.o_head_stride;
@@ -790,12 +1107,37 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
                     }
                 }
             }
+            if (!whole_unit && a.merge_in_kernel) {
+                pend_unit = unit;
+                pend_tiles = cur.ti - first_ti + 1;
+                pend_nt = cur.nt;
+                pend_valid = true;
+            }
         }
-        if (i + 1 < count) {
+        if (c_left > 0) {
             advance(cur, prefix, p.num_seqs, a.units_per_seq);
             if (unit_end) {
                 loadUnit();
             }
+        } else {
+            // The piece is done.  refill() above has already tried to open the next one.
+            if (g_same) {
+                break;
+            }
+            cur = q_start;
+            c_left = q_count;
+            c_id = q_id;
+            g_same = true;
+            loadUnit();
+        }
+    }
+
+    if (!failed && a.merge_in_kernel) {
+        countSegments(); // counts the last segment
+        countSegments(); // looks at that count
+        __syncwarp();
+        for (int i = 0; i < merge_count; ++i) {
+            mergeUnit<T, HD, HPT>(a, prefix, range_len, geom, merge_list[i], lane);
         }
     }
 
@@ -807,7 +1149,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
         // released: they sit in slots `stage`, `stage + 1`, ... in issue order.
         int sidx = stage;
         uint32_t par = parity;
-        for (long long k = i; k < issued; ++k) {
+        for (int k = free_slots; k < stages; ++k) {
             (void)mbarWait(bars + sidx * 8, par);
             if (++sidx == stages) {
                 sidx = 0;
@@ -1269,8 +1611,10 @@ struct CombineShape {
     static constexpr int kMl = HPT * VD;                      // offset of the (m, l) pairs in a record
 };
 
-// HPT: q-heads per head tile (8 for the one-warp kernel, 16 for the wide-head kernel)
-template <typename T, int HD, int VD = HD, int HPT = kHeadsPerTile>
+// HPT: q-heads per head tile (8 or 16 for the one-warp kernel, 16 for the wide-head kernel).
+// BY_UNIT: CTA x merges unit x and finds the unit's records from the plan (one-warp kernel, used when a
+// few very long units are cut into many pieces each); otherwise CTA x executes tasks[x] (wide-head kernel).
+template <typename T, int HD, int VD = HD, int HPT = kHeadsPerTile, bool BY_UNIT = false>
 __global__ void __launch_bounds__(CombineShape<HD, VD, HPT>::kWarps * 32)
     pagedDecodeCombineKernel(const StreamArgs a) {
     using S = CombineShape<HD, VD, HPT>;
@@ -1283,21 +1627,42 @@ __global__ void __launch_bounds__(CombineShape<HD, VD, HPT>::kWarps * 32)
     const int lane = threadIdx.x & 31;
     gridDependencyWait(); // records, plan, tasks and directly written `out` rows come from the main kernel
     gridLaunchDependents();
-    const int r = blockIdx.x;
-    if (r >= a.header->num_ranges) {
-        return;
+    int s, j, n;
+    long long first_piece;
+    if constexpr (BY_UNIT) {
+        s = static_cast<int>(blockIdx.x / a.units_per_seq);
+        j = static_cast<int>(blockIdx.x % a.units_per_seq);
+        const long long nt = a.prefix[s + 1] - a.prefix[s];
+        if (nt == 0) {
+            return;
+        }
+        const long long range_len = a.header->range_len;
+        const PieceGeometry geom = pieceGeometry(range_len, a.max_chunks, a.min_chunk, a.tail_shift);
+        const long long xs = a.prefix[s] * a.units_per_seq + j * nt;
+        first_piece = pieceOf(xs, range_len, geom, a.max_chunks, a.min_chunk);
+        n = static_cast<int>(pieceOf(xs + nt - 1, range_len, geom, a.max_chunks, a.min_chunk) - first_piece) + 1;
+        if (n == 1) {
+            return; // one piece covered the unit and wrote `out` itself
+        }
+    } else {
+        const int r = blockIdx.x;
+        if (r >= a.header->num_ranges) {
+            return;
+        }
+        const int4 task = a.tasks[r];
+        n = task.w;
+        if (n <= 0) {
+            return;
+        }
+        s = task.x;
+        j = task.y;
+        first_piece = task.z;
     }
-    const int4 task = a.tasks[r];
-    const int n = task.w;
-    if (n <= 0) {
-        return;
-    }
-    const int s = task.x, j = task.y;
     const int kv_head = j / a.head_tiles;
     const int head_tile = j % a.head_tiles;
     const int heads_valid = min(HPT, p.group_size - head_tile * HPT);
     const long long unit = static_cast<long long>(s) * a.units_per_seq + j;
-    const float *base = a.partials + (unit + task.z) * S::kRec;
+    const float *base = a.partials + (unit + first_piece) * S::kRec;
     const int slice0 = static_cast<int>(blockIdx.y) * HD; // first value column this CTA merges
 
     // vector v of this lane covers floats [4 * (v * 32 + lane), +4) of the record slice: head
@@ -1442,19 +1807,22 @@ int envInt(const char *name, int fallback, int lo, int hi) {
 size_t roundUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct WorkspaceLayout {
-    size_t header_off, prefix_off, range_off, task_off, partial_off, total;
+    size_t header_off, prefix_off, range_off, task_off, counter_off, partial_off, total;
 };
 
 WorkspaceLayout workspaceLayout(const Info &I, const StreamPlan &plan) {
     WorkspaceLayout L;
+    const size_t units = I.num_seqs * I.num_kv_heads * static_cast<size_t>(plan.head_tiles_per_group);
     L.header_off = 0;
     L.prefix_off = 256;
     L.range_off = roundUp(L.prefix_off + (I.num_seqs + 1) * sizeof(long long), 256);
     L.task_off = roundUp(L.range_off + static_cast<size_t>(plan.num_workers) * sizeof(int4), 256);
-    L.partial_off = roundUp(L.task_off + static_cast<size_t>(plan.num_workers) * sizeof(int4), 256);
-    const size_t units = I.num_seqs * I.num_kv_heads * static_cast<size_t>(plan.head_tiles_per_group);
+    L.counter_off = roundUp(L.task_off + static_cast<size_t>(plan.num_workers) * sizeof(int4), 256);
+    // the wide-head kernel has no counters
+    L.partial_off = roundUp(L.counter_off + (plan.wide ? 0 : (units + 1) * sizeof(int)), 256);
     const size_t rec = static_cast<size_t>(plan.heads_per_tile) * (I.value_size + 2) * sizeof(float);
-    L.total = roundUp(L.partial_off + (units + plan.num_workers) * rec, 256);
+    const size_t pieces = static_cast<size_t>(plan.num_workers) * (plan.max_chunks + 1);
+    L.total = roundUp(L.partial_off + (units + pieces) * rec, 256);
     return L;
 }
 
@@ -1464,17 +1832,18 @@ infiniStatus_t launchTyped(const StreamPlan &plan, const StreamArgs &args, const
     // The opt-in shared memory limit is a per-device, per-kernel attribute; raise it whenever a plan
     // needs more than any earlier plan on that device did.
     static std::mutex attr_mutex;
-    static size_t attr_bytes[64] = {};
-    auto kernel = pagedDecodeStreamKernel<T, HD, HPT>;
+    static size_t attr_bytes[2][64] = {};
+    const int pool = args.max_chunks > 0 ? 1 : 0;
+    auto kernel = pool ? pagedDecodeStreamKernel<T, HD, HPT, true> : pagedDecodeStreamKernel<T, HD, HPT, false>;
     {
         std::lock_guard<std::mutex> lock(attr_mutex);
         const bool tracked = device_id >= 0 && device_id < 64;
-        if (!tracked || attr_bytes[device_id] < plan.smem_bytes) {
+        if (!tracked || attr_bytes[pool][device_id] < plan.smem_bytes) {
             if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan.smem_bytes)) != cudaSuccess) {
                 return checkLaunch("cudaFuncSetAttribute(pagedDecodeStreamKernel)");
             }
             if (tracked) {
-                attr_bytes[device_id] = plan.smem_bytes;
+                attr_bytes[pool][device_id] = plan.smem_bytes;
             }
         }
     }
@@ -1489,6 +1858,19 @@ infiniStatus_t launchTyped(const StreamPlan &plan, const StreamArgs &args, const
     cfg.attrs = &pdl;
     cfg.numAttrs = 1;
 
+    // reset kernel: the chunk counter, the per-unit tile counters when units are merged inside the main
+    // kernel, the error flag
+    const long long units = static_cast<long long>(args.p.num_seqs) * args.units_per_seq;
+    {
+        const long long count = 1 + (args.merge_in_kernel ? units : 0);
+        long long ctas = (count + 4 * kResetThreads - 1) / (4 * kResetThreads);
+        cfg.gridDim = dim3(static_cast<unsigned>(ctas > 64 ? 64 : ctas));
+        cfg.blockDim = dim3(kResetThreads);
+        cfg.dynamicSmemBytes = 0;
+        if (cudaLaunchKernelEx(&cfg, pagedDecodeResetKernel, args, count) != cudaSuccess) {
+            return checkLaunch("pagedDecodeResetKernel");
+        }
+    }
     if (!plan.embedded_plan) {
         cfg.gridDim = dim3(1);
         cfg.blockDim = dim3(kPlanThreads);
@@ -1503,28 +1885,31 @@ infiniStatus_t launchTyped(const StreamPlan &plan, const StreamArgs &args, const
     if (cudaLaunchKernelEx(&cfg, kernel, mk, mv, args) != cudaSuccess) {
         return checkLaunch("pagedDecodeStreamKernel");
     }
-    // Few units split over many workers each (a handful of very long sequences): a unit's records
-    // are merged by several CTAs, 32 value columns each, instead of one.  Records of 16 heads are
-    // always merged in slices (a whole record does not fit one CTA's shared memory).
-    const long long units = static_cast<long long>(args.p.num_seqs) * args.units_per_seq;
+    if (args.merge_in_kernel) {
+        return checkLaunch("pagedDecodeStream");
+    }
+    // One CTA per unit merges the unit's records (a unit that one piece covered has none and its CTA
+    // leaves at once).  Few units cut into many pieces each (a handful of very long sequences): several
+    // CTAs per unit, 32 value columns each.  Records of 16 heads are always merged in slices (a whole
+    // record does not fit one CTA's shared memory).
     cfg.dynamicSmemBytes = 0;
     constexpr int kWideSlice = (HD >= 64) ? 64 : HD;
     if (units * 4 <= plan.num_workers) {
-        cfg.gridDim = dim3(plan.num_workers, HD / 32);
+        cfg.gridDim = dim3(static_cast<unsigned>(units), HD / 32);
         cfg.blockDim = dim3(CombineShape<32, HD, HPT>::kWarps * 32);
-        if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, 32, HD, HPT>, args) != cudaSuccess) {
+        if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, 32, HD, HPT, true>, args) != cudaSuccess) {
             return checkLaunch("pagedDecodeCombineKernel");
         }
     } else if (HPT == 16) {
-        cfg.gridDim = dim3(plan.num_workers, HD / kWideSlice);
+        cfg.gridDim = dim3(static_cast<unsigned>(units), HD / kWideSlice);
         cfg.blockDim = dim3(CombineShape<kWideSlice, HD, HPT>::kWarps * 32);
-        if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, kWideSlice, HD, HPT>, args) != cudaSuccess) {
+        if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, kWideSlice, HD, HPT, true>, args) != cudaSuccess) {
             return checkLaunch("pagedDecodeCombineKernel");
         }
     } else {
-        cfg.gridDim = dim3(plan.num_workers);
+        cfg.gridDim = dim3(static_cast<unsigned>(units));
         cfg.blockDim = dim3(CombineShape<HD, HD, 8>::kWarps * 32);
-        if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, HD, HD, 8>, args) != cudaSuccess) {
+        if (cudaLaunchKernelEx(&cfg, pagedDecodeCombineKernel<T, HD, HD, 8, true>, args) != cudaSuccess) {
             return checkLaunch("pagedDecodeCombineKernel");
         }
     }
@@ -1661,7 +2046,7 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
 
     const size_t stage_bytes = 2 * (hd / 64) * kTileTokens * 128;
     const int default_stages = 2;
-    plan.warps_per_cta = envInt("INFINIOP_PAGED_DECODE_WARPS", 4, 1, kMaxWarps);
+    plan.warps_per_cta = envInt("INFINIOP_PAGED_DECODE_WARPS", 4, 1, hd == 64 ? 4 : kMaxWarps);
     plan.stages = envInt("INFINIOP_PAGED_DECODE_STAGES", default_stages, 1, kMaxStages);
     // Head 64 halves the bytes per tile while the per-tile latencies stay: a third resident CTA per SM
     // (its registers allow it) keeps enough copies in flight - 5.5 TB/s instead of 4.2 at 64 x 4096 tokens.
@@ -1670,8 +2055,20 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
     // a modest slice of shared memory; larger batches use the separate one-CTA plan kernel.
     plan.embedded_plan = envInt("INFINIOP_PAGED_DECODE_EMBEDDED_PLAN", 1, 0, 1) != 0 && I.num_seqs <= 4095;
     plan.use_pdl = envInt("INFINIOP_PAGED_DECODE_PDL", 1, 0, 1) != 0;
+    // Pieces (off by default: INFINIOP_PAGED_DECODE_CHUNKS = 1..8 turns them on): the last eighth of every
+    // range goes to the shared pool in that many chunks of halving size.  A chunk is located by a binary
+    // search over the tile prefix, which only the embedded plan keeps in shared memory: with the separate
+    // plan kernel ranges stay whole.  Measured: the pool evens the workers' finishing times out (they spread
+    // over 5 us instead of 36 at 64 x 4096 tokens), but every piece that does not cover a whole unit leaves
+    // a record, and reading ten records per unit instead of three costs what the balance gains; with more
+    // units than workers it changed the step by -2 % to +4 % from one GPU of the pool to the next.
+    plan.max_chunks = plan.embedded_plan ? envInt("INFINIOP_PAGED_DECODE_CHUNKS", 0, 0, 8) : 0;
+    plan.min_chunk = envInt("INFINIOP_PAGED_DECODE_MIN_CHUNK", 4, 1, 1024);
+    plan.tail_shift = envInt("INFINIOP_PAGED_DECODE_TAIL_SHIFT", 3, 1, 6);
+    plan.merge_in_kernel = envInt("INFINIOP_PAGED_DECODE_MERGE_IN_KERNEL", 1, 0, 1) != 0;
+    plan.l2_evict_first = envInt("INFINIOP_PAGED_DECODE_L2_EVICT_FIRST", 1, 0, 1) != 0;
     const size_t plan_bytes = plan.embedded_plan ? (I.num_seqs + 1 + kMaxWarps) * sizeof(long long) : 0;
-    auto smemFor = [&](int warps, int stages) { return static_cast<size_t>(warps) * stages * (stage_bytes + 8) + plan_bytes + 1024; };
+    auto smemFor = [&](int warps, int stages) { return static_cast<size_t>(warps) * (stages * (stage_bytes + 8) + kMergeList * sizeof(long long)) + plan_bytes + 1024; };
     const size_t budget = props.smem_per_block_optin;
     while (plan.stages > 1 && smemFor(plan.warps_per_cta, plan.stages) > budget) {
         --plan.stages;
@@ -1723,6 +2120,7 @@ infiniStatus_t launchDecodeStream(const Info &I, const StreamPlan &plan, const D
     a.prefix = reinterpret_cast<long long *>(ws + L.prefix_off);
     a.range_start = reinterpret_cast<int4 *>(ws + L.range_off);
     a.tasks = reinterpret_cast<int4 *>(ws + L.task_off);
+    a.counters = reinterpret_cast<int *>(ws + L.counter_off);
     a.partials = reinterpret_cast<float *>(ws + L.partial_off);
     a.head_tiles = plan.head_tiles_per_group;
     a.units_per_seq = static_cast<int>(I.num_kv_heads) * plan.head_tiles_per_group;
@@ -1730,6 +2128,13 @@ infiniStatus_t launchDecodeStream(const Info &I, const StreamPlan &plan, const D
     a.stages = plan.stages;
     a.num_workers = plan.num_workers;
     a.embedded_plan = plan.embedded_plan ? 1 : 0;
+    a.max_chunks = plan.max_chunks;
+    a.min_chunk = plan.min_chunk;
+    a.tail_shift = plan.tail_shift;
+    a.l2_evict_first = plan.l2_evict_first ? 1 : 0;
+    // Units cut into a few pieces each are merged by the last worker to arrive; a handful of units cut
+    // into hundreds of pieces each (4 or more workers per unit) by the combine kernel, many CTAs per unit.
+    a.merge_in_kernel = (!plan.wide && plan.merge_in_kernel && static_cast<long long>(I.num_seqs) * a.units_per_seq * 4 > plan.num_workers) ? 1 : 0;
 
     int device_id = -1;
     (void)cudaGetDevice(&device_id);

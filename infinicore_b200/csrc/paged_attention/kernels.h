@@ -73,6 +73,11 @@ struct StreamPlan {
     bool embedded_plan = false;   // the main kernel derives the plan itself (no plan kernel)
     bool use_pdl = true;          // launches carry the programmatic-serialization attribute
     bool wide = false;            // key width 576: one worker is a CTA of four warps (pagedDecodeWideKernel)
+    int max_chunks = 0;           // one-warp kernel: tail chunks per range that go to the pool shared by all workers
+    int min_chunk = 4;            // smallest such chunk, in 16-token tiles
+    int tail_shift = 3;           // the last range_len >> tail_shift tiles of a range are cut into chunks
+    bool l2_evict_first = true;   // one-warp kernel: K/V copies carry the evict-first L2 policy (they are read once)
+    bool merge_in_kernel = true;  // split units are merged by the last worker to arrive (when few pieces per unit), not by the combine kernel
 };
 
 // Decides at descriptor creation whether the streaming path applies and sizes its workspace.

@@ -8,10 +8,10 @@
 // scratch that infiniopPagedAttention asks for through infiniopGetPagedAttentionWorkspaceSize.
 //
 // Here the scratch lives in this library's own image: a file-scope __device__ array of
-// INFINIOP_PAGED_ATTENTION_STATIC_WORKSPACE_BYTES (16 MiB).  A GPU holds that array from the moment the
+// INFINIOP_PAGED_ATTENTION_STATIC_WORKSPACE_BYTES (32 MiB).  A GPU holds that array from the moment the
 // CUDA runtime loads this file's device code on it until the process exits.  With lazy module loading
 // (the runtime's default) that moment is the first call of this entry point on that device, not the
-// loading of the library: the 16 MiB are taken from the device's free memory THEN.  The split-KV records, the plan
+// loading of the library: the 32 MiB are taken from the device's free memory THEN.  The split-KV records, the plan
 // and the combine tasks of the streaming kernels are placed in it exactly as they would be in a
 // caller's buffer - the call below forwards to infiniopPagedAttention with the array's device
 // address as the workspace - so results are identical to the regular entry point's.
@@ -22,7 +22,7 @@
 //  * the first call on each device looks the array's device address up (cudaGetSymbolAddress, with
 //    that device current), which is also what makes the runtime place the array on that device.  Make
 //    that first call at start-up - before the KV pool takes the rest of the device's memory (otherwise
-//    it fails with INFINI_STATUS_INTERNAL_ERROR for want of 16 MiB) and before any stream capture
+//    it fails with INFINI_STATUS_INTERNAL_ERROR for want of 32 MiB) and before any stream capture
 //    begins.  Later calls take no memory at all;
 //  * all calls on one device share the one array.  It keeps whatever the previous call left in it;
 //    that is harmless, because the kernels rewrite every field they later read (nothing in the

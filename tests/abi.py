@@ -36,6 +36,12 @@ PATH_ENV = {
                            "INFINIOP_PAGED_DECODE_PDL": "0"},
     # other ring geometry: 3 warps per CTA, 4 slots
     "stream-3x4": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_DECODE_WARPS": "3", "INFINIOP_PAGED_DECODE_STAGES": "4"},
+    # split units merged by the combine kernel instead of by the last worker to arrive
+    "stream-combine": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_DECODE_MERGE_IN_KERNEL": "0"},
+    # ranges cut into pieces, tail chunks claimed from the shared pool (merged in the kernel / by the combine kernel)
+    "stream-pool": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_DECODE_CHUNKS": "4"},
+    "stream-pool-combine": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_DECODE_CHUNKS": "3",
+                            "INFINIOP_PAGED_DECODE_MIN_CHUNK": "2", "INFINIOP_PAGED_DECODE_MERGE_IN_KERNEL": "0"},
 }
 
 

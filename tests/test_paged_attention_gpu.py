@@ -219,10 +219,12 @@ def test_block_size_32_and_wide_block_table(abi, path):
     check(c, run_case(abi, c, path), oracle_out(c))
 
 
-@pytest.mark.parametrize("path", ["stream-plan-kernel", "stream-3x4"])
+@pytest.mark.parametrize("path", ["stream-plan-kernel", "stream-3x4", "stream-combine", "stream-pool", "stream-pool-combine"])
 def test_stream_path_variants(abi, path):
-    """The separate plan kernel with plain (non-programmatic) launches, and another ring geometry,
-    on ragged lengths with empty sequences and a split long sequence."""
+    """The separate plan kernel with plain (non-programmatic) launches, another ring geometry, the combine
+    kernel in place of the merge inside the main kernel, and the chunk pool (ranges too short here to be
+    cut: the pool variants must behave like the plain ones), on ragged lengths with empty sequences and a
+    split long sequence."""
     c = workloads.build_case("variants", dtype=torch.bfloat16, seq_lens=[1, 0, 47, 5000, 16, 333, 0, 2049], num_heads=32, num_kv_heads=8,
                              head_size=128, block_size=16, seed=33)
     out = torch.full((8, 32, 128), 2.0, dtype=torch.bfloat16, device="cuda")
@@ -232,6 +234,41 @@ def test_stream_path_variants(abi, path):
     atol, rtol = ATTN_TOL[c.dtype]
     assert_close(got[live].float().cpu().numpy(), want[live], atol, rtol, path)
     assert bool((got[[1, 6]] == 2.0).all())
+
+
+@pytest.mark.parametrize("path", ["stream", "stream-combine", "stream-pool", "stream-pool-combine"])
+@pytest.mark.parametrize("shape", ["few_long_units", "many_units"])
+def test_pieces_and_merges_match_the_oracle_and_repeat_bit_for_bit(abi, path, shape):
+    """Ranges long enough to be cut into a head piece and pool chunks (when the pool is on): every way of
+    merging the split units - inside the main kernel by the last worker to arrive, or by the combine
+    kernel - against the oracle, and three runs bit-identical (piece boundaries and merge order are fixed
+    by the plan; which worker computes a chunk is not)."""
+    g = torch.Generator().manual_seed(35)
+    if shape == "few_long_units":
+        # 12 sequences x 8 kv-heads = 96 units of 600..1300 tiles over 1184 workers: a unit collects many records
+        lens = torch.randint(9000, 21000, (12,), generator=g)
+        lens[3] = 33
+        lens[7] = 1
+        kw = dict(num_heads=32, num_kv_heads=8)
+    else:
+        # 700 sequences x 2 kv-heads = 1400 units, more than workers: most units whole, the rest cut once or twice
+        lens = torch.randint(300, 1500, (700,), generator=g)
+        lens[5] = 0
+        kw = dict(num_heads=8, num_kv_heads=2)
+    c = workloads.build_case("pieces_" + shape, dtype=torch.bfloat16, seq_lens=lens, head_size=128, block_size=16, seed=35, **kw)
+    want = oracle_out(c)
+    live = (lens > 0).nonzero().flatten().tolist()
+    atol, rtol = ATTN_TOL[c.dtype]
+    d = c.to("cuda")
+    runs = []
+    for _ in range(3):
+        out = torch.full((len(lens), kw["num_heads"], 128), 3.0, dtype=torch.bfloat16, device="cuda")
+        runs.append(abi.paged_attention(d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens, d.scale, path=path, out=out).clone())
+    assert_close(runs[0][live].float().cpu().numpy(), want[live], atol, rtol, f"{shape} {path}")
+    for r in runs[1:]:
+        assert torch.equal(r.view(torch.int16), runs[0].view(torch.int16)), "runs differ"
+    if shape == "many_units":
+        assert bool((runs[0][5] == 3.0).all())
 
 
 def test_more_sequences_than_the_embedded_plan_holds(abi):

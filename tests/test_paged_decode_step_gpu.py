@@ -18,7 +18,7 @@ from infinicore_b200.libinfiniop import InfiniDtype
 
 pytestmark = pytest.mark.gpu
 
-PATHS = [None, "generic", "stream-plan-kernel", "stream-3x4"]
+PATHS = [None, "generic", "stream-plan-kernel", "stream-3x4", "stream-pool"]
 
 
 @pytest.fixture(scope="module")

@@ -3,7 +3,7 @@
 Some users of this library have no device memory to offer as workspace: a serving engine that gave
 all free HBM to its KV pool, a process whose allocator is frozen once serving starts, an operator
 callback that may only touch buffers its host framework registered.  For them the library carries
-a 16 MiB scratch array of its own.  This test calls that entry point through the C ABI - passing
+a 32 MiB scratch array of its own.  This test calls that entry point through the C ABI - passing
 inputs and outputs only - and checks the result against the regular infiniopPagedAttention (caller
 workspace) and against the CPU oracle on two different problems in a row, so that whatever the first
 call left in the shared array is in place when the second one runs; that calls after the first leave
@@ -26,7 +26,7 @@ from infinicore_b200 import workloads
 
 pytestmark = pytest.mark.gpu
 
-STATIC_BYTES = 16 << 20
+STATIC_BYTES = 32 << 20
 
 
 @pytest.fixture(scope="module")
@@ -124,7 +124,7 @@ def test_other_kernel_routes_share_the_array(abi, name, kwargs, path):
 
 
 def test_a_problem_larger_than_the_array_is_refused_untouched(abi):
-    # 2048 sequences x 8 kv-heads of records do not fit in 16 MiB; shapes alone decide, so tiny pools do
+    # 2048 sequences x 8 kv-heads of records do not fit in 32 MiB; shapes alone decide, so tiny pools do
     c = workloads.build_case("static_big", dtype=torch.float16, seq_lens=[1] * 2048, num_heads=32, num_kv_heads=8,
                              head_size=128, block_size=16, seed=73)
     d = c.to("cuda")
