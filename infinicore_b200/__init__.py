@@ -20,6 +20,7 @@ _LAZY = {
     "rope": "ops",
     "kv_caching": "ops",
     "RopeAlgo": "ops",
+    "kernel_status": "ops",
     "DecodeStep": "decode_step",
 }
 

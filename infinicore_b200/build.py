@@ -40,6 +40,7 @@ COMMON = [
 RT_SOURCES = ["runtime/infinirt.cu"]
 OP_SOURCES = [
     "handle.cu",
+    "kernel_status.cu",
     "paged_caching/paged_caching.cu",
     "paged_attention/operator.cu",
     "paged_attention/decode_generic.cu",

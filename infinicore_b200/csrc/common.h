@@ -49,7 +49,11 @@ struct DeviceProps {
     int warp_size = 0;
     size_t smem_per_block_optin = 0;
     size_t smem_per_sm = 0;
+    unsigned int *kernel_flags = nullptr; // the device's word of kernel status flags (infiniopGetKernelStatus)
 };
+
+// Device address of that word on `device_id`, which must be the current device the first time.
+infiniStatus_t kernelFlagsAddress(int device_id, unsigned int **ptr);
 
 struct Handle {
     // must stay first: callers read {device, device_id}

@@ -40,6 +40,8 @@ __INFINI_C infiniStatus_t infiniopCreateHandle(infiniopHandle_t *handle_ptr) {
     props->warp_size = prop.warpSize;
     props->smem_per_block_optin = prop.sharedMemPerBlockOptin;
     props->smem_per_sm = prop.sharedMemPerMultiprocessor;
+    st = b200::kernelFlagsAddress(device_id, &props->kernel_flags);
+    B200_RETURN_IF(st != INFINI_STATUS_SUCCESS, st);
 
     auto *h = new Handle{{device, device_id}, std::move(props)};
     *handle_ptr = reinterpret_cast<infiniopHandle_t>(h);

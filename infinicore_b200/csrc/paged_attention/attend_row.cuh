@@ -74,7 +74,7 @@ __device__ inline void attendRow(const DecodeParams &p, const T *q, T *out, int 
     for (int t = warp; t < seq_len; t += kWarps) {
         const int logical_block = t / p.block_size;
         const int row = t - logical_block * p.block_size;
-        const long long block = loadIndex(p.block_tables, bt_row + logical_block, p.index_is_64);
+        const long long block = checkedBlock(p, loadIndex(p.block_tables, bt_row + logical_block, p.index_is_64));
         const T *k_row = k_base + block * p.k_block_stride + row * p.k_row_stride;
         const T *v_row = v_base + block * p.v_block_stride + row * p.v_row_stride;
 

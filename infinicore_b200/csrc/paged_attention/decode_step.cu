@@ -142,6 +142,13 @@ __global__ void __launch_bounds__(128) pagedAppendRowsKernel(const DecodeParams 
     }
     const long long n = len - 1;
     const long long block = loadIndex(p.block_tables, seq * p.bt_seq_stride + n / p.block_size, p.index_is_64);
+    if (static_cast<unsigned long long>(block) >= static_cast<unsigned long long>(p.num_blocks)) {
+        // a table entry outside the pool: nothing is stored (reported when index checking is on)
+        if (lane == 0 && p.check_indices) {
+            atomicOr(p.kernel_flags, 2u);
+        }
+        return;
+    }
     const int row = static_cast<int>(n % p.block_size);
     const int width = is_v ? p.value_size : p.head_size;
     const T *src = is_v ? static_cast<const T *>(p.new_v) + seq * p.new_v_seq_stride + kv_head * p.value_size
@@ -271,6 +278,8 @@ infiniStatus_t createStep(
         info.q_head_stride = static_cast<ptrdiff_t>(info.head_size);
     }
     d->info = info;
+    d->info.kernel_flags = h->props->kernel_flags;
+    d->info.check_indices = b200::paged_attention::checkIndicesFromEnv();
 
     // the same path selection as infiniopPagedAttention (INFINIOP_PAGED_DECODE_PATH = auto | stream | generic)
     const char *path = std::getenv("INFINIOP_PAGED_DECODE_PATH");

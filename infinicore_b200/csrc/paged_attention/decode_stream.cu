@@ -66,7 +66,7 @@ constexpr int kResetThreads = 1024;
 constexpr int kMinDynamicRange = 32; // ranges shorter than this many tiles are not cut into pieces
 
 struct PlanHeader {
-    int error;      // set non-zero by a worker whose bounded wait ran out
+    int reserved;
     int num_ranges; // ranges actually used (<= number of workers)
     long long total_tiles;
     long long range_len;
@@ -91,6 +91,8 @@ struct StreamArgs {
     int tail_shift;      // the last range_len >> tail_shift tiles of a range go to the pool
     int merge_in_kernel; // 1: the last worker to arrive at a unit merges its records; 0: the combine kernel does
     int l2_evict_first;  // 1: K/V copies carry the evict-first L2 policy
+    long long wait_limit_cycles; // a bounded wait gives up after this many cycles of the SM's counter
+    int withhold_first_copy;     // test only: worker 0 leaves out its first copy, so that its first wait runs out
 };
 
 // ---------------------------------------------------------------------------------------
@@ -127,13 +129,13 @@ __device__ __forceinline__ bool mbarTryWait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait: false means the limit ran out (the copy or MMA it waits for never completed).  The
 // bound is counted on the SM's cycle counter, which is cheap to read; roughly 2 s at 2 GHz.
-__device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbarWait(uint32_t bar, uint32_t parity, long long limit = kWaitLimitCycles) {
     if (mbarTryWait(bar, parity)) {
         return true;
     }
     const long long t0 = clock64();
     while (!mbarTryWait(bar, parity)) {
-        if (clock64() - t0 > kWaitLimitCycles) {
+        if (clock64() - t0 > limit) {
             return false;
         }
     }
@@ -343,7 +345,7 @@ __device__ __forceinline__ long long pieceOf(long long x, long long range_len, P
 }
 
 // ---------------------------------------------------------------------------------------
-// Reset kernel: clears the chunk counter and the per-unit tile counters (and the error flag) of the
+// Reset kernel: clears the chunk counter and the per-unit tile counters of the
 // one-warp kernel.  It sits in front of every launch because the workspace is the caller's scratch:
 // nothing can be assumed about what the previous user left in it.
 // ---------------------------------------------------------------------------------------
@@ -354,9 +356,6 @@ __global__ void __launch_bounds__(kResetThreads)
     for (long long i = static_cast<long long>(blockIdx.x) * kResetThreads + threadIdx.x; i < count;
          i += static_cast<long long>(gridDim.x) * kResetThreads) {
         a.counters[i] = 0;
-    }
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
-        a.header->error = 0;
     }
 }
 
@@ -432,7 +431,6 @@ __global__ void __launch_bounds__(kPlanThreads)
     }
     const int num_ranges = static_cast<int>((total + range_len - 1) / range_len);
     if (tid == 0) {
-        a.header->error = 0;
         a.header->num_ranges = num_ranges;
         a.header->total_tiles = total;
         a.header->range_len = range_len;
@@ -460,7 +458,7 @@ __device__ __noinline__ void mergeUnit(const StreamArgs &a, const long long *pre
     constexpr int kRec = HPT * (HD + 2);
     constexpr int kVecs = HPT * HD / 128;             // float4 per lane per record
     constexpr int kRowVecs = HD / 4;                  // float4 per accumulator row
-    constexpr int kBatch = (24 / kVecs) > 0 ? (24 / kVecs) : 1; // records fetched together
+    constexpr int kBatch = (32 / kVecs) > 0 ? (32 / kVecs) : 1; // records fetched together
     const DecodeParams &p = a.p;
     const int s = static_cast<int>(unit / a.units_per_seq);
     const int j = static_cast<int>(unit - static_cast<long long>(s) * a.units_per_seq);
@@ -583,6 +581,12 @@ __global__ void __launch_bounds__(HD == 64 ? 128 : kMaxWarps * 32, HD == 64 ? 3 
     }
     __syncwarp();
 
+    // The two tensor maps are kernel parameters: fetching them into the copy engine's descriptor cache does
+    // not read anything an earlier kernel may still be writing.
+    if (lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_k)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_v)) : "memory");
+    }
     // Everything above touches only this CTA's shared memory; from here on global memory that an
     // earlier kernel in the stream may have produced is read.
     gridDependencyWait();
@@ -694,9 +698,10 @@ __global__ void __launch_bounds__(HD == 64 ? 128 : kMaxWarps * 32, HD == 64 ? 3 
     const int head_tiles = a.head_tiles;
     const uint64_t stream_policy = evictFirstPolicy();
 
+    bool withhold = a.withhold_first_copy != 0 && worker == 0;
     auto tableEntry = [&](const Cursor &c) -> long long {
         const int page = (tpp == 1) ? c.ti : c.ti / tpp;
-        return loadIndex(p.block_tables, c.s * p.bt_seq_stride + page, p.index_is_64);
+        return reportedBlock(p, loadIndex(p.block_tables, c.s * p.bt_seq_stride + page, p.index_is_64));
     };
     auto issue = [&](int stage, const Cursor &c, long long block) {
         const uint32_t bar = bars + stage * 8;
@@ -704,7 +709,9 @@ __global__ void __launch_bounds__(HD == 64 ? 128 : kMaxWarps * 32, HD == 64 ? 3 
         if (lane == 0) {
             mbarExpectTx(bar, kStageBytes);
         }
-        if (lane < 2 * kChunks) {
+        const bool skip = withhold && lane == 0; // test only: the bytes are expected and never arrive
+        withhold = false;
+        if (lane < 2 * kChunks && !skip) {
             const int is_v = lane / kChunks;
             const int chunk = lane % kChunks;
             const int row0 = (tpp == 1) ? 0 : (c.ti % tpp) * kTileTokens;
@@ -881,7 +888,7 @@ __global__ void __launch_bounds__(HD == 64 ? 128 : kMaxWarps * 32, HD == 64 ? 3 
         const uint32_t bar = bars + stage * 8;
         const uint32_t k_tile = ring + stage * kStageBytes;
         const uint32_t v_tile = k_tile + kTensorBytes;
-        if (!mbarWait(bar, parity)) {
+        if (!mbarWait(bar, parity, a.wait_limit_cycles)) {
             failed = true;
             break;
         }
@@ -899,8 +906,11 @@ __global__ void __launch_bounds__(HD == 64 ? 128 : kMaxWarps * 32, HD == 64 ? 3 
             const int row = valid - 1;
             const T *nk = static_cast<const T *>(p.new_k) + cur.s * p.new_k_seq_stride + kv_head * HD;
             const T *nv = static_cast<const T *>(p.new_v) + cur.s * p.new_v_seq_stride + kv_head * HD;
-            const bool writer = (cur.j % head_tiles) == 0;
+            bool writer = (cur.j % head_tiles) == 0;
             const long long block = writer ? tableEntry(cur) : 0;
+            if (static_cast<unsigned long long>(block) >= static_cast<unsigned long long>(p.num_blocks)) {
+                writer = false; // a table entry outside the pool: the row is used for this step but not stored
+            }
             const int row_in_block = (seq_len - 1) % p.block_size;
             T *kc = static_cast<T *>(const_cast<void *>(p.k_cache)) + block * p.k_block_stride + kv_head * p.k_head_stride + row_in_block * p.k_row_stride;
             T *vc = static_cast<T *>(const_cast<void *>(p.v_cache)) + block * p.v_block_stride + kv_head * p.v_head_stride + row_in_block * p.v_row_stride;
@@ -1142,15 +1152,15 @@ __global__ void __launch_bounds__(HD == 64 ? 128 : kMaxWarps * 32, HD == 64 ? 3 
     }
 
     if (failed) {
-        if (lane == 0) {
-            atomicExch(&a.header->error, 1);
+        if (lane == 0 && p.kernel_flags != nullptr) {
+            atomicOr(p.kernel_flags, 1u);
         }
         // Let this worker's copies still in flight land (bounded) before its shared memory is
         // released: they sit in slots `stage`, `stage + 1`, ... in issue order.
         int sidx = stage;
         uint32_t par = parity;
         for (int k = free_slots; k < stages; ++k) {
-            (void)mbarWait(bars + sidx * 8, par);
+            (void)mbarWait(bars + sidx * 8, par, a.wait_limit_cycles);
             if (++sidx == stages) {
                 sidx = 0;
                 par ^= 1u;
@@ -1265,13 +1275,14 @@ __global__ void __launch_bounds__(kWideWarps * 32)
     const int head_tiles = a.head_tiles;
     auto tableEntry = [&](const Cursor &c) -> long long {
         const int page = (tpp == 1) ? c.ti : c.ti / tpp;
-        return loadIndex(p.block_tables, c.s * p.bt_seq_stride + page, p.index_is_64);
+        return reportedBlock(p, loadIndex(p.block_tables, c.s * p.bt_seq_stride + page, p.index_is_64));
     };
     // The copies of a tile are shared out over the four warps (a copy costs its issuing lane on the
     // order of a hundred cycles, and the lanes of one warp issue one after another): warp w takes
     // boxes w, w + 4, ... of the K chunks followed by the V chunks, one box per lane, and announces
     // its own bytes with its own arrival on the slot's barrier.
     constexpr int kBoxes = kKChunks + kVChunks;
+    const uint64_t stream_policy = evictFirstPolicy();
     const int my_box = warp + kWideWarps * lane;
     const bool has_box = my_box < kBoxes;
     const uint32_t my_bytes = static_cast<uint32_t>((kBoxes - warp + kWideWarps - 1) / kWideWarps) * kBoxBytes;
@@ -1287,8 +1298,13 @@ __global__ void __launch_bounds__(kWideWarps * 32)
             const int chunk = is_v ? my_box - kKChunks : my_box;
             const int row0 = (tpp == 1) ? 0 : (c.ti % tpp) * kTileTokens;
             const int kv_head = (head_tiles == 1) ? c.j : c.j / head_tiles;
-            tmaLoadBox(dst + (is_v ? kKBytes : 0) + chunk * kBoxBytes, is_v ? &tmap_v : &tmap_k, bar,
-                       chunk * 64, row0, kv_head, static_cast<int>(block));
+            if (a.l2_evict_first) {
+                tmaLoadBoxHint(dst + (is_v ? kKBytes : 0) + chunk * kBoxBytes, is_v ? &tmap_v : &tmap_k, bar,
+                               chunk * 64, row0, kv_head, static_cast<int>(block), stream_policy);
+            } else {
+                tmaLoadBox(dst + (is_v ? kKBytes : 0) + chunk * kBoxBytes, is_v ? &tmap_v : &tmap_k, bar,
+                           chunk * 64, row0, kv_head, static_cast<int>(block));
+            }
         }
     };
 
@@ -1384,8 +1400,11 @@ __global__ void __launch_bounds__(kWideWarps * 32)
             const int row = valid - 1;
             const T *nk = static_cast<const T *>(p.new_k) + cur.s * p.new_k_seq_stride + kv_head * KD;
             const T *nv = static_cast<const T *>(p.new_v) + cur.s * p.new_v_seq_stride + kv_head * VD;
-            const bool writer = (cur.j % head_tiles) == 0;
+            bool writer = (cur.j % head_tiles) == 0;
             const long long block = writer ? tableEntry(cur) : 0;
+            if (static_cast<unsigned long long>(block) >= static_cast<unsigned long long>(p.num_blocks)) {
+                writer = false; // a table entry outside the pool: the row is used for this step but not stored
+            }
             const int row_in_block = (seq_len - 1) % p.block_size;
             T *kc = static_cast<T *>(const_cast<void *>(p.k_cache)) + block * p.k_block_stride + kv_head * p.k_head_stride + row_in_block * p.k_row_stride;
             T *vc = static_cast<T *>(const_cast<void *>(p.v_cache)) + block * p.v_block_stride + kv_head * p.v_head_stride + row_in_block * p.v_row_stride;
@@ -1576,8 +1595,8 @@ __global__ void __launch_bounds__(kWideWarps * 32)
         }
     }
 
-    if (failed && lane == 0) {
-        atomicExch(&a.header->error, 1);
+    if (failed && lane == 0 && p.kernel_flags != nullptr) {
+        atomicOr(p.kernel_flags, 1u);
     }
     // Copies still in flight must land before the CTA's shared memory is released.  A warp whose
     // wait ran out drains its own slots: whichever phase is pending, a bounded wait on both
@@ -2067,6 +2086,12 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
     plan.tail_shift = envInt("INFINIOP_PAGED_DECODE_TAIL_SHIFT", 3, 1, 6);
     plan.merge_in_kernel = envInt("INFINIOP_PAGED_DECODE_MERGE_IN_KERNEL", 1, 0, 1) != 0;
     plan.l2_evict_first = envInt("INFINIOP_PAGED_DECODE_L2_EVICT_FIRST", 1, 0, 1) != 0;
+    // How long a worker waits for one of its own copies before it gives up (INFINIOP_PAGED_DECODE_WAIT_LIMIT_MS,
+    // default 2000), counted on the SM's cycle counter at a nominal 2 GHz.  And a switch for the test of that
+    // path only: INFINIOP_PAGED_DECODE_TEST_WITHHOLD_COPY=1 makes worker 0 leave out the first copy it would
+    // issue, so that its first wait runs out, the kernel returns and the device's status word says so.
+    plan.wait_limit_cycles = static_cast<long long>(envInt("INFINIOP_PAGED_DECODE_WAIT_LIMIT_MS", 2000, 1, 60000)) * 2000000ll;
+    plan.withhold_first_copy = envInt("INFINIOP_PAGED_DECODE_TEST_WITHHOLD_COPY", 0, 0, 1) != 0;
     const size_t plan_bytes = plan.embedded_plan ? (I.num_seqs + 1 + kMaxWarps) * sizeof(long long) : 0;
     auto smemFor = [&](int warps, int stages) { return static_cast<size_t>(warps) * (stages * (stage_bytes + 8) + kMergeList * sizeof(long long)) + plan_bytes + 1024; };
     const size_t budget = props.smem_per_block_optin;
@@ -2132,6 +2157,8 @@ infiniStatus_t launchDecodeStream(const Info &I, const StreamPlan &plan, const D
     a.min_chunk = plan.min_chunk;
     a.tail_shift = plan.tail_shift;
     a.l2_evict_first = plan.l2_evict_first ? 1 : 0;
+    a.wait_limit_cycles = plan.wait_limit_cycles;
+    a.withhold_first_copy = plan.withhold_first_copy ? 1 : 0;
     // Units cut into a few pieces each are merged by the last worker to arrive; a handful of units cut
     // into hundreds of pieces each (4 or more workers per unit) by the combine kernel, many CTAs per unit.
     a.merge_in_kernel = (!plan.wide && plan.merge_in_kernel && static_cast<long long>(I.num_seqs) * a.units_per_seq * 4 > plan.num_workers) ? 1 : 0;

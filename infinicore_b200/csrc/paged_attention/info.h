@@ -33,6 +33,11 @@ struct Info {
     ptrdiff_t k_block_stride, k_head_stride, k_row_stride;
     ptrdiff_t v_block_stride, v_head_stride, v_row_stride;
     ptrdiff_t block_table_seq_stride;
+
+    // set by the descriptor's creator, not by makeInfo: where the kernels report (the device's status word)
+    // and whether they check block-table entries against the pool (INFINIOP_PAGED_CHECK_INDICES=1)
+    unsigned int *kernel_flags = nullptr;
+    bool check_indices = false;
 };
 
 inline infiniStatus_t makeInfo(Info &I,

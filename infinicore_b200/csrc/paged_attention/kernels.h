@@ -49,7 +49,36 @@ struct DecodeParams {
     static constexpr int kMaxExtraOut = 7;
     void *extra_out[kMaxExtraOut] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     int num_extra_out = 0;
+
+    // Status reporting (include/infiniop/ops/kernel_status.h): the device's flag word, and whether block-table
+    // entries are checked against the pool size before they are used (a bad one raises a flag and reads
+    // block 0 instead).
+    unsigned int *kernel_flags = nullptr;
+    int check_indices = 0;
+    long long num_blocks = 0;
 };
+
+// INFINIOP_PAGED_CHECK_INDICES=1 in the environment when a descriptor is created switches index checking on.
+bool checkIndicesFromEnv();
+
+// Block-table entry as the kernels use it: in checked mode an entry outside [0, num_blocks) raises
+// INFINIOP_KERNEL_FLAG_BLOCK_OUT_OF_RANGE and becomes block 0.
+__device__ __forceinline__ long long checkedBlock(const DecodeParams &p, long long block) {
+    if (p.check_indices && static_cast<unsigned long long>(block) >= static_cast<unsigned long long>(p.num_blocks)) {
+        atomicOr(p.kernel_flags, 2u);
+        return 0;
+    }
+    return block;
+}
+
+// The same check for kernels that fetch pages through the copy engine, which fills a box outside the pool with
+// zeros by itself: the entry is only reported.
+__device__ __forceinline__ long long reportedBlock(const DecodeParams &p, long long block) {
+    if (p.check_indices && static_cast<unsigned long long>(block) >= static_cast<unsigned long long>(p.num_blocks)) {
+        atomicOr(p.kernel_flags, 2u);
+    }
+    return block;
+}
 
 __host__ __device__ inline long long loadIndex(const void *base, long long i, int is64) {
     return is64 ? static_cast<const long long *>(base)[i]
@@ -77,6 +106,8 @@ struct StreamPlan {
     int min_chunk = 4;            // smallest such chunk, in 16-token tiles
     int tail_shift = 3;           // the last range_len >> tail_shift tiles of a range are cut into chunks
     bool l2_evict_first = true;   // one-warp kernel: K/V copies carry the evict-first L2 policy (they are read once)
+    long long wait_limit_cycles = 4000000000ll; // a bounded mbarrier wait gives up after this many SM cycles (~2 s)
+    bool withhold_first_copy = false; // test only: worker 0 never issues its first copy, so that its wait runs out
     bool merge_in_kernel = true;  // split units are merged by the last worker to arrive (when few pieces per unit), not by the combine kernel
 };
 

@@ -52,7 +52,15 @@ DecodeParams makeDecodeParams(const Info &I, void *out, const void *q, const voi
     p.v_row_stride = I.v_row_stride;
     p.bt_seq_stride = I.block_table_seq_stride;
     p.scale_log2e = I.scale * 1.4426950408889634f;
+    p.kernel_flags = I.kernel_flags;
+    p.check_indices = (I.check_indices && I.kernel_flags != nullptr) ? 1 : 0;
+    p.num_blocks = static_cast<long long>(I.num_blocks);
     return p;
+}
+
+bool checkIndicesFromEnv() {
+    const char *v = std::getenv("INFINIOP_PAGED_CHECK_INDICES");
+    return v != nullptr && v[0] == '1';
 }
 
 } // namespace b200::paged_attention
@@ -86,6 +94,8 @@ __INFINI_C infiniStatus_t infiniopCreatePagedAttentionDescriptor(
                    INFINI_STATUS_BAD_TENSOR_SHAPE);
 
     auto *h = reinterpret_cast<b200::Handle *>(handle);
+    info.kernel_flags = h->props->kernel_flags;
+    info.check_indices = b200::paged_attention::checkIndicesFromEnv();
     auto *d = new Descriptor{{handle->device, handle->device_id, b200::OpKind::PagedAttention, h->props}, info, {}, 0};
 
     // INFINIOP_PAGED_DECODE_PATH = auto (default) | stream | generic

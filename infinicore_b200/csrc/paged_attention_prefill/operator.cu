@@ -48,6 +48,8 @@ __INFINI_C infiniStatus_t infiniopCreatePagedAttentionPrefillDescriptor(
                    INFINI_STATUS_BAD_TENSOR_SHAPE);
 
     auto *h = reinterpret_cast<b200::Handle *>(handle);
+    info.attn.kernel_flags = h->props->kernel_flags;
+    info.attn.check_indices = b200::paged_attention::checkIndicesFromEnv();
     auto *d = new Descriptor{{handle->device, handle->device_id, b200::OpKind::PagedAttentionPrefill, h->props}, info, {}, {}};
     // INFINIOP_PAGED_PREFILL_PATH = auto (default) | umma | tiles | generic
     const char *path = std::getenv("INFINIOP_PAGED_PREFILL_PATH");
@@ -139,6 +141,9 @@ __INFINI_C infiniStatus_t infiniopPagedAttentionPrefill(
     p.v_row_stride = A.v_row_stride;
     p.bt_seq_stride = A.block_table_seq_stride;
     p.scale_log2e = A.scale * 1.4426950408889634f;
+    p.kernel_flags = A.kernel_flags;
+    p.check_indices = (A.check_indices && A.kernel_flags != nullptr) ? 1 : 0;
+    p.num_blocks = static_cast<long long>(A.num_blocks);
     pp.cum_seq_lens_q = cum_seq_lens_q;
     pp.total_q = static_cast<int>(d->info.total_q_tokens);
 

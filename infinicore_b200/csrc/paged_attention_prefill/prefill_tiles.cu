@@ -131,7 +131,7 @@ __device__ __forceinline__ void consumerSync() {
 struct TileArgs {
     PrefillParams pp;
     int box_rows; // 8 or 16
-    int *error;   // may be null
+    unsigned int *error; // the device's status word (infiniopGetKernelStatus); may be null
 };
 
 template <typename T, int HD>
@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(kThreads)
             if (kt >= kStages) {
                 if (!mbarWait(empty_bar + stage * 8, parity ^ 1u)) {
                     if (lane == 0 && a.error != nullptr) {
-                        atomicExch(a.error, 1);
+                        atomicOr(a.error, 1u);
                     }
                     return;
                 }
@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(kThreads)
                     const int j0 = kv0 + r * box_rows;
                     const int page = j0 / p.block_size;
                     const int row0 = j0 - page * p.block_size;
-                    const long long block = loadIndex(p.block_tables, seq * p.bt_seq_stride + page, p.index_is_64);
+                    const long long block = paged_attention::reportedBlock(p, loadIndex(p.block_tables, seq * p.bt_seq_stride + page, p.index_is_64));
                     tmaLoadBox(dst + is_v * kTensorBytes + c * (kBN * 128) + r * box_bytes, is_v ? &tmap_v : &tmap_k,
                                full_bar + stage * 8, c * 64, row0, kv_head, static_cast<int>(block));
                 }
@@ -450,7 +450,7 @@ __global__ void __launch_bounds__(kThreads)
 
     if (failed) {
         if (lane == 0 && a.error != nullptr) {
-            atomicExch(a.error, 1);
+            atomicOr(a.error, 1u);
         }
         return;
     }
@@ -587,7 +587,7 @@ infiniStatus_t launchPrefillTiles(const Info &info, const TilePlan &plan, const 
     TileArgs args;
     args.pp = pp;
     args.box_rows = plan.box_rows;
-    args.error = nullptr;
+    args.error = pp.d.kernel_flags;
     const unsigned tiles = static_cast<unsigned>((info.total_q_tokens + kBM - 1) / kBM + A.num_seqs);
     int device_id = -1;
     (void)cudaGetDevice(&device_id);

@@ -520,7 +520,7 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
             if (has_box && kt < num_kv_tiles && j0 < kv_end) {
                 const int page = j0 / p.block_size;
                 row0 = j0 - page * p.block_size;
-                block = loadIndex(p.block_tables, bt_row + page, p.index_is_64);
+                block = paged_attention::reportedBlock(p, loadIndex(p.block_tables, bt_row + page, p.index_is_64));
             }
         };
         long long block_next;
@@ -836,6 +836,9 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
     // ---- common exit: every role gets here on every path; TMEM reads and MMAs are done ------------
     tcgenFenceBefore();
     __syncthreads();
+    if (threadIdx.x == 0 && sh_failed != 0 && p.kernel_flags != nullptr) {
+        atomicOr(p.kernel_flags, 1u); // a bounded wait of this CTA ran out: its rows are missing (infiniopGetKernelStatus)
+    }
     if (warp == kMmaWarp0) {
         tcgenFenceAfter();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");

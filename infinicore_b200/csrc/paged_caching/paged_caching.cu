@@ -40,6 +40,8 @@ struct Descriptor {
     OpDescriptorBase base;
     Info info;
     bool use_pdl; // INFINIOP_PAGED_DECODE_PDL (default 1), read when the descriptor is created
+    bool check_indices; // INFINIOP_PAGED_CHECK_INDICES (default 0), likewise
+    size_t num_blocks;
 };
 
 static infiniStatus_t makeInfo(Info &out,
@@ -116,6 +118,13 @@ struct KernelArgs {
     int v_row_bytes;
     long long k_src_token, k_src_head, v_src_token, v_src_head;
     long long k_blk, k_head, k_slot, v_blk, v_head, v_slot;
+    // index checking (INFINIOP_PAGED_CHECK_INDICES=1 when the descriptor was created): a slot at or beyond
+    // num_slots raises INFINIOP_KERNEL_FLAG_SLOT_OUT_OF_RANGE in the device's status word and its row is
+    // skipped; unchecked, the row goes wherever the slot says, as in the reference's kernel
+    // (src/infiniop/ops/paged_caching/cuda/kernel.cuh:60-78)
+    unsigned int *kernel_flags;
+    long long num_slots;
+    int check_indices;
 };
 
 constexpr int kThreads = 128;
@@ -156,6 +165,12 @@ __global__ void __launch_bounds__(kThreads) pagedCachingScatterKernel(const Kern
     const int64_t slot = a.slot_mapping[token];
     if (slot < 0) {
         return; // padding token
+    }
+    if (a.check_indices && slot >= a.num_slots) {
+        if (item == 0 && head == 0) {
+            atomicOr(a.kernel_flags, 4u);
+        }
+        return;
     }
     long long block, off;
     if (slot <= 0x7fffffffLL) {
@@ -202,6 +217,9 @@ static infiniStatus_t launch(const Descriptor &desc,
     a.num_pairs = static_cast<long long>(I.num_tokens) * static_cast<long long>(I.num_kv_heads);
     a.num_kv_heads = static_cast<int>(I.num_kv_heads);
     a.block_size = static_cast<int>(I.block_size);
+    a.kernel_flags = desc.base.props->kernel_flags;
+    a.num_slots = static_cast<long long>(desc.num_blocks) * static_cast<long long>(I.block_size);
+    a.check_indices = (desc.check_indices && a.kernel_flags != nullptr) ? 1 : 0;
     a.k_row_bytes = static_cast<int>(I.head_size * I.elem_size);
     a.v_row_bytes = static_cast<int>(I.v_head_size * I.elem_size);
     a.k_src_token = I.k_src_token_stride * es;
@@ -274,7 +292,10 @@ __INFINI_C infiniStatus_t infiniopCreatePagedCachingDescriptor(
     auto *h = reinterpret_cast<b200::Handle *>(handle);
     const char *pdl_env = std::getenv("INFINIOP_PAGED_DECODE_PDL");
     const bool use_pdl = !(pdl_env != nullptr && pdl_env[0] == '0');
-    auto *d = new Descriptor{{handle->device, handle->device_id, b200::OpKind::PagedCaching, h->props}, info, use_pdl};
+    const char *check_env = std::getenv("INFINIOP_PAGED_CHECK_INDICES");
+    const bool check = check_env != nullptr && check_env[0] == '1';
+    auto *d = new Descriptor{{handle->device, handle->device_id, b200::OpKind::PagedCaching, h->props}, info, use_pdl, check,
+                             k_cache_desc->dim(0)};
     *desc_ptr = reinterpret_cast<infiniopPagedCachingDescriptor_t>(d);
     return INFINI_STATUS_SUCCESS;
 }

@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_float, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p
+from ctypes import POINTER, Structure, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_uint64, c_void_p
 from pathlib import Path
 
 import torch
@@ -94,6 +94,7 @@ INFINIOP_SYMBOLS = [
     "infiniopCreateRoPEDescriptor", "infiniopGetRoPEWorkspaceSize", "infiniopRoPE", "infiniopDestroyRoPEDescriptor",
     "infiniopCreateKVCachingDescriptor", "infiniopGetKVCachingWorkspaceSize", "infiniopKVCaching",
     "infiniopDestroyKVCachingDescriptor",
+    "infiniopGetKernelStatus",
 ]
 INFINIRT_SYMBOLS = [
     "infinirtInit", "infinirtGetAllDeviceCount", "infinirtGetDeviceCount", "infinirtSetDevice",
@@ -186,6 +187,10 @@ def _bind(lib: InfiniLib) -> None:
         ]
     op.infiniopDestroyPagedAttentionDescriptor.restype = c_int32
     op.infiniopDestroyPagedAttentionDescriptor.argtypes = [infiniopOperatorDescriptor_t]
+    # No reference counterpart: the device's word of kernel status flags, read and cleared.
+    if hasattr(op, "infiniopGetKernelStatus"):
+        op.infiniopGetKernelStatus.restype = c_int32
+        op.infiniopGetKernelStatus.argtypes = [infiniopHandle_t, c_void_p, POINTER(c_uint32)]
 
     # reference test/infiniop/libinfiniop/op_register.py:2272-2320
     if hasattr(op, "infiniopCreatePagedAttentionPrefillDescriptor"):

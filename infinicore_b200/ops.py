@@ -37,6 +37,24 @@ def _state(device_index: int):
     return st
 
 
+WAIT_EXPIRED, BLOCK_OUT_OF_RANGE, SLOT_OUT_OF_RANGE = 1, 2, 4
+
+
+def kernel_status(device=None, stream=None) -> int:
+    """Waits for `stream` (default: torch's current stream on `device`) and returns the device's word of
+    kernel status flags, clearing it: 0 when every kernel of this library did all of its work, else a
+    combination of WAIT_EXPIRED (a worker gave up waiting for one of its own copies: output rows are
+    missing), BLOCK_OUT_OF_RANGE and SLOT_OUT_OF_RANGE (index checking, switched on with
+    INFINIOP_PAGED_CHECK_INDICES=1 when a descriptor is created, met an index outside the pool).
+    No counterpart in the reference, whose kernels report nothing."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    st = _state(dev)
+    sptr = torch.cuda.current_stream(dev).cuda_stream if stream is None else int(stream)
+    flags = ctypes.c_uint32(0)
+    check_error(LIBINFINIOP.infiniopGetKernelStatus(st["handle"], ctypes.c_void_p(sptr), ctypes.byref(flags)))
+    return int(flags.value)
+
+
 def _meta(t, index_dtype=None):
     if t is None:
         return None

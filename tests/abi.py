@@ -42,7 +42,35 @@ PATH_ENV = {
     "stream-pool": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_DECODE_CHUNKS": "4"},
     "stream-pool-combine": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_DECODE_CHUNKS": "3",
                             "INFINIOP_PAGED_DECODE_MIN_CHUNK": "2", "INFINIOP_PAGED_DECODE_MERGE_IN_KERNEL": "0"},
+    # block-table entries checked against the pool before use
+    "stream-checked": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_CHECK_INDICES": "1"},
+    "generic-checked": {"INFINIOP_PAGED_DECODE_PATH": "generic", "INFINIOP_PAGED_CHECK_INDICES": "1"},
+    # the test of the bounded wait: worker 0 never issues its first copy and gives up after 20 ms
+    "stream-withheld-copy": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_DECODE_TEST_WITHHOLD_COPY": "1",
+                             "INFINIOP_PAGED_DECODE_WAIT_LIMIT_MS": "20"},
 }
+
+
+def kernel_status(stream=None):
+    """infiniopGetKernelStatus on device 0: waits for the stream, returns the flag word and clears it."""
+    flags = ctypes.c_uint32(0)
+    check_error(LIBINFINIOP.infiniopGetKernelStatus(handle(), ctypes.c_void_p(stream), ctypes.byref(flags)))
+    return flags.value
+
+
+@contextlib.contextmanager
+def environment(**values):
+    """Environment variables for the duration of a descriptor creation (the library reads its knobs there)."""
+    old = {k: os.environ.get(k) for k in values}
+    os.environ.update({k: str(v) for k, v in values.items()})
+    try:
+        yield
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
 
 
 @contextlib.contextmanager
@@ -95,12 +123,6 @@ class AttentionOp:
             out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
             block_tables.data_ptr(), seq_lens.data_ptr(), alibi.data_ptr() if alibi is not None else None, stream)
 
-    def error_flag(self) -> int:
-        """First int of the workspace: set non-zero by a worker whose bounded wait ran out."""
-        if self.workspace is None or self.workspace.tensor is None:
-            return 0
-        return int(self.workspace.tensor[:4].view(torch.int32).item())
-
     def destroy(self):
         if self.status == 0 and self.desc:
             check_error(LIBINFINIOP.infiniopDestroyPagedAttentionDescriptor(self.desc))
@@ -135,11 +157,6 @@ class DecodeStepOp:
             out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), new_k.data_ptr(), new_v.data_ptr(),
             block_tables.data_ptr(), seq_lens.data_ptr(), alibi.data_ptr() if alibi is not None else None, stream)
 
-    def error_flag(self) -> int:
-        if self.workspace is None or self.workspace.tensor is None:
-            return 0
-        return int(self.workspace.tensor[:4].view(torch.int32).item())
-
     def destroy(self):
         if self.status == 0 and self.desc:
             check_error(LIBINFINIOP.infiniopDestroyPagedDecodeStepDescriptor(self.desc))
@@ -156,7 +173,6 @@ def paged_decode_step(q, k_cache, v_cache, new_k, new_v, block_tables, seq_lens,
     try:
         check_error(op.run(out, q, k_cache, v_cache, new_k, new_v, block_tables, seq_lens, alibi))
         torch.cuda.synchronize()
-        assert op.error_flag() == 0 or op.workspace_size == 0, "a worker's bounded wait ran out"
     finally:
         op.destroy()
     return out
@@ -245,13 +261,10 @@ def paged_decode_step_rope(q, k_cache, v_cache, new_k, new_v, block_tables, seq_
             new_k.data_ptr(), new_v.data_ptr(), block_tables.data_ptr(), seq_lens.data_ptr(),
             alibi.data_ptr() if alibi is not None else None, pos_ids.data_ptr(), sin_table.data_ptr(), cos_table.data_ptr(), None))
         torch.cuda.synchronize()
-        # the workspace ends with the rotated q and K rows; what precedes them (if anything) is the
-        # streaming kernel's, whose first int is its error flag
+        # the workspace ends with the rotated q and K rows; what precedes them (if anything) is the streaming kernel's
         r256 = lambda n: (n + 255) // 256 * 256
         rotated = r256(q.shape[0] * q.shape[1] * q.shape[2] * q.element_size()) + r256(new_k.numel() * new_k.element_size())
         assert size.value >= rotated
-        if size.value > rotated:
-            assert int(workspace.tensor[:4].view(torch.int32).item()) == 0, "a worker's bounded wait ran out"
     finally:
         check_error(LIBINFINIOP.infiniopDestroyPagedDecodeStepDescriptor(desc))
     return out
@@ -267,7 +280,6 @@ def paged_attention(q, k_cache, v_cache, block_tables, seq_lens, scale, alibi=No
     try:
         check_error(op.run(out, q, k_cache, v_cache, block_tables, seq_lens, alibi))
         torch.cuda.synchronize()
-        assert op.error_flag() == 0 or op.workspace_size == 0, "a worker's bounded wait ran out"
     finally:
         op.destroy()
     return out

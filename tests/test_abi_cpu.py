@@ -109,6 +109,8 @@ def test_null_pointers_are_reported():
     assert LIBINFINIOP.infiniopCreatePagedDecodeStepRoPEDescriptor(None, ctypes.byref(d), *([None] * 12), 1, 1.0) == 4
     assert LIBINFINIOP.infiniopPagedDecodeStepRoPE(None, None, 0, *([None] * 13)) == 4
     assert LIBINFINIOP.infiniopGetPagedDecodeStepWorkspaceSize(None, None) == 4
+    # the kernel status word: no handle, or nowhere to put the flags
+    assert LIBINFINIOP.infiniopGetKernelStatus(None, None, None) == 4
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU behaviour")

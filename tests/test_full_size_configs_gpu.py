@@ -86,9 +86,9 @@ def run(abi, d):
         assert op.run(out, d.q, d.k_cache, d.v_cache, d.block_tables, d.seq_lens) == 0
         torch.cuda.synchronize()
         head = op.workspace.tensor[:32].cpu()
-        plan = {"error": int(head[:4].view(torch.int32)), "num_ranges": int(head[4:8].view(torch.int32)),
+        plan = {"num_ranges": int(head[4:8].view(torch.int32)),
                 "total_tiles": int(head[8:16].view(torch.int64)), "range_len": int(head[16:24].view(torch.int64))}
-        assert plan["error"] == 0, "a worker's bounded wait ran out"
+        assert abi.kernel_status() == 0, "a worker's bounded wait ran out"
     finally:
         op.destroy()
     return out, plan
