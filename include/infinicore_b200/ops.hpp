@@ -212,25 +212,30 @@ struct DeviceState {
                 infinirtFree(kv.second.ptr);
             }
         }
+        for (void *old : retired) {
+            infinirtFree(old);
+        }
         if (handle != nullptr) {
             infiniopDestroyHandle(handle);
         }
     }
 
-    // Grow-only scratch per stream.  A larger request first drains the stream (kernels in flight may still use
-    // the old buffer), so steady-state calls never allocate and can be captured into a CUDA graph.
+    // Grow-only scratch per stream.  A buffer that a larger request supersedes is not freed but kept until this
+    // state dies: kernels in flight, and CUDA graphs captured earlier, may still hold its address.  Steady-state
+    // calls never allocate, which stream capture needs; run the largest problem of a stream once BEFORE
+    // capturing on it, because growing means infinirtMalloc, and that is not allowed inside a capture.
     void *workspace(size_t bytes, infinirtStream_t stream) {
         if (bytes == 0) {
             return nullptr;
         }
         Workspace &w = workspaces[stream];
         if (w.bytes < bytes) {
+            void *fresh = nullptr;
+            check(infinirtMalloc(&fresh, bytes), "infinirtMalloc");
             if (w.ptr != nullptr) {
-                check(infinirtStreamSynchronize(stream), "infinirtStreamSynchronize");
-                check(infinirtFree(w.ptr), "infinirtFree");
-                w = Workspace{};
+                retired.push_back(w.ptr);
             }
-            check(infinirtMalloc(&w.ptr, bytes), "infinirtMalloc");
+            w.ptr = fresh;
             w.bytes = bytes;
         }
         return w.ptr;
@@ -240,6 +245,7 @@ struct DeviceState {
     infiniopHandle_t handle = nullptr;
     LruCache cache;
     std::map<infinirtStream_t, Workspace> workspaces;
+    std::vector<void *> retired; // superseded workspaces, freed with the state
 };
 
 // The calling thread's state for its current device (libinfinirt's current device is thread-local and
@@ -285,6 +291,14 @@ inline CacheStats cache_stats() { return detail::state().cache.stats; }
 inline size_t cached_descriptors() { return detail::state().cache.size(); }
 // Destroys the calling thread's cached descriptors for its current device.
 inline void clear_cache() { detail::state().cache.clear(); }
+
+// Waits for `stream`, returns the current device's word of kernel status flags and clears it
+// (include/infiniop/ops/kernel_status.h): 0 when every kernel of the library did all of its work.
+inline unsigned int kernel_status(infinirtStream_t stream = nullptr) {
+    unsigned int flags = 0;
+    check(infiniopGetKernelStatus(detail::state().handle, stream, &flags), "infiniopGetKernelStatus");
+    return flags;
+}
 
 namespace op {
 

@@ -28,8 +28,10 @@ __INFINI_C __export infiniStatus_t infinirtGetMemInfo(infiniDevice_t device, int
 
 /* Resource snapshot (reference include/infinirt.h:13-60).  `valid_fields` says which members the
  * backend filled; a consumer must test the bit before it reads a member.  This library fills the
- * memory-capacity members from the driver; the utilisation and communication members stay clear -
- * they need the management library and a collective-timing store, which this path does not carry. */
+ * memory-capacity members from the CUDA runtime and, where the driver's management library (NVML)
+ * can be loaded at run time, the compute / memory-bandwidth utilisation and the kernel-time ratio
+ * (the same sample, flagged in `estimated_fields`) by read-only queries; the communication members
+ * stay clear - they would need a store of collective timings, which this path does not keep. */
 typedef enum {
     INFINIRT_RESOURCE_FIELD_NONE = 0,
     INFINIRT_RESOURCE_FIELD_MEMORY_CAPACITY = 1ull << 0,

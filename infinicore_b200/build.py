@@ -112,7 +112,7 @@ def _link(objs, out: Path, extra, verbose: bool) -> None:
 
 
 def build(force: bool = False, verbose: bool = False) -> dict:
-    """Compiles what is stale and returns {"infinirt": path, "infiniop": path, "infiniccl": path}."""
+    """Compiles what is stale and returns {"infinirt": path, "infiniop": path, "infiniccl": path, "pybind": path}."""
     LIB.mkdir(exist_ok=True)
     OBJ.mkdir(exist_ok=True)
     if force:
@@ -127,12 +127,43 @@ def build(force: bool = False, verbose: bool = False) -> dict:
     libccl = LIB / "libinfiniccl.so"
     newest_obj = max(o.stat().st_mtime for o in rt_objs + op_objs + ccl_objs)
     if force or not librt.exists() or librt.stat().st_mtime < newest_obj:
-        _link(rt_objs, librt, [], verbose)
+        _link(rt_objs, librt, ["-ldl"], verbose)
     if force or not libop.exists() or libop.stat().st_mtime < newest_obj:
         _link(op_objs, libop, [f"-L{LIB}", "-linfinirt", "-Xlinker", "-rpath=$ORIGIN"], verbose)
     if force or not libccl.exists() or libccl.stat().st_mtime < newest_obj:
         _link(ccl_objs, libccl, [f"-L{LIB}", "-linfinirt", "-lnccl", "-Xlinker", "-rpath=$ORIGIN"], verbose)
-    return {"infinirt": librt, "infiniop": libop, "infiniccl": libccl}
+    return {"infinirt": librt, "infiniop": libop, "infiniccl": libccl, "pybind": build_pybind(force, verbose)}
+
+
+def build_pybind(force: bool = False, verbose: bool = False) -> Path:
+    """Compiles the Python module over the C++ host layer (csrc/pybind/module.cpp) with g++ and pybind11,
+    in-tree, linked to the libraries in lib/ (found again at run time through $ORIGIN/lib)."""
+    import sysconfig
+
+    import pybind11
+
+    src = CSRC / "pybind" / "module.cpp"
+    out = PKG / ("_infinicore_b200" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
+    stamp = OBJ / "pybind_module.sha"
+    want = _digest([src, INCLUDE / "infinicore_b200" / "ops.hpp"] + list(INCLUDE.rglob("*.h")))
+    newest_lib = max((LIB / n).stat().st_mtime for n in ("libinfinirt.so", "libinfiniop.so"))
+    if not force and out.exists() and stamp.exists() and stamp.read_text() == want and out.stat().st_mtime >= newest_lib:
+        return out
+    gxx = shutil.which("g++")
+    if gxx is None:
+        raise RuntimeError("g++ not found")
+    cmd = [gxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wextra",
+           f"-I{pybind11.get_include()}", f"-I{sysconfig.get_paths()['include']}", f"-I{INCLUDE}",
+           str(src), "-o", str(out), f"-L{LIB}", "-linfiniop", "-linfinirt", "-Wl,-rpath,$ORIGIN/lib"]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError("g++ failed on pybind/module.cpp")
+    stamp.write_text(want)
+    return out
 
 
 def main() -> None:

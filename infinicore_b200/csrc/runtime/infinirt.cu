@@ -11,6 +11,9 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
+#include <dlfcn.h>
+#include <mutex>
 
 namespace {
 
@@ -143,7 +146,86 @@ __INFINI_C infiniStatus_t infinirtGetMemInfo(infiniDevice_t device, int device_i
     return fromCuda(err, "cudaMemGetInfo");
 }
 
-// Only the capacity members are filled (and flagged); the rest of the snapshot is zero with its bits clear.
+// ---- utilisation figures from the driver's management library --------------------------------------------
+// The snapshot's utilisation members (reference src/infinirt/cuda/infinirt_cuda.cu:163-262) come from NVML,
+// which is not linked: it is looked up at run time (dlopen), only its read-only queries are used, and a
+// machine without it simply leaves those members' bits clear.  The device is found by its PCI bus id, so the
+// figures belong to the CUDA device asked about whatever CUDA_VISIBLE_DEVICES does to the numbering.
+// INFINIRT_MANAGEMENT_LIBRARY names another library to load instead (the tests put a stand-in there).
+namespace {
+
+struct Utilization {
+    unsigned int gpu;    // percent of the last sample period in which a kernel was running
+    unsigned int memory; // percent in which device memory was being read or written
+};
+
+class ManagementLibrary {
+public:
+    static ManagementLibrary &get() {
+        static ManagementLibrary lib;
+        return lib;
+    }
+
+    bool utilization(const char *pci_bus_id, Utilization *out) {
+        std::lock_guard<std::mutex> lock(mutex_);
+        if (!ready()) {
+            return false;
+        }
+        void *device = nullptr;
+        if (by_bus_id_(pci_bus_id, &device) != 0 || device == nullptr) {
+            return false;
+        }
+        return rates_(device, out) == 0;
+    }
+
+private:
+    using InitFn = int (*)();
+    using ByBusIdFn = int (*)(const char *, void **);
+    using RatesFn = int (*)(void *, Utilization *);
+
+    ManagementLibrary() {
+        const char *override_path = std::getenv("INFINIRT_MANAGEMENT_LIBRARY");
+        const char *names[] = {override_path, "libnvidia-ml.so.1", "libnvidia-ml.so"};
+        for (const char *name : names) {
+            if (name == nullptr || *name == '\0') {
+                continue;
+            }
+            handle_ = dlopen(name, RTLD_LAZY | RTLD_LOCAL);
+            if (handle_ != nullptr || name == override_path) {
+                break; // a named stand-in that does not load is not replaced by the real thing
+            }
+        }
+        if (handle_ == nullptr) {
+            return;
+        }
+        init_ = reinterpret_cast<InitFn>(dlsym(handle_, "nvmlInit_v2"));
+        by_bus_id_ = reinterpret_cast<ByBusIdFn>(dlsym(handle_, "nvmlDeviceGetHandleByPciBusId_v2"));
+        rates_ = reinterpret_cast<RatesFn>(dlsym(handle_, "nvmlDeviceGetUtilizationRates"));
+    }
+
+    bool ready() {
+        if (init_ == nullptr || by_bus_id_ == nullptr || rates_ == nullptr) {
+            return false;
+        }
+        if (!initialised_) {
+            initialised_ = (init_() == 0); // stays initialised for the life of the process
+        }
+        return initialised_;
+    }
+
+    std::mutex mutex_;
+    void *handle_ = nullptr;
+    InitFn init_ = nullptr;
+    ByBusIdFn by_bus_id_ = nullptr;
+    RatesFn rates_ = nullptr;
+    bool initialised_ = false;
+};
+
+} // namespace
+
+// Memory capacity from the CUDA runtime; compute and memory-bandwidth utilisation from the management library
+// when it is there (kernel_time_ratio is the same sample, marked as an estimate, as in the reference).  The
+// communication members stay clear: they would need a store of collective timings, which this path does not keep.
 __INFINI_C infiniStatus_t infinirtGetDeviceResourceSnapshot(infiniDevice_t device, int device_id,
                                                            infinirtDeviceResourceSnapshot_t *snapshot) {
     RT_REQUIRE_PTR(snapshot);
@@ -159,6 +241,21 @@ __INFINI_C infiniStatus_t infinirtGetDeviceResourceSnapshot(infiniDevice_t devic
     snapshot->total_bytes = total_bytes;
     snapshot->used_bytes = total_bytes - free_bytes;
     snapshot->valid_fields = INFINIRT_RESOURCE_FIELD_MEMORY_CAPACITY;
+
+    char bus_id[32] = {};
+    if (cudaDeviceGetPCIBusId(bus_id, static_cast<int>(sizeof(bus_id)), device_id) == cudaSuccess) {
+        Utilization u{};
+        if (ManagementLibrary::get().utilization(bus_id, &u)) {
+            snapshot->compute_utilization = static_cast<float>(u.gpu) / 100.0f;
+            snapshot->memory_bandwidth_utilization = static_cast<float>(u.memory) / 100.0f;
+            snapshot->kernel_time_ratio = snapshot->compute_utilization;
+            snapshot->valid_fields |= INFINIRT_RESOURCE_FIELD_COMPUTE_UTILIZATION | INFINIRT_RESOURCE_FIELD_MEMORY_BANDWIDTH_UTILIZATION
+                                      | INFINIRT_RESOURCE_FIELD_KERNEL_TIME_RATIO;
+            snapshot->estimated_fields |= INFINIRT_RESOURCE_FIELD_KERNEL_TIME_RATIO;
+        }
+    } else {
+        (void)cudaGetLastError();
+    }
     return INFINI_STATUS_SUCCESS;
 }
 

@@ -147,3 +147,21 @@ def test_missing_library_fails_loudly(tmp_path, monkeypatch):
     monkeypatch.setattr(L, "_PKG", tmp_path)
     with pytest.raises(FileNotFoundError, match="no non-CUDA fallback"):
         L.library_paths()
+
+
+def test_pybind_module_imports_and_describes_views_without_a_device():
+    """The Python module over the C++ host layer: importable on a machine without a GPU (it only links the two
+    libraries), tensor views carry shape / strides / dtype, and the reference's operator names are there."""
+    from infinicore_b200 import _infinicore_b200 as m
+
+    for name in ("paged_attention", "paged_attention_", "paged_caching_", "Tensor", "DataType", "kernel_status"):
+        assert hasattr(m, name)
+    t = m.Tensor.from_blob(4096, [2, 3, 4], None, m.DataType.BF16)
+    assert t.shape == [2, 3, 4] and t.strides == [12, 4, 1] and t.numel() == 24 and t.data_ptr() == 4096
+    s = m.Tensor.from_blob(4096, [3, 2], [1, 3], m.DataType.I64, 1)
+    assert s.strides == [1, 3] and s.device_index == 1
+    with pytest.raises(ValueError):
+        m.Tensor.from_blob(0, [2, 2], [1], m.DataType.F16)
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            m.kernel_status()

@@ -157,24 +157,3 @@ def test_argument_checks_return_status_codes(comms):
         ccl.check_error(ccl.lib().infinicclAllReduce(x.data_ptr(), x.data_ptr(), 8, 1, ccl.SUM, c.handle, None))  # dtype 1 = BYTE
     assert e.value.status == 10  # INFINI_STATUS_BAD_TENSOR_DTYPE
     assert ccl.lib().infinicclCommDestroy(None) == 0  # NULL is accepted
-
-
-def test_resource_snapshot_reports_memory(comms):
-    """infinirtGetDeviceResourceSnapshot: capacity members filled and flagged, the rest clear."""
-    import ctypes
-
-    from infinicore_b200.libinfiniop import LIBINFINIOP
-
-    class Snapshot(ctypes.Structure):
-        _fields_ = [("device_type", ctypes.c_int), ("device_id", ctypes.c_int), ("valid_fields", ctypes.c_uint64),
-                    ("estimated_fields", ctypes.c_uint64), ("free_bytes", ctypes.c_size_t), ("total_bytes", ctypes.c_size_t),
-                    ("used_bytes", ctypes.c_size_t), ("reserved_bytes", ctypes.c_size_t), ("compute_utilization", ctypes.c_float),
-                    ("memory_bandwidth_utilization", ctypes.c_float), ("kernel_time_ratio", ctypes.c_float),
-                    ("communication_time_ratio", ctypes.c_float), ("communication_bytes", ctypes.c_uint64)]
-
-    snap = Snapshot()
-    fn = LIBINFINIOP.librt.infinirtGetDeviceResourceSnapshot
-    fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(Snapshot)]
-    assert fn(1, 0, ctypes.byref(snap)) == 0
-    assert snap.valid_fields == 1 and snap.total_bytes > (100 << 30) and snap.used_bytes == snap.total_bytes - snap.free_bytes
-    assert fn(1, 0, None) == 4  # INFINI_STATUS_NULL_POINTER
