@@ -635,8 +635,10 @@ def gpu_arm(args):
                           max_blocks_per_seq=case.block_tables.shape[1], scale=case.scale)
     for k in ("q", "new_k", "new_v", "slot_mapping", "block_tables", "seq_lens"):
         estep.host[k].copy_(getattr(case, k).cpu())
-    estep.capture()
+    estep.capture()  # records both ways of delivering the output (copy node / the kernels' own stores) and keeps the faster
     h2d, d2h = estep.h2d_bytes, estep.d2h_bytes
+    e2e_route = {"output_route": "kernels store into pinned host memory" if estep.direct_output else "device-to-host copy node",
+                 "chosen_at_capture_from_us": {k: round(v * 1e6, 2) for k, v in getattr(estep, "auto_times", {}).items()}}
 
     def e2e_step():
         estep.run(sync=True)  # the host reads the step's result before it issues the next step
@@ -799,6 +801,35 @@ def gpu_arm(args):
                 hs = None
             side["head_sharded"] = hs
 
+    # ---- the path's upstream neighbour: infiniopPagedAttentionPrefill (N = 1 only; never costs the run its line) ----
+    if not args.no_side and args.workload == "c2" and world == 1:
+        try:
+            pcase = workloads.prefill_llama8b(device=device)
+            pout = torch.empty((pcase.q.shape[0], pcase.num_heads, pcase.head_size), dtype=pcase.dtype, device=device)
+
+            def prefill_call():
+                ib.paged_attention_prefill(pcase.q, pcase.k_cache, pcase.v_cache, pcase.block_tables, pcase.seq_lens,
+                                           pcase.cum_seq_lens_q, None, pcase.scale, out=pout)
+
+            for _ in range(5):
+                prefill_call()
+            torch.cuda.synchronize()
+            pms = timed_blocks(prefill_call, 50, 5)[0]
+            try:
+                tpeak, tkind = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["bf16_tflops"]), "measured"
+            except Exception:  # noqa: BLE001
+                tpeak, tkind = 1590.0, "fallback"
+            ptf = pcase.flops / (pms * 1e-3) / 1e12
+            side["prefill"] = {"ms": pms, "tflops": ptf, "frac": ptf / tpeak, "peak": tpeak, "peak_kind": f"of {tkind} (burst bf16 GEMM)",
+                               "bound": "tensor", "kernel": "pagedPrefillUmmaKernel (tcgen05 + TMEM)",
+                               "workload": "infiniopPagedAttentionPrefill, Llama-3-8B head shape: bf16, 8 prompts x 2048 new tokens, 32/8 heads, "
+                                           "head 128, block 16; flops = 4 x heads x head x causal pairs; median of 5 blocks of 50 calls"}
+            del pcase, pout
+            torch.cuda.empty_cache()
+        except Exception as exc:  # noqa: BLE001
+            print(f"[bench] prefill side record skipped: {exc}", file=sys.stderr)
+            side["prefill"] = None
+
     # ---- CPU baseline and the reference's own GPU kernels (rank 0, N = 1 only) -------------------------
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -831,7 +862,7 @@ def gpu_arm(args):
                 "attn_ms_max": attn_max, "caching_ms_mean": cache_ms,
             },
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                    "ms_per_step_min": e2e_min, "ms_per_step_max": e2e_max,
+                    "ms_per_step_min": e2e_min, "ms_per_step_max": e2e_max, **e2e_route,
                     "note": "q, new K/V rows, slots, block tables and lengths copied in from pinned host memory and the output copied "
                             "back every step, the host waiting for the result before it issues the next step; the KV cache itself "
                             "is device state"},

@@ -677,15 +677,14 @@ __global__ void __launch_bounds__(HD == 64 ? 128 : kMaxWarps * 32, HD == 64 ? 3 
 
     // Consumer side: the piece whose tiles are being consumed.  Generator side: the piece whose tiles
     // are being fetched - the same one (g_same) or, once that is fully issued, the next one (q_*).
-    long long c_left = range_len - geom.budget; // tiles of the piece still to consume
-    if (total_tiles - x0 < c_left) {
-        c_left = total_tiles - x0;
-    }
-    long long c_id = static_cast<long long>(worker) * pieces_per_range;
-    long long g_left = c_left; // tiles of the generator's piece still to issue
+    // (a range holds fewer than 2^31 tiles: the plan refuses shapes where it could hold more)
+    const long long head_tiles_left = (total_tiles - x0 < range_len - geom.budget) ? (total_tiles - x0) : (range_len - geom.budget);
+    int c_left = static_cast<int>(head_tiles_left); // tiles of the piece still to consume
+    int c_id = worker * pieces_per_range;
+    int g_left = c_left; // tiles of the generator's piece still to issue
     bool g_same = true;
     Cursor q_start = gen;
-    long long q_id = 0;
+    int q_id = 0;
     int q_count = 0;
     bool pool_empty = (pool_total == 0);
     bool stop_claiming = false; // this worker has noted enough units to merge: it takes no further chunk
@@ -765,7 +764,7 @@ __global__ void __launch_bounds__(HD == 64 ? 128 : kMaxWarps * 32, HD == 64 ? 3 
                     continue; // the last range is shorter than the others
                 }
                 q_count = avail < len ? static_cast<int>(avail) : len;
-                q_id = static_cast<long long>(r) * pieces_per_range + 1 + j;
+                q_id = r * pieces_per_range + 1 + j;
                 const int4 qs = locate(prefix, p.num_seqs, a.units_per_seq, qx0);
                 gen.s = qs.x;
                 gen.j = qs.y;
@@ -2108,6 +2107,11 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
     }
     plan.grid = props.sm_count * ctas_per_sm;
     plan.num_workers = plan.grid * plan.warps_per_cta;
+    // a worker counts the tiles of its range in 32 bits
+    const unsigned long long units_per_seq = static_cast<unsigned long long>(I.num_kv_heads) * plan.head_tiles_per_group;
+    if (static_cast<unsigned long long>(I.num_seqs) * tiles_per_seq_max * units_per_seq / plan.num_workers >= 0x7fffffffull) {
+        return plan;
+    }
     plan.workspace_bytes = workspaceLayout(I, plan).total;
     plan.eligible = true;
     return plan;

@@ -517,7 +517,7 @@ def test_python_operators_match_the_abi_path(abi):
     assert torch.equal(got, again)
 
 
-@pytest.mark.parametrize("direct_output", [False, True])
+@pytest.mark.parametrize("direct_output", [False, True, "auto"])
 def test_decode_step_graph_replay_matches_direct_calls(abi, direct_output):
     """infinicore_b200.DecodeStep: host inputs -> H2D -> caching -> attention -> D2H captured once and
     replayed; two replays with different inputs, each checked against the oracle.  With direct_output the
