@@ -4,7 +4,9 @@ reference checkout.  Nothing is copied into this repository and the reference's 
 (xmake) is not used: this is a plain nvcc recipe over the ~18 translation units the path needs.
 
 The result is a GPU-side checker and a "reference kernels on the same B200" comparison point:
-only tests/ and bench.py's comparison leg load it, through the same C ABI as the product.
+only tests/ and bench.py's comparison leg load it, through the same C ABI as the product.  The
+reference's own ctypes test scripts for these operators are staged beside the libraries
+(oracle/_ref/test_infiniop/, verbatim, not committed) so that they can be run against this library.
 
     python -m oracle.build_ref [/path/to/InfiniCore]
 """
@@ -105,7 +107,29 @@ def build(ref: Path | None = None, force: bool = False) -> tuple[Path, Path]:
 
     link(rt_objs, rt, [])
     link(op_objs, op, [f"-L{LIBDIR}", "-linfinirt", "-lcublas", "-Xlinker", "-rpath=$ORIGIN"])
+    stage_test_harness(ref)
     return rt, op
+
+
+# The reference's own ctypes test harness for this path (test/infiniop/libinfiniop + the operators' test
+# scripts), staged verbatim next to the libraries built from its sources - like them an artefact of the
+# reference checkout that lives only under oracle/_ref/ and is never committed.  tests/ref_harness.py runs
+# these scripts against THIS library (the drop-in claim: the reference's tests, unmodified, pass on it).
+HARNESS = OUT / "test_infiniop"
+HARNESS_SCRIPTS = ["paged_attention.py", "paged_caching.py", "paged_attention_prefill.py", "rope.py", "kv_caching.py"]
+
+
+def stage_test_harness(ref: Path) -> Path | None:
+    src = ref / "test" / "infiniop"
+    if not (src / "libinfiniop").is_dir():
+        return None
+    (HARNESS / "libinfiniop").mkdir(parents=True, exist_ok=True)
+    for f in (src / "libinfiniop").glob("*.py"):
+        shutil.copyfile(f, HARNESS / "libinfiniop" / f.name)
+    for name in HARNESS_SCRIPTS:
+        if (src / name).is_file():
+            shutil.copyfile(src / name, HARNESS / name)
+    return HARNESS
 
 
 if __name__ == "__main__":

@@ -26,11 +26,15 @@ def test_attention_reference_mode_matches_reference_output(name):
     got = oracle.paged_attention(g["q"], g["k_cache"], g["v_cache"], g["block_tables"], g["seq_lens"],
                                  float(g["scale"]), dt, alibi, mode="reference")
     want = bits_to_float(g["out"], dt)
-    # Same roundings, different summation order: a rounded probability or output can flip by one
-    # ulp; allow 3 ulps of the output plus the spread that one-ulp probability flips can cause.
+    # Same roundings, different summation order: a rounded score or probability can flip by one ulp of the
+    # tensor type.  For an output element of ordinary size that is a few of ITS ulps (first term); an
+    # element that is a near-cancellation of large terms moves by a flip's share of those terms instead,
+    # which is measured against the largest output, not against the element (second term).  Observed on
+    # the committed vectors: 99.87 % of all elements within one ulp, the worst 4.9 of its own ulps and
+    # 2.7e-4 of the largest output; four of the eight vectors match bit for bit.
     err = np.abs(got - want)
-    assert np.all(err <= 4 * _ulp(dt, want) + 1e-3 * np.abs(want).max()), f"max err {err.max():.3e}"
-    assert np.mean(err <= _ulp(dt, want)) > 0.9
+    assert np.all(err <= 4 * _ulp(dt, want) + 5e-4 * np.abs(want).max()), f"max err {err.max():.3e}"
+    assert np.mean(err <= _ulp(dt, want)) > 0.998
 
 
 @pytest.mark.parametrize("name", golden_names("attn_"))
