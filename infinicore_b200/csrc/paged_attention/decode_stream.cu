@@ -322,7 +322,9 @@ __device__ __forceinline__ void chunkSpan(long long range_len, PieceGeometry g, 
 
 // Id of the piece that holds linear position x.
 __device__ __forceinline__ long long pieceOf(long long x, long long range_len, PieceGeometry g, int max_chunks, int min_chunk) {
-    const long long r = x / range_len;
+    // (positions and range lengths below 2^32 take the 32-bit division, several times cheaper than the 64-bit one)
+    const long long r = ((x | range_len) >> 32) == 0 ? static_cast<long long>(static_cast<unsigned>(x) / static_cast<unsigned>(range_len))
+                                                       : x / range_len;
     const long long id = r * (g.chunks + 1);
     if (g.chunks == 0) {
         return id;
@@ -471,7 +473,7 @@ __device__ __noinline__ void mergeUnit(const StreamArgs &a, const long long *pre
     const int heads_valid = min(HPT, p.group_size - head_tile * HPT);
     const float *base = a.partials + (unit + p_first) * kRec;
 
-    __threadfence(); // the other workers' records were published before they counted their tiles
+    // (the caller has fenced: the other workers' records were published before they counted their tiles)
     float mx[kVecs], ls[kVecs];
     float4 acc[kVecs];
 #pragma unroll
@@ -1142,9 +1144,33 @@ __global__ void __launch_bounds__(HD == 64 ? 128 : kMaxWarps * 32, HD == 64 ? 3 
     }
 
     if (!failed && a.merge_in_kernel) {
-        countSegments(); // counts the last segment
-        countSegments(); // looks at that count
+        // The stream is over: count the last segment first (its fence and the atomic's round trip then
+        // overlap the look at the count that is still in flight), note what this worker arrived last at,
+        // and merge.
+        int before_last = 0;
+        if (pend_valid) {
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) {
+                before_last = atomicAdd(a.counters + 1 + pend_unit, pend_tiles);
+            }
+        }
+        const bool had_pending = pend_valid;
+        pend_valid = false;
+        countSegments(); // looks at the count in flight
+        if (had_pending) {
+            before_last = __shfl_sync(0xffffffffu, before_last, 0);
+            if (before_last + pend_tiles == pend_nt) {
+                if (lane == 0) {
+                    merge_list[merge_count] = pend_unit;
+                }
+                ++merge_count;
+            }
+        }
         __syncwarp();
+        if (merge_count > 0) {
+            __threadfence(); // the other workers' records were published before they counted their tiles
+        }
         for (int i = 0; i < merge_count; ++i) {
             mergeUnit<T, HD, HPT>(a, prefix, range_len, geom, merge_list[i], lane);
         }

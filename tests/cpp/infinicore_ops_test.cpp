@@ -211,6 +211,12 @@ int main(int argc, char **argv) {
             ib::check(infinirtGraphInstantiate(&exec, graph, nullptr, nullptr, 0), "infinirtGraphInstantiate");
             const ib::CacheStats after = ib::cache_stats();
             report << "capture_misses " << after.misses - before.misses << "\n";
+            // a later, larger problem on this stream makes its workspace grow: the buffer the graph captured must
+            // stay valid (it is retired, not freed), so the replays below still see their own scratch
+            void *captured_ws = ib::detail::state().workspace(1, stream);
+            void *grown_ws = ib::detail::state().workspace(static_cast<size_t>(96) << 20, stream);
+            report << "workspace_moved " << (grown_ws != captured_ws ? 1 : 0) << "\n";
+            ib::check(infinirtMemsetAsync(grown_ws, 0xff, static_cast<size_t>(96) << 20, stream), "infinirtMemsetAsync");
             for (int i = 0; i < 2; ++i) {
                 ib::check(infinirtGraphLuanch(exec, stream), "infinirtGraphLuanch");
             }
@@ -292,6 +298,7 @@ int main(int argc, char **argv) {
             report << "error_status " << static_cast<int>(e.status) << "\n";
         }
         ib::clear_cache();
+        report << "kernel_status " << ib::kernel_status() << "\n";
         report << "cached_after_clear " << ib::cached_descriptors() << "\n";
         report << "ok 1\n";
     } catch (const std::exception &e) {

@@ -124,6 +124,8 @@ def test_every_wrapper_against_the_oracle(tmp_path):
     # cache behaviour
     assert report["two_call_misses"] == "2" and report["two_call_hits"] == "2"
     assert report["capture_misses"] == "0"
+    assert report["workspace_moved"] == "1"  # the stream's workspace grew after the capture; the replays above still ran on theirs
+    assert report["kernel_status"] == "0"
     assert int(report["evictions"]) >= 10 and int(report["cached"]) <= int(report["capacity"])
     assert report["error_status"] == "10"
     assert report["cached_after_clear"] == "0"
