@@ -30,8 +30,8 @@ __INFINI_C __export infiniStatus_t infinirtGetMemInfo(infiniDevice_t device, int
  * backend filled; a consumer must test the bit before it reads a member.  This library fills the
  * memory-capacity members from the CUDA runtime and, where the driver's management library (NVML)
  * can be loaded at run time, the compute / memory-bandwidth utilisation and the kernel-time ratio
- * (the same sample, flagged in `estimated_fields`) by read-only queries; the communication members
- * stay clear - they would need a store of collective timings, which this path does not keep. */
+ * (the same sample, flagged in `estimated_fields`) by read-only queries; and the communication members
+ * from the samples libinfiniccl files around its collectives (payload bytes and share of the last second). */
 typedef enum {
     INFINIRT_RESOURCE_FIELD_NONE = 0,
     INFINIRT_RESOURCE_FIELD_MEMORY_CAPACITY = 1ull << 0,
@@ -60,6 +60,19 @@ typedef struct {
 __INFINI_C __export infiniStatus_t infinirtGetDeviceResourceSnapshot(infiniDevice_t device, int device_id,
                                                                     infinirtDeviceResourceSnapshot_t *snapshot);
 __INFINI_C __export infiniStatus_t infinirtDeviceSynchronize();
+
+/* Communication samples behind the snapshot's `communication_*` members.  No counterpart in the reference's
+ * public header: the reference keeps the same service internal to its libraries
+ * (src/infinirt/cuda/infinirt_cuda.cu:31-160,356-380 - infiniccl brackets every collective with a pair of events
+ * and hands it to infinirt; the snapshot reports the bytes and the share of the last second those collectives
+ * took).  Here it is this library's libinfiniccl that calls the pair below around each collective (or around a
+ * whole group):
+ *   Begin  records a start event on `stream` of the calling thread's current device and returns a token
+ *          (NULL, and nothing recorded, while the stream is being captured into a graph);
+ *   End    records the end event on the same stream and files the sample with `bytes` of payload.
+ * Neither synchronises; finished samples are collected whenever a snapshot is taken. */
+__INFINI_C __export infiniStatus_t infinirtCommunicationBegin(infinirtStream_t stream, void **sample);
+__INFINI_C __export infiniStatus_t infinirtCommunicationEnd(void *sample, infinirtStream_t stream, uint64_t bytes);
 
 /* Stream */
 __INFINI_C __export infiniStatus_t infinirtStreamCreate(infinirtStream_t *stream_ptr);

@@ -6,6 +6,7 @@
 // an element type or reduction outside the supported set is refused with a status code instead of
 // aborting the process.
 #include "infiniccl.h"
+#include "infinirt.h"
 
 #include <cstdio>
 #include <cstring>
@@ -85,6 +86,40 @@ infiniStatus_t fromNccl(ncclResult_t r, const char *what) {
 
 cudaStream_t cudaStreamOf(infinirtStream_t s) { return static_cast<cudaStream_t>(s); }
 
+// Brackets one collective (or one whole group of them) with the event pair that libinfinirt turns into the
+// resource snapshot's communication figures (reference src/infiniccl/cuda/infiniccl_cuda.cu records the same
+// samples).  Inside a caller's infinicclGroupStart / GroupEnd the launches only happen at GroupEnd, so the
+// calls in between just add their payload and the group is bracketed as one sample.
+thread_local int t_group_depth = 0;
+thread_local uint64_t t_group_bytes = 0;
+thread_local infinirtStream_t t_group_stream = nullptr;
+
+class Sampled {
+public:
+    Sampled(infinirtStream_t stream, uint64_t bytes) : stream_(stream), bytes_(bytes) {
+        if (t_group_depth > 0) {
+            t_group_bytes += bytes;
+            t_group_stream = stream;
+        } else {
+            (void)infinirtCommunicationBegin(stream, &sample_);
+        }
+    }
+    ~Sampled() {
+        if (sample_ != nullptr) {
+            (void)infinirtCommunicationEnd(sample_, stream_, launched_ ? bytes_ : 0);
+        }
+    }
+    void launched() { launched_ = true; }
+    Sampled(const Sampled &) = delete;
+    Sampled &operator=(const Sampled &) = delete;
+
+private:
+    infinirtStream_t stream_;
+    uint64_t bytes_;
+    void *sample_ = nullptr;
+    bool launched_ = false;
+};
+
 bool nvidiaFamily(infiniDevice_t d) { return d == INFINI_DEVICE_NVIDIA; }
 
 } // namespace
@@ -157,11 +192,23 @@ __INFINI_C infiniStatus_t infinicclCommDestroy(infinicclComm_t comm) {
 __INFINI_C infiniStatus_t infinicclGroupStart(infinicclComm_t comm) {
     CCL_REQUIRE(comm != nullptr, INFINI_STATUS_NULL_POINTER);
     CCL_NCCL(ncclGroupStart());
+    if (t_group_depth++ == 0) {
+        t_group_bytes = 0;
+    }
     return INFINI_STATUS_SUCCESS;
 }
 
 __INFINI_C infiniStatus_t infinicclGroupEnd(infinicclComm_t comm) {
     CCL_REQUIRE(comm != nullptr, INFINI_STATUS_NULL_POINTER);
+    if (t_group_depth > 0 && --t_group_depth == 0 && t_group_bytes > 0) {
+        // the outermost group ends: everything queued since GroupStart is launched by this call
+        void *sample = nullptr;
+        (void)infinirtCommunicationBegin(t_group_stream, &sample);
+        const ncclResult_t r = ncclGroupEnd();
+        (void)infinirtCommunicationEnd(sample, t_group_stream, r == ncclSuccess ? t_group_bytes : 0);
+        t_group_bytes = 0;
+        return fromNccl(r, "ncclGroupEnd");
+    }
     CCL_NCCL(ncclGroupEnd());
     return INFINI_STATUS_SUCCESS;
 }
@@ -174,7 +221,9 @@ __INFINI_C infiniStatus_t infinicclAllReduce(void *sendbuf, void *recvbuf, size_
     ncclRedOp_t rop;
     CCL_REQUIRE(toNccl(datatype, &dt, &esize), INFINI_STATUS_BAD_TENSOR_DTYPE);
     CCL_REQUIRE(toNccl(op, &rop), INFINI_STATUS_BAD_PARAM);
+    Sampled sample(stream, count * esize);
     CCL_NCCL(ncclAllReduce(sendbuf, recvbuf, count, dt, rop, comm->comm, cudaStreamOf(stream)));
+    sample.launched();
     return INFINI_STATUS_SUCCESS;
 }
 
@@ -185,7 +234,9 @@ __INFINI_C infiniStatus_t infinicclBroadcast(const void *sendbuf, void *recvbuf,
     ncclDataType_t dt;
     size_t esize;
     CCL_REQUIRE(toNccl(datatype, &dt, &esize), INFINI_STATUS_BAD_TENSOR_DTYPE);
+    Sampled sample(stream, count * esize);
     CCL_NCCL(ncclBroadcast(sendbuf, recvbuf, count, dt, root, comm->comm, cudaStreamOf(stream)));
+    sample.launched();
     return INFINI_STATUS_SUCCESS;
 }
 
@@ -196,7 +247,9 @@ __INFINI_C infiniStatus_t infinicclSend(const void *sendbuf, size_t count, infin
     ncclDataType_t dt;
     size_t esize;
     CCL_REQUIRE(toNccl(datatype, &dt, &esize), INFINI_STATUS_BAD_TENSOR_DTYPE);
+    Sampled sample(stream, count * esize);
     CCL_NCCL(ncclSend(sendbuf, count, dt, peer, comm->comm, cudaStreamOf(stream)));
+    sample.launched();
     return INFINI_STATUS_SUCCESS;
 }
 
@@ -207,7 +260,9 @@ __INFINI_C infiniStatus_t infinicclRecv(void *recvbuf, size_t count, infiniDtype
     ncclDataType_t dt;
     size_t esize;
     CCL_REQUIRE(toNccl(datatype, &dt, &esize), INFINI_STATUS_BAD_TENSOR_DTYPE);
+    Sampled sample(stream, count * esize);
     CCL_NCCL(ncclRecv(recvbuf, count, dt, peer, comm->comm, cudaStreamOf(stream)));
+    sample.launched();
     return INFINI_STATUS_SUCCESS;
 }
 
@@ -217,7 +272,9 @@ __INFINI_C infiniStatus_t infinicclAllGather(void *sendbuf, void *recvbuf, size_
     ncclDataType_t dt;
     size_t esize;
     CCL_REQUIRE(toNccl(datatype, &dt, &esize), INFINI_STATUS_BAD_TENSOR_DTYPE);
+    Sampled sample(stream, send_count * esize * static_cast<size_t>(comm->world_size)); // what this rank receives
     CCL_NCCL(ncclAllGather(sendbuf, recvbuf, send_count, dt, comm->comm, cudaStreamOf(stream)));
+    sample.launched();
     return INFINI_STATUS_SUCCESS;
 }
 
@@ -230,6 +287,11 @@ __INFINI_C infiniStatus_t infinicclAllGatherV(void *sendbuf, void *recvbuf, cons
     CCL_REQUIRE(toNccl(datatype, &dt, &esize), INFINI_STATUS_BAD_TENSOR_DTYPE);
     CCL_REQUIRE(nranks == comm->world_size, INFINI_STATUS_BAD_PARAM);
     char *dst = static_cast<char *>(recvbuf);
+    uint64_t total = 0;
+    for (int r = 0; r < nranks; ++r) {
+        total += recv_counts[r] * esize;
+    }
+    Sampled sample(stream, total);
     CCL_NCCL(ncclGroupStart());
     for (int root = 0; root < nranks; ++root) {
         const ncclResult_t r = ncclBroadcast(sendbuf, dst, recv_counts[root], dt, root, comm->comm, cudaStreamOf(stream));
@@ -240,6 +302,7 @@ __INFINI_C infiniStatus_t infinicclAllGatherV(void *sendbuf, void *recvbuf, cons
         dst += recv_counts[root] * esize;
     }
     CCL_NCCL(ncclGroupEnd());
+    sample.launched();
     return INFINI_STATUS_SUCCESS;
 }
 
@@ -251,7 +314,9 @@ __INFINI_C infiniStatus_t infinicclReduceScatter(void *sendbuf, void *recvbuf, s
     ncclRedOp_t rop;
     CCL_REQUIRE(toNccl(datatype, &dt, &esize), INFINI_STATUS_BAD_TENSOR_DTYPE);
     CCL_REQUIRE(toNccl(op, &rop), INFINI_STATUS_BAD_PARAM);
+    Sampled sample(stream, recv_count * esize * static_cast<size_t>(comm->world_size)); // what this rank contributes
     CCL_NCCL(ncclReduceScatter(sendbuf, recvbuf, recv_count, dt, rop, comm->comm, cudaStreamOf(stream)));
+    sample.launched();
     return INFINI_STATUS_SUCCESS;
 }
 
@@ -266,6 +331,11 @@ __INFINI_C infiniStatus_t infinicclReduceScatterV(void *sendbuf, void *recvbuf, 
     CCL_REQUIRE(toNccl(op, &rop), INFINI_STATUS_BAD_PARAM);
     CCL_REQUIRE(nranks == comm->world_size, INFINI_STATUS_BAD_PARAM);
     const char *src = static_cast<const char *>(sendbuf);
+    uint64_t total = 0;
+    for (int r = 0; r < nranks; ++r) {
+        total += send_counts[r] * esize;
+    }
+    Sampled sample(stream, total);
     CCL_NCCL(ncclGroupStart());
     for (int root = 0; root < nranks; ++root) {
         const ncclResult_t r = ncclReduce(src, recvbuf, send_counts[root], dt, rop, root, comm->comm, cudaStreamOf(stream));
@@ -276,5 +346,6 @@ __INFINI_C infiniStatus_t infinicclReduceScatterV(void *sendbuf, void *recvbuf, 
         src += send_counts[root] * esize;
     }
     CCL_NCCL(ncclGroupEnd());
+    sample.launched();
     return INFINI_STATUS_SUCCESS;
 }

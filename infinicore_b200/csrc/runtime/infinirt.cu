@@ -11,9 +11,14 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <chrono>
 #include <cstdlib>
+#include <deque>
 #include <dlfcn.h>
+#include <memory>
 #include <mutex>
+#include <utility>
+#include <vector>
 
 namespace {
 
@@ -223,9 +228,135 @@ private:
 
 } // namespace
 
+// ---- communication samples ------------------------------------------------------------------------------
+// One ledger per device: event pairs in flight, and the samples that completed during the last second.
+namespace {
+
+constexpr int kLedgerDevices = 64;
+constexpr double kWindowSeconds = 1.0;
+
+struct EventPair {
+    cudaEvent_t start = nullptr;
+    cudaEvent_t end = nullptr;
+};
+
+struct OpenSample { // what infinirtCommunicationBegin hands out
+    EventPair events;
+    int device = 0;
+};
+
+struct Finished {
+    std::chrono::steady_clock::time_point when;
+    double ms;
+    uint64_t bytes;
+};
+
+struct Ledger {
+    std::mutex mutex;
+    std::vector<EventPair> spare;                      // event pairs ready for reuse
+    std::vector<std::pair<EventPair, uint64_t>> inflight; // end event recorded, not yet seen complete
+    std::deque<Finished> window;
+};
+
+Ledger &ledgerOf(int device) {
+    static Ledger ledgers[kLedgerDevices];
+    return ledgers[(device >= 0 && device < kLedgerDevices) ? device : 0];
+}
+
+// Moves completed samples into the window and drops what is older than the window.  Device `device` is current.
+void collectFinished(Ledger &ledger) {
+    const auto now = std::chrono::steady_clock::now();
+    size_t keep = 0;
+    for (size_t i = 0; i < ledger.inflight.size(); ++i) {
+        auto &entry = ledger.inflight[i];
+        const cudaError_t q = cudaEventQuery(entry.first.end);
+        if (q == cudaErrorNotReady) {
+            ledger.inflight[keep++] = entry;
+            continue;
+        }
+        float ms = 0.f;
+        if (q == cudaSuccess && cudaEventElapsedTime(&ms, entry.first.start, entry.first.end) == cudaSuccess) {
+            ledger.window.push_back({now, static_cast<double>(ms), entry.second});
+            ledger.spare.push_back(entry.first);
+        } else {
+            (void)cudaGetLastError(); // an event that cannot be read (e.g. its stream was destroyed): drop the pair
+            (void)cudaEventDestroy(entry.first.start);
+            (void)cudaEventDestroy(entry.first.end);
+        }
+    }
+    ledger.inflight.resize(keep);
+    while (!ledger.window.empty() && std::chrono::duration<double>(now - ledger.window.front().when).count() > kWindowSeconds) {
+        ledger.window.pop_front();
+    }
+}
+
+} // namespace
+
+__INFINI_C infiniStatus_t infinirtCommunicationBegin(infinirtStream_t stream, void **sample) {
+    RT_REQUIRE_PTR(sample);
+    *sample = nullptr;
+    // (the CUDA runtime's current device counts here, whether or not the thread went through infinirtSetDevice:
+    // a collective library may be driven by a host framework that selects devices itself)
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone) {
+        (void)cudaGetLastError();
+        return INFINI_STATUS_SUCCESS; // a graph being recorded: its replays are not sampled
+    }
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return INFINI_STATUS_SUCCESS;
+    }
+    Ledger &ledger = ledgerOf(device);
+    EventPair pair;
+    {
+        std::lock_guard<std::mutex> lock(ledger.mutex);
+        if (!ledger.spare.empty()) {
+            pair = ledger.spare.back();
+            ledger.spare.pop_back();
+        }
+    }
+    if (pair.start == nullptr) {
+        if (cudaEventCreate(&pair.start) != cudaSuccess || cudaEventCreate(&pair.end) != cudaSuccess) {
+            (void)cudaGetLastError();
+            if (pair.start != nullptr) {
+                (void)cudaEventDestroy(pair.start);
+            }
+            return INFINI_STATUS_SUCCESS; // sampling is best effort: the collective itself must not fail over it
+        }
+    }
+    if (cudaEventRecord(pair.start, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        std::lock_guard<std::mutex> lock(ledger.mutex);
+        ledger.spare.push_back(pair);
+        return INFINI_STATUS_SUCCESS;
+    }
+    *sample = new OpenSample{pair, device};
+    return INFINI_STATUS_SUCCESS;
+}
+
+__INFINI_C infiniStatus_t infinirtCommunicationEnd(void *sample, infinirtStream_t stream, uint64_t bytes) {
+    if (sample == nullptr) {
+        return INFINI_STATUS_SUCCESS;
+    }
+    std::unique_ptr<OpenSample> open(static_cast<OpenSample *>(sample));
+    Ledger &ledger = ledgerOf(open->device);
+    const bool recorded = bytes > 0 && cudaEventRecord(open->events.end, static_cast<cudaStream_t>(stream)) == cudaSuccess;
+    if (!recorded) {
+        (void)cudaGetLastError();
+    }
+    std::lock_guard<std::mutex> lock(ledger.mutex);
+    if (recorded) {
+        ledger.inflight.emplace_back(open->events, bytes);
+    } else {
+        ledger.spare.push_back(open->events);
+    }
+    return INFINI_STATUS_SUCCESS;
+}
+
 // Memory capacity from the CUDA runtime; compute and memory-bandwidth utilisation from the management library
-// when it is there (kernel_time_ratio is the same sample, marked as an estimate, as in the reference).  The
-// communication members stay clear: they would need a store of collective timings, which this path does not keep.
+// when it is there (kernel_time_ratio is the same sample, marked as an estimate, as in the reference); payload
+// bytes and time share of the collectives that completed during the last second from the device's ledger.
 __INFINI_C infiniStatus_t infinirtGetDeviceResourceSnapshot(infiniDevice_t device, int device_id,
                                                            infinirtDeviceResourceSnapshot_t *snapshot) {
     RT_REQUIRE_PTR(snapshot);
@@ -252,6 +383,29 @@ __INFINI_C infiniStatus_t infinirtGetDeviceResourceSnapshot(infiniDevice_t devic
             snapshot->valid_fields |= INFINIRT_RESOURCE_FIELD_COMPUTE_UTILIZATION | INFINIRT_RESOURCE_FIELD_MEMORY_BANDWIDTH_UTILIZATION
                                       | INFINIRT_RESOURCE_FIELD_KERNEL_TIME_RATIO;
             snapshot->estimated_fields |= INFINIRT_RESOURCE_FIELD_KERNEL_TIME_RATIO;
+        }
+    } else {
+        (void)cudaGetLastError();
+    }
+
+    // the ledger's events belong to `device_id`: make it current while they are queried
+    int previous = -1;
+    if (cudaGetDevice(&previous) == cudaSuccess && (previous == device_id || cudaSetDevice(device_id) == cudaSuccess)) {
+        Ledger &ledger = ledgerOf(device_id);
+        std::lock_guard<std::mutex> lock(ledger.mutex);
+        collectFinished(ledger);
+        double ms = 0.0;
+        uint64_t bytes = 0;
+        for (const Finished &f : ledger.window) {
+            ms += f.ms;
+            bytes += f.bytes;
+        }
+        const double ratio = ms / (kWindowSeconds * 1000.0);
+        snapshot->communication_bytes = bytes;
+        snapshot->communication_time_ratio = static_cast<float>(ratio > 1.0 ? 1.0 : ratio);
+        snapshot->valid_fields |= INFINIRT_RESOURCE_FIELD_COMMUNICATION;
+        if (previous != device_id) {
+            (void)cudaSetDevice(previous);
         }
     } else {
         (void)cudaGetLastError();

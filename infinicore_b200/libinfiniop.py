@@ -107,6 +107,7 @@ INFINIRT_SYMBOLS = [
     "infinirtMemset", "infinirtMemsetAsync",
     "infinirtStreamBeginCapture", "infinirtStreamEndCapture", "infinirtGraphDestroy",
     "infinirtGraphInstantiate", "infinirtGraphExecDestroy", "infinirtGraphLuanch",
+    "infinirtCommunicationBegin", "infinirtCommunicationEnd",
 ]
 
 

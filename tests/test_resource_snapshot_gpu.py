@@ -51,7 +51,8 @@ def check_memory(s):
     assert s["status"] == 0 and s["null_status"] == 4  # INFINI_STATUS_NULL_POINTER
     assert s["device_type"] == 1 and s["device_id"] == 0
     assert s["valid_fields"] & 1 and s["total_bytes"] > (100 << 30) and s["used_bytes"] == s["total_bytes"] - s["free_bytes"]
-    assert s["valid_fields"] & 16 == 0 and s["communication_bytes"] == 0  # no collective-timing store on this path
+    # no collective has run in these processes: the communication members are valid and say so
+    assert s["valid_fields"] & 16 and s["communication_bytes"] == 0 and s["communication_time_ratio"] == 0
 
 
 @pytest.mark.skipif(shutil.which("gcc") is None, reason="needs gcc for the stand-in library")
@@ -60,7 +61,7 @@ def test_utilisation_comes_from_the_management_library(tmp_path):
     subprocess.run(["gcc", "-shared", "-fPIC", "-O1", "-o", str(fake), str(ROOT / "tests" / "cpp" / "fake_management_library.c")], check=True)
     s = snapshot(fake)
     check_memory(s)
-    assert s["valid_fields"] == 1 | 2 | 4 | 8
+    assert s["valid_fields"] == 1 | 2 | 4 | 8 | 16
     assert s["estimated_fields"] == 8  # the kernel-time ratio is the compute sample again
     assert abs(s["compute_utilization"] - 0.37) < 1e-6 and abs(s["memory_bandwidth_utilization"] - 0.12) < 1e-6
     assert abs(s["kernel_time_ratio"] - 0.37) < 1e-6
@@ -69,7 +70,7 @@ def test_utilisation_comes_from_the_management_library(tmp_path):
 def test_without_a_management_library_only_memory_is_flagged(tmp_path):
     s = snapshot(tmp_path / "no_such_library.so")
     check_memory(s)
-    assert s["valid_fields"] == 1 and s["estimated_fields"] == 0
+    assert s["valid_fields"] == 1 | 16 and s["estimated_fields"] == 0
     assert s["compute_utilization"] == 0 and s["memory_bandwidth_utilization"] == 0
 
 
@@ -79,3 +80,77 @@ def test_with_the_machines_own_library():
     if s["valid_fields"] & 2:
         assert s["valid_fields"] & 4 and s["valid_fields"] & 8
         assert 0.0 <= s["compute_utilization"] <= 1.0 and 0.0 <= s["memory_bandwidth_utilization"] <= 1.0
+
+
+COMM_CHILD = r"""
+import ctypes, json, sys, time
+sys.path.insert(0, %r)
+import torch
+from infinicore_b200 import ccl
+from infinicore_b200.libinfiniop import LIBINFINIOP
+
+class Snapshot(ctypes.Structure):
+    _fields_ = [("device_type", ctypes.c_int), ("device_id", ctypes.c_int), ("valid_fields", ctypes.c_uint64),
+                ("estimated_fields", ctypes.c_uint64), ("free_bytes", ctypes.c_size_t), ("total_bytes", ctypes.c_size_t),
+                ("used_bytes", ctypes.c_size_t), ("reserved_bytes", ctypes.c_size_t), ("compute_utilization", ctypes.c_float),
+                ("memory_bandwidth_utilization", ctypes.c_float), ("kernel_time_ratio", ctypes.c_float),
+                ("communication_time_ratio", ctypes.c_float), ("communication_bytes", ctypes.c_uint64)]
+
+fn = LIBINFINIOP.librt.infinirtGetDeviceResourceSnapshot
+fn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.POINTER(Snapshot)]
+
+def snap():
+    s = Snapshot()
+    assert fn(1, 0, ctypes.byref(s)) == 0
+    return {"valid": s.valid_fields, "bytes": s.communication_bytes, "ratio": s.communication_time_ratio}
+
+torch.cuda.set_device(0)
+comm = ccl.init_all([0])[0]
+n = 16 << 20                                   # 64 MiB of fp32 per collective
+x = torch.ones(n, dtype=torch.float32, device="cuda:0")
+y = torch.empty_like(x)
+out = {"before": snap()}
+for _ in range(3):
+    comm.all_reduce(x, y)                      # three samples of 64 MiB each
+comm.group_start()                             # a caller's group is one sample carrying the sum of its payloads
+comm.broadcast(x[: n // 2], y[: n // 2], 0)
+comm.broadcast(x[n // 2:], y[n // 2:], 0)
+comm.group_end()
+torch.cuda.synchronize()
+out["after"] = snap()
+out["sum_ok"] = bool((y == 1).all())
+# captured collectives are not sampled (their events could not be read back)
+g = torch.cuda.CUDAGraph()
+side = torch.cuda.Stream()
+with torch.cuda.stream(side):
+    comm.all_reduce(x, y)
+    side.synchronize()
+    before_capture = snap()["bytes"]
+    with torch.cuda.graph(g, stream=side):
+        comm.all_reduce(x, y)
+    g.replay()
+    side.synchronize()
+out["captured_added"] = snap()["bytes"] - before_capture
+time.sleep(1.3)                                # the window is one second
+out["later"] = snap()
+torch.cuda.synchronize()
+comm.destroy()
+print(json.dumps(out))
+""" % str(ROOT)
+
+
+def test_collectives_show_up_in_the_communication_members():
+    import os
+
+    env = dict(os.environ)
+    env.pop("INFINIRT_MANAGEMENT_LIBRARY", None)
+    res = subprocess.run([sys.executable, "-c", COMM_CHILD], env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-3000:]
+    r = json.loads(res.stdout.strip().splitlines()[-1])
+    assert r["sum_ok"]
+    assert r["before"]["valid"] & 16 and r["before"]["bytes"] == 0
+    assert r["after"]["valid"] & 16
+    assert r["after"]["bytes"] == 4 * (64 << 20), "three all-reduces of 64 MiB and one group of two 32 MiB broadcasts"
+    assert 0.0 < r["after"]["ratio"] <= 1.0
+    assert r["captured_added"] == 0
+    assert r["later"]["bytes"] == 0 and r["later"]["ratio"] == 0, "samples older than a second leave the window"
