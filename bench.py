@@ -376,7 +376,8 @@ class AbiStep:
         # caching + (reset kernel, [plan kernel for more than 4095 sequences], main kernel, [combine kernel when units * 4 <= workers])
         units = case.num_seqs * case.k_cache.shape[1] * (1 if case.num_heads // case.k_cache.shape[1] <= 8 else -(-(case.num_heads // case.k_cache.shape[1]) // 16))
         combine = 1 if units * 4 <= 148 * 2 * 4 else 0
-        self.launches_per_step = 1 + ((2 + (0 if case.num_seqs <= 4095 else 1) + combine) if self.ws_size > 0 else 1)
+        reset = 1 - combine  # the counters are only used (and cleared) when the units are merged inside the main kernel
+        self.launches_per_step = 1 + ((1 + reset + (0 if case.num_seqs <= 4095 else 1) + combine) if self.ws_size > 0 else 1)
 
     def caching(self, stream):
         c = self.case

@@ -1905,7 +1905,9 @@ infiniStatus_t launchTyped(const StreamPlan &plan, const StreamArgs &args, const
     // reset kernel: the chunk counter, the per-unit tile counters when units are merged inside the main
     // kernel, the error flag
     const long long units = static_cast<long long>(args.p.num_seqs) * args.units_per_seq;
-    {
+    // (nothing to clear when the units are merged by the combine kernel and ranges are not cut into pieces:
+    // small and long-context calls are launch-bound, and a kernel that does nothing still costs microseconds)
+    if (args.merge_in_kernel || pool) {
         const long long count = 1 + (args.merge_in_kernel ? units : 0);
         long long ctas = (count + 4 * kResetThreads - 1) / (4 * kResetThreads);
         cfg.gridDim = dim3(static_cast<unsigned>(ctas > 64 ? 64 : ctas));
