@@ -1200,10 +1200,13 @@ __global__ void __launch_bounds__(HD == 64 ? 128 : kMaxWarps * 32, HD == 64 ? 3 
 // Same decomposition, plan, partial records and combine as above, with two differences.
 //  * One worker is a CTA of four warps instead of one warp: a 16-token tile is 36 KiB here and the O
 //    accumulator of a head tile does not fit one warp's registers.  The four warps share one ring of
-//    staged tiles; every warp computes the full S^T = Q.K^T of the tile (four times the score MMAs,
-//    still far below the tensor pipe's rate next to 36 KiB of HBM traffic per tile) and owns a quarter
-//    of the value columns for O += P.V.  Each warp issues a quarter of a tile's copies and arrives for
-//    its own bytes.  A slot is handed back through an "empty" mbarrier on which each of the four warps
+//    staged tiles.  Each warp multiplies a quarter of the key width (9 of the 36 k-steps) for the
+//    scores S^T = Q.K^T of the tile, the four partial sums meet in shared memory (1 KiB per warp, two
+//    buffers so that one CTA-wide barrier per tile is enough) and every warp adds them in the same
+//    order, so the four hold identical scores and identical softmax state; each owns a quarter of the
+//    value columns for O += P.V.  (Every warp computing all 36 k-steps itself needs no barrier but
+//    2.6 times the tensor-core and ldmatrix instructions per tile, and the kernel is bound by those, not
+//    by HBM.)  Each warp issues a quarter of a tile's copies and arrives for its own bytes.  A slot is handed back through an "empty" mbarrier on which each of the four warps
 //    arrives once it has read the slot; before they consume tile i, the warps refill the slot tile
 //    i - 1 has just left.
 //  * A head tile is 16 q-heads, all 16 rows of the MMA's M dimension: shapes with many q-heads per
@@ -1231,13 +1234,15 @@ __global__ void __launch_bounds__(kWideWarps * 32)
     constexpr int kVBytes = kVChunks * kBoxBytes;
     constexpr int kStageBytes = kKBytes + kVBytes;
     constexpr int kKSteps = KD / 16;
-    constexpr int kKChunk = 6;                        // k-steps fetched per batch of ldmatrix (divides 36)
+    constexpr int kWarpKSteps = kKSteps / kWideWarps; // k-steps of the scores each warp multiplies: 9
+    constexpr int kKChunk = 3;                        // k-steps fetched per batch of ldmatrix (divides 9)
+    constexpr int kPartialBytes = kWideHeads * kTileTokens * 4; // one warp's partial scores: 1 KiB
     constexpr int kCols = VD / kWideWarps;            // value columns per warp: 144 or 128
     constexpr int kNTiles = kCols / 8;                // 18 or 16 (even)
     constexpr int kVPieces = kCols / 8;               // 16-byte pieces of a V row per warp
     constexpr int kQStride = KD * 2 + 16;             // bytes per Q row in shared memory: odd multiple of 16 -> conflict-free ldmatrix
     constexpr int kQBytes = kWideHeads * kQStride;
-    static_assert(kKSteps % kKChunk == 0 && kNTiles % 2 == 0 && kKChunks + kVChunks <= 32, "shape");
+    static_assert(kKSteps % kWideWarps == 0 && kWarpKSteps % kKChunk == 0 && kNTiles % 2 == 0 && kKChunks + kVChunks <= 32, "shape");
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5;
@@ -1251,6 +1256,7 @@ __global__ void __launch_bounds__(kWideWarps * 32)
     const uint32_t q_smem = ring + stages * kStageBytes;
     const uint32_t full = q_smem + kQBytes;
     const uint32_t empty = full + stages * 8;
+    const uint32_t partials = empty + stages * 8; // [2 buffers][4 warps][1 KiB]; 16-byte aligned (every term is)
     unsigned char *q_ptr = smem_raw + stages * kStageBytes;
 
     if (threadIdx.x == 0) {
@@ -1415,6 +1421,27 @@ __global__ void __launch_bounds__(kWideWarps * 32)
         const int tok0 = cur.ti * kTileTokens;
         const int valid = seq_len - tok0; // >= 1 by construction
         const int v_piece0 = warp * kVPieces; // this warp's first 16-byte piece of a V row
+        const int k_row = ((lane >> 4) << 3) + (lane & 7);
+        const int k_half = (lane >> 3) & 1;
+        const int v_row = (((lane >> 3) & 1) << 3) + (lane & 7);
+        const int v_sel = lane >> 4;
+        auto kAddr = [&](int ks) {
+            const int col = ks * 2 + k_half;
+            return k_tile + (col >> 3) * kBoxBytes + k_row * 128 + (((col & 7) ^ (k_row & 7)) << 4);
+        };
+        auto vAddr = [&](int np) { // np counts pairs of 8-column n-tiles inside this warp's slice
+            const int col = v_piece0 + np * 2 + v_sel;
+            return v_tile + (col >> 3) * kBoxBytes + v_row * 128 + (((col & 7) ^ (v_row & 7)) << 4);
+        };
+        // A fragment of k-step ks: matrices (rows 0-7 | 8-15) x (columns 16 ks .. +8 | +8 .. +16)
+        const uint32_t q_lane = q_smem + ((lane & 7) + ((lane >> 3) & 1) * 8) * kQStride + (lane >> 4) * 16;
+
+        float sa[2][4], sb[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            sa[n][0] = sa[n][1] = sa[n][2] = sa[n][3] = 0.f;
+            sb[n][0] = sb[n][1] = sb[n][2] = sb[n][3] = 0.f;
+        }
 
         if (!failed) {
         if (p.new_k != nullptr && valid <= kTileTokens) {
@@ -1466,44 +1493,52 @@ __global__ void __launch_bounds__(kWideWarps * 32)
             __syncwarp();
         }
 
-        const int k_row = ((lane >> 4) << 3) + (lane & 7);
-        const int k_half = (lane >> 3) & 1;
-        const int v_row = (((lane >> 3) & 1) << 3) + (lane & 7);
-        const int v_sel = lane >> 4;
-        auto kAddr = [&](int ks) {
-            const int col = ks * 2 + k_half;
-            return k_tile + (col >> 3) * kBoxBytes + k_row * 128 + (((col & 7) ^ (k_row & 7)) << 4);
-        };
-        auto vAddr = [&](int np) { // np counts pairs of 8-column n-tiles inside this warp's slice
-            const int col = v_piece0 + np * 2 + v_sel;
-            return v_tile + (col >> 3) * kBoxBytes + v_row * 128 + (((col & 7) ^ (v_row & 7)) << 4);
-        };
-        // A fragment of k-step ks: matrices (rows 0-7 | 8-15) x (columns 16 ks .. +8 | +8 .. +16)
-        const uint32_t q_lane = q_smem + ((lane & 7) + ((lane >> 3) & 1) * 8) * kQStride + (lane >> 4) * 16;
-
-        // ---- S^T = Q . K^T over the whole key width (every warp), 16 heads x 16 tokens --------------
-        float sa[2][4], sb[2][4];
+        // ---- S^T = Q . K^T, 16 heads x 16 tokens: this warp's quarter of the key width ---------------
+        const int ks0 = warp * kWarpKSteps;
 #pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            sa[n][0] = sa[n][1] = sa[n][2] = sa[n][3] = 0.f;
-            sb[n][0] = sb[n][1] = sb[n][2] = sb[n][3] = 0.f;
-        }
-#pragma unroll
-        for (int c0 = 0; c0 < kKSteps; c0 += kKChunk) {
+        for (int c0 = 0; c0 < kWarpKSteps; c0 += kKChunk) {
             uint32_t kb[kKChunk][4], qf[kKChunk][4];
 #pragma unroll
             for (int ks = 0; ks < kKChunk; ++ks) {
-                ldmatrixX4(kAddr(c0 + ks), kb[ks][0], kb[ks][1], kb[ks][2], kb[ks][3]);
-                ldmatrixX4(q_lane + (c0 + ks) * 32, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+                ldmatrixX4(kAddr(ks0 + c0 + ks), kb[ks][0], kb[ks][1], kb[ks][2], kb[ks][3]);
+                ldmatrixX4(q_lane + (ks0 + c0 + ks) * 32, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
             }
 #pragma unroll
-            for (int ks = 0; ks < kKChunk; ks += 2) {
-                mma16816<T>(sa[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], kb[ks][0], kb[ks][1]);
-                mma16816<T>(sa[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], kb[ks][2], kb[ks][3]);
-                mma16816<T>(sb[0], qf[ks + 1][0], qf[ks + 1][1], qf[ks + 1][2], qf[ks + 1][3], kb[ks + 1][0], kb[ks + 1][1]);
-                mma16816<T>(sb[1], qf[ks + 1][0], qf[ks + 1][1], qf[ks + 1][2], qf[ks + 1][3], kb[ks + 1][2], kb[ks + 1][3]);
+            for (int ks = 0; ks < kKChunk; ++ks) {
+                // two independent accumulator chains, alternating
+                if (((c0 + ks) & 1) == 0) {
+                    mma16816<T>(sa[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], kb[ks][0], kb[ks][1]);
+                    mma16816<T>(sa[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], kb[ks][2], kb[ks][3]);
+                } else {
+                    mma16816<T>(sb[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], kb[ks][0], kb[ks][1]);
+                    mma16816<T>(sb[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], kb[ks][2], kb[ks][3]);
+                }
             }
         }
+        } // !failed
+        // ---- the four partial sums meet: every warp of the CTA takes part in the barrier on every tile,
+        // also one whose wait ran out (its scores are then meaningless; the status word says so) ----------
+        {
+            const uint32_t mine = partials + ((static_cast<uint32_t>(i) & 1u) * kWideWarps + warp) * kPartialBytes + lane * 32;
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(mine), "f"(sa[0][0] + sb[0][0]), "f"(sa[0][1] + sb[0][1]),
+                         "f"(sa[0][2] + sb[0][2]), "f"(sa[0][3] + sb[0][3]) : "memory");
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(mine + 16), "f"(sa[1][0] + sb[1][0]), "f"(sa[1][1] + sb[1][1]),
+                         "f"(sa[1][2] + sb[1][2]), "f"(sa[1][3] + sb[1][3]) : "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(kWideWarps * 32) : "memory");
+            float part[kWideWarps][8];
+#pragma unroll
+            for (int w = 0; w < kWideWarps; ++w) {
+                const uint32_t src = partials + ((static_cast<uint32_t>(i) & 1u) * kWideWarps + w) * kPartialBytes + lane * 32;
+                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(part[w][0]), "=f"(part[w][1]), "=f"(part[w][2]), "=f"(part[w][3]) : "r"(src) : "memory");
+                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(part[w][4]), "=f"(part[w][5]), "=f"(part[w][6]), "=f"(part[w][7]) : "r"(src + 16) : "memory");
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                sa[0][e] = (part[0][e] + part[1][e]) + (part[2][e] + part[3][e]);
+                sa[1][e] = (part[0][4 + e] + part[1][4 + e]) + (part[2][4 + e] + part[3][4 + e]);
+            }
+        }
+        if (!failed) {
 
         // ---- online softmax (log2 domain) of rows g and g + 8, identical in the four warps ----------
         uint32_t pa[4]; // A fragment of P: (row g | g + 8) x (tokens 2t, 2t+1 | 2t+8, 2t+9)
@@ -1511,10 +1546,10 @@ __global__ void __launch_bounds__(kWideWarps * 32)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             float x[4];
-            x[0] = (sa[0][2 * h] + sb[0][2 * h]) * p.scale_log2e;
-            x[1] = (sa[0][2 * h + 1] + sb[0][2 * h + 1]) * p.scale_log2e;
-            x[2] = (sa[1][2 * h] + sb[1][2 * h]) * p.scale_log2e;
-            x[3] = (sa[1][2 * h + 1] + sb[1][2 * h + 1]) * p.scale_log2e;
+            x[0] = sa[0][2 * h] * p.scale_log2e;
+            x[1] = sa[0][2 * h + 1] * p.scale_log2e;
+            x[2] = sa[1][2 * h] * p.scale_log2e;
+            x[3] = sa[1][2 * h + 1] * p.scale_log2e;
             if (slope_log2[h] != 0.f) {
                 const int rel = tok0 + 2 * t - (seq_len - 1);
                 x[0] += slope_log2[h] * static_cast<float>(rel);
@@ -2059,7 +2094,8 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
         plan.embedded_plan = false;
         plan.use_pdl = envInt("INFINIOP_PAGED_DECODE_PDL", 1, 0, 1) != 0;
         const size_t stage_bytes = (hd / 64 + I.value_size / 64) * kTileTokens * 128;
-        const size_t q_bytes = kWideHeads * (hd * 2 + 16); // the unit's Q rows, padded
+        // the unit's Q rows, padded, and the two buffers of four 1 KiB partial score tiles
+        const size_t q_bytes = kWideHeads * (hd * 2 + 16) + 2 * kWideWarps * kWideHeads * kTileTokens * 4;
         auto smemFor = [&](int stages) { return static_cast<size_t>(stages) * (stage_bytes + 16) + q_bytes + 1024; };
         while (plan.stages > 2 && smemFor(plan.stages) > props.smem_per_block_optin) {
             --plan.stages;

@@ -117,7 +117,8 @@ infiniStatus_t launchPrefillTiles(const Info &info, const TilePlan &plan, const 
 struct UmmaPlan {
     bool eligible = false;
     int box_rows = 16;
-    int stages = 2;  // slots of the K and V rings
+    int stages = 2;  // slots of the V ring
+    int k_stages = 3; // slots of the K ring (>= stages)
     int q_tiles = 1; // q-heads of one GQA group per CTA (share every staged KV tile)
 };
 UmmaPlan planPrefillUmma(const Info &info, const DeviceProps &props);

@@ -339,10 +339,14 @@ struct UmmaArgs {
 //   k_full/v_full[stage]   producers -> MMA (bytes landed; one arrival per producer warp)
 //   k_empty/v_empty[stage] MMA -> producers (tcgen05.commit, one per MMA warp)
 //   s_ready[i][buf]        score MMA i -> softmax i (S retired)     s_free[i][buf]  P.V MMA i -> score MMA i (P consumed)
-//   p_ready[i]             softmax i -> MMA i (P stored, 4 arrivals) o_done[i]      MMA i -> softmax i (P.V retired)
+//   p_ready[i][buf]        softmax i -> MMA i (P stored, 4 arrivals) o_done[i]      MMA i -> softmax i (P.V retired)
+// (p_ready is one barrier per S buffer like the other two: the softmax may be two tiles ahead of P.V - P of
+// tiles kt + 1 and kt + 2 stored while P.V of tile kt + 1 still waits for its V tile - and a waiter that is two
+// phases behind a single barrier reads its parity wrongly and waits for ever; per buffer the softmax cannot
+// store P of tile kt + 2 before P.V of tile kt has retired.)
 // The score warp runs ahead of the softmax as far as the two S buffers allow, so the tensor core works
 // on the next scores while the softmax warps are busy with the current ones.
-template <typename T, int kStages, int kQ, int kHD>
+template <typename T, int kStages, int kKStages, int kQ, int kHD>
 __global__ void __launch_bounds__((8 * kQ) * 32)
     pagedPrefillUmmaKernel(const __grid_constant__ CUtensorMap tmap_q,
                            const __grid_constant__ CUtensorMap tmap_k,
@@ -361,28 +365,31 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
     constexpr int kQBytes = qTileBytes(kHD);
     constexpr int kTensorBytes = kvTileBytes(kHD);
     constexpr int kRingOff = kQ * kQBytes;
-    constexpr int kBarOff = kRingOff + kStages * 2 * kTensorBytes;
+    constexpr int kBarOff = kRingOff + (kKStages + kStages) * kTensorBytes; // K ring [kKStages], then V ring [kStages]
     const uint32_t smem0 = smemAddr(smem_raw);
     const uint32_t q_tiles = smem0;
     const uint32_t ring = smem0 + kRingOff;
-    const uint32_t k_full = smem0 + kBarOff;              // [kStages]
-    const uint32_t k_empty = k_full + kStages * 8;        // [kStages]
-    const uint32_t v_full = k_empty + kStages * 8;        // [kStages]
+    const uint32_t k_full = smem0 + kBarOff;              // [kKStages]
+    const uint32_t k_empty = k_full + kKStages * 8;       // [kKStages]
+    const uint32_t v_full = k_empty + kKStages * 8;       // [kStages]
     const uint32_t v_empty = v_full + kStages * 8;        // [kStages]
     const uint32_t s_ready = v_empty + kStages * 8;       // [kQ][2]
     const uint32_t s_free = s_ready + kQ * 16;            // [kQ][2]
-    const uint32_t p_ready = s_free + kQ * 16;            // [kQ]
-    const uint32_t o_done = p_ready + kQ * 8;             // [kQ]
+    const uint32_t p_ready = s_free + kQ * 16;            // [kQ][2]
+    const uint32_t o_done = p_ready + kQ * 16;            // [kQ]
     const uint32_t drain_bar = o_done + kQ * 8;           // [2 kQ]
     const uint32_t q_bar = drain_bar + 2 * kQ * 8;
-    constexpr int kNumBars = 4 * kStages + 8 * kQ + 1;
+    constexpr int kNumBars = 2 * kKStages + 2 * kStages + 9 * kQ + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + kBarOff + kNumBars * 8);
     int *scratch = reinterpret_cast<int *>(tmem_slot + 2);
     int &sh_seq = scratch[0];
     int &sh_t0 = scratch[1];
     int &sh_found = scratch[2];
     int &sh_failed = scratch[3];
-    int *sh_warp_tot = scratch + 4;
+    int &sh_n_new = scratch[4];
+    int &sh_total_len = scratch[5];
+    long long &sh_q_begin = *reinterpret_cast<long long *>(scratch + 6); // 8-byte aligned: the barriers and the TMEM slot before it are
+    int *sh_warp_tot = scratch + 8;
 
     const DecodeParams &p = a.pp.d;
     const int tid = threadIdx.x;
@@ -395,9 +402,11 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
         prefetchTensorMap(&tmap_q);
         prefetchTensorMap(&tmap_k);
         prefetchTensorMap(&tmap_v);
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kKStages; ++s) {
             mbarInit(k_full + s * 8, kProducers);
             mbarInit(k_empty + s * 8, kQ);
+        }
+        for (int s = 0; s < kStages; ++s) {
             mbarInit(v_full + s * 8, kProducers);
             mbarInit(v_empty + s * 8, kQ);
         }
@@ -406,7 +415,8 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
                 mbarInit(s_ready + (i * 2 + b) * 8, 1);
                 mbarInit(s_free + (i * 2 + b) * 8, 1);
             }
-            mbarInit(p_ready + i * 8, 4);
+            mbarInit(p_ready + (i * 2) * 8, 4);
+            mbarInit(p_ready + (i * 2 + 1) * 8, 4);
             mbarInit(o_done + i * 8, 1);
             mbarInit(drain_bar + i * 8, 1);
             mbarInit(drain_bar + (kQ + i) * 8, 1);
@@ -425,9 +435,13 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
         for (int base = 0; base < p.num_seqs; base += kNT) {
             const int i = base + tid;
             int tiles = 0;
+            long long my_begin = 0, my_n = 0, my_len = 0;
             if (i < p.num_seqs) {
-                const long long n = loadIndex(a.pp.cum_seq_lens_q, i + 1, p.index_is_64) - loadIndex(a.pp.cum_seq_lens_q, i, p.index_is_64);
-                tiles = n > 0 ? static_cast<int>((n + kBM - 1) / kBM) : 0;
+                // all three loads in flight together; the sequence that owns this tile publishes them below
+                my_begin = loadIndex(a.pp.cum_seq_lens_q, i, p.index_is_64);
+                my_n = loadIndex(a.pp.cum_seq_lens_q, i + 1, p.index_is_64) - my_begin;
+                my_len = loadIndex(p.seq_lens, i, p.index_is_64);
+                tiles = my_n > 0 ? static_cast<int>((my_n + kBM - 1) / kBM) : 0;
             }
             int incl = tiles;
 #pragma unroll
@@ -449,8 +463,12 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
             }
             const int excl = carry + prev + incl - tiles;
             if (tiles > 0 && tile_id >= excl && tile_id < excl + tiles) {
+                const long long capacity = static_cast<long long>(p.max_blocks_per_seq) * p.block_size;
                 sh_seq = i;
                 sh_t0 = (tile_id - excl) * kBM;
+                sh_q_begin = my_begin;
+                sh_n_new = static_cast<int>(my_n);
+                sh_total_len = static_cast<int>(my_len > capacity ? capacity : my_len);
                 sh_found = 1;
             }
             __syncthreads();
@@ -465,12 +483,9 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
     }
     const int seq = sh_seq;
     const int t0 = sh_t0;
-    const long long q_begin = loadIndex(a.pp.cum_seq_lens_q, seq, p.index_is_64);
-    const int n_new = static_cast<int>(loadIndex(a.pp.cum_seq_lens_q, seq + 1, p.index_is_64) - q_begin);
-    const long long capacity = static_cast<long long>(p.max_blocks_per_seq) * p.block_size;
-    long long total_ll = loadIndex(p.seq_lens, seq, p.index_is_64);
-    total_ll = total_ll > capacity ? capacity : total_ll;
-    const int total_len = static_cast<int>(total_ll);
+    const long long q_begin = sh_q_begin;
+    const int n_new = sh_n_new;
+    const int total_len = sh_total_len;
     const int cache_len = total_len - n_new;
     const int rows_valid = min(kBM, n_new - t0);
     const int kv_end = min(total_len, cache_len + t0 + rows_valid);
@@ -523,51 +538,68 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
                 block = paged_attention::reportedBlock(p, loadIndex(p.block_tables, bt_row + page, p.index_is_64));
             }
         };
-        long long block_next;
-        int row0_next;
-        locateBox(0, block_next, row0_next);
-        int issued = 0;
-        bool ok = true;
-        for (int kt = 0; kt < num_kv_tiles; ++kt) {
-            const int stage = kt % kStages;
-            const uint32_t parity = (kt / kStages) & 1;
-            const long long block = block_next;
-            const int row0 = row0_next;
-            locateBox(kt + 1, block_next, row0_next);       // in flight while this tile's copies are issued
+        // One tile's K (is_v = 0) or V copies of this warp: wait for the slot, announce the bytes, issue.
+        auto issueTile = [&](int is_v, int kt, long long block, int row0) -> bool {
+            const int depth = is_v ? kStages : kKStages;
+            const int stage = kt % depth;
+            const uint32_t parity = (kt / depth) & 1;
+            const uint32_t full = (is_v ? v_full : k_full) + stage * 8;
+            const uint32_t empty = (is_v ? v_empty : k_empty) + stage * 8;
             const bool live = block >= 0;
             const uint32_t bytes = static_cast<uint32_t>(__popc(__ballot_sync(0xffffffffu, live))) * box_bytes;
-            // K first (its slot frees after S of tile kt - kStages), then V (frees after that tile's P.V):
-            // the same order in which the two slots become free.
-#pragma unroll
-            for (int is_v = 0; is_v < 2; ++is_v) {
-                const uint32_t full = (is_v ? v_full : k_full) + stage * 8;
-                const uint32_t empty = (is_v ? v_empty : k_empty) + stage * 8;
-                if (kt >= kStages) {
-                    ok = __all_sync(0xffffffffu, mbarWait(empty, parity ^ 1u));
-                    if (!ok) {
-                        break;
-                    }
-                }
-                if (lane == 0) {
-                    mbarExpectTx(full, bytes); // this warp's arrival, announcing its share of the tile
-                }
-                __syncwarp();
-                if (live) {
-                    const uint32_t dst = ring + (is_v * kStages + stage) * kTensorBytes + my_chunk * (kBN * 128)
-                                         + my_group * box_bytes;
-                    tmaLoad4d(dst, is_v ? &tmap_v : &tmap_k, full, my_chunk * 64, row0, kv_head, static_cast<int>(block));
-                }
+            if (kt >= depth && !__all_sync(0xffffffffu, mbarWait(empty, parity ^ 1u))) {
+                return false;
             }
+            if (lane == 0) {
+                mbarExpectTx(full, bytes); // this warp's arrival, announcing its share of the tile
+            }
+            __syncwarp();
+            if (live) {
+                const uint32_t dst = ring + (is_v * kKStages + stage) * kTensorBytes + my_chunk * (kBN * 128) + my_group * box_bytes;
+                tmaLoad4d(dst, is_v ? &tmap_v : &tmap_k, full, my_chunk * 64, row0, kv_head, static_cast<int>(block));
+            }
+            return true;
+        };
+        // The K copies run one tile ahead of the V copies: the scores of tile kt + 1 are wanted while the
+        // softmax still works on tile kt, its values a whole tile later, and a V slot only frees when P.V two
+        // tiles back has retired - K(kt + 1) must not queue behind that wait.  (A K slot frees when the scores
+        // kKStages tiles back have retired, which is long before.)  Page-table entries are fetched two tiles
+        // ahead of their first use.
+        long long block0, block1, block2;
+        int row00, row01, row02;
+        locateBox(0, block0, row00);
+        locateBox(1, block1, row01);
+        int issued_k = 0, issued_v = 0;
+        bool ok = issueTile(0, 0, block0, row00);
+        if (ok) {
+            issued_k = 1;
+        }
+        for (int kt = 0; kt < num_kv_tiles && ok; ++kt) {
+            locateBox(kt + 2, block2, row02); // in flight while this step's copies are issued
+            if (kt + 1 < num_kv_tiles) {
+                ok = issueTile(0, kt + 1, block1, row01);
+                if (!ok) {
+                    break;
+                }
+                issued_k = kt + 2;
+            }
+            ok = issueTile(1, kt, block0, row00);
             if (!ok) {
                 break;
             }
-            issued = kt + 1;
+            issued_v = kt + 1;
+            block0 = block1;
+            row00 = row01;
+            block1 = block2;
+            row01 = row02;
         }
         if (!ok) {
             sh_failed = 1;
-            // bounded wait for the copies of the last (up to kStages) tiles this warp issued
-            for (int kt = max(0, issued - kStages); kt < issued; ++kt) {
-                (void)mbarWait(k_full + (kt % kStages) * 8, (kt / kStages) & 1);
+            // bounded wait for the copies of the last tiles this warp issued (as many as each ring holds)
+            for (int kt = max(0, issued_k - kKStages); kt < issued_k; ++kt) {
+                (void)mbarWait(k_full + (kt % kKStages) * 8, (kt / kKStages) & 1);
+            }
+            for (int kt = max(0, issued_v - kStages); kt < issued_v; ++kt) {
                 (void)mbarWait(v_full + (kt % kStages) * 8, (kt / kStages) & 1);
             }
         }
@@ -587,7 +619,7 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
             // descriptors differ only in their start-address field: build one per operand and add
             const uint64_t q_desc = smemDesc(q_tiles + i * kQBytes, 16, 1024);
             const uint64_t k_desc = smemDesc(ring, 16, 1024);
-            const uint64_t v_desc = smemDesc(ring + kStages * kTensorBytes, kBN * 128, 1024);
+            const uint64_t v_desc = smemDesc(ring + kKStages * kTensorBytes, kBN * 128, 1024);
             const uint32_t tmem_q = __shfl_sync(0xffffffffu, tmem_base, 0) + i * 256;
             const uint32_t my_s_ready = s_ready + i * 16;
             auto waitAll = [&](uint32_t bar, uint32_t parity) -> bool { return __all_sync(0xffffffffu, mbarWait(bar, parity)); };
@@ -595,11 +627,11 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
             if (scores) {
                 ok = waitAll(q_bar, 0);
                 for (int kt = 0; kt < num_kv_tiles && ok; ++kt) {
-                    const int stage = kt % kStages;
+                    const int stage = kt % kKStages;
                     // The S buffer also holds P of tile kt - 2 (written over the scores it came from): P.V of
                     // that tile must have retired before new scores land there.  (A barrier per buffer: its
                     // next arrival needs these very scores, so it is never more than one phase ahead.)
-                    ok = waitAll(k_full + stage * 8, (kt / kStages) & 1)
+                    ok = waitAll(k_full + stage * 8, (kt / kKStages) & 1)
                          && (kt < 2 || waitAll(s_free + (i * 2 + (kt & 1)) * 8, ((kt >> 1) - 1) & 1));
                     if (!ok) {
                         break;
@@ -623,7 +655,7 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
             } else {
                 for (int kt = 0; kt < num_kv_tiles && ok; ++kt) {
                     const int stage = kt % kStages;
-                    ok = waitAll(v_full + stage * 8, (kt / kStages) & 1) && waitAll(p_ready + i * 8, kt & 1);
+                    ok = waitAll(v_full + stage * 8, (kt / kStages) & 1) && waitAll(p_ready + (i * 2 + (kt & 1)) * 8, (kt >> 1) & 1);
                     if (!ok) {
                         break;
                     }
@@ -664,7 +696,7 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
         const uint32_t tmem_q = tmem_base + qi * 256;
         const uint32_t tmem_o = tmem_q + 128;
         const uint32_t my_s_ready = s_ready + qi * 16;
-        const uint32_t my_p_ready = p_ready + qi * 8, my_o_done = o_done + qi * 8;
+        const uint32_t my_p_ready = p_ready + qi * 16, my_o_done = o_done + qi * 8;
         const int gtid = tid & 127;                                    // thread index within this q-tile's four warps
         const float c_log2 = p.scale_log2e;
 
@@ -680,7 +712,7 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
             const int kv0 = kt * kBN;
             const int valid = kv_end - kv0;
             const uint32_t tmem_s = tmem_q + (kt & 1) * kBN;
-            const uint32_t v_tile = ring + (kStages + stage) * kTensorBytes;
+            const uint32_t v_tile = ring + (kKStages + stage) * kTensorBytes;
 
             ok = mbarWait(my_s_ready + (kt & 1) * 8, (kt >> 1) & 1);
             if (!ok) {
@@ -780,7 +812,7 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
             tcgenFenceBefore();
             __syncwarp();
             if (lane == 0) {
-                mbarArrive(my_p_ready);
+                mbarArrive(my_p_ready + (kt & 1) * 8);
             }
         }
 
@@ -919,21 +951,21 @@ bool encodeOutMap(CUtensorMap *map, const Info &info, const void *base) {
 }
 
 // tiles + barriers / TMEM slot / scan scratch
-constexpr size_t smemBytes(int stages, int nq, int hd) {
-    return static_cast<size_t>(nq) * qTileBytes(hd) + static_cast<size_t>(stages) * 2 * kvTileBytes(hd) + 512;
+constexpr size_t smemBytes(int stages, int k_stages, int nq, int hd) {
+    return static_cast<size_t>(nq) * qTileBytes(hd) + static_cast<size_t>(stages + k_stages) * kvTileBytes(hd) + 512;
 }
 
-template <typename T, int STAGES, int NQ, int HD>
+template <typename T, int STAGES, int KSTAGES, int NQ, int HD>
 infiniStatus_t launchTyped(const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mo,
                            unsigned tiles, int device_id, cudaStream_t stream) {
     static std::mutex attr_mutex;
     static bool attr_done[64] = {};
-    auto kernel = pagedPrefillUmmaKernel<T, STAGES, NQ, HD>;
+    auto kernel = pagedPrefillUmmaKernel<T, STAGES, KSTAGES, NQ, HD>;
     {
         std::lock_guard<std::mutex> lock(attr_mutex);
         const bool tracked = device_id >= 0 && device_id < 64;
         if (!tracked || !attr_done[device_id]) {
-            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes(STAGES, NQ, HD))) != cudaSuccess) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smemBytes(STAGES, KSTAGES, NQ, HD))) != cudaSuccess) {
                 return checkLaunch("cudaFuncSetAttribute(pagedPrefillUmmaKernel)");
             }
             if (tracked) {
@@ -942,30 +974,31 @@ infiniStatus_t launchTyped(const UmmaArgs &args, const CUtensorMap &mq, const CU
         }
     }
     const dim3 grid(tiles, args.pp.d.num_heads / NQ);
-    kernel<<<grid, 8 * NQ * 32, smemBytes(STAGES, NQ, HD), stream>>>(mq, mk, mv, mo, args);
+    kernel<<<grid, 8 * NQ * 32, smemBytes(STAGES, KSTAGES, NQ, HD), stream>>>(mq, mk, mv, mo, args);
     return checkLaunch("pagedPrefillUmmaKernel");
 }
 
 template <typename T, int HD>
-infiniStatus_t launchShape(int stages, int nq, const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mo,
+infiniStatus_t launchShape(int stages, int k_stages, int nq, const UmmaArgs &args, const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv, const CUtensorMap &mo,
                            unsigned tiles, int device_id, cudaStream_t stream) {
     if (nq == 2) {
         switch (stages) {
         case 2:
-            return launchTyped<T, 2, 2, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
+            return launchTyped<T, 2, 2, 2, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
         case 3:
-            return launchTyped<T, 3, 2, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
+            return launchTyped<T, 3, 3, 2, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
         default:
-            return launchTyped<T, 4, 2, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
+            return launchTyped<T, 4, 4, 2, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
         }
     }
     switch (stages) {
     case 2:
-        return launchTyped<T, 2, 1, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
+        return k_stages == 3 ? launchTyped<T, 2, 3, 1, HD>(args, mq, mk, mv, mo, tiles, device_id, stream)
+                             : launchTyped<T, 2, 2, 1, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
     case 3:
-        return launchTyped<T, 3, 1, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
+        return launchTyped<T, 3, 3, 1, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
     default:
-        return launchTyped<T, 4, 1, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
+        return launchTyped<T, 4, 4, 1, HD>(args, mq, mk, mv, mo, tiles, device_id, stream);
     }
 }
 
@@ -1008,7 +1041,13 @@ UmmaPlan planPrefillUmma(const Info &info, const DeviceProps &props) {
             plan.q_tiles = v;
         }
     }
-    // Two ring slots per tensor measured fastest in both shapes (and let two one-head CTAs share an SM).
+    // Two slots in the V ring and three in the K ring by default.  With two K slots the copy of a K tile
+    // can only start when the scores two tiles earlier have retired and then lands about when its own scores
+    // are wanted: cycle stamps of one CTA under load showed the softmax warps waiting ~1000 cycles for scores
+    // every fourth or fifth tile.  The third K slot gives the copy a whole tile period of slack; the V tile
+    // is wanted a tile later anyway.  32 KiB of Q + 3 x 16 + 2 x 16 KiB still lets two one-head CTAs share an
+    // SM (head 128).  INFINIOP_PAGED_PREFILL_STAGES = 2..4 sets the V ring (and, from 3 up, both rings);
+    // INFINIOP_PAGED_PREFILL_K_STAGES = 2 | 3 the K ring beside a two-slot V ring.
     plan.stages = 2;
     if (const char *env = std::getenv("INFINIOP_PAGED_PREFILL_STAGES")) {
         const int v = std::atoi(env);
@@ -1016,10 +1055,19 @@ UmmaPlan planPrefillUmma(const Info &info, const DeviceProps &props) {
             plan.stages = v;
         }
     }
-    while (plan.stages > 2 && smemBytes(plan.stages, plan.q_tiles, static_cast<int>(A.head_size)) > props.smem_per_block_optin) {
-        --plan.stages;
+    plan.k_stages = (plan.stages == 2 && plan.q_tiles == 1) ? 3 : plan.stages;
+    if (const char *env = std::getenv("INFINIOP_PAGED_PREFILL_K_STAGES")) {
+        const int v = std::atoi(env);
+        if (plan.stages == 2 && plan.q_tiles == 1 && (v == 2 || v == 3)) {
+            plan.k_stages = v;
+        }
     }
-    if (smemBytes(plan.stages, plan.q_tiles, static_cast<int>(A.head_size)) > props.smem_per_block_optin) {
+    const int hd_i = static_cast<int>(A.head_size);
+    while (plan.stages > 2 && smemBytes(plan.stages, plan.k_stages, plan.q_tiles, hd_i) > props.smem_per_block_optin) {
+        --plan.stages;
+        plan.k_stages = plan.stages;
+    }
+    if (smemBytes(plan.stages, plan.k_stages, plan.q_tiles, hd_i) > props.smem_per_block_optin) {
         return plan;
     }
     plan.eligible = true;
@@ -1049,11 +1097,11 @@ infiniStatus_t launchPrefillUmma(const Info &info, const UmmaPlan &plan, const P
     int device_id = -1;
     (void)cudaGetDevice(&device_id);
     if (A.head_size == 64) {
-        return A.dtype == INFINI_DTYPE_F16 ? launchShape<__half, 64>(plan.stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream)
-                                           : launchShape<__nv_bfloat16, 64>(plan.stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream);
+        return A.dtype == INFINI_DTYPE_F16 ? launchShape<__half, 64>(plan.stages, plan.k_stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream)
+                                           : launchShape<__nv_bfloat16, 64>(plan.stages, plan.k_stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream);
     }
-    return A.dtype == INFINI_DTYPE_F16 ? launchShape<__half, 128>(plan.stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream)
-                                       : launchShape<__nv_bfloat16, 128>(plan.stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream);
+    return A.dtype == INFINI_DTYPE_F16 ? launchShape<__half, 128>(plan.stages, plan.k_stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream)
+                                       : launchShape<__nv_bfloat16, 128>(plan.stages, plan.k_stages, plan.q_tiles, args, mq, mk, mv, mo, tiles, device_id, stream);
 }
 
 } // namespace b200::paged_attention_prefill
