@@ -77,6 +77,7 @@ struct StreamArgs {
     PlanHeader *header;
     long long *prefix;  // [num_seqs + 1] tiles before each sequence (one kv-head, one head tile)
     int4 *range_start;  // [workers] (sequence, unit-within-sequence, tile) where a range begins
+    int row_boxes;      // the tensor maps are the 5-D ones: one copy per tensor and tile
     int4 *tasks;        // [workers] combine tasks of the wide-head kernel: (sequence, unit-within-sequence, first range, records)
     int *counters;      // one-warp kernel: [0] next chunk of the pool, [1 + unit] tiles of the unit done so far; cleared by the reset kernel
     float *partials;    // [(units + pieces)] records of 8 * (HD + 2) floats
@@ -161,6 +162,28 @@ __device__ __forceinline__ void tmaLoadBoxHint(uint32_t dst, const CUtensorMap *
         "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
         " [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
+        : "memory");
+}
+
+// One TMA box {64 elements, 16 rows, all 64-element column chunks, 1 kv-head, 1 block} of the 5-D map
+// {64, block_size, width / 64, num_kv_heads, num_blocks}: the whole K (or V) part of a tile in one copy.  The
+// chunk dimension's stride is 128 bytes - smaller than the row stride below it - so the box lands as
+// [chunk][row][128 bytes], which is the layout the kernels read.  Issuing a copy holds the issuing warp for a
+// couple of hundred cycles whatever its size, so one copy per tensor instead of one per chunk matters where a
+// tile has many chunks (9 + 8 at key width 576).
+__device__ __forceinline__ void tmaLoadRows(uint32_t dst, const CUtensorMap *map, uint32_t bar, int row0, int kv_head, int block) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(0), "r"(row0), "r"(0), "r"(kv_head), "r"(block)
+        : "memory");
+}
+__device__ __forceinline__ void tmaLoadRowsHint(uint32_t dst, const CUtensorMap *map, uint32_t bar, int row0, int kv_head, int block,
+                                                uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(0), "r"(row0), "r"(0), "r"(kv_head), "r"(block), "l"(policy)
         : "memory");
 }
 
@@ -712,7 +735,17 @@ __global__ void __launch_bounds__(HD == 64 ? 128 : kMaxWarps * 32, HD == 64 ? 3 
         }
         const bool skip = withhold && lane == 0; // test only: the bytes are expected and never arrive
         withhold = false;
-        if (lane < 2 * kChunks && !skip) {
+        if (a.row_boxes) {
+            if (lane < 2 && !skip) {
+                const int row0 = (tpp == 1) ? 0 : (c.ti % tpp) * kTileTokens;
+                const int kv_head = (head_tiles == 1) ? c.j : c.j / head_tiles;
+                if (a.l2_evict_first) {
+                    tmaLoadRowsHint(dst + lane * kTensorBytes, lane ? &tmap_v : &tmap_k, bar, row0, kv_head, static_cast<int>(block), stream_policy);
+                } else {
+                    tmaLoadRows(dst + lane * kTensorBytes, lane ? &tmap_v : &tmap_k, bar, row0, kv_head, static_cast<int>(block));
+                }
+            }
+        } else if (lane < 2 * kChunks && !skip) {
             const int is_v = lane / kChunks;
             const int chunk = lane % kChunks;
             const int row0 = (tpp == 1) ? 0 : (c.ti % tpp) * kTileTokens;
@@ -1316,7 +1349,9 @@ __global__ void __launch_bounds__(kWideWarps * 32)
     const uint64_t stream_policy = evictFirstPolicy();
     const int my_box = warp + kWideWarps * lane;
     const bool has_box = my_box < kBoxes;
-    const uint32_t my_bytes = static_cast<uint32_t>((kBoxes - warp + kWideWarps - 1) / kWideWarps) * kBoxBytes;
+    // (with the 5-D maps: warp 0 copies the K part of a tile, warp 1 the V part, the other two only arrive)
+    const uint32_t my_bytes = a.row_boxes ? (warp == 0 ? kKBytes : warp == 1 ? kVBytes : 0u)
+                                          : static_cast<uint32_t>((kBoxes - warp + kWideWarps - 1) / kWideWarps) * kBoxBytes;
     auto issue = [&](int stage, const Cursor &c, long long block) {
         const uint32_t bar = full + stage * 8;
         const uint32_t dst = ring + stage * kStageBytes;
@@ -1324,7 +1359,17 @@ __global__ void __launch_bounds__(kWideWarps * 32)
             mbarExpectTx(bar, my_bytes);
         }
         __syncwarp();
-        if (has_box) {
+        if (a.row_boxes) {
+            if (warp < 2 && lane == 0) {
+                const int row0 = (tpp == 1) ? 0 : (c.ti % tpp) * kTileTokens;
+                const int kv_head = (head_tiles == 1) ? c.j : c.j / head_tiles;
+                if (a.l2_evict_first) {
+                    tmaLoadRowsHint(dst + (warp ? kKBytes : 0), warp ? &tmap_v : &tmap_k, bar, row0, kv_head, static_cast<int>(block), stream_policy);
+                } else {
+                    tmaLoadRows(dst + (warp ? kKBytes : 0), warp ? &tmap_v : &tmap_k, bar, row0, kv_head, static_cast<int>(block));
+                }
+            }
+        } else if (has_box) {
             const int is_v = my_box >= kKChunks;
             const int chunk = is_v ? my_box - kKChunks : my_box;
             const int row0 = (tpp == 1) ? 0 : (c.ti % tpp) * kTileTokens;
@@ -1852,12 +1897,23 @@ EncodeTiledFn encodeTiled() {
     return fn;
 }
 
-// 4-D map {head_size, block_size, num_kv_heads, num_blocks} over one cache pool.
+// 4-D map {head_size, block_size, num_kv_heads, num_blocks} over one cache pool, or (row_boxes) the 5-D map
+// {64, block_size, width / 64, num_kv_heads, num_blocks} whose box is every column chunk of 16 rows.
 bool encodeCacheMap(CUtensorMap *map, const Info &I, const void *base,
-                    ptrdiff_t row_stride, ptrdiff_t head_stride, ptrdiff_t block_stride, size_t width) {
+                    ptrdiff_t row_stride, ptrdiff_t head_stride, ptrdiff_t block_stride, size_t width, bool row_boxes) {
     EncodeTiledFn fn = encodeTiled();
     if (fn == nullptr) {
         return false;
+    }
+    if (row_boxes) {
+        const cuuint64_t dims[5] = {64, I.block_size, width / 64, I.num_kv_heads, I.num_blocks};
+        const cuuint64_t strides[4] = {static_cast<cuuint64_t>(row_stride) * 2, 128, static_cast<cuuint64_t>(head_stride) * 2,
+                                       static_cast<cuuint64_t>(block_stride) * 2};
+        const cuuint32_t box[5] = {64, kTileTokens, static_cast<cuuint32_t>(width / 64), 1, 1};
+        const cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+        const CUtensorMapDataType dt = (I.dtype == INFINI_DTYPE_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        return fn(map, dt, 5, const_cast<void *>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
     }
     const cuuint64_t dims[4] = {width, I.block_size, I.num_kv_heads, I.num_blocks};
     const cuuint64_t strides[3] = {static_cast<cuuint64_t>(row_stride) * 2, static_cast<cuuint64_t>(head_stride) * 2,
@@ -2076,10 +2132,17 @@ StreamPlan planStream(const Info &I, const DeviceProps &props) {
     // Trial encode with a stand-in base address: checks that the driver accepts these strides.
     CUtensorMap probe;
     void *fake = reinterpret_cast<void *>(static_cast<uintptr_t>(1) << 30);
-    if (!encodeCacheMap(&probe, I, fake, I.k_row_stride, I.k_head_stride, I.k_block_stride, hd)
-        || !encodeCacheMap(&probe, I, fake, I.v_row_stride, I.v_head_stride, I.v_block_stride, I.value_size)) {
+    if (!encodeCacheMap(&probe, I, fake, I.k_row_stride, I.k_head_stride, I.k_block_stride, hd, false)
+        || !encodeCacheMap(&probe, I, fake, I.v_row_stride, I.v_head_stride, I.v_block_stride, I.value_size, false)) {
         return plan;
     }
+    // One copy per tensor and tile (the 5-D maps, where the driver takes them) for key width 576, whose tile is
+    // 9 + 8 chunks: 13 % faster at 128 heads x 64 x 4096 tokens, 8 % at 16 heads.  At head 64 / 128 (1 or 2 chunks
+    // per tensor) it measured the same to 1.4 % slower, so those keep one copy per chunk.
+    // INFINIOP_PAGED_DECODE_ROW_BOXES = 0 | 1 overrides either way.
+    plan.row_boxes = envInt("INFINIOP_PAGED_DECODE_ROW_BOXES", wide ? 1 : 0, 0, 1) != 0
+                     && encodeCacheMap(&probe, I, fake, I.k_row_stride, I.k_head_stride, I.k_block_stride, hd, true)
+                     && encodeCacheMap(&probe, I, fake, I.v_row_stride, I.v_head_stride, I.v_block_stride, I.value_size, true);
     if (wide && (!mult8(I.q_seq_stride) || !mult8(I.q_head_stride))) {
         return plan; // q rows are copied 16 bytes at a time
     }
@@ -2202,8 +2265,8 @@ infiniStatus_t launchDecodeStream(const Info &I, const StreamPlan &plan, const D
         return launchDecodeGeneric(I, p, stream);
     }
     CUtensorMap mk, mv;
-    B200_RETURN_IF(!encodeCacheMap(&mk, I, p.k_cache, I.k_row_stride, I.k_head_stride, I.k_block_stride, I.head_size), INFINI_STATUS_INTERNAL_ERROR);
-    B200_RETURN_IF(!encodeCacheMap(&mv, I, p.v_cache, I.v_row_stride, I.v_head_stride, I.v_block_stride, I.value_size), INFINI_STATUS_INTERNAL_ERROR);
+    B200_RETURN_IF(!encodeCacheMap(&mk, I, p.k_cache, I.k_row_stride, I.k_head_stride, I.k_block_stride, I.head_size, plan.row_boxes), INFINI_STATUS_INTERNAL_ERROR);
+    B200_RETURN_IF(!encodeCacheMap(&mv, I, p.v_cache, I.v_row_stride, I.v_head_stride, I.v_block_stride, I.value_size, plan.row_boxes), INFINI_STATUS_INTERNAL_ERROR);
 
     const WorkspaceLayout L = workspaceLayout(I, plan);
     auto *ws = static_cast<unsigned char *>(workspace);
@@ -2219,6 +2282,7 @@ infiniStatus_t launchDecodeStream(const Info &I, const StreamPlan &plan, const D
     a.units_per_seq = static_cast<int>(I.num_kv_heads) * plan.head_tiles_per_group;
     a.tiles_per_page = static_cast<int>(I.block_size / kTileTokens);
     a.stages = plan.stages;
+    a.row_boxes = plan.row_boxes ? 1 : 0;
     a.num_workers = plan.num_workers;
     a.embedded_plan = plan.embedded_plan ? 1 : 0;
     a.max_chunks = plan.max_chunks;

@@ -108,6 +108,7 @@ struct StreamPlan {
     bool l2_evict_first = true;   // one-warp kernel: K/V copies carry the evict-first L2 policy (they are read once)
     long long wait_limit_cycles = 4000000000ll; // a bounded mbarrier wait gives up after this many SM cycles (~2 s)
     bool withhold_first_copy = false; // test only: worker 0 never issues its first copy, so that its wait runs out
+    bool row_boxes = false;   // 5-D tensor maps: one copy per tensor and tile instead of one per 64-element column chunk
     bool merge_in_kernel = true;  // split units are merged by the last worker to arrive (when few pieces per unit), not by the combine kernel
 };
 

@@ -42,6 +42,10 @@ PATH_ENV = {
     "stream-pool": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_DECODE_CHUNKS": "4"},
     "stream-pool-combine": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_DECODE_CHUNKS": "3",
                             "INFINIOP_PAGED_DECODE_MIN_CHUNK": "2", "INFINIOP_PAGED_DECODE_MERGE_IN_KERNEL": "0"},
+    # one copy per 64-element column chunk (the 4-D tensor maps; default at head 64 / 128) or one per tensor and
+    # tile (the 5-D maps; default at key width 576)
+    "stream-chunk-boxes": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_DECODE_ROW_BOXES": "0"},
+    "stream-row-boxes": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_DECODE_ROW_BOXES": "1"},
     # block-table entries checked against the pool before use
     "stream-checked": {"INFINIOP_PAGED_DECODE_PATH": "stream", "INFINIOP_PAGED_CHECK_INDICES": "1"},
     "generic-checked": {"INFINIOP_PAGED_DECODE_PATH": "generic", "INFINIOP_PAGED_CHECK_INDICES": "1"},

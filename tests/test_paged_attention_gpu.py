@@ -219,10 +219,11 @@ def test_block_size_32_and_wide_block_table(abi, path):
     check(c, run_case(abi, c, path), oracle_out(c))
 
 
-@pytest.mark.parametrize("path", ["stream-plan-kernel", "stream-3x4", "stream-combine", "stream-pool", "stream-pool-combine"])
+@pytest.mark.parametrize("path", ["stream-plan-kernel", "stream-3x4", "stream-combine", "stream-pool", "stream-pool-combine", "stream-row-boxes"])
 def test_stream_path_variants(abi, path):
     """The separate plan kernel with plain (non-programmatic) launches, another ring geometry, the combine
-    kernel in place of the merge inside the main kernel, and the chunk pool (ranges too short here to be
+    kernel in place of the merge inside the main kernel, one copy per tensor and tile instead of one per
+    column chunk, and the chunk pool (ranges too short here to be
     cut: the pool variants must behave like the plain ones), on ragged lengths with empty sequences and a
     split long sequence."""
     c = workloads.build_case("variants", dtype=torch.bfloat16, seq_lens=[1, 0, 47, 5000, 16, 333, 0, 2049], num_heads=32, num_kv_heads=8,
@@ -550,7 +551,7 @@ def test_decode_step_graph_replay_matches_direct_calls(abi, direct_output):
 
 # ---- key width 576: the four-warp wide-head kernel (and the generic kernel beside it) -------------------
 
-WIDE_PATHS = [None, "generic", "stream-3x4"]
+WIDE_PATHS = [None, "generic", "stream-3x4", "stream-chunk-boxes"]
 
 
 @pytest.mark.parametrize("path", WIDE_PATHS)
