@@ -1239,7 +1239,9 @@ __global__ void __launch_bounds__(HD == 64 ? 128 : kMaxWarps * 32, HD == 64 ? 3 
 //    order, so the four hold identical scores and identical softmax state; each owns a quarter of the
 //    value columns for O += P.V.  (Every warp computing all 36 k-steps itself needs no barrier but
 //    2.6 times the tensor-core and ldmatrix instructions per tile, and the kernel is bound by those, not
-//    by HBM.)  Each warp issues a quarter of a tile's copies and arrives for its own bytes.  A slot is handed back through an "empty" mbarrier on which each of the four warps
+//    by HBM.)  A tile is two copies (5-D tensor maps: all column chunks of the K part, of the V part), issued by
+//    warps 0 and 1; with the 4-D maps it is 17 or 18 copies shared out over the four warps.  Every warp arrives
+//    on the slot's barrier for the bytes it asked for.  A slot is handed back through an "empty" mbarrier on which each of the four warps
 //    arrives once it has read the slot; before they consume tile i, the warps refill the slot tile
 //    i - 1 has just left.
 //  * A head tile is 16 q-heads, all 16 rows of the MMA's M dimension: shapes with many q-heads per
