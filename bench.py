@@ -47,8 +47,8 @@ FALLBACK_HBM_GBS = 6650.0
 # capture of this workload.  A capture describes the kernel source it was taken from: the entry is only
 # reported while that source file still has the recorded hash, so it cannot silently go stale.
 NCU_TRAFFIC = {
-    "c2": {"bytes": 1077992000 + 3985000, "kernel": "pagedDecodeStreamKernel<bf16,128,8,pool off>", "captured": "2026-11-25",
-           "source": "infinicore_b200/csrc/paged_attention/decode_stream.cu", "source_sha256_16": "e83ecb007c0187d5"},
+    "c2": {"bytes": 1077984000 + 4757000, "kernel": "pagedDecodeStreamKernel<bf16,128,8,pool off>", "captured": "2026-11-25",
+           "source": "infinicore_b200/csrc/paged_attention/decode_stream.cu", "source_sha256_16": "d799af565937714a"},
 }
 
 
