@@ -174,6 +174,30 @@ def test_large_rows_match_the_oracle(abi):
     check(abi, x, pos, sin, cos, GPT_J, inplace=True)
 
 
+@pytest.mark.parametrize("algo", [GPT_J, GPT_NEOX])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_prefill_sized_calls(abi, dtype, algo):
+    """Calls of a thousand tokens and more on the vector path: an odd token count, a batch dimension with
+    per-batch positions, strided rows (q as a slice of a fused qkv buffer), 8 and 40 heads, positions outside
+    the tables, in place."""
+    gen = torch.Generator().manual_seed(9)
+    sin, cos = tables(300, 128, dtype)
+    # 1025 tokens x 8 heads: the second token of the last pair does not exist
+    x = torch.randn((1025, 8, 128), generator=gen).to(dtype)
+    pos = torch.randint(0, 300, (1025,), generator=gen)
+    pos[7] = 300  # outside: the row is copied
+    pos[1024] = -1
+    check(abi, x, pos, sin, cos, algo)
+    # batch 3 x 400 tokens x 40 heads, positions per batch, rows strided (a head is 128 of 192 columns), in place
+    x4 = strided((3, 400, 40, 128), (400 * 40 * 192, 40 * 192, 192, 1), dtype, gen)
+    pos4 = torch.randint(0, 300, (3, 400), generator=gen)
+    check(abi, x4, pos4, sin, cos, algo, inplace=True)
+    # head 64 (4 or 8 items per row), separate strided output
+    sin64, cos64 = tables(300, 64, dtype)
+    x64 = torch.randn((1500, 16, 64), generator=gen).to(dtype)
+    check(abi, x64, torch.randint(0, 300, (1500,), generator=gen), sin64, cos64, algo, y_strides=(16 * 80, 80, 1))
+
+
 def test_rejected_inputs(abi):
     x = torch.zeros((4, 2, 64), dtype=torch.float16, device="cuda")
     pos = torch.zeros(4, dtype=torch.int64, device="cuda")
