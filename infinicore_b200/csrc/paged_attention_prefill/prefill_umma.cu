@@ -427,9 +427,16 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
         sh_found = 0;
         sh_failed = 0;
     }
+    // TMEM: the first MMA warp allocates while the others look for the CTA's tile; everyone reads the base address
+    // after the barriers of the search.  (A CTA past the last tile gives its columns back at the common exit.)
+    if (warp == kMmaWarp0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tcgenFenceBefore();
+    }
     __syncthreads();
 
-    // ---- which (sequence, first new token) is this tile? (before any TMEM is held) ----------------
+    // ---- which (sequence, first new token) is this tile? ---------------------------------------------
     {
         int carry = 0;
         for (int base = 0; base < p.num_seqs; base += kNT) {
@@ -478,9 +485,7 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
             carry += total;
         }
     }
-    if (!sh_found) {
-        return;
-    }
+    const bool found = sh_found != 0;
     const int seq = sh_seq;
     const int t0 = sh_t0;
     const long long q_begin = sh_q_begin;
@@ -489,23 +494,14 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
     const int cache_len = total_len - n_new;
     const int rows_valid = min(kBM, n_new - t0);
     const int kv_end = min(total_len, cache_len + t0 + rows_valid);
-    if (kv_end <= 0) {
-        return;
-    }
+    const bool skip = !found || kv_end <= 0; // nothing to do: straight to the common exit, where TMEM is released
     const int num_kv_tiles = (kv_end + kBN - 1) / kBN;
     const int kv_head = head0 / p.group_size;
-
-    // ---- TMEM: the first MMA warp allocates, everyone reads the base address ----------------------
-    if (warp == kMmaWarp0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(tmem_slot)), "r"(kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tcgenFenceBefore();
-    __syncthreads();
     tcgenFenceAfter();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp >= kProducerWarp0) {
+    if (skip) {
+    } else if (warp >= kProducerWarp0) {
         // ================================ TMA producers ==========================================
         // A K/V tile is kBN / box_rows boxes of rows (one page or part of one) times kChunks column
         // chunks, per tensor.  Producer r takes row groups r, r + kProducers, ...; inside the warp one
