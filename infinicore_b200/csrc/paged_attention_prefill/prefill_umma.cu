@@ -8,19 +8,22 @@
 //    the 128-byte swizzle, which is exactly the canonical K-major (Q, K) / MN-major (V) operand layout
 //    of `tcgen05.mma`, so the MMA reads them through shared-memory descriptors with no repacking.
 //  * S[128 x 64] = Q.K^T is 8 `tcgen05.mma.cta_group::1.kind::f16` (M=128, N=64, K=16) issued by one
-//    thread into TMEM columns [0, 64); completion reaches the other threads through `tcgen05.commit`
-//    on an mbarrier.
+//    thread of the score-issuing warp into one of two 64-column S buffers in TMEM; completion reaches
+//    the other warps through `tcgen05.commit` on an mbarrier.
 //  * thread r of the four softmax warps owns query row r: it reads its S row with `tcgen05.ld`
 //    (32x32b: TMEM lane = row), does the fp32 online softmax without any cross-thread traffic, rounds
-//    P to the cache dtype and writes its row into a swizzled K-major shared-memory tile.
-//  * O[128 x 128] += P.V is 4 more `tcgen05.mma` (M=128, N=128, K=16) accumulating in TMEM columns
-//    [64, 192) across all KV tiles.  The running maximum used for the exponentials is only raised
-//    when a row's true maximum exceeds it by more than 2^8 (the result is unchanged: numerator and
-//    denominator share the same reference); only then does a warp read its O rows back, scale them
-//    and store them (`tcgen05.ld` / `tcgen05.st`).  O is read once more at the end for the
-//    normalised store.  The same commit that publishes O also releases the KV stage to the producer,
-//    and P.V of tile i overlaps the S MMA and softmax arithmetic of tile i + 1.
-//  * a fifth warp is the TMA producer (block-table lookups, K/V boxes) and owns the TMEM allocation.
+//    P to the cache dtype and stores it back over the scores it came from (`tcgen05.st`, two 16-bit
+//    values per column): P never touches shared memory.
+//  * O[128 x 128] += P.V is 4 more `tcgen05.mma` (M=128, N=128, K=16; A operand P read from TMEM, B
+//    operand V from shared memory) issued by a second warp, accumulating in TMEM columns [128, 256)
+//    across all KV tiles.  The running maximum used for the exponentials is only raised when a row's
+//    true maximum exceeds it by more than 2^8 (the result is unchanged: numerator and denominator share
+//    the same reference); only then does a warp read its O rows back, scale them and store them
+//    (`tcgen05.ld` / `tcgen05.st`).  O is read once more at the end for the normalised store.  The
+//    commits of the two issuing warps also release the K and V ring slots to the producers, and P.V of
+//    tile i overlaps the S MMA and softmax arithmetic of tile i + 1.
+//  * two more warps are the TMA producers (block-table lookups, K/V boxes; K copies run one tile ahead
+//    of the V copies).  The first MMA warp owns the TMEM allocation.
 //
 // Every wait is an mbarrier wait with a time limit; on every path the CTA reaches the common exit,
 // where the TMEM columns are released.
