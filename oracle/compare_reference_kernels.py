@@ -4,7 +4,7 @@ child process of its own (they export the same symbols).  Prints one JSON line p
 library, environment).  This is what the tables under profiles/ that compare the two were made with;
 it is a checker's tool like the rest of this folder - nothing in the library uses it.
 
-    python oracle/compare_reference_kernels.py [c1 c2 c3 c4 b1 b8 b1long g16 h64 h192 h256 h576 mla p1 p2]
+    python oracle/compare_reference_kernels.py [c1 c2 c3 c4 b1 b8 b1long g16 h64 h192 h256 h576 mla mla37 p1 p2]
 """
 import json
 import os
@@ -45,6 +45,10 @@ SPECS = {
     # latent attention: keys 576 wide, values 512 wide, one shared kv-head, 128 query heads
     "mla": {"builder": "build_case", "kwargs": {"name": "mla", "dtype": "bfloat16", "seq_lens": [4096] * 64, "num_heads": 128, "num_kv_heads": 1,
                                                 "head_size": 576, "value_size": 512, "block_size": 16, "seed": 577, "std": 0.3, "device": "cuda"}},
+    # the same with 37 sequences: 37 x 8 head tiles = 296 units, one per worker of the wide kernel, so the eight head
+    # tiles of a sequence walk the same tokens at the same time (what the L2 does for them shows in an ncu capture)
+    "mla37": {"builder": "build_case", "kwargs": {"name": "mla37", "dtype": "bfloat16", "seq_lens": [4096] * 37, "num_heads": 128, "num_kv_heads": 1,
+                                                  "head_size": 576, "value_size": 512, "block_size": 16, "seed": 578, "std": 0.3, "device": "cuda"}},
     # prefill, Llama-3-8B head shape: 8 prompts x 2048 new tokens; and 4 x 1024 new over 3072 cached
     "p1": {"builder": "prefill_llama8b", "kwargs": {"device": "cuda", "num_seqs": 8, "new_len": 2048, "cached_len": 0}},
     "p2": {"builder": "prefill_llama8b", "kwargs": {"device": "cuda", "num_seqs": 4, "new_len": 1024, "cached_len": 3072}},
