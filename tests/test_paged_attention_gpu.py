@@ -602,6 +602,20 @@ def test_wide_heads_long_batch_matches_generic_kernel(abi):
     assert_close(a.float().cpu().numpy(), b.float().cpu().numpy(), atol, rtol, "wide vs generic")
 
 
+@pytest.mark.parametrize("dtype,heads,value,hd,bs", [(torch.bfloat16, 128, 512, 576, 16), (torch.float16, 16, 576, 576, 32),
+                                                    (torch.bfloat16, 32, 128, 128, 16), (torch.float16, 8, 64, 64, 16)])
+def test_copies_per_chunk_and_per_tensor_give_the_same_bits(abi, dtype, heads, value, hd, bs):
+    """The two ways of fetching a tile (one copy per 64-element column chunk through the 4-D tensor maps, one per
+    tensor through the 5-D maps) move the same bytes to the same places: bit-identical outputs, at key width 576
+    (where the 5-D maps are the default) and at head 128 / 64 (where they are not)."""
+    c = workloads.build_case("boxes", dtype=dtype, seq_lens=[2500, 31, 700, 1, 4097, 16], num_heads=heads, num_kv_heads=1 if hd == 576 else 4,
+                             head_size=hd, value_size=value, block_size=bs, seed=66, std=0.3)
+    a = run_case(abi, c, "stream-chunk-boxes")
+    b = run_case(abi, c, "stream-row-boxes")
+    assert np.array_equal(torch_to_bits(a), torch_to_bits(b))
+    check(c, b, oracle_out(c))
+
+
 # ---- several destinations for the output rows (what the KV-head-sharded mode stores into its peers) -------
 
 @pytest.mark.parametrize("path", [None, "generic", "stream-3x4"])
