@@ -120,6 +120,7 @@ struct UmmaPlan {
     int stages = 2;  // slots of the V ring
     int k_stages = 3; // slots of the K ring (>= stages)
     int q_tiles = 1; // q-heads of one GQA group per CTA (share every staged KV tile)
+    long long test_delay_v_cycles = 0; // test only: every V copy from the second tile on is held back this long
 };
 UmmaPlan planPrefillUmma(const Info &info, const DeviceProps &props);
 infiniStatus_t launchPrefillUmma(const Info &info, const UmmaPlan &plan, const PrefillParams &p, cudaStream_t stream);

@@ -322,6 +322,7 @@ struct UmmaArgs {
     PrefillParams pp;
     int box_rows;  // rows of one K/V TMA box: the largest of 64, 32, 16, 8 that divides block_size
     int tma_store; // out's strides allow a tensor map: full tiles leave through shared memory and one bulk store
+    long long test_delay_v_cycles; // test only (0 in normal use): the V copies are held back this many cycles
 };
 
 // smem layout (dynamic, 1024-aligned):
@@ -546,6 +547,13 @@ __global__ void __launch_bounds__((8 * kQ) * 32)
             const uint32_t empty = (is_v ? v_empty : k_empty) + stage * 8;
             const bool live = block >= 0;
             const uint32_t bytes = static_cast<uint32_t>(__popc(__ballot_sync(0xffffffffu, live))) * box_bytes;
+            if (is_v && kt >= 1 && a.test_delay_v_cycles > 0) {
+                // test only: a V tile that arrives late lets the softmax run two tiles ahead of the P.V issuer -
+                // the situation in which a single P-ready barrier for both score buffers is read wrongly
+                const long long t_begin = clock64();
+                while (clock64() - t_begin < a.test_delay_v_cycles) {
+                }
+            }
             if (kt >= depth && !__all_sync(0xffffffffu, mbarWait(empty, parity ^ 1u))) {
                 return false;
             }
@@ -1069,6 +1077,14 @@ UmmaPlan planPrefillUmma(const Info &info, const DeviceProps &props) {
     if (smemBytes(plan.stages, plan.k_stages, plan.q_tiles, hd_i) > props.smem_per_block_optin) {
         return plan;
     }
+    // INFINIOP_PAGED_PREFILL_TEST_DELAY_V_US (test only, at most 1000): the producers hold every V copy from the second
+    // tile on back by that long, which puts the P.V issuer behind the softmax warps.
+    if (const char *env = std::getenv("INFINIOP_PAGED_PREFILL_TEST_DELAY_V_US")) {
+        const long long us = std::atoll(env);
+        if (us >= 1 && us <= 1000) {
+            plan.test_delay_v_cycles = us * 2000; // SM cycles at a nominal 2 GHz
+        }
+    }
     plan.eligible = true;
     return plan;
 }
@@ -1087,6 +1103,7 @@ infiniStatus_t launchPrefillUmma(const Info &info, const UmmaPlan &plan, const P
     UmmaArgs args;
     args.pp = pp;
     args.box_rows = plan.box_rows;
+    args.test_delay_v_cycles = plan.test_delay_v_cycles;
     CUtensorMap mo;
     args.tma_store = encodeOutMap(&mo, info, p.out) ? 1 : 0;
     if (!args.tma_store) {

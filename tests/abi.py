@@ -298,8 +298,12 @@ PREFILL_ENV = {
     "umma": {"INFINIOP_PAGED_PREFILL_PATH": "umma"},
     "umma-q1": {"INFINIOP_PAGED_PREFILL_PATH": "umma", "INFINIOP_PAGED_PREFILL_QTILES": "1"},
     "umma-q2-s3": {"INFINIOP_PAGED_PREFILL_PATH": "umma", "INFINIOP_PAGED_PREFILL_QTILES": "2", "INFINIOP_PAGED_PREFILL_STAGES": "3"},
+    # every V copy from the second tile on held back 3 us: the P.V issuer falls behind the softmax warps
+    "umma-late-v": {"INFINIOP_PAGED_PREFILL_PATH": "umma", "INFINIOP_PAGED_PREFILL_TEST_DELAY_V_US": "3"},
+    "umma-late-v-k2": {"INFINIOP_PAGED_PREFILL_PATH": "umma", "INFINIOP_PAGED_PREFILL_TEST_DELAY_V_US": "3", "INFINIOP_PAGED_PREFILL_K_STAGES": "2"},
 }
-_PREFILL_KEYS = ("INFINIOP_PAGED_PREFILL_PATH", "INFINIOP_PAGED_PREFILL_QTILES", "INFINIOP_PAGED_PREFILL_STAGES")
+_PREFILL_KEYS = ("INFINIOP_PAGED_PREFILL_PATH", "INFINIOP_PAGED_PREFILL_QTILES", "INFINIOP_PAGED_PREFILL_STAGES", "INFINIOP_PAGED_PREFILL_K_STAGES",
+                 "INFINIOP_PAGED_PREFILL_TEST_DELAY_V_US")
 
 
 @contextlib.contextmanager

@@ -148,6 +148,20 @@ def test_long_prompt_against_oracle(abi, path):
     check(c, run_case(abi, c, path), oracle_out(c))
 
 
+@pytest.mark.parametrize("path", ["umma-late-v", "umma-late-v-k2"])
+def test_late_value_tiles_change_nothing(abi, path):
+    """V copies held back (a test switch of the producers): the softmax warps store P of two tiles while the P.V
+    issuer still waits for the first one's values.  Every barrier the issuer can fall behind on exists once per
+    score buffer, so it reads their phases rightly: same bits as the undisturbed run, nothing reported."""
+    c = workloads.build_prefill_case("late_v", dtype=torch.bfloat16, new_lens=[700, 129], cached_lens=[300, 0], num_heads=8,
+                                     num_kv_heads=2, head_size=128, block_size=16, seed=97)
+    want = run_case(abi, c, "umma")
+    got = run_case(abi, c, path)
+    assert torch.equal(got.cpu(), want.cpu())
+    assert abi.kernel_status() == 0
+    check(c, got, oracle_out(c))
+
+
 def test_prefill_of_one_token_equals_decode(abi):
     """A chunk of one new token per sequence is the decode problem: same result as infiniopPagedAttention
     within rounding of the two kernels."""
